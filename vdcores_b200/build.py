@@ -1,0 +1,30 @@
+"""Builds libvdcores_b200.so in-tree with nvcc for sm_100a:  python -m vdcores_b200.build"""
+import os
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB = os.path.join(HERE, "libvdcores_b200.so")
+SOURCES = [os.path.join(HERE, "csrc", f) for f in ("megakernel.cu", "capi.cu")]
+FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-shared",
+         "-Xcompiler", "-fPIC"]
+
+
+def needs_build() -> bool:
+    if not os.path.exists(LIB):
+        return True
+    t = os.path.getmtime(LIB)
+    deps = SOURCES + [os.path.join(HERE, "csrc", "isa.h"), os.path.join(HERE, "..", "include", "vdcores.h")]
+    return any(os.path.getmtime(d) > t for d in deps)
+
+
+def build(force: bool = False, verbose: bool = False) -> str:
+    if force or needs_build():
+        nvcc = os.environ.get("NVCC", "nvcc")
+        cmd = [nvcc, *FLAGS, *(["-Xptxas", "-v"] if verbose else []), "-o", LIB, *SOURCES]
+        subprocess.check_call(cmd)
+    return LIB
+
+
+if __name__ == "__main__":
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))

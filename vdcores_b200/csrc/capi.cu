@@ -1,0 +1,268 @@
+// Host side of the C ABI declared in include/vdcores.h.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <string>
+
+#include "../../include/vdcores.h"
+
+extern "C" size_t vdc_megakernel_dynamic_smem();
+extern "C" cudaError_t vdc_megakernel_prepare();
+extern "C" cudaError_t vdc_megakernel_launch(int num_sms, const void* cinsts, const void* minsts, const void* tmas,
+                                             int* bars, uint64_t* profile, vdc_status* status, int insts_per_sm,
+                                             uint64_t timeout_ns, cudaStream_t stream);
+
+namespace {
+
+thread_local std::string g_err;
+constexpr int kMaxDevices = 16;
+vdc_status* g_status[kMaxDevices] = {nullptr};
+int g_sm_count[kMaxDevices] = {0};
+
+int fail_cuda(cudaError_t e, const char* what) {
+  g_err = std::string(what) + ": " + cudaGetErrorString(e);
+  return VDC_ERR_CUDA;
+}
+int fail_arg(const char* what) {
+  g_err = what;
+  return VDC_ERR_ARG;
+}
+
+struct OpEntry {
+  const char* name;
+  int value;
+  int is_compute;
+};
+const OpEntry kOps[] = {
+#define X(name, value) {#name, (int)(value), 0},
+    VDC_MEMORY_OPS(X)
+#undef X
+#define X(name, value) {#name, (int)(value), 1},
+        VDC_COMPUTE_OPS(X)
+#undef X
+};
+constexpr int kNumOps = sizeof(kOps) / sizeof(kOps[0]);
+
+int current_device(int* dev) {
+  cudaError_t e = cudaGetDevice(dev);
+  if (e != cudaSuccess) return fail_cuda(e, "cudaGetDevice");
+  if (*dev < 0 || *dev >= kMaxDevices) return fail_arg("device index out of range");
+  return VDC_OK;
+}
+
+int check_launch_args(int dev, int num_sms, int insts_per_sm, const void* ci, const void* mi, const int* bars,
+                      const uint64_t* profile) {
+  if (!g_status[dev]) return fail_arg("vdc_init was not called on this device");
+  if (num_sms <= 0 || num_sms > g_sm_count[dev]) return fail_arg("num_sms must be in [1, SM count of the device]");
+  if (insts_per_sm <= 0 || insts_per_sm > 65536) return fail_arg("insts_per_sm out of range");
+  if (!ci || !mi || !bars || !profile) return fail_arg("null instruction, barrier or profile pointer");
+  if (((uintptr_t)ci & 7) || ((uintptr_t)mi & 15) || ((uintptr_t)bars & 3) || ((uintptr_t)profile & 7))
+    return fail_arg("misaligned instruction, barrier or profile pointer");
+  return VDC_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int vdc_version(void) { return 100; }
+
+const char* vdc_last_error(void) { return g_err.c_str(); }
+
+int vdc_init(void) {
+  int dev;
+  if (int r = current_device(&dev)) return r;
+  if (g_status[dev]) return VDC_OK;
+  cudaDeviceProp prop{};
+  cudaError_t e = cudaGetDeviceProperties(&prop, dev);
+  if (e != cudaSuccess) return fail_cuda(e, "cudaGetDeviceProperties");
+  if (prop.major != 10) return fail_arg("this library is built for sm_100a (B200) only");
+  g_sm_count[dev] = prop.multiProcessorCount;
+  e = vdc_megakernel_prepare();
+  if (e != cudaSuccess) return fail_cuda(e, "cudaFuncSetAttribute(MaxDynamicSharedMemorySize)");
+  vdc_status* st = nullptr;
+  e = cudaMalloc(&st, sizeof(vdc_status));
+  if (e != cudaSuccess) return fail_cuda(e, "cudaMalloc(status)");
+  e = cudaMemset(st, 0, sizeof(vdc_status));
+  if (e != cudaSuccess) return fail_cuda(e, "cudaMemset(status)");
+  g_status[dev] = st;
+  return VDC_OK;
+}
+
+int vdc_set_smem_size(int bytes) {
+  if (bytes < 0 || (size_t)bytes > 232448) return fail_arg("shared-memory size beyond the 227 KB a B200 CTA can have");
+  return VDC_OK;
+}
+
+int vdc_launch_async(int num_sms, int insts_per_sm, const void* compute_insts, const void* memory_insts,
+                     const void* tma_descs, int* bars, const int* bars_init, uint64_t* profile, uint64_t stream,
+                     uint64_t timeout_ns) {
+  int dev;
+  if (int r = current_device(&dev)) return r;
+  if (int r = check_launch_args(dev, num_sms, insts_per_sm, compute_insts, memory_insts, bars, profile)) return r;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (bars_init) {
+    cudaError_t e = cudaMemcpyAsync(bars, bars_init, sizeof(int) * VDC_MAX_BARS, cudaMemcpyDeviceToDevice, s);
+    if (e != cudaSuccess) return fail_cuda(e, "cudaMemcpyAsync(bars)");
+  }
+  if (timeout_ns == 0) timeout_ns = 2000000000ull;
+  cudaError_t e = vdc_megakernel_launch(num_sms, compute_insts, memory_insts, tma_descs, bars, profile,
+                                        g_status[dev], insts_per_sm, timeout_ns, s);
+  if (e != cudaSuccess) return fail_cuda(e, "megakernel launch");
+  return VDC_OK;
+}
+
+int vdc_read_status(uint64_t stream, vdc_status* status, int clear) {
+  int dev;
+  if (int r = current_device(&dev)) return r;
+  if (!g_status[dev]) return fail_arg("vdc_init was not called on this device");
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaStreamSynchronize(s);
+  if (e != cudaSuccess) return fail_cuda(e, "cudaStreamSynchronize");
+  vdc_status h{};
+  e = cudaMemcpy(&h, g_status[dev], sizeof(h), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return fail_cuda(e, "cudaMemcpy(status)");
+  if (clear && h.abort) {
+    e = cudaMemset(g_status[dev], 0, sizeof(vdc_status));
+    if (e != cudaSuccess) return fail_cuda(e, "cudaMemset(status)");
+  }
+  if (status) *status = h;
+  if (h.abort) {
+    char buf[256];
+    snprintf(buf, sizeof buf, "megakernel gave up: code=%d sm=%d role=%d pc=%d opcode=0x%x bar=%d aux=%d", h.code, h.sm,
+             h.role, h.pc, h.opcode, h.bar, h.aux);
+    g_err = buf;
+    return h.code ? h.code : VDC_ERR_TIMEOUT;
+  }
+  return VDC_OK;
+}
+
+int vdc_launch(int num_sms, int insts_per_sm, const void* compute_insts, const void* memory_insts,
+               const void* tma_descs, int* bars, uint64_t* profile, uint64_t stream, uint64_t timeout_ns,
+               vdc_status* status) {
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return fail_cuda(e, "cudaDeviceSynchronize (before launch)");
+  if (int r = vdc_launch_async(num_sms, insts_per_sm, compute_insts, memory_insts, tma_descs, bars, nullptr, profile,
+                               stream, timeout_ns))
+    return r;
+  e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return fail_cuda(e, "cudaDeviceSynchronize (after launch)");
+  return vdc_read_status(stream, status, 1);
+}
+
+int vdc_build_tma_desc(void* out_desc, const void* base, int dtype, int rank, const uint64_t* shape,
+                       const uint64_t* strides_bytes, const uint32_t* box_dim, const uint32_t* elem_strides,
+                       int swizzle_bytes, int interleave_bytes) {
+  if (!out_desc || !base || !shape || !box_dim || !elem_strides) return fail_arg("null argument");
+  if (rank < 1 || rank > 5) return fail_arg("tensor-map rank must be 1..5");
+  if ((uintptr_t)base & 15) return fail_arg("tensor-map base address must be 16-byte aligned");
+  static const CUtensorMapDataType kTypes[] = {CU_TENSOR_MAP_DATA_TYPE_UINT8,   CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                                               CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
+                                               CU_TENSOR_MAP_DATA_TYPE_INT32,   CU_TENSOR_MAP_DATA_TYPE_UINT32};
+  if (dtype < 0 || dtype > 5) return fail_arg("unsupported dtype code");
+  CUtensorMapSwizzle swz;
+  switch (swizzle_bytes) {
+    case 0: swz = CU_TENSOR_MAP_SWIZZLE_NONE; break;
+    case 32: swz = CU_TENSOR_MAP_SWIZZLE_32B; break;
+    case 64: swz = CU_TENSOR_MAP_SWIZZLE_64B; break;
+    case 128: swz = CU_TENSOR_MAP_SWIZZLE_128B; break;
+    default: return fail_arg("swizzle_bytes must be 0, 32, 64 or 128");
+  }
+  CUtensorMapInterleave il;
+  switch (interleave_bytes) {
+    case 0: il = CU_TENSOR_MAP_INTERLEAVE_NONE; break;
+    case 16: il = CU_TENSOR_MAP_INTERLEAVE_16B; break;
+    case 32: il = CU_TENSOR_MAP_INTERLEAVE_32B; break;
+    default: return fail_arg("interleave_bytes must be 0, 16 or 32");
+  }
+  cuuint64_t gdim[5] = {1, 1, 1, 1, 1}, gstride[5] = {0, 0, 0, 0, 0};
+  cuuint32_t bdim[5] = {1, 1, 1, 1, 1}, estride[5] = {1, 1, 1, 1, 1};
+  for (int i = 0; i < rank; ++i) {
+    if (shape[i] == 0 || box_dim[i] == 0 || elem_strides[i] == 0) return fail_arg("shape, box and element strides must be positive");
+    gdim[i] = shape[i];
+    bdim[i] = box_dim[i];
+    estride[i] = elem_strides[i];
+    if (i < rank - 1) {
+      if (!strides_bytes) return fail_arg("strides_bytes is required for rank > 1");
+      gstride[i] = strides_bytes[i];
+    }
+  }
+  // The driver entry point is resolved at run time so that the library has no
+  // link-time dependency on libcuda (it must load on machines without a GPU).
+  typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                               const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                               CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  static EncodeFn encode = nullptr;
+  if (!encode) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+    if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !fn)
+      return fail_cuda(e == cudaSuccess ? cudaErrorNotSupported : e, "cudaGetDriverEntryPoint(cuTensorMapEncodeTiled)");
+    encode = reinterpret_cast<EncodeFn>(fn);
+  }
+  alignas(64) CUtensorMap map;
+  CUresult r = encode(&map, kTypes[dtype], (cuuint32_t)rank, const_cast<void*>(base), gdim, gstride, bdim, estride, il,
+                      swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    char buf[96];
+    snprintf(buf, sizeof buf, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    g_err = buf;
+    return VDC_ERR_CUDA;
+  }
+  memcpy(out_desc, &map, sizeof(map));
+  return VDC_OK;
+}
+
+int vdc_set_cache_policy(const void* ptr, size_t bytes, uint64_t stream, float hit_ratio, int hit_policy,
+                         int miss_policy) {
+  if (!ptr || bytes == 0) return fail_arg("empty range");
+  int dev;
+  if (int r = current_device(&dev)) return r;
+  int max_window = 0;
+  cudaError_t e = cudaDeviceGetAttribute(&max_window, cudaDevAttrMaxAccessPolicyWindowSize, dev);
+  if (e != cudaSuccess) return fail_cuda(e, "cudaDeviceGetAttribute");
+  if (max_window > 0 && bytes > (size_t)max_window) bytes = (size_t)max_window;
+  cudaStreamAttrValue attr{};
+  attr.accessPolicyWindow.base_ptr = const_cast<void*>(ptr);
+  attr.accessPolicyWindow.num_bytes = bytes;
+  attr.accessPolicyWindow.hitRatio = hit_ratio;
+  attr.accessPolicyWindow.hitProp = static_cast<cudaAccessProperty>(hit_policy);
+  attr.accessPolicyWindow.missProp = static_cast<cudaAccessProperty>(miss_policy);
+  e = cudaStreamSetAttribute(reinterpret_cast<cudaStream_t>(stream), cudaStreamAttributeAccessPolicyWindow, &attr);
+  if (e != cudaSuccess) return fail_cuda(e, "cudaStreamSetAttribute");
+  return VDC_OK;
+}
+
+int vdc_opcode_count(void) { return kNumOps; }
+const char* vdc_opcode_name(int i) { return (i >= 0 && i < kNumOps) ? kOps[i].name : nullptr; }
+int vdc_opcode_value(int i) { return (i >= 0 && i < kNumOps) ? kOps[i].value : -1; }
+int vdc_opcode_is_compute(int i) { return (i >= 0 && i < kNumOps) ? kOps[i].is_compute : 0; }
+
+int64_t vdc_config(const char* name) {
+  if (!name) return -1;
+  struct {
+    const char* k;
+    int64_t v;
+  } const tbl[] = {{"slot_size", VDC_SLOT_BYTES},
+                   {"num_slots", VDC_NUM_SLOTS},
+                   {"max_insts", VDC_MAX_INSTS},
+                   {"num_profile_events", VDC_NUM_PROFILE_EVENTS},
+                   {"max_tmas", VDC_MAX_TMAS},
+                   {"max_bars", VDC_MAX_BARS},
+                   {"num_special_slots", VDC_NUM_SPECIAL_SLOTS},
+                   {"compute_threads", VDC_COMPUTE_THREADS},
+                   {"threads", VDC_THREADS},
+                   {"kv_page", VDC_KV_PAGE},
+                   {"head_dim", VDC_HEAD_DIM},
+                   {"dynamic_smem", (int64_t)((size_t)VDC_NUM_SLOTS * VDC_SLOT_BYTES + 1024)}};
+  for (auto& e : tbl)
+    if (strcmp(e.k, name) == 0) return e.v;
+  return -1;
+}
+
+const char* vdc_family_specs(void) { return ""; }
+
+}  // extern "C"

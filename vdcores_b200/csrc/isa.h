@@ -1,0 +1,150 @@
+// Instruction-set constants shared by the host library and the megakernel.
+//
+// The encodings keep the reference's wire format so that instruction streams
+// produced by its Python schedules stay valid:
+//   * 8-byte compute instruction {u16 opcode, u16 args[3]}   (reference include/dae/context.cuh:51-54)
+//   * 16-byte memory instruction {u16 opcode|flags, u16 size, u16 nslot|bar<<6, u16 arg, u64 address}
+//     (reference include/dae/context.cuh:87-113), six flag bits (context.cuh:58-66)
+//   * memory opcode ids 1..23 (reference include/dae/opcode.cuh.inc:1-32)
+// Ids 24 and up, and every compute opcode, are this runtime's own.
+#pragma once
+#include <stdint.h>
+
+#define VDC_SLOT_BYTES 8192
+#define VDC_NUM_SLOTS 24
+#define VDC_NUM_SPECIAL_SLOTS 9
+#define VDC_MAX_INSTS 4096
+#define VDC_NUM_PROFILE_EVENTS 128
+#define VDC_MAX_TMAS 1024
+#define VDC_MAX_BARS 1024
+#define VDC_QUEUE_LEN 32
+
+#define VDC_COMPUTE_WARPS 8
+#define VDC_COMPUTE_THREADS (VDC_COMPUTE_WARPS * 32)
+#define VDC_MEMORY_WARPS 4
+#define VDC_THREADS ((VDC_COMPUTE_WARPS + VDC_MEMORY_WARPS) * 32)
+#define VDC_MAX_SMS 160
+
+// memory-instruction flag bits (low 6 bits of the opcode field)
+#define VDC_F_ALLOCATE 0x01
+#define VDC_F_WRITEBACK 0x02
+#define VDC_F_GROUP 0x04
+#define VDC_F_JUMP 0x08
+#define VDC_F_BARRIER 0x10
+#define VDC_F_PORT 0x20
+#define VDC_FLAG_BITS 6
+#define VDC_MOP(id, flags) ((uint16_t)(((id) << VDC_FLAG_BITS) | (flags)))
+
+// X(name, value)
+#define VDC_MEMORY_OPS(X)                                                              \
+  X(OP_TERMINATE, VDC_MOP(1, 0))                                                       \
+  X(OP_REPEAT, VDC_MOP(2, 0))                                                          \
+  X(OP_LOOP, VDC_MOP(3, 0))                                                            \
+  X(OP_SHIFT_RESOURCE, VDC_MOP(4, 0))                                                  \
+  X(OP_ISSUE_BARRIER, VDC_MOP(5, 0))                                                   \
+  X(OP_CC0, VDC_MOP(6, 0))                                                             \
+  X(OP_CC0_ROW_BYTES, VDC_MOP(7, 0))                                                   \
+  X(OP_ALLOC_REG_LOAD, VDC_MOP(8, VDC_F_ALLOCATE))                                     \
+  X(OP_ALLOC_TMA_LOAD_1D, VDC_MOP(9, VDC_F_ALLOCATE))                                  \
+  X(OP_ALLOC_TMA_LOAD_TENSOR_1D, VDC_MOP(10, VDC_F_ALLOCATE))                          \
+  X(OP_ALLOC_TMA_LOAD_2D, VDC_MOP(11, VDC_F_ALLOCATE))                                 \
+  X(OP_ALLOC_TMA_LOAD_3D, VDC_MOP(12, VDC_F_ALLOCATE))                                 \
+  X(OP_ALLOC_TMA_LOAD_4D, VDC_MOP(13, VDC_F_ALLOCATE))                                 \
+  X(OP_ALLOC_TMA_LOAD_5D_FIX0, VDC_MOP(14, VDC_F_ALLOCATE))                            \
+  X(OP_ALLOC_WB_REG_STORE, VDC_MOP(15, VDC_F_ALLOCATE))                                \
+  X(OP_ALLOC_WB_TMA_STORE_1D, VDC_MOP(16, VDC_F_ALLOCATE | VDC_F_WRITEBACK))           \
+  X(OP_ALLOC_WB_TMA_STORE_2D, VDC_MOP(17, VDC_F_ALLOCATE | VDC_F_WRITEBACK))           \
+  X(OP_ALLOC_WB_TMA_STORE_3D, VDC_MOP(18, VDC_F_ALLOCATE | VDC_F_WRITEBACK))           \
+  X(OP_ALLOC_WB_TMA_STORE_4D, VDC_MOP(19, VDC_F_ALLOCATE | VDC_F_WRITEBACK))           \
+  X(OP_ALLOC_WB_TMA_STORE_5D_FIX0, VDC_MOP(20, VDC_F_ALLOCATE | VDC_F_WRITEBACK))      \
+  X(OP_ALLOC_WB_TMA_REDUCE_ADD_2D, VDC_MOP(21, VDC_F_ALLOCATE | VDC_F_WRITEBACK))      \
+  X(OP_ALLOC_WB_TMA_REDUCE_ADD_3D, VDC_MOP(22, VDC_F_ALLOCATE | VDC_F_WRITEBACK))      \
+  X(OP_ALLOC_WB_RAW_ADDRESS, VDC_MOP(23, VDC_F_ALLOCATE))                              \
+  X(OP_ALLOC_WB_TMA_REDUCE_ADD_1D, VDC_MOP(24, VDC_F_ALLOCATE | VDC_F_WRITEBACK))      \
+  X(OP_DYN_COUNT, VDC_MOP(25, 0))
+
+// Compute opcodes.  The first block keeps reference names (control ops and the
+// ops whose tile contracts this runtime still honours); the second block is
+// the B200-native decode set.
+#define VDC_COMPUTE_OPS(X)                                                             \
+  X(OP_TERMINATEC, 0x7000)                                                             \
+  X(OP_LOOPC, 0x7001)                                                                  \
+  X(OP_DUMMY, 0x7002)                                                                  \
+  X(OP_COPY, 0x7003)                                                                   \
+  X(OP_GEMV_ROWS_BF16, 0x7200)                                                         \
+  X(OP_ATTN_DECODE_PAGED_G4, 0x7210)                                                   \
+  X(OP_ATTN_DECODE_PAGED_G8, 0x7211)                                                   \
+  X(OP_ATTN_MERGE, 0x7212)                                                             \
+  X(OP_ARGMAX_FINAL, 0x7220)                                                          \
+  X(OP_EXT, 0x7FFF)
+
+// OP_EXT is never dispatched: it marks the second 8-byte word of a two-word
+// compute instruction (GEMV_ROWS, ATTN_DECODE_PAGED).
+//
+// GEMV_ROWS args[1] layout: bits 0..4 rows per chunk (1,2,4,8,16), bits 8..10
+// epilogue mode, bit 11 accumulate into the output (residual add), bit 12 fused
+// RMSNorm of the activation vector.  args[2]: K/256 in the low byte.  Second
+// word: fp32 bits of the norm eps (hi, lo), first output row / 8 (argmax mode).
+#define VDC_GEMV_MODE_STORE 0
+#define VDC_GEMV_MODE_SILU_PAIRS 1
+#define VDC_GEMV_MODE_ARGMAX 2
+#define VDC_GEMV_ACC_BIT 0x0800
+#define VDC_GEMV_NORM_BIT 0x1000
+
+// ATTN_DECODE args[2] bits
+#define VDC_ATTN_QKNORM_BIT 0x1
+
+// words of the per-sequence decode state block in device memory
+#define VDC_ST_POS 0        // number of cached positions = position of the token being decoded
+#define VDC_ST_NPAGES 1     // pos / 64 + 1
+#define VDC_ST_TOKEN 2      // id of the token being decoded
+#define VDC_ST_STEP 3       // decode steps completed
+#define VDC_ST_NEWROW 4     // page_table[pos/64] * 64 * n_kv_heads + pos % 64   (256-byte row units)
+#define VDC_ST_NKVH 5       // n_kv_heads (constant, used to advance NEWROW)
+#define VDC_ST_MAXPAGES 6
+#define VDC_ST_ERR 7
+#define VDC_ST_PAGETABLE 8  // int32 page ids follow
+
+#define VDC_KV_PAGE 64      // positions per KV page
+#define VDC_HEAD_DIM 128
+
+// status codes written to vdc_status.code
+#define VDC_OK 0
+#define VDC_ERR_TIMEOUT 1
+#define VDC_ERR_BAD_OPCODE 2
+#define VDC_ERR_CUDA 3
+#define VDC_ERR_ARG 4
+
+typedef struct vdc_status {
+  int32_t abort;    // non-zero once any wait gave up; every other wait then returns
+  int32_t code;     // VDC_ERR_*
+  int32_t sm;       // CTA that raised it
+  int32_t role;     // 0 compute, 1 control warp, 2 store warp, 3/4 load port 0/1
+  int32_t pc;       // instruction index where it happened (role dependent)
+  int32_t opcode;   // raw opcode field
+  int32_t bar;      // global barrier id being waited for, or -1
+  int32_t aux;
+} vdc_status;
+
+#ifdef __cplusplus
+struct alignas(8) VdcCInst {
+  uint16_t opcode;
+  uint16_t args[3];
+};
+struct alignas(16) VdcMInst {
+  uint16_t opcode;
+  uint16_t size;
+  union {
+    struct {
+      uint16_t num_slots;
+      uint16_t arg;
+    };
+    uint32_t shifter;
+  };
+  union {
+    uint64_t address;
+    uint16_t coords[4];
+  };
+};
+static_assert(sizeof(VdcCInst) == 8 && sizeof(VdcMInst) == 16, "wire format");
+#endif

@@ -1,0 +1,473 @@
+"""Batch-1 decode engine: packs a Llama / Qwen3 style model for the megakernel,
+builds the per-SM instruction program once, and runs one kernel launch per
+generated token.
+
+The program plays the role of the reference's model schedule scripts
+(reference app/python/llama3/sched.py:255-571, app/python/qwen3/sched.py): the
+same stages — fused-norm QKV projection, GQA decode attention, output
+projection with residual add, fused-norm gate/up with SiLU·mul, down projection
+with residual add, final norm + vocabulary projection + argmax — cross-SM
+ordering through countdown barriers, weights prefetched ahead of the
+activations they wait for.  Unlike the reference it is laid out for all SMs of
+a B200, a paged KV cache, and position-independent instruction streams (the
+position comes from a small state block in device memory), so one program
+serves every step.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import List, Optional
+
+import numpy as np
+import torch
+
+from . import isa, runtime
+from .program import Dst, Program, Src
+
+BF16 = torch.bfloat16
+
+
+@dataclass
+class DecodeConfig:
+    hidden: int = 4096
+    n_heads: int = 32
+    n_kv_heads: int = 8
+    head_dim: int = 128
+    ffn: int = 14336
+    vocab: int = 128256
+    n_layers: int = 32
+    eps: float = 1e-5
+    theta: float = 500000.0
+    qk_norm: bool = False
+    qk_norm_eps: float = 1e-6
+
+    @property
+    def q_width(self):
+        return self.n_heads * self.head_dim
+
+    @property
+    def kv_width(self):
+        return self.n_kv_heads * self.head_dim
+
+    @property
+    def group(self):
+        return self.n_heads // self.n_kv_heads
+
+
+LLAMA31_8B = DecodeConfig()
+QWEN3_8B = DecodeConfig(ffn=12288, vocab=151936, n_layers=36, eps=1e-6, theta=1e6, qk_norm=True)
+
+
+@dataclass
+class DenseWeights:
+    """Unpacked bf16 weights, one entry per layer, in the usual [out, in] layout."""
+    embed: torch.Tensor
+    lm_head: torch.Tensor
+    norm: torch.Tensor
+    ln1: List[torch.Tensor]
+    ln2: List[torch.Tensor]
+    wq: List[torch.Tensor]
+    wk: List[torch.Tensor]
+    wv: List[torch.Tensor]
+    wo: List[torch.Tensor]
+    gate: List[torch.Tensor]
+    up: List[torch.Tensor]
+    down: List[torch.Tensor]
+    q_norm: Optional[List[torch.Tensor]] = None
+    k_norm: Optional[List[torch.Tensor]] = None
+
+
+def rows_per_chunk(K: int, even: bool = False) -> int:
+    """Largest power-of-two row count whose bf16 rows fit one 32 KB bulk copy."""
+    r = 16
+    while r > 1 and r * K * 2 > 32768:
+        r //= 2
+    if r * K * 2 > 32768 or (even and r < 2):
+        raise ValueError(f"K={K} rows do not fit the 32 KB chunk limit")
+    return r
+
+
+class DecodeEngine:
+    def __init__(self, cfg: DecodeConfig, max_seq: int, device="cuda", num_sms: Optional[int] = None,
+                 taps: bool = False, page_perm_seed: Optional[int] = None, max_steps: int = 4096,
+                 timeout_ns: int = 0):
+        assert cfg.head_dim == isa.HEAD_DIM, "the attention task is built for head_dim 128"
+        assert cfg.group in (4, 8), "GQA group size must be 4 or 8"
+        assert cfg.n_kv_heads & (cfg.n_kv_heads - 1) == 0, "n_kv_heads must be a power of two"
+        assert cfg.hidden % 256 == 0 and cfg.ffn % 256 == 0 and cfg.q_width % 256 == 0
+        self.cfg = cfg
+        self.dev = torch.device(device)
+        props = torch.cuda.get_device_properties(self.dev)
+        self.num_sms = num_sms or props.multi_processor_count
+        self.max_seq = max_seq
+        self.max_pages = (max_seq + isa.KV_PAGE - 1) // isa.KV_PAGE
+        self.taps_enabled = taps
+        self.max_steps = max_steps
+        self.timeout_ns = timeout_ns
+        self.stream = torch.cuda.current_stream(self.dev)
+        runtime.init()
+
+        L, H, F, V = cfg.n_layers, cfg.hidden, cfg.ffn, cfg.vocab
+        z = lambda *s, dt=BF16: torch.zeros(*s, dtype=dt, device=self.dev)
+        self.qkv_rows = cfg.q_width + 2 * cfg.kv_width
+        self.hidden = z(H)
+        self.qkv = z(self.qkv_rows)
+        self.attn_out = z(cfg.q_width)
+        self.act = z(F)
+        self.logits = z(V)
+        G = cfg.group
+        self.rec_floats = G * isa.HEAD_DIM + 16 * ((2 * G + 15) // 16)
+        max_rec_per_load = 32768 // (self.rec_floats * 4)
+        self.n_splits = max(1, min(self.num_sms // cfg.n_kv_heads, self.max_pages, 2 * max_rec_per_load))
+        self.pages_per_split = (self.max_pages + self.n_splits - 1) // self.n_splits
+        self.n_splits = (self.max_pages + self.pages_per_split - 1) // self.pages_per_split
+        self.max_rec_per_load = max_rec_per_load
+        self.attn_part = z(cfg.n_kv_heads, self.n_splits, self.rec_floats, dt=torch.float32)
+        self.argmax_rec = z(self.num_sms, 4, dt=torch.float32)
+        self.state = z(isa.ST_PAGETABLE + self.max_pages, dt=torch.int32)
+        self.state_host = torch.zeros(isa.ST_PAGETABLE + self.max_pages, dtype=torch.int32).pin_memory()
+        self.token_log = z(max_steps, dt=torch.int32)
+        self.kpool = z(L, self.max_pages, cfg.n_kv_heads, isa.KV_PAGE, isa.HEAD_DIM)
+        self.vpool = z(L, self.max_pages, cfg.n_kv_heads, isa.KV_PAGE, isa.HEAD_DIM)
+        self.taps = z(L, H) if taps else None
+        if page_perm_seed is None:
+            self.page_table = torch.arange(self.max_pages, dtype=torch.int32)
+        else:
+            g = torch.Generator().manual_seed(page_perm_seed)
+            self.page_table = torch.randperm(self.max_pages, generator=g).to(torch.int32)
+        # rope table: cos[64] | sin[64] per position, values rounded to bf16 like HF's tables, kept as fp32
+        pos = torch.arange(max_seq, dtype=torch.float32)
+        inv = 1.0 / (cfg.theta ** (torch.arange(0, isa.HEAD_DIM, 2, dtype=torch.float32) / isa.HEAD_DIM))
+        fr = pos[:, None] * inv[None, :]
+        self.rope = torch.cat((fr.cos().to(BF16).float(), fr.sin().to(BF16).float()), dim=1).contiguous().to(self.dev)
+        self.bars = z(isa.MAX_BARS, dt=torch.int32)
+        self.profile = z(self.num_sms * isa.NUM_PROFILE_EVENTS, dt=torch.int64)
+        self.w = None
+        self.program = None
+        self.pos = 0
+        self.steps_done = 0
+
+    # ------------------------------------------------------------------ weights
+    def load_weights(self, w: DenseWeights):
+        cfg, dev = self.cfg, self.dev
+        L = cfg.n_layers
+        to = lambda t: t.to(device=dev, dtype=BF16).contiguous()
+        self.embed = to(w.embed)
+        self.lm_head = to(w.lm_head)
+        self.norm_w = to(w.norm)
+        self.ln1 = torch.stack([to(t) for t in w.ln1])
+        self.ln2 = torch.stack([to(t) for t in w.ln2])
+        self.wqkv = torch.stack([torch.cat((to(w.wq[l]), to(w.wk[l]), to(w.wv[l])), dim=0) for l in range(L)])
+        self.wo = torch.stack([to(w.wo[l]) for l in range(L)])
+        # gate and up rows interleaved: row 2j = gate_j, row 2j+1 = up_j
+        self.wgu = torch.stack([torch.stack((to(w.gate[l]), to(w.up[l])), dim=1).reshape(2 * cfg.ffn, cfg.hidden)
+                                for l in range(L)])
+        self.wd = torch.stack([to(w.down[l]) for l in range(L)])
+        if cfg.qk_norm:
+            self.qknorm = torch.stack([torch.cat((to(w.q_norm[l]), to(w.k_norm[l]))) for l in range(L)])
+        else:
+            self.qknorm = None
+        self.w = True
+        self._build_program()
+
+    def init_random_weights(self, seed: int = 0, std: float = 0.02):
+        """Random N(0, std) weights generated on the device (benchmarks)."""
+        cfg, dev = self.cfg, self.dev
+        g = torch.Generator(device=dev).manual_seed(seed)
+        L, H, F, V = cfg.n_layers, cfg.hidden, cfg.ffn, cfg.vocab
+
+        def rnd(*shape):
+            t = torch.empty(*shape, dtype=BF16, device=dev)
+            t.normal_(0.0, std, generator=g)
+            return t
+        self.embed = rnd(V, H)
+        self.lm_head = rnd(V, H)
+        self.norm_w = torch.ones(H, dtype=BF16, device=dev)
+        self.ln1 = torch.ones(L, H, dtype=BF16, device=dev)
+        self.ln2 = torch.ones(L, H, dtype=BF16, device=dev)
+        self.wqkv = rnd(L, self.qkv_rows, H)
+        self.wo = rnd(L, H, cfg.q_width)
+        self.wgu = rnd(L, 2 * F, H)
+        self.wd = rnd(L, H, F)
+        self.qknorm = torch.ones(L, 2 * isa.HEAD_DIM, dtype=BF16, device=dev) if cfg.qk_norm else None
+        self.w = True
+        self._build_program()
+
+    def weight_bytes(self) -> int:
+        ts = [self.lm_head, self.norm_w, self.ln1, self.ln2, self.wqkv, self.wo, self.wgu, self.wd]
+        if self.qknorm is not None:
+            ts.append(self.qknorm)
+        return sum(t.numel() * t.element_size() for t in ts) + self.cfg.hidden * 2
+
+    def algorithmic_bytes(self, pos: int) -> int:
+        """HBM bytes one decode step at position `pos` has to read: every weight
+        once, one embedding row, and the KV rows of pos+1 positions."""
+        cfg = self.cfg
+        return self.weight_bytes() + 2 * cfg.kv_width * 2 * (pos + 1) * cfg.n_layers
+
+    # ------------------------------------------------------------------ program
+    def _ranges(self, P: Program, n_units: int, unit_bytes: int, granule: int = 1):
+        """Splits n_units into one contiguous range per SM (multiples of granule);
+        the SMs that have loaded the fewest bytes so far take the larger share."""
+        S = self.num_sms
+        assert n_units % granule == 0
+        n_g = n_units // granule
+        base, rem = divmod(n_g, S)
+        order = sorted(range(S), key=lambda s: (P.bytes_loaded[s], s))
+        extra = set(order[:rem])
+        out, u = [], 0
+        for sm in range(S):
+            cnt = (base + (1 if sm in extra else 0)) * granule
+            if cnt:
+                out.append((sm, u, cnt))
+            u += cnt
+        assert u == n_units
+        return out
+
+    def _pick(self, P: Program, n: int):
+        order = sorted(range(self.num_sms), key=lambda s: (P.bytes_loaded[s], s))
+        return [order[i % self.num_sms] for i in range(n)]
+
+    def _build_program(self):
+        cfg = self.cfg
+        L, H, F, V, G = cfg.n_layers, cfg.hidden, cfg.ffn, cfg.vocab, cfg.group
+        D = isa.HEAD_DIM
+        S = self.num_sms
+        P = Program(S, insts_per_sm=isa.MAX_INSTS)
+        st = self.state.data_ptr()
+        page_bytes = isa.KV_PAGE * D * 2
+        page_stride = cfg.n_kv_heads * page_bytes
+        page_shift = int(math.log2(page_stride))
+        assert 1 << page_shift == page_stride
+        hid, qkv, ao, act = (t.data_ptr() for t in (self.hidden, self.qkv, self.attn_out, self.act))
+        embed_src = lambda: Src(self.embed.data_ptr(), H * 2, indirect=(st + 4 * isa.ST_TOKEN, None, H * 2))
+
+        b_hid = None
+        for l in range(L):
+            # ---- QKV projection with fused input RMSNorm
+            b_qkv = P.new_barrier()
+            R = rows_per_chunk(H)
+            for sm, u0, cnt in self._ranges(P, self.qkv_rows // R, R * H * 2, granule=max(1, 8 // R)):
+                r0, n = u0 * R, cnt * R
+                x = Src(hid, H * 2, wait=b_hid) if l > 0 else embed_src()
+                P.gemv(sm, w_addr=self.wqkv[l].data_ptr() + r0 * H * 2, n_rows=n, K=H, R=R, x=x,
+                       out=Dst(qkv + r0 * 2, n * 2, "store", release=b_qkv),
+                       norm_w=Src(self.ln1[l].data_ptr(), H * 2), eps=cfg.eps)
+            if l == 0:
+                sm = self._pick(P, 1)[0]
+                P.copy(sm, embed_src(), Dst(hid, H * 2, release=b_qkv), H * 2)
+            elif self.taps_enabled:
+                sm = self._pick(P, 1)[0]
+                P.copy(sm, Src(hid, H * 2, wait=b_hid), Dst(self.taps[l - 1].data_ptr(), H * 2, release=b_qkv), H * 2)
+
+            # ---- split-K GQA decode attention over the paged cache
+            b_attn = P.new_barrier()
+            units = [(h, s) for s in range(self.n_splits) for h in range(cfg.n_kv_heads)]
+            kp, vp = self.kpool[l].data_ptr(), self.vpool[l].data_ptr()
+            q_off = lambda h: qkv + h * G * D * 2
+            k_off = lambda h: qkv + (cfg.q_width + h * D) * 2
+            v_off = lambda h: qkv + (cfg.q_width + cfg.kv_width + h * D) * 2
+            for (h, s), sm in zip(units, self._pick(P, len(units))):
+                P.attn_decode(
+                    sm, G=G, state_addr=st,
+                    rope=Src(self.rope.data_ptr(), D * 4, indirect=(st + 4 * isa.ST_POS, 9, None)),
+                    norm_w=Src(self.qknorm[l].data_ptr(), 2 * D * 2) if cfg.qk_norm else None,
+                    q=Src(q_off(h), G * D * 2, wait=b_qkv), k_new=Src(k_off(h), D * 2), v_new=Src(v_off(h), D * 2),
+                    k_row=Dst(kp + h * page_bytes, D * 2, indirect=(st + 4 * isa.ST_NEWROW, 8, None)),
+                    v_row=Dst(vp + h * page_bytes, D * 2, indirect=(st + 4 * isa.ST_NEWROW, 8, None)),
+                    k_page_addr=kp + h * page_bytes, v_page_addr=vp + h * page_bytes, page_shift=page_shift,
+                    base_page=s * self.pages_per_split, max_pages=self.pages_per_split,
+                    out=Dst(self.attn_part[h, s].data_ptr(), self.rec_floats * 4, release=b_attn),
+                    qk_eps=cfg.qk_norm_eps)
+
+            # ---- merge of the split partials, one task per KV head
+            b_merge = P.new_barrier()
+            n1 = min(self.n_splits, self.max_rec_per_load)
+            for h, sm in zip(range(cfg.n_kv_heads), self._pick(P, cfg.n_kv_heads)):
+                base = self.attn_part[h].data_ptr()
+                recs = [Src(base, n1 * self.rec_floats * 4, wait=b_attn)]
+                if self.n_splits > n1:
+                    recs.append(Src(base + n1 * self.rec_floats * 4, (self.n_splits - n1) * self.rec_floats * 4,
+                                    wait=b_attn))
+                P.attn_merge(sm, G=G, n_splits=self.n_splits, records=recs, n_first=n1,
+                             out=Dst(ao + h * G * D * 2, G * D * 2, release=b_merge))
+
+            # ---- output projection, residual add into hidden
+            b_o = P.new_barrier()
+            K = cfg.q_width
+            R = rows_per_chunk(K)
+            for sm, u0, cnt in self._ranges(P, H // R, R * K * 2):
+                r0, n = u0 * R, cnt * R
+                P.gemv(sm, w_addr=self.wo[l].data_ptr() + r0 * K * 2, n_rows=n, K=K, R=R,
+                       x=Src(ao, K * 2, wait=b_merge), out=Dst(hid + r0 * 2, n * 2, "add_bf16", release=b_o))
+
+            # ---- gate/up projection with fused post-attention RMSNorm and SiLU·mul
+            b_gu = P.new_barrier()
+            R = rows_per_chunk(H, even=True)
+            for sm, u0, cnt in self._ranges(P, 2 * F // R, R * H * 2):
+                r0, n = u0 * R, cnt * R
+                P.gemv(sm, w_addr=self.wgu[l].data_ptr() + r0 * H * 2, n_rows=n, K=H, R=R,
+                       x=Src(hid, H * 2, wait=b_o), out=Dst(act + (r0 // 2) * 2, n, "store", release=b_gu),
+                       mode=isa.GEMV_MODE_SILU_PAIRS, norm_w=Src(self.ln2[l].data_ptr(), H * 2), eps=cfg.eps)
+
+            # ---- down projection, residual add into hidden
+            b_hid = P.new_barrier()
+            R = rows_per_chunk(F)
+            for sm, u0, cnt in self._ranges(P, H // R, R * F * 2):
+                r0, n = u0 * R, cnt * R
+                P.gemv(sm, w_addr=self.wd[l].data_ptr() + r0 * F * 2, n_rows=n, K=F, R=R,
+                       x=Src(act, F * 2, wait=b_gu), out=Dst(hid + r0 * 2, n * 2, "add_bf16", release=b_hid))
+
+        # ---- final norm + vocabulary projection + per-SM argmax candidates
+        b_logits = P.new_barrier()
+        R = rows_per_chunk(H)
+        if self.taps_enabled:
+            sm = self._pick(P, 1)[0]
+            b_tap = P.new_barrier()
+            P.copy(sm, Src(hid, H * 2, wait=b_hid), Dst(self.taps[L - 1].data_ptr(), H * 2, release=b_tap), H * 2)
+        lm_ranges = self._ranges(P, V // R, R * H * 2, granule=max(1, 8 // R))
+        for i, (sm, u0, cnt) in enumerate(lm_ranges):
+            r0, n = u0 * R, cnt * R
+            P.gemv(sm, w_addr=self.lm_head.data_ptr() + r0 * H * 2, n_rows=n, K=H, R=R,
+                   x=Src(hid, H * 2, wait=b_hid), out=Dst(self.logits.data_ptr() + r0 * 2, n * 2, "store", release=b_logits),
+                   mode=isa.GEMV_MODE_ARGMAX, norm_w=Src(self.norm_w.data_ptr(), H * 2), eps=cfg.eps,
+                   pair_out=Dst(self.argmax_rec[i].data_ptr(), 16, release=b_logits), row_base=r0)
+        sm = self._pick(P, 1)[0]
+        P.argmax_final(sm, records=Src(self.argmax_rec.data_ptr(), len(lm_ranges) * 16, wait=b_logits),
+                       n=len(lm_ranges), state_addr=st, log_addr=self.token_log.data_ptr())
+
+        st_ = P.stats()
+        n_insts = max(st_["max_minsts"], st_["max_cinsts"]) + 2
+        P.insts_per_sm = ((n_insts + 63) // 64) * 64
+        c, m, bars = P.finalize()
+        self.program = P
+        self.insts_per_sm = P.insts_per_sm
+        self.cinsts = torch.from_numpy(c).to(self.dev)
+        self.minsts = torch.from_numpy(m).to(self.dev)
+        self.bars_init = torch.from_numpy(bars).to(self.dev)
+        self.launches_per_step = 1
+
+    # ------------------------------------------------------------------ state
+    def set_state(self, pos: int, token: int):
+        """Positions [0, pos) are cached; `token` is decoded next at position pos."""
+        assert pos < self.max_seq
+        s = self.state_host
+        s.zero_()
+        page = pos // isa.KV_PAGE
+        s[isa.ST_POS] = pos
+        s[isa.ST_NPAGES] = page + 1
+        s[isa.ST_TOKEN] = token
+        s[isa.ST_STEP] = 0
+        s[isa.ST_NEWROW] = int(self.page_table[page]) * isa.KV_PAGE * self.cfg.n_kv_heads + pos % isa.KV_PAGE
+        s[isa.ST_NKVH] = self.cfg.n_kv_heads
+        s[isa.ST_MAXPAGES] = self.max_pages
+        s[isa.ST_PAGETABLE:] = self.page_table
+        self.state.copy_(s, non_blocking=True)
+        self.pos = pos
+        self.steps_done = 0
+
+    def load_kv(self, k: List[torch.Tensor], v: List[torch.Tensor]):
+        """Fills the paged pools from per-layer contiguous caches [T, n_kv_heads, 128]."""
+        cfg = self.cfg
+        pt = self.page_table.long().to(self.dev)
+        for l in range(cfg.n_layers):
+            for src, pool in ((k[l], self.kpool[l]), (v[l], self.vpool[l])):
+                T = src.shape[0]
+                n_pages = (T + isa.KV_PAGE - 1) // isa.KV_PAGE
+                pad = torch.zeros(n_pages * isa.KV_PAGE, cfg.n_kv_heads, isa.HEAD_DIM, dtype=BF16, device=self.dev)
+                pad[:T] = src.to(self.dev)
+                pool[pt[:n_pages]] = pad.view(n_pages, isa.KV_PAGE, cfg.n_kv_heads, isa.HEAD_DIM).permute(0, 2, 1, 3)
+
+    def read_kv(self, layer: int, T: int):
+        """Contiguous [T, n_kv_heads, 128] views of layer `layer`'s cache (tests)."""
+        n_pages = (T + isa.KV_PAGE - 1) // isa.KV_PAGE
+        pt = self.page_table.long().to(self.dev)[:n_pages]
+        out = []
+        for pool in (self.kpool[layer], self.vpool[layer]):
+            t = pool[pt].permute(0, 2, 1, 3).reshape(n_pages * isa.KV_PAGE, self.cfg.n_kv_heads, isa.HEAD_DIM)
+            out.append(t[:T])
+        return out
+
+    # ------------------------------------------------------------------ prefill (PyTorch, not the timed path)
+    @torch.no_grad()
+    def prefill(self, tokens: torch.Tensor) -> int:
+        """Runs the prompt through plain PyTorch ops on the GPU, fills the KV
+        pools and returns the greedy next token.  The decode path starts after it."""
+        cfg, dev = self.cfg, self.dev
+        D, G = isa.HEAD_DIM, cfg.group
+        T = tokens.numel()
+        ids = tokens.to(dev).long()
+        h = self.embed[ids]
+        cos = self.rope[:T, :64].to(BF16)
+        sin = self.rope[:T, 64:].to(BF16)
+        cos = torch.cat((cos, cos), -1)[:, None, :]
+        sin = torch.cat((sin, sin), -1)[:, None, :]
+
+        def norm(x, w, eps):
+            xf = x.float()
+            return w * (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(BF16)
+
+        def rot(x):
+            return torch.cat((-x[..., D // 2:], x[..., :D // 2]), -1)
+        ks, vs = [], []
+        for l in range(cfg.n_layers):
+            x = norm(h, self.ln1[l], cfg.eps)
+            qkv = x @ self.wqkv[l].t()
+            q = qkv[:, :cfg.q_width].view(T, cfg.n_heads, D)
+            k = qkv[:, cfg.q_width:cfg.q_width + cfg.kv_width].view(T, cfg.n_kv_heads, D)
+            v = qkv[:, cfg.q_width + cfg.kv_width:].view(T, cfg.n_kv_heads, D)
+            if cfg.qk_norm:
+                q = norm(q, self.qknorm[l, :D], cfg.qk_norm_eps)
+                k = norm(k, self.qknorm[l, D:], cfg.qk_norm_eps)
+            q = q * cos + rot(q) * sin
+            k = k * cos + rot(k) * sin
+            ks.append(k)
+            vs.append(v)
+            o = torch.nn.functional.scaled_dot_product_attention(
+                q.transpose(0, 1)[None], k.transpose(0, 1)[None], v.transpose(0, 1)[None], is_causal=True,
+                enable_gqa=True)[0].transpose(0, 1).reshape(T, cfg.q_width)
+            h = h + o @ self.wo[l].t()
+            x = norm(h, self.ln2[l], cfg.eps)
+            gu = x @ self.wgu[l].t()
+            a = torch.nn.functional.silu(gu[:, 0::2]) * gu[:, 1::2]
+            h = h + a @ self.wd[l].t()
+        self.load_kv(ks, vs)
+        hn = norm(h[-1], self.norm_w, cfg.eps)
+        logits = hn @ self.lm_head.t()
+        tok = int(torch.argmax(logits.float()))
+        self.set_state(T, tok)
+        return tok
+
+    # ------------------------------------------------------------------ decode
+    def step_async(self):
+        """Enqueues one decode step (one kernel launch); no synchronisation."""
+        assert self.program is not None, "load weights first"
+        if self.pos >= self.max_seq or self.steps_done >= self.max_steps:
+            raise RuntimeError("out of KV pages or token-log space")
+        runtime.launch_async(self.num_sms, self.insts_per_sm, self.cinsts, self.minsts, None, self.bars,
+                             self.bars_init, self.profile, self.stream.cuda_stream, self.timeout_ns)
+        self.pos += 1
+        self.steps_done += 1
+
+    def generate(self, n_steps: int) -> List[int]:
+        """Greedy decode of n_steps tokens, device resident; returns the ids."""
+        first = self.steps_done
+        for _ in range(n_steps):
+            self.step_async()
+        runtime.read_status(self.stream.cuda_stream)
+        return self.token_log[first:first + n_steps].tolist()
+
+    def step_host(self, token: int) -> int:
+        """One decode step driven from host buffers: the token id goes up, the
+        next id comes back (synchronous)."""
+        if not hasattr(self, "_tok_in"):
+            self._tok_in = torch.zeros(1, dtype=torch.int32).pin_memory()
+            self._tok_out = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self._tok_in[0] = token
+        self.state[isa.ST_TOKEN:isa.ST_TOKEN + 1].copy_(self._tok_in, non_blocking=True)
+        idx = self.steps_done
+        self.step_async()
+        self._tok_out.copy_(self.token_log[idx:idx + 1], non_blocking=True)
+        runtime.read_status(self.stream.cuda_stream)
+        return int(self._tok_out[0])

@@ -1,0 +1,299 @@
+"""Per-SM instruction streams for the decode megakernel.
+
+A ``Program`` holds, for every SM, the memory-core stream (16-byte
+instructions) and the compute-core stream (8-byte instructions) in the wire
+format of the reference ISA (reference include/dae/context.cuh:51-113), and
+derives the initial value of every global countdown barrier from the stores
+that release it, the way the reference's launcher does from its schedules
+(reference python/dae/schedule.py:39-55, python/dae/launcher.py:343-351).
+
+The task helpers (``gemv``, ``attn_decode`` ...) emit the memory and the
+compute instructions of one task on one SM in the order the device task pops
+its operands.
+"""
+from __future__ import annotations
+
+import math
+import struct
+from dataclasses import dataclass
+from typing import List, Optional
+
+import numpy as np
+
+from . import isa
+
+MINST = np.dtype([("opcode", "<u2"), ("size", "<u2"), ("num_slots", "<u2"), ("arg", "<u2"), ("address", "<u8")])
+CINST = np.dtype([("opcode", "<u2"), ("a0", "<u2"), ("a1", "<u2"), ("a2", "<u2")])
+assert MINST.itemsize == 16 and CINST.itemsize == 8
+
+SLOT = isa.SLOT_BYTES
+
+
+def slots_for(nbytes: int) -> int:
+    return max(1, (nbytes + SLOT - 1) // SLOT)
+
+
+def f32_bits(x: float) -> int:
+    return struct.unpack("<I", struct.pack("<f", float(x)))[0]
+
+
+@dataclass
+class Src:
+    """A 1-D bulk load: `nbytes` from device address `addr`.
+
+    wait: global barrier id that must reach zero first (None: no wait).
+    indirect: (word_address, shift, row_bytes): the address is offset by the
+      32-bit word read at issue time, `word << shift` when row_bytes is None,
+      `word * row_bytes` otherwise (embedding row / KV page gather)."""
+    addr: int
+    nbytes: int
+    wait: Optional[int] = None
+    indirect: Optional[tuple] = None
+    port: Optional[int] = None
+
+
+@dataclass
+class Dst:
+    """A write-back: bulk store (kind 'store') or bulk reduce-add ('add_bf16',
+    'add_f32') of `nbytes` to `addr`; `release` names the barrier it counts
+    down once the data is globally visible."""
+    addr: int
+    nbytes: int
+    kind: str = "store"
+    release: Optional[int] = None
+    indirect: Optional[tuple] = None
+
+
+class Program:
+    def __init__(self, num_sms: int, insts_per_sm: int = isa.MAX_INSTS):
+        self.num_sms = num_sms
+        self.insts_per_sm = insts_per_sm
+        self.m: List[list] = [[] for _ in range(num_sms)]
+        self.c: List[list] = [[] for _ in range(num_sms)]
+        self.bar_counts = {}
+        self.bytes_loaded = [0] * num_sms       # bulk-load bytes issued per SM (for balancing)
+        self._next_bar = 0
+        self._finalized = False
+
+    # ------------------------------------------------------------------ barriers
+    def new_barrier(self) -> int:
+        b = self._next_bar
+        self._next_bar += 1
+        if b >= isa.MAX_BARS:
+            raise ValueError("out of global barriers")
+        self.bar_counts[b] = 0
+        return b
+
+    # ------------------------------------------------------------------ raw emitters
+    def mem(self, sm, opcode, *, size=0, nslot=0, bar=0, arg=0, address=0, flags=0, reg_range=None):
+        if reg_range is not None:
+            num_slots = (reg_range[0] & 0xFF) | ((reg_range[1] & 0xFF) << 8)
+        else:
+            assert 0 <= nslot < 64 and 0 <= bar < isa.MAX_BARS
+            num_slots = nslot | (bar << 6)
+        assert 0 <= size <= 0xFFFF and 0 <= arg <= 0xFFFF
+        self.m[sm].append((opcode | flags, size, num_slots, arg, address & 0xFFFFFFFFFFFFFFFF))
+
+    def comp(self, sm, opcode, a0=0, a1=0, a2=0):
+        for a in (a0, a1, a2):
+            assert 0 <= a <= 0xFFFF, a
+        self.c[sm].append((opcode, a0, a1, a2))
+
+    # ------------------------------------------------------------------ operand emitters
+    def load(self, sm, src: Src, default_port=0):
+        assert src.nbytes % 16 == 0 and src.addr % 16 == 0, (src.nbytes, src.addr)
+        assert 0 < src.nbytes <= 32768
+        if src.indirect is not None:
+            waddr, shift, row_bytes = src.indirect
+            if row_bytes is None:
+                self.mem(sm, isa.OP_CC0, arg=shift, address=waddr)
+            else:
+                self.mem(sm, isa.OP_CC0_ROW_BYTES, size=row_bytes, address=waddr)
+        flags = 0
+        port = src.port if src.port is not None else (1 if src.wait is not None else default_port)
+        if port:
+            flags |= isa.F_PORT
+        bar = 0
+        if src.wait is not None:
+            flags |= isa.F_BARRIER
+            bar = src.wait
+        self.mem(sm, isa.OP_ALLOC_TMA_LOAD_1D, size=src.nbytes, nslot=slots_for(src.nbytes), bar=bar,
+                 address=src.addr, flags=flags)
+        self.bytes_loaded[sm] += src.nbytes
+
+    def store(self, sm, dst: Dst):
+        assert dst.nbytes % 16 == 0 and dst.addr % 16 == 0, (dst.nbytes, dst.addr)
+        assert 0 < dst.nbytes <= SLOT * 4
+        if dst.indirect is not None:
+            waddr, shift, row_bytes = dst.indirect
+            if row_bytes is None:
+                self.mem(sm, isa.OP_CC0, arg=shift, address=waddr)
+            else:
+                self.mem(sm, isa.OP_CC0_ROW_BYTES, size=row_bytes, address=waddr)
+        flags, bar, arg = 0, 0, 0
+        if dst.release is not None:
+            flags |= isa.F_BARRIER
+            bar = dst.release
+            self.bar_counts[bar] += 1
+        if dst.kind == "store":
+            op = isa.OP_ALLOC_WB_TMA_STORE_1D
+        elif dst.kind == "add_bf16":
+            op = isa.OP_ALLOC_WB_TMA_REDUCE_ADD_1D
+        elif dst.kind == "add_f32":
+            op, arg = isa.OP_ALLOC_WB_TMA_REDUCE_ADD_1D, 1
+        else:
+            raise ValueError(dst.kind)
+        self.mem(sm, op, size=dst.nbytes, nslot=slots_for(dst.nbytes), bar=bar, arg=arg, address=dst.addr, flags=flags)
+
+    def raw_address(self, sm, addr, special_slot, release=None, wait=None):
+        """Hands a 64-bit value to the compute task through special slot
+        `special_slot` (24..32).  With `release` the store warp counts that
+        barrier down when the task pushes the slot back; with `wait` the load
+        port holds the hand-over until that barrier reached zero."""
+        assert isa.NUM_SLOTS <= special_slot < isa.NUM_SLOTS + isa.NUM_SPECIAL_SLOTS
+        flags, bar = 0, 0
+        if release is not None:
+            flags |= isa.F_BARRIER | isa.F_WRITEBACK
+            bar = release
+            self.bar_counts[bar] += 1
+        elif wait is not None:
+            flags |= isa.F_BARRIER | isa.F_PORT
+            bar = wait
+        self.mem(sm, isa.OP_ALLOC_WB_RAW_ADDRESS, nslot=special_slot, bar=bar, arg=special_slot, address=addr,
+                 flags=flags)
+
+    def repeat(self, sm, count, deltas, dynamic=False):
+        """Loop header for the next len(deltas) memory instructions: instruction
+        i gets `address += iteration * deltas[i]`.  The caller sets F_JUMP on the
+        last body instruction.  dynamic: the count comes from the last DYN_COUNT."""
+        n = len(deltas)
+        assert 1 <= n <= 32
+        # one header per run of equal consecutive deltas; the last header carries the count
+        runs = []
+        for i, d in enumerate(deltas):
+            if runs and runs[-1][2] == d:
+                runs[-1][1] = i + 1
+            else:
+                runs.append([i, i + 1, d])
+        for k, (lo, hi, d) in enumerate(runs):
+            last = k == len(runs) - 1
+            size = (0xFFFF if dynamic else count) if last else 0
+            self.mem(sm, isa.OP_REPEAT, size=size, arg=(n if (last and dynamic) else 0), address=d,
+                     reg_range=(lo, hi))
+
+    def dyn_count(self, sm, word_addr, base, maximum):
+        self.mem(sm, isa.OP_DYN_COUNT, size=maximum, address=word_addr, reg_range=None, nslot=0, bar=0)
+        # base travels in the num_slots field
+        op, size, _, arg, addr = self.m[sm][-1]
+        assert 0 <= base <= 0xFFFF
+        self.m[sm][-1] = (op, size, base, arg, addr)
+
+    # ------------------------------------------------------------------ tasks
+    def copy(self, sm, src: Src, dst: Dst, nbytes: int):
+        self.load(sm, src)
+        self.store(sm, dst)
+        self.comp(sm, isa.OP_COPY, 1, nbytes // 4)
+
+    def gemv(self, sm, *, w_addr, n_rows, K, R, x: Src, out: Dst, mode=isa.GEMV_MODE_STORE,
+             norm_w: Optional[Src] = None, eps: float = 0.0, pair_out: Optional[Dst] = None, row_base: int = 0):
+        """y[0:n_rows] = W[0:n_rows, :K] @ x for the contiguous bf16 row block at
+        w_addr, streamed as chunks of R rows.  The task writes y straight to
+        out.addr (kind 'store') or adds it there (kind 'add_bf16'); in SILU_PAIRS
+        mode rows (2j, 2j+1) are (gate_j, up_j) and n_rows/2 values are written."""
+        assert K % 256 == 0 and K * 2 * R <= 32768 and R in (1, 2, 4, 8, 16)
+        assert n_rows % R == 0 and n_rows > 0
+        assert mode != isa.GEMV_MODE_SILU_PAIRS or R % 2 == 0
+        assert out.kind in ("store", "add_bf16") and out.addr % 2 == 0
+        n_chunks = n_rows // R
+        assert n_chunks < 0xFFFF
+        chunk_bytes = R * K * 2
+        assert x.nbytes == K * 2
+        if norm_w is not None:
+            self.load(sm, norm_w, default_port=1)
+        self.load(sm, x, default_port=1)
+        self.raw_address(sm, out.addr, 24, release=out.release)
+        if mode == isa.GEMV_MODE_ARGMAX:
+            assert pair_out is not None and row_base % 8 == 0
+            self.raw_address(sm, pair_out.addr, 25, release=pair_out.release)
+        self.repeat(sm, n_chunks, [chunk_bytes])
+        self.mem(sm, isa.OP_ALLOC_TMA_LOAD_1D, size=chunk_bytes, nslot=slots_for(chunk_bytes), address=w_addr,
+                 flags=isa.F_JUMP)
+        self.bytes_loaded[sm] += chunk_bytes * n_chunks
+        rb8 = row_base // 8
+        a1 = R | (mode << 8) | (isa.GEMV_NORM_BIT if norm_w is not None else 0) | \
+            (isa.GEMV_ACC_BIT if out.kind == "add_bf16" else 0)
+        a2 = (K // 256) | ((rb8 >> 16) << 8)
+        e = f32_bits(eps)
+        self.comp(sm, isa.OP_GEMV_ROWS_BF16, n_chunks, a1, a2)
+        self.comp(sm, isa.OP_EXT, e >> 16, e & 0xFFFF, rb8 & 0xFFFF)
+
+    def attn_decode(self, sm, *, G, state_addr, rope: Src, norm_w: Optional[Src], q: Src, k_new: Src, v_new: Src,
+                    k_row: Dst, v_row: Dst, k_page_addr, v_page_addr, page_shift, base_page, max_pages,
+                    out: Dst, qk_eps: float = 1e-6, state_slot=24):
+        page_bytes = isa.KV_PAGE * isa.HEAD_DIM * 2
+        self.raw_address(sm, state_addr, state_slot)
+        self.load(sm, rope, default_port=1)
+        if norm_w is not None:
+            self.load(sm, norm_w, default_port=1)
+        self.load(sm, q)
+        self.load(sm, k_new, default_port=1)
+        self.load(sm, v_new, default_port=1)
+        self.store(sm, k_row)
+        self.store(sm, v_row)
+        tbl = state_addr + 4 * (isa.ST_PAGETABLE + base_page)
+        self.dyn_count(sm, state_addr + 4 * isa.ST_NPAGES, base_page, max_pages)
+        self.repeat(sm, 0, [4, 0, 4, 0], dynamic=True)
+        self.mem(sm, isa.OP_CC0, arg=page_shift, address=tbl)
+        self.mem(sm, isa.OP_ALLOC_TMA_LOAD_1D, size=page_bytes, nslot=slots_for(page_bytes), address=k_page_addr)
+        self.mem(sm, isa.OP_CC0, arg=page_shift, address=tbl)
+        self.mem(sm, isa.OP_ALLOC_TMA_LOAD_1D, size=page_bytes, nslot=slots_for(page_bytes), address=v_page_addr,
+                 flags=isa.F_JUMP)
+        self.bytes_loaded[sm] += 2 * page_bytes * max_pages
+        self.store(sm, out)
+        e = f32_bits(qk_eps)
+        op = isa.OP_ATTN_DECODE_PAGED_G4 if G == 4 else isa.OP_ATTN_DECODE_PAGED_G8
+        self.comp(sm, op, max_pages, base_page, isa.ATTN_QKNORM_BIT if norm_w is not None else 0)
+        self.comp(sm, isa.OP_EXT, e >> 16, e & 0xFFFF, 0)
+
+    def attn_merge(self, sm, *, G, n_splits, records: List[Src], n_first: int, out: Dst):
+        assert 1 <= len(records) <= 2
+        for r in records:
+            self.load(sm, r)
+        self.store(sm, out)
+        self.comp(sm, isa.OP_ATTN_MERGE, n_splits, G, n_first)
+
+    def argmax_final(self, sm, *, records: Src, n: int, state_addr, log_addr, release=None):
+        self.load(sm, records)
+        self.raw_address(sm, state_addr, 25)
+        self.raw_address(sm, log_addr, 26, release=release)
+        self.comp(sm, isa.OP_ARGMAX_FINAL, n)
+
+    # ------------------------------------------------------------------ output
+    def finalize(self):
+        """Appends the terminators and returns (compute u8[S*N,8], memory
+        u8[S*N,16], bars int32[MAX_BARS]) as numpy arrays."""
+        if not self._finalized:
+            for sm in range(self.num_sms):
+                self.mem(sm, isa.OP_TERMINATE)
+                self.comp(sm, isa.OP_TERMINATEC)
+            self._finalized = True
+        n = self.insts_per_sm
+        cm = np.zeros((self.num_sms, n), dtype=CINST)
+        mm = np.zeros((self.num_sms, n), dtype=MINST)
+        for sm in range(self.num_sms):
+            if len(self.c[sm]) > n or len(self.m[sm]) > n:
+                raise ValueError(f"SM {sm}: {len(self.c[sm])} compute / {len(self.m[sm])} memory instructions "
+                                 f"exceed the ring of {n}")
+            if self.c[sm]:
+                cm[sm, :len(self.c[sm])] = np.array(self.c[sm], dtype=CINST)
+            if self.m[sm]:
+                mm[sm, :len(self.m[sm])] = np.array(self.m[sm], dtype=MINST)
+        bars = np.zeros(isa.MAX_BARS, dtype=np.int32)
+        for b, cnt in self.bar_counts.items():
+            bars[b] = cnt
+        return (cm.view(np.uint8).reshape(self.num_sms * n, 8), mm.view(np.uint8).reshape(self.num_sms * n, 16), bars)
+
+    def stats(self):
+        return {"max_minsts": max(len(x) for x in self.m), "max_cinsts": max(len(x) for x in self.c),
+                "barriers": self._next_bar,
+                "bytes_loaded_max": max(self.bytes_loaded), "bytes_loaded_min": min(self.bytes_loaded)}
