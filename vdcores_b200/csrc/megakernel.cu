@@ -182,6 +182,10 @@ __device__ __noinline__ void raise_abort(const Ctx& c, int code, int role, int p
 template <class Pred>
 __device__ __forceinline__ bool wait_until(const Ctx& c, Pred ready, int role, int pc, int opcode, int bar,
                                            unsigned sleep_ns) {
+  // Waits on a named global barrier use the budget as given; queue waits (a
+  // role idling for work) get twice as long, so that when something is stuck
+  // the wait that names the culprit is the one that reports.
+  const uint64_t budget = bar >= 0 ? c.timeout_ns : 2 * c.timeout_ns;
   if (ready()) return true;
   uint32_t it = 0;
   uint64_t t0 = 0;
@@ -193,7 +197,7 @@ __device__ __forceinline__ bool wait_until(const Ctx& c, Pred ready, int role, i
       uint64_t now = globaltimer_ns();
       if (t0 == 0) {
         t0 = now;
-      } else if (now - t0 > c.timeout_ns) {
+      } else if (now - t0 > budget) {
         raise_abort(c, VDC_ERR_TIMEOUT, role, pc, opcode, bar, (int)it);
         return false;
       }
@@ -273,7 +277,7 @@ __device__ void control_warp(const Ctx& c, const VdcMInst* __restrict__ insts, i
               ab = ld_relaxed_gpu(&c.status->abort);
               uint64_t now = globaltimer_ns();
               if (t0 == 0) t0 = now;
-              else if (now - t0 > c.timeout_ns) {
+              else if (now - t0 > 2 * c.timeout_ns) {
                 raise_abort(c, VDC_ERR_TIMEOUT, 1, (int)pc, inst.opcode, -1, req);
                 ab = 1;
               }
@@ -882,8 +886,12 @@ __device__ void task_attn_decode(Compute& q, int max_pages, int base_page, int f
       b1 = bf16_round(__bfloat162float(w[i0 + 65]) * bf16_round(b1 * rstd));
     }
     const float c0 = rope[i0], c1 = rope[i0 + 1], s0 = rope[64 + i0], s1 = rope[64 + i0 + 1];
-    const float r0 = bf16_round(a0 * c0 - b0 * s0), r1 = bf16_round(a1 * c1 - b1 * s1);
-    const float r64 = bf16_round(b0 * c0 + a0 * s0), r65 = bf16_round(b1 * c1 + a1 * s1);
+    // x*cos + rotate_half(x)*sin with every product and the sum rounded to bf16,
+    // the way a bf16 tensor expression evaluates it
+    const float r0 = bf16_round(bf16_round(a0 * c0) - bf16_round(b0 * s0));
+    const float r1 = bf16_round(bf16_round(a1 * c1) - bf16_round(b1 * s1));
+    const float r64 = bf16_round(bf16_round(b0 * c0) + bf16_round(a0 * s0));
+    const float r65 = bf16_round(bf16_round(b1 * c1) + bf16_round(a1 * s1));
     if (is_k) {
       krow[i0] = __float2bfloat16_rn(r0);
       krow[i0 + 1] = __float2bfloat16_rn(r1);
