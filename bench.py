@@ -1,0 +1,254 @@
+#!/usr/bin/env python
+"""Decode benchmark: tokens/s at batch 1 on the Llama-3.1-8B shape.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+One step = one greedy decode step (one megakernel launch) after a 2048-token
+prompt has been prefilled into the paged KV cache.  Weights are random
+N(0, 0.02) bf16 of the named shape, the prompt is uniform random ids (synthetic
+stand-ins for a checkpoint and a dataset; there is no network).  Prints ONE
+JSON line.  `value` is timed with the state resident on the device; `e2e` goes
+through the host-buffer step API (token id up, next id down, every step).
+`--impl reference` times the CPU oracle of the same math on the host cores.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+PROMPT_LEN = 2048
+METRIC = "decode tokens/s at batch 1 (Llama-3.1-8B shape)"
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index=0):
+        self.index = index
+        self.proc = None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                 "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            time.sleep(0.3)
+        except Exception:
+            self.proc = None
+        return self
+
+    def __exit__(self, *a):
+        self.lines = []
+        if self.proc is not None:
+            time.sleep(0.1)
+            self.proc.terminate()
+            try:
+                out, _ = self.proc.communicate(timeout=5)
+                self.lines = [l for l in out.splitlines() if l.strip()]
+            except Exception:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], 0, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for l in getattr(self, "lines", []):
+            f = [x.strip() for x in l.split(",")]
+            try:
+                sm.append(float(f[0]))
+                mx = max(mx, float(f[1]))
+            except Exception:
+                continue
+            for n, v in zip(names, f[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        busy = [x for x in sm if x > 0.5 * mx] or sm
+        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": mx or None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_oracle_tokens_per_s(n_layers_sample=2, steps=2, threads=None):
+    """Times the CPU oracle on a bounded sample of the workload: `n_layers_sample`
+    Llama-3.1-8B-shaped layers plus the final norm and vocabulary projection,
+    `steps` decode steps at context PROMPT_LEN, extrapolated linearly to 32 layers."""
+    import torch
+    from oracle import decode_oracle as O
+    threads = threads or os.cpu_count()
+    torch.set_num_threads(threads)
+    cfg = O.DecodeConfig(n_layers=n_layers_sample)
+    gen = torch.Generator().manual_seed(0)
+    layers = [O.LayerWeights.random(cfg, gen) for _ in range(n_layers_sample)]
+    lm_head = O.randn_bf16(gen, cfg.vocab, cfg.hidden)
+    norm = torch.ones(cfg.hidden, dtype=torch.bfloat16)
+    T = PROMPT_LEN + steps + 1
+    kc = [O.randn_bf16(gen, T, cfg.n_kv_heads, cfg.head_dim, std=1.0) for _ in layers]
+    vc = [O.randn_bf16(gen, T, cfg.n_kv_heads, cfg.head_dim, std=1.0) for _ in layers]
+    h0 = O.randn_bf16(gen, cfg.hidden, std=1.0)
+    O.FAST_LINEAR = True        # bf16 kernels of the host BLAS, fp32 accumulation inside them
+
+    def one(pos):
+        h = h0
+        t0 = time.perf_counter()
+        for i, lw in enumerate(layers):
+            h = O.decode_layer(cfg, lw, h, pos, kc[i], vc[i])
+        t1 = time.perf_counter()
+        logits = O.linear(O.rms_norm(h, norm, cfg.eps)[None], lm_head)[0]
+        int(torch.argmax(logits.float()))
+        t2 = time.perf_counter()
+        return t1 - t0, t2 - t1
+    one(PROMPT_LEN)                                   # warm-up
+    tl, th = [], []
+    for s in range(steps):
+        a, b = one(PROMPT_LEN + 1 + s)
+        tl.append(a)
+        th.append(b)
+    per_token = statistics.mean(tl) / n_layers_sample * 32 + statistics.mean(th)
+    return 1.0 / per_token, threads, (f"{n_layers_sample} of 32 layers + final norm/lm_head/argmax, {steps} steps at "
+                                      f"context {PROMPT_LEN}, layer time scaled x{32 // n_layers_sample}")
+
+
+def run_reference(args):
+    """The reference arm: its PyTorch decode math on the host CPU (rank 0 only)."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    steps = max(1, min(args.steps, 3))
+    tps, cores, sample = cpu_oracle_tokens_per_s(n_layers_sample=2, steps=steps)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": tps, "unit": "tokens/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 / tps, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "Llama-3.1-8B shape, bf16, batch 1, 2048-token prompt, greedy decode",
+                   "timing": "CPU oracle of the reference's PyTorch decode math on a bounded sample"},
+        "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+def run_gpu(args):
+    import torch
+    import torch.distributed as dist
+    from vdcores_b200 import runtime
+    from vdcores_b200.decode import LLAMA31_8B, DecodeEngine
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    K, W = args.steps, max(args.warmup, 3)
+    cfg = LLAMA31_8B
+    max_seq = ((PROMPT_LEN + W + K + 8 + 63) // 64) * 64
+    eng = DecodeEngine(cfg, max_seq=max_seq, device=dev, max_steps=W + K + 8)
+    eng.init_random_weights(seed=rank)
+    g = torch.Generator().manual_seed(0)
+    prompt = torch.randint(0, cfg.vocab, (PROMPT_LEN,), generator=g)
+    first = eng.prefill(prompt)
+    stream = torch.cuda.current_stream()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident arm: K launches back to back, CUDA events on the launching stream
+    eng.set_state(PROMPT_LEN, first)
+    for _ in range(W):
+        eng.step_async()
+    runtime.read_status(stream.cuda_stream)
+    pos0 = eng.pos
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    with ClockSampler(local) as clk:
+        e0.record(stream)
+        for _ in range(K):
+            eng.step_async()
+        e1.record(stream)
+        torch.cuda.synchronize()
+    barrier()
+    runtime.read_status(stream.cuda_stream)
+    ms = e0.elapsed_time(e1)
+    tokens = eng.token_log[W:W + K].tolist()
+    # ---- end-to-end arm: host token in, host token out, every step
+    eng.set_state(PROMPT_LEN, first)
+    tok = first
+    for _ in range(W):
+        tok = eng.step_host(tok)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(K):
+        tok = eng.step_host(tok)
+    torch.cuda.synchronize()
+    t1 = time.perf_counter()
+    barrier()
+    e2e_ms = (t1 - t0) * 1000.0
+    if world > 1:
+        t = torch.tensor([ms, e2e_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_ms = t.tolist()
+    if rank != 0:
+        return
+    peak, peak_kind = measured_peaks()
+    mid_pos = pos0 + K // 2
+    bytes_per_launch = eng.algorithmic_bytes(mid_pos)
+    achieved = bytes_per_launch / (ms / K * 1e-3) / 1e9
+    line = {
+        "metric": METRIC, "value": K / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
+        "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "Llama-3.1-8B shape (32 layers, hidden 4096, 32q/8kv heads, FFN 14336, vocab 128256), "
+                               "bf16, batch 1, 2048-token prompt prefilled, greedy decode",
+                   "l2": "inputs larger than L2: every step streams ~15 GB of weights through a 126 MB L2",
+                   "parallelism": "single GPU" if world == 1 else f"replicas x{world}",
+                   "num_sms": eng.num_sms, "kv_splits": eng.n_splits, "first_tokens": tokens[:4]},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": None, "peak_kind": f"of {peak_kind}", "frac_of_8TBs": achieved / 8000.0,
+                     "bytes_per_launch": bytes_per_launch},
+        "e2e": {"value": K / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4},
+        "gpu_launches": K * eng.launches_per_step,
+        "clocks": clk.summary(),
+    }
+    if not args.no_cpu_baseline:
+        tps, cores, sample = cpu_oracle_tokens_per_s(n_layers_sample=2, steps=2)
+        line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample}
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="vdcores_b200", choices=["vdcores_b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()
