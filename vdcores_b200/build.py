@@ -14,7 +14,7 @@ def needs_build() -> bool:
     if not os.path.exists(LIB):
         return True
     t = os.path.getmtime(LIB)
-    deps = SOURCES + [os.path.join(HERE, "csrc", "isa.h"), os.path.join(HERE, "..", "include", "vdcores.h")]
+    deps = SOURCES + [os.path.join(HERE, "csrc", f) for f in ("isa.h", "mk_common.cuh", "mk_memory.cuh", "mk_compute.cuh")] + [os.path.join(HERE, "csrc", "isa.h"), os.path.join(HERE, "..", "include", "vdcores.h")]
     return any(os.path.getmtime(d) > t for d in deps)
 
 

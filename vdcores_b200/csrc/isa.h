@@ -21,7 +21,7 @@
 
 #define VDC_COMPUTE_WARPS 8
 #define VDC_COMPUTE_THREADS (VDC_COMPUTE_WARPS * 32)
-#define VDC_MEMORY_WARPS 4
+#define VDC_MEMORY_WARPS 5
 #define VDC_THREADS ((VDC_COMPUTE_WARPS + VDC_MEMORY_WARPS) * 32)
 #define VDC_MAX_SMS 160
 
@@ -61,7 +61,10 @@
   X(OP_ALLOC_WB_TMA_REDUCE_ADD_3D, VDC_MOP(22, VDC_F_ALLOCATE | VDC_F_WRITEBACK))      \
   X(OP_ALLOC_WB_RAW_ADDRESS, VDC_MOP(23, VDC_F_ALLOCATE))                              \
   X(OP_ALLOC_WB_TMA_REDUCE_ADD_1D, VDC_MOP(24, VDC_F_ALLOCATE | VDC_F_WRITEBACK))      \
-  X(OP_DYN_COUNT, VDC_MOP(25, 0))
+  X(OP_DYN_COUNT, VDC_MOP(25, 0))                                                      \
+  X(OP_PREFETCH_L2, VDC_MOP(26, 0))                                                    \
+  X(OP_STREAM_LIST, VDC_MOP(27, 0))                                                    \
+  X(OP_ALLOC_TMA_LOAD_1D_STREAM, VDC_MOP(28, VDC_F_ALLOCATE))
 
 // Compute opcodes.  The first block keeps reference names (control ops and the
 // ops whose tile contracts this runtime still honours); the second block is
@@ -84,7 +87,8 @@
 // GEMV_ROWS args[1] layout: bits 0..4 rows per chunk (1,2,4,8,16), bits 8..10
 // epilogue mode, bit 11 accumulate into the output (residual add), bit 12 fused
 // RMSNorm of the activation vector.  args[2]: K/256 in the low byte.  Second
-// word: fp32 bits of the norm eps (hi, lo), first output row / 8 (argmax mode).
+// word: fp32 bits of the norm eps (hi, lo), index of the first chunk within the
+// whole matrix (argmax mode: candidate row = (first chunk + i) * R + r).
 #define VDC_GEMV_MODE_STORE 0
 #define VDC_GEMV_MODE_SILU_PAIRS 1
 #define VDC_GEMV_MODE_ARGMAX 2

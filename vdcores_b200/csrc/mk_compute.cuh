@@ -1,0 +1,656 @@
+// Compute virtual core of the megakernel: queue access and the decode tasks.
+#pragma once
+#include "mk_common.cuh"
+
+namespace vdc {
+
+// ------------------------------------------------------------------------- //
+// compute virtual core: queue access
+// ------------------------------------------------------------------------- //
+struct Compute {
+  const Ctx& c;
+  Shared* sh;
+  int tid, warp, lane;
+  unsigned head;     // ring entries consumed so far (uniform across the 256 threads)
+  unsigned st_tail;  // store-queue pushes so far (thread 0)
+  uint32_t pc;
+  bool aborted;
+  uint64_t stall;    // cycles thread 0 spent waiting for data
+
+  // CTA-wide pop: thread 0 waits for the entry (bounded), everybody gets its
+  // word after one compute_sync.  Returns kPopAbort once a wait was given up.
+  __device__ __forceinline__ int pop() {
+    if (tid == 0) {
+      const unsigned e = head % kQ;
+      const uint32_t parity = (head / kQ) & 1u;
+      uint64_t* bar = &sh->full[e];
+      bool ok = mbar_try_wait(bar, parity);
+      if (!ok) {
+        const long long t0 = clock64();
+        ok = wait_until(c, [&] { return mbar_try_wait(bar, parity); }, 0, (int)pc, 0, -1, 0);
+        stall += (uint64_t)(clock64() - t0);
+      }
+      sh->pop_val[head & 1u] = ok ? sh->ring_word[e] : kPopAbort;
+      sh->pop_addr[head & 1u] = sh->ring[e].address;
+      sh->pop_meta[head & 1u] = (uint32_t)sh->ring[e].opcode | ((uint32_t)sh->ring[e].num_slots << 16);
+      if (!ok) sh->aborted = 1;
+      __threadfence_block();
+      sh->cta_head = head + 1;
+    }
+    compute_sync();
+    const int v = sh->pop_val[head & 1u];
+    head++;
+    if (v == kPopAbort) aborted = true;
+    return v;
+  }
+  // Address / (opcode | num_slots << 16) of the instruction behind the last pop.
+  __device__ __forceinline__ uint64_t addr() const { return sh->pop_addr[(head - 1u) & 1u]; }
+  __device__ __forceinline__ uint32_t meta() const { return sh->pop_meta[(head - 1u) & 1u]; }
+
+  // Per-warp phase: the next `n` ring entries are consumed by the warps
+  // independently, entry head+i by warp i % 8.  begin/end are CTA-wide.
+  __device__ __forceinline__ void warp_phase_begin(unsigned n) {
+    if (lane == 0) sh->warp_next[warp] = (unsigned)warp < n ? head + warp : 0xFFFFFFFFu;
+    compute_sync();
+    if (tid == 0) sh->cta_head = head + n;
+  }
+  // Waits for entry head+i (whole warp); returns its word or kPopAbort.
+  __device__ __forceinline__ int warp_wait(unsigned i) {
+    const unsigned idx = head + i;
+    uint64_t* bar = &sh->full[idx % kQ];
+    const uint32_t parity = (idx / kQ) & 1u;
+    int ok = 1;
+    if (lane == 0 && !mbar_try_wait(bar, parity)) {
+      ok = wait_until(c, [&] { return mbar_try_wait(bar, parity); }, 0, (int)pc, 0, -1, 0);
+      if (!ok) sh->aborted = 1;
+    }
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    // lanes other than 0 did not observe the barrier themselves: order their
+    // reads after lane 0's acquire
+    __syncwarp();
+    return ok ? sh->ring_word[idx % kQ] : kPopAbort;
+  }
+  // Entry head+i is finished: free its slots and publish this warp's next entry.
+  __device__ __forceinline__ void warp_done(unsigned i, unsigned n, int mask) {
+    __syncwarp();
+    if (lane == 0) {
+      if (mask > 0) atomicOr(&sh->slot_avail, (uint32_t)mask & kSlotMaskAll);
+      sh->warp_next[warp] = i + kCW < n ? head + i + kCW : 0xFFFFFFFFu;
+    }
+  }
+  __device__ __forceinline__ void warp_phase_end(unsigned n) {
+    compute_sync();
+    head += n;
+    if (sh->aborted) aborted = true;
+  }
+
+  // Counts down the global barrier named by a popped raw-address instruction
+  // that carries BARRIER|WRITEBACK.  Caller guarantees every writer executed
+  // __threadfence() and a compute_sync() since its last global write.
+  __device__ __forceinline__ void release(uint32_t m) {
+    if (tid == 0 && (m & VDC_F_BARRIER) && (m & VDC_F_WRITEBACK)) {
+      __threadfence();
+      red_release_gpu_add(c.bars + (m >> 22), -1);
+    }
+  }
+  // Caller guarantees (with a compute_sync) that no thread still reads the slots.
+  __device__ __forceinline__ void free_slots(int mask) {
+    if (tid == 0 && mask > 0) atomicOr(&sh->slot_avail, (uint32_t)mask & kSlotMaskAll);
+  }
+  // Hands slots to the store warp.  Caller guarantees all writers executed
+  // fence_proxy_async_smem() and a compute_sync() since their last write.
+  __device__ __forceinline__ void push_store(int mask) {
+    if (mask < 0) return;  // RegStore'd result stays resident
+    if (tid == 0) {
+      bool ok = wait_until(c, [&] { return st_tail - sh->st_head < (unsigned)kQ; }, 0, (int)pc, 0, -1, 0);
+      if (ok) {
+        sh->st_q[st_tail % kQ] = mask;
+        __threadfence_block();
+        sh->st_tail = st_tail + 1;
+        st_tail++;
+      }
+    }
+  }
+};
+
+__device__ __forceinline__ int first_slot(int mask) { return __ffs(mask & 0x7fffffff) - 1; }
+
+// ------------------------------------------------------------------------- //
+// task: row-block GEMV  y[r] = sum_k W[r,k] x[k]   (batch-1 decode projections)
+// ------------------------------------------------------------------------- //
+// Pop order: [norm weight], x, out (raw address), [argmax record (raw address)],
+// then n_chunks weight chunks of R rows x K bf16 (row-major, contiguous).
+// Operands are popped CTA-wide; the chunks are consumed by the eight warps
+// independently (chunk i by warp i % 8), each warp doing the whole dot products
+// of its chunk, so the streaming loop has no CTA-wide synchronisation.
+struct ArgBest {
+  float val;
+  int idx;
+};
+
+__device__ __forceinline__ float2 bf2(uint32_t u) { return make_float2(bf_lo(u), bf_hi(u)); }
+
+// One warp's dot products for a chunk of R rows, with packed fp32 FMAs.  Each
+// row keeps NA independent partial sums so the FMA chains stay short when R is
+// small (a single 28 KB row would otherwise be one long dependent chain).
+template <int R>
+__device__ __forceinline__ void gemv_chunk(const uint8_t* w, const uint8_t* x, int K, int lane, float (&out)[R]) {
+  constexpr int NA = R >= 8 ? 1 : (R == 4 ? 2 : 4);
+  constexpr int UNROLL = R >= 8 ? 1 : (R == 4 ? 2 : 4);
+  float2 acc[R][NA];
+#pragma unroll
+  for (int r = 0; r < R; ++r)
+#pragma unroll
+    for (int a = 0; a < NA; ++a) acc[r][a] = make_float2(0.f, 0.f);
+  const int iters = K >> 8;
+#pragma unroll UNROLL
+  for (int it = 0; it < iters; ++it) {
+    const int off = (it << 9) + (lane << 4);  // byte offset of this lane's 8 elements
+    const uint4 xv = lds128(x + off);
+    const float2 xf[4] = {bf2(xv.x), bf2(xv.y), bf2(xv.z), bf2(xv.w)};
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const uint4 wv = lds128(w + (size_t)r * K * 2 + off);
+      acc[r][0 % NA] = __ffma2_rn(bf2(wv.x), xf[0], acc[r][0 % NA]);
+      acc[r][1 % NA] = __ffma2_rn(bf2(wv.y), xf[1], acc[r][1 % NA]);
+      acc[r][2 % NA] = __ffma2_rn(bf2(wv.z), xf[2], acc[r][2 % NA]);
+      acc[r][3 % NA] = __ffma2_rn(bf2(wv.w), xf[3], acc[r][3 % NA]);
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    float v = acc[r][0].x + acc[r][0].y;
+#pragma unroll
+    for (int a = 1; a < NA; ++a) v += acc[r][a].x + acc[r][a].y;
+    out[r] = warp_sum(v);
+  }
+}
+
+template <int R>
+__device__ void task_gemv_rows(Compute& q, int n_chunks, int mode, bool accumulate, bool norm, int K, int row_base) {
+  Shared* sh = q.sh;
+  const Ctx& c = q.c;
+  int normw_mask = 0;
+  if (norm) normw_mask = q.pop();
+  const int x_mask = q.pop();
+  q.pop();  // output vector: raw address
+  __nv_bfloat16* outg = reinterpret_cast<__nv_bfloat16*>(q.addr());
+  const uint32_t out_meta = q.meta();
+  float* recg = nullptr;
+  uint32_t rec_meta = 0;
+  if (mode == VDC_GEMV_MODE_ARGMAX) {
+    q.pop();  // candidate record: raw address
+    recg = reinterpret_cast<float*>(q.addr());
+    rec_meta = q.meta();
+  }
+  if (q.aborted) return;
+  uint8_t* x = (uint8_t*)slot_ptr(c, first_slot(x_mask));
+
+  if (norm) {
+    // RMSNorm of the activation vector in place: bf16(w * bf16(x * rstd)), fp32 statistics
+    const uint8_t* nw = (const uint8_t*)slot_ptr(c, first_slot(normw_mask));
+    float ss = 0.f;
+    for (int i = q.tid * 8; i < K; i += kCT * 8) {
+      const uint4 v = lds128(x + i * 2);
+      const float f[8] = {bf_lo(v.x), bf_hi(v.x), bf_lo(v.y), bf_hi(v.y), bf_lo(v.z), bf_hi(v.z), bf_lo(v.w), bf_hi(v.w)};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss = fmaf(f[j], f[j], ss);
+    }
+    ss = warp_sum(ss);
+    if (q.lane == 0) sh->misc[q.warp] = ss;
+    compute_sync();
+    float tot = 0.f;
+#pragma unroll
+    for (int w = 0; w < kCW; ++w) tot += sh->misc[w];
+    const float rstd = rsqrtf(tot / (float)K + sh->misc[32]);  // misc[32]: eps, set by the dispatcher
+    for (int i = q.tid * 2; i < K; i += kCT * 2) {
+      const uint32_t xv = *reinterpret_cast<const uint32_t*>(x + i * 2);
+      const uint32_t wv = *reinterpret_cast<const uint32_t*>(nw + i * 2);
+      const float a = bf16_round(bf_lo(wv) * bf16_round(bf_lo(xv) * rstd));
+      const float b = bf16_round(bf_hi(wv) * bf16_round(bf_hi(xv) * rstd));
+      *reinterpret_cast<uint32_t*>(x + i * 2) = (__float_as_uint(a) >> 16) | (__float_as_uint(b) & 0xffff0000u);
+    }
+    // the sync inside warp_phase_begin publishes the normalised vector
+  }
+
+  ArgBest best = {-INFINITY, 0x7fffffff};
+  q.warp_phase_begin((unsigned)n_chunks);  // its sync also publishes the normalised vector
+  if (norm) q.free_slots(normw_mask);
+  for (int i = q.warp; i < n_chunks; i += kCW) {
+    const int w_mask = q.warp_wait((unsigned)i);
+    if (w_mask == kPopAbort) break;
+    const uint8_t* w = (const uint8_t*)slot_ptr(c, first_slot(w_mask));
+    float acc[R];
+    gemv_chunk<R>(w, x, K, q.lane, acc);
+    q.warp_done((unsigned)i, (unsigned)n_chunks, w_mask);
+    const int row0 = i * R;
+    if (mode == VDC_GEMV_MODE_SILU_PAIRS) {
+      float g = 0.f, u = 0.f;
+#pragma unroll
+      for (int j = 0; j < R / 2; ++j)
+        if (q.lane == j) {
+          g = acc[2 * j];
+          u = acc[2 * j + 1];
+        }
+      if (q.lane < R / 2) {
+        g = bf16_round(g);
+        u = bf16_round(u);
+        const float sg = bf16_round(g / (1.f + __expf(-g)));
+        outg[row0 / 2 + q.lane] = __float2bfloat16_rn(sg * u);
+      }
+    } else {
+      float v = 0.f;
+#pragma unroll
+      for (int r = 0; r < R; ++r)
+        if (q.lane == r) v = acc[r];
+      if (q.lane < R) {
+        const __nv_bfloat16 bq = __float2bfloat16_rn(v);
+        if (accumulate) atomicAdd(outg + row0 + q.lane, bq);  // residual add: bf16(old + bf16(W x))
+        else outg[row0 + q.lane] = bq;
+        if (mode == VDC_GEMV_MODE_ARGMAX) {
+          const float bv = __bfloat162float(bq);
+          if (bv > best.val || (bv == best.val && row0 + q.lane < best.idx)) {
+            best.val = bv;
+            best.idx = row0 + q.lane;
+          }
+        }
+      }
+    }
+  }
+  if (mode == VDC_GEMV_MODE_ARGMAX) {
+    // candidates sit in lanes 0..R-1 of every warp; the lowest row index wins ties
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best.val, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, best.idx, o);
+      if (ov > best.val || (ov == best.val && oi < best.idx)) {
+        best.val = ov;
+        best.idx = oi;
+      }
+    }
+    if (q.lane == 0) {
+      sh->misc[40 + q.warp] = best.val;
+      reinterpret_cast<int*>(sh->misc)[48 + q.warp] = best.idx;
+    }
+  }
+  __threadfence();  // output rows were written by lanes of every warp
+  q.warp_phase_end((unsigned)n_chunks);
+  if (q.aborted) return;
+  if (mode == VDC_GEMV_MODE_ARGMAX && q.tid == 0) {
+    float bv = sh->misc[40];
+    int bi = reinterpret_cast<int*>(sh->misc)[48];
+    for (int w = 1; w < kCW; ++w) {
+      const float ov = sh->misc[40 + w];
+      const int oi = reinterpret_cast<int*>(sh->misc)[48 + w];
+      if (ov > bv || (ov == bv && oi < bi)) {
+        bv = ov;
+        bi = oi;
+      }
+    }
+    recg[0] = bv;
+    reinterpret_cast<int*>(recg)[1] = bi + row_base;
+    recg[2] = 0.f;
+    recg[3] = 0.f;
+  }
+  q.release(out_meta);
+  q.release(rec_meta);
+  q.free_slots(x_mask);
+}
+
+// ------------------------------------------------------------------------- //
+// task: split-K GQA decode attention over 64-position KV pages
+// ------------------------------------------------------------------------- //
+// Pop order: state (raw address), rope row (cos[64] sin[64] fp32), [q/k norm
+// weights 2x128 bf16], q (G x 128 bf16, raw projection output), k_new, v_new
+// (128 bf16 each, raw projection output of the token being decoded), k_row_out,
+// v_row_out (write-back slots for the new cache rows), `count` x (K page, V page),
+// out (write-back: G x 128 fp32 unnormalised O, then m[G], l[G]).
+// count = clamp(n_pages - base, 0, max_pages) is read from the state block; the
+// memory stream uses the same rule (DYN_COUNT + REPEAT).
+template <int G>
+__device__ void task_attn_decode(Compute& q, int max_pages, int base_page, int flags) {
+  constexpr int D = VDC_HEAD_DIM;
+  constexpr int LPP = (G == 4) ? 8 : 16;  // lanes per position in the QK phase
+  constexpr int DPL = D / LPP;            // dims per lane: 16 or 8
+  constexpr int PPW = 32 / LPP;           // positions per warp per round
+  constexpr int ROUNDS = VDC_KV_PAGE / (PPW * kCW);
+  Shared* sh = q.sh;
+  const Ctx& c = q.c;
+  const bool qk_norm = flags & VDC_ATTN_QKNORM_BIT;
+
+  q.pop();  // decode state block: raw address
+  const int* state = reinterpret_cast<const int*>(q.addr());
+  const int rope_mask = q.pop();
+  int nw_mask = 0;
+  if (qk_norm) nw_mask = q.pop();
+  const int q_mask = q.pop();
+  const int kn_mask = q.pop();
+  const int vn_mask = q.pop();
+  const int kro_mask = q.pop();
+  const int vro_mask = q.pop();
+  if (q.aborted) return;
+
+  const int pos = ld_relaxed_gpu(state + VDC_ST_POS);
+  const int n_pages = ld_relaxed_gpu(state + VDC_ST_NPAGES);
+  int count = n_pages - base_page;
+  count = count < 0 ? 0 : (count > max_pages ? max_pages : count);
+  const bool owner = count > 0 && base_page + count == n_pages;
+  const int tail_valid = (pos % VDC_KV_PAGE) + 1;  // valid rows of the last page, new row included
+
+  const float* rope = (const float*)slot_ptr(c, first_slot(rope_mask));
+  const __nv_bfloat16* nw = qk_norm ? (const __nv_bfloat16*)slot_ptr(c, first_slot(nw_mask)) : nullptr;
+  const __nv_bfloat16* qraw = (const __nv_bfloat16*)slot_ptr(c, first_slot(q_mask));
+  const __nv_bfloat16* knew = (const __nv_bfloat16*)slot_ptr(c, first_slot(kn_mask));
+  __nv_bfloat16* krow = (__nv_bfloat16*)slot_ptr(c, first_slot(kro_mask));
+  __nv_bfloat16* vrow = (__nv_bfloat16*)slot_ptr(c, first_slot(vro_mask));
+  const float eps = sh->misc[33];
+
+  // --- prologue: optional per-head RMSNorm, then half-rotation RoPE.  One warp
+  // per head: heads 0..G-1 are the queries, "head" G is the new key row.
+  for (int head = q.warp; head <= G; head += kCW) {
+    const bool is_k = head == G;
+    const __nv_bfloat16* src = is_k ? knew : qraw + head * D;
+    const int i0 = q.lane * 2;  // pairs (i0, i0+64), (i0+1, i0+65)
+    float a0 = __bfloat162float(src[i0]), a1 = __bfloat162float(src[i0 + 1]);
+    float b0 = __bfloat162float(src[i0 + 64]), b1 = __bfloat162float(src[i0 + 65]);
+    if (qk_norm) {
+      float ss = warp_sum(a0 * a0 + a1 * a1 + b0 * b0 + b1 * b1);
+      const float rstd = rsqrtf(ss / (float)D + eps);
+      const __nv_bfloat16* w = nw + (is_k ? D : 0);
+      a0 = bf16_round(__bfloat162float(w[i0]) * bf16_round(a0 * rstd));
+      a1 = bf16_round(__bfloat162float(w[i0 + 1]) * bf16_round(a1 * rstd));
+      b0 = bf16_round(__bfloat162float(w[i0 + 64]) * bf16_round(b0 * rstd));
+      b1 = bf16_round(__bfloat162float(w[i0 + 65]) * bf16_round(b1 * rstd));
+    }
+    const float c0 = rope[i0], c1 = rope[i0 + 1], s0 = rope[64 + i0], s1 = rope[64 + i0 + 1];
+    // x*cos + rotate_half(x)*sin with every product and the sum rounded to bf16,
+    // the way a bf16 tensor expression evaluates it
+    const float r0 = bf16_round(bf16_round(a0 * c0) - bf16_round(b0 * s0));
+    const float r1 = bf16_round(bf16_round(a1 * c1) - bf16_round(b1 * s1));
+    const float r64 = bf16_round(bf16_round(b0 * c0) + bf16_round(a0 * s0));
+    const float r65 = bf16_round(bf16_round(b1 * c1) + bf16_round(a1 * s1));
+    if (is_k) {
+      krow[i0] = __float2bfloat16_rn(r0);
+      krow[i0 + 1] = __float2bfloat16_rn(r1);
+      krow[i0 + 64] = __float2bfloat16_rn(r64);
+      krow[i0 + 65] = __float2bfloat16_rn(r65);
+    } else {
+      float* dst = sh->qrot + head * D;
+      dst[i0] = r0;
+      dst[i0 + 1] = r1;
+      dst[i0 + 64] = r64;
+      dst[i0 + 65] = r65;
+    }
+  }
+  if (q.tid < D / 8) {  // v_new row copied as is (16 threads x 16 bytes)
+    reinterpret_cast<uint4*>(vrow)[q.tid] = reinterpret_cast<const uint4*>(slot_ptr(c, first_slot(vn_mask)))[q.tid];
+  }
+  fence_proxy_async_smem();
+  compute_sync();
+  q.free_slots(rope_mask | nw_mask | q_mask | kn_mask | vn_mask);
+
+  // per-lane slice of the rotated queries
+  const int sub = q.lane % LPP, pl = q.lane / LPP;
+  float qreg[G][DPL];
+#pragma unroll
+  for (int g = 0; g < G; ++g)
+#pragma unroll
+    for (int h = 0; h < DPL / 8; ++h)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) qreg[g][h * 8 + j] = sh->qrot[g * D + (sub + h * 8) * 8 + j];
+  const float scale_log2 = 1.4426950408889634f * rsqrtf((float)D);
+
+  float m_run[G], l_run[G], acc[G][2];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    m_run[g] = -INFINITY;
+    l_run[g] = 0.f;
+    acc[g][0] = acc[g][1] = 0.f;
+  }
+  const int pg = q.tid >> 6, dp = q.tid & 63;  // PV phase: position group, dim pair
+
+  int v_prev = 0;
+  for (int blk = 0; blk < count; ++blk) {
+    const int k_mask = q.pop();  // its sync also ends the previous block's PV phase
+    if (q.aborted) return;
+    q.free_slots(v_prev);
+    uint8_t* kb = (uint8_t*)slot_ptr(c, first_slot(k_mask));
+    const bool last = owner && blk == count - 1;
+    const int valid = last ? tail_valid : VDC_KV_PAGE;
+    if (last) {
+      // the page in HBM does not hold the new row yet: patch it in shared memory
+      if (q.tid < D / 8)
+        reinterpret_cast<uint4*>(kb + (valid - 1) * D * 2)[q.tid] = reinterpret_cast<const uint4*>(krow)[q.tid];
+      compute_sync();
+    }
+    // ---- phase 1: scores = q . k for 64 positions
+    float wm[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) wm[g] = -INFINITY;
+#pragma unroll
+    for (int rd = 0; rd < ROUNDS; ++rd) {
+      const int p = rd * (PPW * kCW) + q.warp * PPW + pl;
+      float s[G];
+#pragma unroll
+      for (int g = 0; g < G; ++g) s[g] = 0.f;
+#pragma unroll
+      for (int h = 0; h < DPL / 8; ++h) {
+        const uint4 kv = lds128(kb + p * (D * 2) + (sub + h * 8) * 16);
+        const float kf[8] = {bf_lo(kv.x), bf_hi(kv.x), bf_lo(kv.y), bf_hi(kv.y),
+                             bf_lo(kv.z), bf_hi(kv.z), bf_lo(kv.w), bf_hi(kv.w)};
+#pragma unroll
+        for (int g = 0; g < G; ++g)
+#pragma unroll
+          for (int j = 0; j < 8; ++j) s[g] = fmaf(qreg[g][h * 8 + j], kf[j], s[g]);
+      }
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+#pragma unroll
+        for (int o = 1; o < LPP; o <<= 1) s[g] += __shfl_xor_sync(0xffffffffu, s[g], o);
+        s[g] = (p < valid) ? s[g] * scale_log2 : -INFINITY;
+        wm[g] = fmaxf(wm[g], s[g]);
+      }
+      if (sub == 0) {
+#pragma unroll
+        for (int g = 0; g < G; ++g) sh->scores[p * G + g] = s[g];
+      }
+    }
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+#pragma unroll
+      for (int o = LPP; o < 32; o <<= 1) wm[g] = fmaxf(wm[g], __shfl_xor_sync(0xffffffffu, wm[g], o));
+      if (q.lane == 0) sh->wmax[q.warp * G + g] = wm[g];
+    }
+    compute_sync();  // (A) scores and warp maxima visible; K page fully read
+    q.free_slots(k_mask);
+    // ---- phase 2: running max, rescale factors, probabilities
+    float alpha[G], m_new[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      float mb = sh->wmax[g];
+#pragma unroll
+      for (int w = 1; w < kCW; ++w) mb = fmaxf(mb, sh->wmax[w * G + g]);
+      m_new[g] = fmaxf(m_run[g], mb);
+      alpha[g] = (m_new[g] == -INFINITY) ? 1.f : exp2f(m_run[g] - m_new[g]);
+      m_run[g] = m_new[g];
+    }
+    for (int t = q.tid; t < VDC_KV_PAGE * G; t += kCT) {
+      const int g = t % G;
+      const float s = sh->scores[t];
+      // HF rounds probabilities to bf16 after the softmax; here they stay fp32
+      sh->probs[t] = (m_new[g] == -INFINITY) ? 0.f : exp2f(s - m_new[g]);
+    }
+    const int v_mask = q.pop();  // (B) its sync publishes probs
+    if (q.aborted) return;
+    uint8_t* vb = (uint8_t*)slot_ptr(c, first_slot(v_mask));
+    if (last) {
+      if (q.tid < D / 8)
+        reinterpret_cast<uint4*>(vb + (valid - 1) * D * 2)[q.tid] = reinterpret_cast<const uint4*>(vrow)[q.tid];
+      compute_sync();
+    }
+    // ---- phase 3: O += P V over this thread's 16 positions, two dims per thread
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      acc[g][0] *= alpha[g];
+      acc[g][1] *= alpha[g];
+      l_run[g] *= alpha[g];
+    }
+    const int p_end = min(pg * 16 + 16, valid);
+    for (int p = pg * 16; p < p_end; ++p) {
+      const uint32_t vv = *reinterpret_cast<const uint32_t*>(vb + p * (D * 2) + dp * 4);
+      const float v0 = bf_lo(vv), v1 = bf_hi(vv);
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        const float pr = sh->probs[p * G + g];
+        l_run[g] += pr;
+        acc[g][0] = fmaf(pr, v0, acc[g][0]);
+        acc[g][1] = fmaf(pr, v1, acc[g][1]);
+      }
+    }
+    v_prev = v_mask;
+  }
+
+  const int out_mask = q.pop();  // sync: everyone is done with the last V page
+  if (q.aborted) return;
+  q.free_slots(v_prev);
+  float* out = (float*)slot_ptr(c, first_slot(out_mask));
+  // cross position-group reduction: groups 1..3 publish, group 0 adds
+  float* red = sh->red;  // [3][G][128] then l: [3][G]
+  if (pg > 0) {
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      red[((pg - 1) * G + g) * D + dp * 2] = acc[g][0];
+      red[((pg - 1) * G + g) * D + dp * 2 + 1] = acc[g][1];
+      if (dp == 0) red[3 * G * D + (pg - 1) * G + g] = l_run[g];
+    }
+  }
+  compute_sync();
+  if (pg == 0) {
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      float o0 = acc[g][0], o1 = acc[g][1], l = l_run[g];
+#pragma unroll
+      for (int r = 0; r < 3; ++r) {
+        o0 += red[(r * G + g) * D + dp * 2];
+        o1 += red[(r * G + g) * D + dp * 2 + 1];
+        l += red[3 * G * D + r * G + g];
+      }
+      out[g * D + dp * 2] = o0;
+      out[g * D + dp * 2 + 1] = o1;
+      if (dp == 0) {
+        out[G * D + g] = m_run[g];
+        out[G * D + G + g] = l;
+      }
+    }
+  }
+  fence_proxy_async_smem();
+  compute_sync();
+  q.push_store(out_mask);
+  if (owner) {
+    q.push_store(kro_mask);
+    q.push_store(vro_mask);
+  } else {
+    q.free_slots(kro_mask | vro_mask);
+  }
+}
+
+// ------------------------------------------------------------------------- //
+// task: merge the split partials of one KV head:  O = sum_s 2^(m_s-m) O_s / sum_s 2^(m_s-m) l_s
+// ------------------------------------------------------------------------- //
+// Pop order: records part 1 (n1 records), [records part 2], out (G*128 bf16).
+// Record = G*128 fp32 O, G fp32 m, G fp32 l, padded to a multiple of 64 bytes.
+__device__ void task_attn_merge(Compute& q, int n_splits, int G, int n1) {
+  constexpr int D = VDC_HEAD_DIM;
+  const Ctx& c = q.c;
+  const int rec_floats = G * D + 16 * ((2 * G + 15) / 16);
+  const int m1 = q.pop();
+  int m2 = 0;
+  if (n_splits > n1) m2 = q.pop();
+  const int out_mask = q.pop();
+  if (q.aborted) return;
+  const float* r1 = (const float*)slot_ptr(c, first_slot(m1));
+  const float* r2 = m2 ? (const float*)slot_ptr(c, first_slot(m2)) : nullptr;
+  __nv_bfloat16* out = (__nv_bfloat16*)slot_ptr(c, first_slot(out_mask));
+  for (int o = q.tid; o < G * D; o += kCT) {
+    const int g = o / D;
+    float m = -INFINITY;
+    for (int s = 0; s < n_splits; ++s) {
+      const float* r = s < n1 ? r1 + s * rec_floats : r2 + (s - n1) * rec_floats;
+      m = fmaxf(m, r[G * D + g]);
+    }
+    float num = 0.f, den = 0.f;
+    for (int s = 0; s < n_splits; ++s) {
+      const float* r = s < n1 ? r1 + s * rec_floats : r2 + (s - n1) * rec_floats;
+      const float ms = r[G * D + g];
+      const float w = (ms == -INFINITY) ? 0.f : exp2f(ms - m);
+      num = fmaf(w, r[o], num);
+      den = fmaf(w, r[G * D + G + g], den);
+    }
+    out[o] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+  }
+  fence_proxy_async_smem();
+  compute_sync();
+  q.push_store(out_mask);
+  q.free_slots(m1 | m2);
+}
+
+// ------------------------------------------------------------------------- //
+// task: final argmax over the per-SM candidates, token hand-over, state advance
+// ------------------------------------------------------------------------- //
+// Pop order: candidate records (n x {f32 val, i32 idx, pad, pad}), state (raw
+// address), token log (raw address, int32 per step), done (raw address slot that
+// is pushed back so the store warp can release a barrier).
+__device__ void task_argmax_final(Compute& q, int n) {
+  const Ctx& c = q.c;
+  const int rec_mask = q.pop();
+  q.pop();
+  int* state = reinterpret_cast<int*>(q.addr());
+  q.pop();
+  int* log = reinterpret_cast<int*>(q.addr());
+  const uint32_t log_meta = q.meta();
+  if (q.aborted) return;
+  if (q.warp == 0) {
+    const float* rec = (const float*)slot_ptr(c, first_slot(rec_mask));
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = q.lane; i < n; i += 32) {
+      const float v = rec[i * 4];
+      const int idx = reinterpret_cast<const int*>(rec)[i * 4 + 1];
+      if (v > bv || (v == bv && idx < bi)) {
+        bv = v;
+        bi = idx;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > bv || (ov == bv && oi < bi)) {
+        bv = ov;
+        bi = oi;
+      }
+    }
+    if (q.lane == 0) {
+      const int step = state[VDC_ST_STEP];
+      const int pos = state[VDC_ST_POS] + 1;
+      log[step] = bi;
+      state[VDC_ST_TOKEN] = bi;
+      state[VDC_ST_STEP] = step + 1;
+      state[VDC_ST_POS] = pos;
+      const int page = pos / VDC_KV_PAGE;
+      state[VDC_ST_NPAGES] = page + 1;
+      if (page < state[VDC_ST_MAXPAGES]) {
+        state[VDC_ST_NEWROW] = state[VDC_ST_PAGETABLE + page] * VDC_KV_PAGE * state[VDC_ST_NKVH] + pos % VDC_KV_PAGE;
+      } else {
+        state[VDC_ST_ERR] = 1;  // out of KV pages: the host must not launch another step
+      }
+      __threadfence();
+    }
+  }
+  compute_sync();
+  q.release(log_meta);
+  q.free_slots(rec_mask);
+}
+
+
+}  // namespace vdc

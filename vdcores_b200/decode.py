@@ -91,7 +91,7 @@ def rows_per_chunk(K: int, even: bool = False) -> int:
 class DecodeEngine:
     def __init__(self, cfg: DecodeConfig, max_seq: int, device="cuda", num_sms: Optional[int] = None,
                  taps: bool = False, page_perm_seed: Optional[int] = None, max_steps: int = 4096,
-                 timeout_ns: int = 0):
+                 timeout_ns: int = 0, l2_prefetch_bytes: int = 384 * 1024):
         assert cfg.head_dim == isa.HEAD_DIM, "the attention task is built for head_dim 128"
         assert cfg.group in (4, 8), "GQA group size must be 4 or 8"
         assert cfg.n_kv_heads & (cfg.n_kv_heads - 1) == 0, "n_kv_heads must be a power of two"
@@ -105,6 +105,7 @@ class DecodeEngine:
         self.taps_enabled = taps
         self.max_steps = max_steps
         self.timeout_ns = timeout_ns
+        self.l2_prefetch_bytes = l2_prefetch_bytes     # per SM; 0 disables the L2 prefetch
         self.stream = torch.cuda.current_stream(self.dev)
         runtime.init()
 
@@ -207,29 +208,36 @@ class DecodeEngine:
         return self.weight_bytes() + 2 * cfg.kv_width * 2 * (pos + 1) * cfg.n_layers
 
     # ------------------------------------------------------------------ program
-    def _ranges(self, P: Program, n_units: int, unit_bytes: int, granule: int = 1):
-        """Splits n_units into one contiguous range per SM (multiples of granule);
-        the SMs that have loaded the fewest bytes so far take the larger share."""
+    def _ranges(self, load, n_units: int, unit_bytes: int):
+        """Splits n_units into one contiguous range per SM; the SMs that carry
+        the fewest bytes so far take the larger share."""
         S = self.num_sms
-        assert n_units % granule == 0
-        n_g = n_units // granule
-        base, rem = divmod(n_g, S)
-        order = sorted(range(S), key=lambda s: (P.bytes_loaded[s], s))
+        base, rem = divmod(n_units, S)
+        order = sorted(range(S), key=lambda s: (load[s], s))
         extra = set(order[:rem])
         out, u = [], 0
         for sm in range(S):
-            cnt = (base + (1 if sm in extra else 0)) * granule
+            cnt = base + (1 if sm in extra else 0)
             if cnt:
                 out.append((sm, u, cnt))
+                load[sm] += cnt * unit_bytes
             u += cnt
         assert u == n_units
         return out
 
-    def _pick(self, P: Program, n: int):
-        order = sorted(range(self.num_sms), key=lambda s: (P.bytes_loaded[s], s))
-        return [order[i % self.num_sms] for i in range(n)]
+    def _pick(self, load, n: int, cost: int = 0):
+        order = sorted(range(self.num_sms), key=lambda s: (load[s], s))
+        sms = [order[i % self.num_sms] for i in range(n)]
+        for sm in sms:
+            load[sm] += cost
+        return sms
 
     def _build_program(self):
+        """Plans every task of one decode step per SM (stage by stage, balancing
+        the bytes each SM streams), then emits the instruction streams.  After
+        the weight loads of a task have been issued, the memory core prefetches
+        the next `l2_prefetch_bytes` of that SM's weight stream into L2, so HBM
+        keeps streaming while the compute core waits on a cross-SM dependency."""
         cfg = self.cfg
         L, H, F, V, G = cfg.n_layers, cfg.hidden, cfg.ffn, cfg.vocab, cfg.group
         D = isa.HEAD_DIM
@@ -242,100 +250,133 @@ class DecodeEngine:
         assert 1 << page_shift == page_stride
         hid, qkv, ao, act = (t.data_ptr() for t in (self.hidden, self.qkv, self.attn_out, self.act))
         embed_src = lambda: Src(self.embed.data_ptr(), H * 2, indirect=(st + 4 * isa.ST_TOKEN, None, H * 2))
+        load = [0] * S
+        plan = [[] for _ in range(S)]      # per SM: (emit(sm), weight segment or None)
+
+        def add_gemv(sm, wseg, **kw):
+            plan[sm].append((lambda sm=sm, kw=kw: P.gemv(sm, stream=self.l2_prefetch_bytes > 0, **kw), wseg))
 
         b_hid = None
         for l in range(L):
             # ---- QKV projection with fused input RMSNorm
             b_qkv = P.new_barrier()
             R = rows_per_chunk(H)
-            for sm, u0, cnt in self._ranges(P, self.qkv_rows // R, R * H * 2, granule=max(1, 8 // R)):
+            for sm, u0, cnt in self._ranges(load, self.qkv_rows // R, R * H * 2):
                 r0, n = u0 * R, cnt * R
                 x = Src(hid, H * 2, wait=b_hid) if l > 0 else embed_src()
-                P.gemv(sm, w_addr=self.wqkv[l].data_ptr() + r0 * H * 2, n_rows=n, K=H, R=R, x=x,
-                       out=Dst(qkv + r0 * 2, n * 2, "store", release=b_qkv),
-                       norm_w=Src(self.ln1[l].data_ptr(), H * 2), eps=cfg.eps)
+                wa = self.wqkv[l].data_ptr() + r0 * H * 2
+                add_gemv(sm, (wa, n * H * 2), w_addr=wa, n_rows=n, K=H, R=R, x=x,
+                         out=Dst(qkv + r0 * 2, n * 2, "store", release=b_qkv),
+                         norm_w=Src(self.ln1[l].data_ptr(), H * 2), eps=cfg.eps)
             if l == 0:
-                sm = self._pick(P, 1)[0]
-                P.copy(sm, embed_src(), Dst(hid, H * 2, release=b_qkv), H * 2)
+                sm = self._pick(load, 1)[0]
+                plan[sm].append((lambda sm=sm, b=b_qkv: P.copy(sm, embed_src(), Dst(hid, H * 2, release=b), H * 2), None))
             elif self.taps_enabled:
-                sm = self._pick(P, 1)[0]
-                P.copy(sm, Src(hid, H * 2, wait=b_hid), Dst(self.taps[l - 1].data_ptr(), H * 2, release=b_qkv), H * 2)
+                sm = self._pick(load, 1)[0]
+                plan[sm].append((lambda sm=sm, b=b_qkv, bw=b_hid, t=self.taps[l - 1].data_ptr():
+                                 P.copy(sm, Src(hid, H * 2, wait=bw), Dst(t, H * 2, release=b), H * 2), None))
 
             # ---- split-K GQA decode attention over the paged cache
             b_attn = P.new_barrier()
             units = [(h, s) for s in range(self.n_splits) for h in range(cfg.n_kv_heads)]
             kp, vp = self.kpool[l].data_ptr(), self.vpool[l].data_ptr()
-            q_off = lambda h: qkv + h * G * D * 2
-            k_off = lambda h: qkv + (cfg.q_width + h * D) * 2
-            v_off = lambda h: qkv + (cfg.q_width + cfg.kv_width + h * D) * 2
-            for (h, s), sm in zip(units, self._pick(P, len(units))):
-                P.attn_decode(
-                    sm, G=G, state_addr=st,
+            for (h, s), sm in zip(units, self._pick(load, len(units), 2 * page_bytes * self.pages_per_split)):
+                kw = dict(
+                    G=G, state_addr=st,
                     rope=Src(self.rope.data_ptr(), D * 4, indirect=(st + 4 * isa.ST_POS, 9, None)),
                     norm_w=Src(self.qknorm[l].data_ptr(), 2 * D * 2) if cfg.qk_norm else None,
-                    q=Src(q_off(h), G * D * 2, wait=b_qkv), k_new=Src(k_off(h), D * 2), v_new=Src(v_off(h), D * 2),
+                    q=Src(qkv + h * G * D * 2, G * D * 2, wait=b_qkv),
+                    k_new=Src(qkv + (cfg.q_width + h * D) * 2, D * 2),
+                    v_new=Src(qkv + (cfg.q_width + cfg.kv_width + h * D) * 2, D * 2),
                     k_row=Dst(kp + h * page_bytes, D * 2, indirect=(st + 4 * isa.ST_NEWROW, 8, None)),
                     v_row=Dst(vp + h * page_bytes, D * 2, indirect=(st + 4 * isa.ST_NEWROW, 8, None)),
                     k_page_addr=kp + h * page_bytes, v_page_addr=vp + h * page_bytes, page_shift=page_shift,
                     base_page=s * self.pages_per_split, max_pages=self.pages_per_split,
                     out=Dst(self.attn_part[h, s].data_ptr(), self.rec_floats * 4, release=b_attn),
                     qk_eps=cfg.qk_norm_eps)
+                plan[sm].append((lambda sm=sm, kw=kw: P.attn_decode(sm, **kw), None))
 
             # ---- merge of the split partials, one task per KV head
             b_merge = P.new_barrier()
             n1 = min(self.n_splits, self.max_rec_per_load)
-            for h, sm in zip(range(cfg.n_kv_heads), self._pick(P, cfg.n_kv_heads)):
+            for h, sm in zip(range(cfg.n_kv_heads), self._pick(load, cfg.n_kv_heads, self.n_splits * self.rec_floats * 4)):
                 base = self.attn_part[h].data_ptr()
                 recs = [Src(base, n1 * self.rec_floats * 4, wait=b_attn)]
                 if self.n_splits > n1:
                     recs.append(Src(base + n1 * self.rec_floats * 4, (self.n_splits - n1) * self.rec_floats * 4,
                                     wait=b_attn))
-                P.attn_merge(sm, G=G, n_splits=self.n_splits, records=recs, n_first=n1,
-                             out=Dst(ao + h * G * D * 2, G * D * 2, release=b_merge))
+                kw = dict(G=G, n_splits=self.n_splits, records=recs, n_first=n1,
+                          out=Dst(ao + h * G * D * 2, G * D * 2, release=b_merge))
+                plan[sm].append((lambda sm=sm, kw=kw: P.attn_merge(sm, **kw), None))
 
             # ---- output projection, residual add into hidden
             b_o = P.new_barrier()
             K = cfg.q_width
             R = rows_per_chunk(K)
-            for sm, u0, cnt in self._ranges(P, H // R, R * K * 2):
+            for sm, u0, cnt in self._ranges(load, H // R, R * K * 2):
                 r0, n = u0 * R, cnt * R
-                P.gemv(sm, w_addr=self.wo[l].data_ptr() + r0 * K * 2, n_rows=n, K=K, R=R,
-                       x=Src(ao, K * 2, wait=b_merge), out=Dst(hid + r0 * 2, n * 2, "add_bf16", release=b_o))
+                wa = self.wo[l].data_ptr() + r0 * K * 2
+                add_gemv(sm, (wa, n * K * 2), w_addr=wa, n_rows=n, K=K, R=R, x=Src(ao, K * 2, wait=b_merge),
+                         out=Dst(hid + r0 * 2, n * 2, "add_bf16", release=b_o))
 
             # ---- gate/up projection with fused post-attention RMSNorm and SiLU·mul
             b_gu = P.new_barrier()
             R = rows_per_chunk(H, even=True)
-            for sm, u0, cnt in self._ranges(P, 2 * F // R, R * H * 2):
+            for sm, u0, cnt in self._ranges(load, 2 * F // R, R * H * 2):
                 r0, n = u0 * R, cnt * R
-                P.gemv(sm, w_addr=self.wgu[l].data_ptr() + r0 * H * 2, n_rows=n, K=H, R=R,
-                       x=Src(hid, H * 2, wait=b_o), out=Dst(act + (r0 // 2) * 2, n, "store", release=b_gu),
-                       mode=isa.GEMV_MODE_SILU_PAIRS, norm_w=Src(self.ln2[l].data_ptr(), H * 2), eps=cfg.eps)
+                wa = self.wgu[l].data_ptr() + r0 * H * 2
+                add_gemv(sm, (wa, n * H * 2), w_addr=wa, n_rows=n, K=H, R=R, x=Src(hid, H * 2, wait=b_o),
+                         out=Dst(act + (r0 // 2) * 2, n, "store", release=b_gu), mode=isa.GEMV_MODE_SILU_PAIRS,
+                         norm_w=Src(self.ln2[l].data_ptr(), H * 2), eps=cfg.eps)
 
             # ---- down projection, residual add into hidden
             b_hid = P.new_barrier()
             R = rows_per_chunk(F)
-            for sm, u0, cnt in self._ranges(P, H // R, R * F * 2):
+            for sm, u0, cnt in self._ranges(load, H // R, R * F * 2):
                 r0, n = u0 * R, cnt * R
-                P.gemv(sm, w_addr=self.wd[l].data_ptr() + r0 * F * 2, n_rows=n, K=F, R=R,
-                       x=Src(act, F * 2, wait=b_gu), out=Dst(hid + r0 * 2, n * 2, "add_bf16", release=b_hid))
+                wa = self.wd[l].data_ptr() + r0 * F * 2
+                add_gemv(sm, (wa, n * F * 2), w_addr=wa, n_rows=n, K=F, R=R, x=Src(act, F * 2, wait=b_gu),
+                         out=Dst(hid + r0 * 2, n * 2, "add_bf16", release=b_hid))
 
         # ---- final norm + vocabulary projection + per-SM argmax candidates
         b_logits = P.new_barrier()
         R = rows_per_chunk(H)
         if self.taps_enabled:
-            sm = self._pick(P, 1)[0]
+            sm = self._pick(load, 1)[0]
             b_tap = P.new_barrier()
-            P.copy(sm, Src(hid, H * 2, wait=b_hid), Dst(self.taps[L - 1].data_ptr(), H * 2, release=b_tap), H * 2)
-        lm_ranges = self._ranges(P, V // R, R * H * 2, granule=max(1, 8 // R))
+            plan[sm].append((lambda sm=sm: P.copy(sm, Src(hid, H * 2, wait=b_hid),
+                                                  Dst(self.taps[L - 1].data_ptr(), H * 2, release=b_tap), H * 2), None))
+        lm_ranges = self._ranges(load, V // R, R * H * 2)
         for i, (sm, u0, cnt) in enumerate(lm_ranges):
             r0, n = u0 * R, cnt * R
-            P.gemv(sm, w_addr=self.lm_head.data_ptr() + r0 * H * 2, n_rows=n, K=H, R=R,
-                   x=Src(hid, H * 2, wait=b_hid), out=Dst(self.logits.data_ptr() + r0 * 2, n * 2, "store", release=b_logits),
-                   mode=isa.GEMV_MODE_ARGMAX, norm_w=Src(self.norm_w.data_ptr(), H * 2), eps=cfg.eps,
-                   pair_out=Dst(self.argmax_rec[i].data_ptr(), 16, release=b_logits), row_base=r0)
-        sm = self._pick(P, 1)[0]
-        P.argmax_final(sm, records=Src(self.argmax_rec.data_ptr(), len(lm_ranges) * 16, wait=b_logits),
-                       n=len(lm_ranges), state_addr=st, log_addr=self.token_log.data_ptr())
+            wa = self.lm_head.data_ptr() + r0 * H * 2
+            add_gemv(sm, (wa, n * H * 2), w_addr=wa, n_rows=n, K=H, R=R, x=Src(hid, H * 2, wait=b_hid),
+                     out=Dst(self.logits.data_ptr() + r0 * 2, n * 2, "store", release=b_logits),
+                     mode=isa.GEMV_MODE_ARGMAX, norm_w=Src(self.norm_w.data_ptr(), H * 2), eps=cfg.eps,
+                     pair_out=Dst(self.argmax_rec[i].data_ptr(), 16, release=b_logits), row_base=r0)
+        sm = self._pick(load, 1)[0]
+        plan[sm].append((lambda sm=sm: P.argmax_final(
+            sm, records=Src(self.argmax_rec.data_ptr(), len(lm_ranges) * 16, wait=b_logits), n=len(lm_ranges),
+            state_addr=st, log_addr=self.token_log.data_ptr()), None))
+
+        # ---- emission; every SM first hands its weight-stream segment list to the L2 streamer
+        use_stream = self.l2_prefetch_bytes > 0
+        max_segs = max(sum(1 for _, w in plan[sm] if w is not None) for sm in range(S))
+        seg_tbl = np.zeros((S, max(max_segs, 1), 2), dtype=np.uint64)
+        for sm in range(S):
+            k = 0
+            for _, w in plan[sm]:
+                if w is not None:
+                    seg_tbl[sm, k, 0] = w[0]
+                    seg_tbl[sm, k, 1] = w[1]          # low 32 bits: bytes, high 32 bits: pad
+                    k += 1
+        self.seg_table = torch.from_numpy(seg_tbl.view(np.int64)).to(self.dev)
+        for sm in range(S):
+            n_seg = sum(1 for _, w in plan[sm] if w is not None)
+            if use_stream and n_seg:
+                P.stream_list(sm, self.seg_table[sm].data_ptr(), n_seg, self.l2_prefetch_bytes)
+            for emit, _ in plan[sm]:
+                emit()
 
         st_ = P.stats()
         n_insts = max(st_["max_minsts"], st_["max_cinsts"]) + 2

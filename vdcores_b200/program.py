@@ -181,6 +181,24 @@ class Program:
             self.mem(sm, isa.OP_REPEAT, size=size, arg=(n if (last and dynamic) else 0), address=d,
                      reg_range=(lo, hi))
 
+    def prefetch_l2(self, sm, addr, nbytes):
+        """Pulls [addr, addr+nbytes) into L2 (no shared-memory slot, no completion)."""
+        assert addr % 16 == 0 and nbytes % 16 == 0
+        while nbytes > 0:
+            n = min(nbytes, 65536)
+            self.mem(sm, isa.OP_PREFETCH_L2, size=n & 0xFFFF, arg=n >> 16, address=addr)
+            addr += n
+            nbytes -= n
+
+    def stream_list(self, sm, list_addr, n_segments, window_bytes):
+        """Starts the SM's HBM->L2 streamer on a device array of n_segments
+        {u64 address, u32 bytes, u32 pad} records: the weight bytes this SM will
+        load with stream=True, in order."""
+        assert n_segments <= 0xFFFF and window_bytes % 1024 == 0 and window_bytes >> 10 <= 0xFFFF
+        self.mem(sm, isa.OP_STREAM_LIST, size=n_segments, address=list_addr, reg_range=None)
+        op, size, _, arg, addr = self.m[sm][-1]
+        self.m[sm][-1] = (op, size, window_bytes >> 10, arg, addr)
+
     def dyn_count(self, sm, word_addr, base, maximum):
         self.mem(sm, isa.OP_DYN_COUNT, size=maximum, address=word_addr, reg_range=None, nslot=0, bar=0)
         # base travels in the num_slots field
@@ -195,7 +213,8 @@ class Program:
         self.comp(sm, isa.OP_COPY, 1, nbytes // 4)
 
     def gemv(self, sm, *, w_addr, n_rows, K, R, x: Src, out: Dst, mode=isa.GEMV_MODE_STORE,
-             norm_w: Optional[Src] = None, eps: float = 0.0, pair_out: Optional[Dst] = None, row_base: int = 0):
+             norm_w: Optional[Src] = None, eps: float = 0.0, pair_out: Optional[Dst] = None, row_base: int = 0,
+             stream: bool = False):
         """y[0:n_rows] = W[0:n_rows, :K] @ x for the contiguous bf16 row block at
         w_addr, streamed as chunks of R rows.  The task writes y straight to
         out.addr (kind 'store') or adds it there (kind 'add_bf16'); in SILU_PAIRS
@@ -213,13 +232,13 @@ class Program:
         self.load(sm, x, default_port=1)
         self.raw_address(sm, out.addr, 24, release=out.release)
         if mode == isa.GEMV_MODE_ARGMAX:
-            assert pair_out is not None and row_base % 8 == 0
+            assert pair_out is not None and row_base % R == 0
             self.raw_address(sm, pair_out.addr, 25, release=pair_out.release)
         self.repeat(sm, n_chunks, [chunk_bytes])
-        self.mem(sm, isa.OP_ALLOC_TMA_LOAD_1D, size=chunk_bytes, nslot=slots_for(chunk_bytes), address=w_addr,
-                 flags=isa.F_JUMP)
+        self.mem(sm, isa.OP_ALLOC_TMA_LOAD_1D_STREAM if stream else isa.OP_ALLOC_TMA_LOAD_1D, size=chunk_bytes,
+                 nslot=slots_for(chunk_bytes), address=w_addr, flags=isa.F_JUMP)
         self.bytes_loaded[sm] += chunk_bytes * n_chunks
-        rb8 = row_base // 8
+        rb8 = row_base // R     # index of the first chunk within the whole matrix
         a1 = R | (mode << 8) | (isa.GEMV_NORM_BIT if norm_w is not None else 0) | \
             (isa.GEMV_ACC_BIT if out.kind == "add_bf16" else 0)
         a2 = (K // 256) | ((rb8 >> 16) << 8)
