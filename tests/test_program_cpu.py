@@ -1,0 +1,85 @@
+"""Host-side logic of the instruction program builder (no GPU)."""
+import numpy as np
+import pytest
+
+from vdcores_b200 import isa
+from vdcores_b200.program import CINST, MINST, Dst, Program, Src, f32_bits, slots_for
+
+
+def decode(P):
+    c, m, bars = P.finalize()
+    n = P.insts_per_sm
+    return c.view(CINST).reshape(P.num_sms, n), m.view(MINST).reshape(P.num_sms, n), bars
+
+
+def test_gemv_emission_matches_pop_order():
+    P = Program(2, insts_per_sm=32)
+    b_in, b_out = P.new_barrier(), P.new_barrier()
+    P.gemv(1, w_addr=0x10000, n_rows=64, K=4096, R=4, x=Src(0x2000, 8192, wait=b_in),
+           out=Dst(0x3000, 128, "add_bf16", release=b_out), norm_w=Src(0x4000, 8192), eps=1e-5)
+    c, m, bars = decode(P)
+    ops = [int(x) for x in m[1]["opcode"][:7]]
+    # norm weight, x (port 1, waits on b_in), out (raw address, releases b_out), REPEAT header, chunk load, TERMINATE
+    assert ops[0] == isa.OP_ALLOC_TMA_LOAD_1D | isa.F_PORT
+    assert ops[1] == isa.OP_ALLOC_TMA_LOAD_1D | isa.F_PORT | isa.F_BARRIER
+    assert int(m[1]["num_slots"][1]) == 1 | (b_in << 6)
+    assert ops[2] == isa.OP_ALLOC_WB_RAW_ADDRESS | isa.F_BARRIER | isa.F_WRITEBACK
+    assert int(m[1]["num_slots"][2]) >> 6 == b_out
+    assert ops[3] == isa.OP_REPEAT and int(m[1]["size"][3]) == 16 and int(m[1]["address"][3]) == 4 * 4096 * 2
+    assert ops[4] == isa.OP_ALLOC_TMA_LOAD_1D | isa.F_JUMP and int(m[1]["size"][4]) == 32768
+    assert int(m[1]["num_slots"][4]) == 4
+    assert ops[5] == isa.OP_TERMINATE
+    assert int(bars[b_out]) == 1 and int(bars[b_in]) == 0
+    # compute side: two words, then TERMINATEC; SM 0 only terminates
+    assert int(c[1]["opcode"][0]) == isa.OP_GEMV_ROWS_BF16 and int(c[1]["opcode"][1]) == isa.OP_EXT
+    a1 = int(c[1]["a1"][0])
+    assert a1 & 31 == 4 and a1 & isa.GEMV_NORM_BIT and a1 & isa.GEMV_ACC_BIT and int(c[1]["a2"][0]) & 0xFF == 16
+    e = f32_bits(1e-5)
+    assert (int(c[1]["a0"][1]) << 16 | int(c[1]["a1"][1])) == e
+    assert int(c[1]["opcode"][2]) == isa.OP_TERMINATEC and int(c[0]["opcode"][0]) == isa.OP_TERMINATEC
+
+
+def test_repeat_headers_group_equal_deltas():
+    P = Program(1, insts_per_sm=16)
+    P.repeat(0, 0, [4, 0, 4, 0], dynamic=True)
+    _, m, _ = decode(P)
+    hdr = m[0][:4]
+    assert [int(x) for x in hdr["opcode"]] == [isa.OP_REPEAT] * 4
+    assert [int(x) for x in hdr["address"]] == [4, 0, 4, 0]
+    assert [int(x) for x in hdr["num_slots"]] == [0 | 1 << 8, 1 | 2 << 8, 2 | 3 << 8, 3 | 4 << 8]
+    assert [int(x) for x in hdr["size"]] == [0, 0, 0, 0xFFFF] and int(hdr["arg"][3]) == 4
+    P2 = Program(1, insts_per_sm=16)
+    P2.repeat(0, 7, [512, 512, 512])
+    _, m2, _ = decode(P2)
+    assert int(m2[0]["num_slots"][0]) == 0 | 3 << 8 and int(m2[0]["size"][0]) == 7
+
+
+def test_barrier_counts_follow_releases():
+    P = Program(3, insts_per_sm=32)
+    b = P.new_barrier()
+    for sm in range(3):
+        P.copy(sm, Src(0x1000, 256), Dst(0x2000 + 256 * sm, 256, release=b), 256)
+    P.raw_address(0, 0x9000, 25, release=b)
+    _, _, bars = decode(P)
+    assert int(bars[b]) == 4 and int(bars.sum()) == 4
+
+
+def test_alignment_and_size_checks():
+    P = Program(1)
+    with pytest.raises(AssertionError):
+        P.load(0, Src(0x1008, 256))            # bulk copies start on 16-byte boundaries
+    with pytest.raises(AssertionError):
+        P.load(0, Src(0x1000, 40000))          # at most 32 KB per instruction
+    with pytest.raises(AssertionError):
+        P.gemv(0, w_addr=0, n_rows=6, K=4096, R=4, x=Src(0, 8192), out=Dst(0, 12))   # rows not a multiple of R
+    with pytest.raises(AssertionError):
+        P.gemv(0, w_addr=0, n_rows=8, K=4096, R=8, x=Src(0, 8192), out=Dst(0, 16))   # chunk beyond 32 KB
+    assert slots_for(1) == 1 and slots_for(8192) == 1 and slots_for(8193) == 2 and slots_for(28672) == 4
+
+
+def test_ring_overflow_is_reported():
+    P = Program(1, insts_per_sm=4)
+    for _ in range(5):
+        P.load(0, Src(0x1000, 256))
+    with pytest.raises(ValueError):
+        P.finalize()

@@ -21,7 +21,11 @@
 
 #define VDC_COMPUTE_WARPS 8
 #define VDC_COMPUTE_THREADS (VDC_COMPUTE_WARPS * 32)
+#ifdef VDC_NO_STREAMER
+#define VDC_MEMORY_WARPS 4
+#else
 #define VDC_MEMORY_WARPS 5
+#endif
 #define VDC_THREADS ((VDC_COMPUTE_WARPS + VDC_MEMORY_WARPS) * 32)
 #define VDC_MAX_SMS 160
 

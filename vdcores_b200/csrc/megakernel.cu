@@ -13,11 +13,31 @@ __device__ void compute_core(const Ctx& c, const VdcCInst* __restrict__ insts, i
   uint32_t count = 0;
   int n_traced = 0;
   bool finish = false;
+  // The next two instruction words are always in registers: their loads were
+  // issued before the previous task started, so a task never begins by waiting
+  // on an L2 round trip for its own instruction.
+  auto ld_word = [&](uint32_t at) { return __ldg(reinterpret_cast<const uint2*>(insts + (at % (uint32_t)n_insts))); };
+  uint2 w0 = ld_word(0), w1 = ld_word(1);
+  uint32_t w_pc = 0;  // instruction index of w0
   while (!finish && !q.aborted) {
-    const uint2 raw = __ldg(reinterpret_cast<const uint2*>(insts + (q.pc % (uint32_t)n_insts)));
-    VdcCInst ci;
-    *reinterpret_cast<uint2*>(&ci) = raw;
-    q.pc++;
+    if (w_pc != q.pc) {  // a LOOPC jump: refill
+      w0 = ld_word(q.pc);
+      w1 = ld_word(q.pc + 1);
+      w_pc = q.pc;
+    }
+    VdcCInst ci, ex;
+    *reinterpret_cast<uint2*>(&ci) = w0;
+    *reinterpret_cast<uint2*>(&ex) = w1;
+    const bool two_words = ci.opcode == 0x7200 || ci.opcode == 0x7210 || ci.opcode == 0x7211;
+    q.pc += two_words ? 2 : 1;
+    if (two_words) {
+      w0 = ld_word(q.pc);
+      w1 = ld_word(q.pc + 1);
+    } else {
+      w0 = w1;
+      w1 = ld_word(q.pc + 1);
+    }
+    w_pc = q.pc;
     // task trace: (start, end) global-timer stamps of the first 56 tasks of this SM
     const bool traced = tid == 0 && n_traced < 56 && ci.opcode != 0x7000;
     if (traced) c.profile[c.sm * VDC_NUM_PROFILE_EVENTS + 16 + 2 * n_traced] = globaltimer_ns();
@@ -45,7 +65,7 @@ __device__ void compute_core(const Ctx& c, const VdcCInst* __restrict__ insts, i
         for (int i = 0; i < ci.args[0] && !q.aborted; ++i) {
           const int m = q.pop();
           if (q.aborted) break;
-          __nanosleep(ci.args[1]);
+          if (ci.args[1]) __nanosleep(ci.args[1]);
           q.free_slots(m);
         }
         break;
@@ -68,9 +88,6 @@ __device__ void compute_core(const Ctx& c, const VdcCInst* __restrict__ insts, i
         const bool accumulate = ci.args[1] & VDC_GEMV_ACC_BIT;
         const bool norm = ci.args[1] & VDC_GEMV_NORM_BIT;
         const int K = (ci.args[2] & 0xFF) << 8;
-        VdcCInst ex;
-        *reinterpret_cast<uint2*>(&ex) = __ldg(reinterpret_cast<const uint2*>(insts + (q.pc % (uint32_t)n_insts)));
-        q.pc++;
         if (tid == 0) q.sh->misc[32] = __uint_as_float(((uint32_t)ex.args[0] << 16) | ex.args[1]);  // norm eps
         const int row_base = ((int)ex.args[2] | ((int)(ci.args[2] >> 8) << 16)) * R;  // first output row (argmax)
         switch (R) {
@@ -85,9 +102,6 @@ __device__ void compute_core(const Ctx& c, const VdcCInst* __restrict__ insts, i
       }
       case 0x7210:
       case 0x7211: {
-        VdcCInst ex;
-        *reinterpret_cast<uint2*>(&ex) = __ldg(reinterpret_cast<const uint2*>(insts + (q.pc % (uint32_t)n_insts)));
-        q.pc++;
         if (tid == 0) q.sh->misc[33] = __uint_as_float(((uint32_t)ex.args[0] << 16) | ex.args[1]);  // qk-norm eps
         compute_sync();
         if (ci.opcode == 0x7210) task_attn_decode<4>(q, ci.args[0], ci.args[1], ci.args[2]);
@@ -148,7 +162,9 @@ vdc_megakernel(const VdcCInst* __restrict__ cinsts, const VdcMInst* __restrict__
     const int w = (tid - kCT) >> 5, lane = tid & 31;
     if (w == 0) control_warp(c, minsts + (size_t)c.sm * insts_per_sm, insts_per_sm, lane);
     else if (w == 1) { if (lane == 0) store_warp(c); }
+#ifndef VDC_NO_STREAMER
     else if (w == 4) streamer_warp(c, lane);
+#endif
     else if (lane == 0) load_port(c, w - 2);
   }
   __syncthreads();

@@ -27,6 +27,9 @@
 
 namespace vdc {
 
+#ifndef VDC_SPIN_SLEEP
+#define VDC_SPIN_SLEEP 0
+#endif
 constexpr int kSlots = VDC_NUM_SLOTS;
 constexpr int kQ = VDC_QUEUE_LEN;
 constexpr int kCT = VDC_COMPUTE_THREADS;
@@ -135,6 +138,7 @@ struct __align__(16) Shared {
   // instruction; both load ports walk it (each takes the entries of its port),
   // the compute core consumes the entries in order through `full`.
   VdcMInst ring[kQ];
+  VdcMInst icache[64];      // control warp's window of the memory instruction stream
   int ring_word[kQ];        // slot mask of the entry, or the special slot id
   uint64_t full[kQ];        // completion barrier of the entry (1 arrival + TMA bytes)
   int st_q[kQ];             // compute -> store warp slot masks
@@ -205,6 +209,7 @@ __device__ __forceinline__ bool wait_until(const Ctx& c, Pred ready, int role, i
   while (true) {
     if (ready()) return true;
     if (sleep_ns) __nanosleep(sleep_ns);
+    else if (VDC_SPIN_SLEEP) __nanosleep(VDC_SPIN_SLEEP);
     if ((++it & 63u) == 0) {
       if (ld_relaxed_gpu(&c.status->abort) != 0) return false;
       uint64_t now = globaltimer_ns();

@@ -307,6 +307,12 @@ __device__ void task_gemv_rows(Compute& q, int n_chunks, int mode, bool accumula
 // out (write-back: G x 128 fp32 unnormalised O, then m[G], l[G]).
 // count = clamp(n_pages - base, 0, max_pages) is read from the state block; the
 // memory stream uses the same rule (DYN_COUNT + REPEAT).
+#ifdef VDC_TRACE_ATTN
+#define ATTN_STAMP(i) if (q.tid == 0) c.profile[c.sm * VDC_NUM_PROFILE_EVENTS + 100 + (i)] = globaltimer_ns()
+#else
+#define ATTN_STAMP(i)
+#endif
+
 template <int G>
 __device__ void task_attn_decode(Compute& q, int max_pages, int base_page, int flags) {
   constexpr int D = VDC_HEAD_DIM;
@@ -318,6 +324,7 @@ __device__ void task_attn_decode(Compute& q, int max_pages, int base_page, int f
   const Ctx& c = q.c;
   const bool qk_norm = flags & VDC_ATTN_QKNORM_BIT;
 
+  ATTN_STAMP(0);
   q.pop();  // decode state block: raw address
   const int* state = reinterpret_cast<const int*>(q.addr());
   const int rope_mask = q.pop();
@@ -329,6 +336,7 @@ __device__ void task_attn_decode(Compute& q, int max_pages, int base_page, int f
   const int kro_mask = q.pop();
   const int vro_mask = q.pop();
   if (q.aborted) return;
+  ATTN_STAMP(1);
 
   const int pos = ld_relaxed_gpu(state + VDC_ST_POS);
   const int n_pages = ld_relaxed_gpu(state + VDC_ST_NPAGES);
@@ -388,6 +396,7 @@ __device__ void task_attn_decode(Compute& q, int max_pages, int base_page, int f
   fence_proxy_async_smem();
   compute_sync();
   q.free_slots(rope_mask | nw_mask | q_mask | kn_mask | vn_mask);
+  ATTN_STAMP(2);
 
   // per-lane slice of the rotated queries
   const int sub = q.lane % LPP, pl = q.lane / LPP;
@@ -413,6 +422,7 @@ __device__ void task_attn_decode(Compute& q, int max_pages, int base_page, int f
   for (int blk = 0; blk < count; ++blk) {
     const int k_mask = q.pop();  // its sync also ends the previous block's PV phase
     if (q.aborted) return;
+    ATTN_STAMP(3 + 4 * (blk & 1));
     q.free_slots(v_prev);
     uint8_t* kb = (uint8_t*)slot_ptr(c, first_slot(k_mask));
     const bool last = owner && blk == count - 1;
@@ -462,6 +472,7 @@ __device__ void task_attn_decode(Compute& q, int max_pages, int base_page, int f
       if (q.lane == 0) sh->wmax[q.warp * G + g] = wm[g];
     }
     compute_sync();  // (A) scores and warp maxima visible; K page fully read
+    ATTN_STAMP(4 + 4 * (blk & 1));
     q.free_slots(k_mask);
     // ---- phase 2: running max, rescale factors, probabilities
     float alpha[G], m_new[G];
@@ -482,6 +493,7 @@ __device__ void task_attn_decode(Compute& q, int max_pages, int base_page, int f
     }
     const int v_mask = q.pop();  // (B) its sync publishes probs
     if (q.aborted) return;
+    ATTN_STAMP(5 + 4 * (blk & 1));
     uint8_t* vb = (uint8_t*)slot_ptr(c, first_slot(v_mask));
     if (last) {
       if (q.tid < D / 8)
@@ -508,10 +520,12 @@ __device__ void task_attn_decode(Compute& q, int max_pages, int base_page, int f
       }
     }
     v_prev = v_mask;
+    ATTN_STAMP(6 + 4 * (blk & 1));
   }
 
   const int out_mask = q.pop();  // sync: everyone is done with the last V page
   if (q.aborted) return;
+  ATTN_STAMP(11);
   q.free_slots(v_prev);
   float* out = (float*)slot_ptr(c, first_slot(out_mask));
   // cross position-group reduction: groups 1..3 publish, group 0 adds
@@ -545,6 +559,7 @@ __device__ void task_attn_decode(Compute& q, int max_pages, int base_page, int f
   }
   fence_proxy_async_smem();
   compute_sync();
+  ATTN_STAMP(12);
   q.push_store(out_mask);
   if (owner) {
     q.push_store(kro_mask);

@@ -7,13 +7,6 @@ namespace vdc {
 // ------------------------------------------------------------------------- //
 // memory virtual core: control warp
 // ------------------------------------------------------------------------- //
-__device__ __forceinline__ VdcMInst load_minst(const VdcMInst* p) {
-  uint4 v = __ldg(reinterpret_cast<const uint4*>(p));
-  VdcMInst m;
-  *reinterpret_cast<uint4*>(&m) = v;
-  return m;
-}
-
 // Oldest ring entry that some consumer may still read: the CTA-wide head, or
 // the next entry of the slowest warp while a per-warp phase is running.
 __device__ __forceinline__ unsigned ring_head(const Shared* sh, int lane) {
@@ -24,6 +17,39 @@ __device__ __forceinline__ unsigned ring_head(const Shared* sh, int lane) {
   unsigned v = lane < kCW ? sh->warp_next[lane] : 0xFFFFFFFFu;
   v = v < ch ? v : ch;
   return __reduce_min_sync(0xffffffffu, v);
+}
+
+// The control warp keeps instructions as four 32-bit words in registers:
+//   w.x = opcode | size << 16,  w.y = num_slots | arg << 16 (the "shifter"),
+//   w.z / w.w = low / high half of the address (or the four 16-bit coordinates).
+// The instruction stream lives in global memory; the control warp keeps a
+// 64-instruction window of it in shared memory (filled 32 lanes at a time), so
+// that loop bodies are re-read from shared memory, never from L2.
+__device__ __forceinline__ void icache_fill(Shared* sh, const VdcMInst* insts, uint32_t base, int n_insts, int lane) {
+  const uint4 a = __ldg(reinterpret_cast<const uint4*>(insts + ((base + lane) % (uint32_t)n_insts)));
+  const uint4 b = __ldg(reinterpret_cast<const uint4*>(insts + ((base + 32 + lane) % (uint32_t)n_insts)));
+  __syncwarp();
+  *reinterpret_cast<uint4*>(&sh->icache[lane]) = a;
+  *reinterpret_cast<uint4*>(&sh->icache[32 + lane]) = b;
+  __syncwarp();
+}
+
+// Bounded warp-wide back-off used by the control warp's two resource waits.
+// Returns non-zero when the wait must be given up.
+__device__ __forceinline__ int control_backoff(const Ctx& c, int lane, uint32_t& it, uint64_t& t0, uint32_t pc,
+                                               uint32_t opcode, int aux) {
+  if ((++it & 63u) != 0) return 0;
+  int ab = 0;
+  if (lane == 0) {
+    ab = ld_relaxed_gpu(&c.status->abort);
+    const uint64_t now = globaltimer_ns();
+    if (t0 == 0) t0 = now;
+    else if (now - t0 > 2 * c.timeout_ns) {
+      raise_abort(c, VDC_ERR_TIMEOUT, 1, (int)pc, (int)opcode, -1, aux);
+      ab = 1;
+    }
+  }
+  return __shfl_sync(0xffffffffu, ab, 0);
 }
 
 __device__ void control_warp(const Ctx& c, const VdcMInst* __restrict__ insts, int n_insts, int lane) {
@@ -37,46 +63,45 @@ __device__ void control_warp(const Ctx& c, const VdcMInst* __restrict__ insts, i
   bool ind_pending = false;
   unsigned tail = 0;        // ring entries published
   unsigned head_cache = 0;  // last known ring head
-  bool running = true;
   unsigned demand = 0;      // bytes of the weight stream whose loads were issued
-  long long t_fetch = 0, t_alloc = 0, t_pub = 0, n_inst = 0;
+  unsigned n_inst = 0, n_alloc_retry = 0, n_ring_wait = 0;
+  const long long t_begin = clock64();
+  bool running = true;
 
-  // two-entry register cache of the instruction stream: the instruction being
-  // executed (re-used by single-instruction REPEAT bodies) and its successor
-  VdcMInst cur = load_minst(insts);
-  uint32_t cur_pc = 0;
-  VdcMInst nxt = load_minst(insts + (1 % n_insts));
-  uint32_t nxt_pc = 1;
+  uint32_t ic_base = 0;  // first instruction index held in the shared-memory window
+  icache_fill(sh, insts, 0, n_insts, lane);
 
   while (running) {
     pc = next_pc;
-    const long long tf0 = clock64();
-    if (pc != cur_pc) {
-      if (pc == nxt_pc) cur = nxt;
-      else cur = load_minst(insts + (pc % (uint32_t)n_insts));
-      cur_pc = pc;
+    if (pc - ic_base >= 64u) {
+      ic_base = pc & ~31u;
+      icache_fill(sh, insts, ic_base, n_insts, lane);
     }
-    if (nxt_pc != pc + 1) {
-      nxt = load_minst(insts + ((pc + 1) % (uint32_t)n_insts));  // consumed on the next trip at the earliest
-      nxt_pc = pc + 1;
-    }
-    VdcMInst inst = cur;
+    uint4 w = *reinterpret_cast<const uint4*>(&sh->icache[pc - ic_base]);
     next_pc = pc + 1;
-
-    if (loop_counter > 0) inst.address += __shfl_sync(0xffffffffu, accum, (int)((pc - (uint32_t)loop_start) & 31u));
-    if (inst.opcode & VDC_F_GROUP) inst.shifter += shift;
-    const uint16_t opid = inst.opcode >> VDC_FLAG_BITS;
-    t_fetch += clock64() - tf0;
     n_inst++;
 
-    if (inst.opcode & VDC_F_ALLOCATE) {
+    if (loop_counter > 0) {
+      const uint64_t a = __shfl_sync(0xffffffffu, accum, (int)((pc - (uint32_t)loop_start) & 31u));
+      const uint64_t addr = (((uint64_t)w.w << 32) | w.z) + a;
+      w.z = (uint32_t)addr;
+      w.w = (uint32_t)(addr >> 32);
+    }
+    const uint32_t opcode = w.x & 0xFFFFu;
+    if (opcode & VDC_F_GROUP) w.y += shift;
+    const uint32_t opid = opcode >> VDC_FLAG_BITS;
+    const uint32_t size = w.x >> 16;
+    const uint32_t num_slots = w.y & 0xFFFFu;
+
+    if (opcode & VDC_F_ALLOCATE) {
       if (ind_pending) {
-        inst.address += ind_off;
+        const uint64_t addr = (((uint64_t)w.w << 32) | w.z) + ind_off;
+        w.z = (uint32_t)addr;
+        w.w = (uint32_t)(addr >> 32);
         ind_pending = false;
       }
-      const int req = inst.num_slots & 63;
+      const int req = (int)(num_slots & 63u);
       int slot, word;
-      const long long ta0 = clock64();
       if (req >= kSlots) {
         slot = req;  // special slot: nothing is allocated, the id itself is handed over
         word = req;
@@ -93,22 +118,11 @@ __device__ void control_warp(const Ctx& c, const VdcMInst* __restrict__ insts, i
             slot = __ffs(cand) - 1;
             break;
           }
+          n_alloc_retry++;
           __nanosleep(20);
-          if ((++it & 63u) == 0) {
-            int ab = 0;
-            if (lane == 0) {
-              ab = ld_relaxed_gpu(&c.status->abort);
-              const uint64_t now = globaltimer_ns();
-              if (t0 == 0) t0 = now;
-              else if (now - t0 > 2 * c.timeout_ns) {
-                raise_abort(c, VDC_ERR_TIMEOUT, 1, (int)pc, inst.opcode, -1, req);
-                ab = 1;
-              }
-            }
-            if (__shfl_sync(0xffffffffu, ab, 0)) {
-              ok = false;
-              break;
-            }
+          if (control_backoff(c, lane, it, t0, pc, opcode, req)) {
+            ok = false;
+            break;
           }
         }
         if (!ok) break;
@@ -116,9 +130,7 @@ __device__ void control_warp(const Ctx& c, const VdcMInst* __restrict__ insts, i
         if (lane == 0) atomicAnd(&sh->slot_avail, ~mask);
         word = (int)mask;
       }
-      t_alloc += clock64() - ta0;
 
-      const long long tp0 = clock64();
       // a ring entry is recycled only after every consumer moved past it
       if (tail - head_cache >= (unsigned)kQ) {
         uint32_t it = 0;
@@ -127,82 +139,161 @@ __device__ void control_warp(const Ctx& c, const VdcMInst* __restrict__ insts, i
         while (true) {
           head_cache = ring_head(sh, lane);
           if (tail - head_cache < (unsigned)kQ) break;
-          if ((++it & 63u) == 0) {
-            int ab = 0;
-            if (lane == 0) {
-              ab = ld_relaxed_gpu(&c.status->abort);
-              const uint64_t now = globaltimer_ns();
-              if (t0 == 0) t0 = now;
-              else if (now - t0 > 2 * c.timeout_ns) {
-                raise_abort(c, VDC_ERR_TIMEOUT, 1, (int)pc, inst.opcode, -1, -2);
-                ab = 1;
-              }
-            }
-            if (__shfl_sync(0xffffffffu, ab, 0)) {
-              ok = false;
-              break;
-            }
+          n_ring_wait++;
+          if (control_backoff(c, lane, it, t0, pc, opcode, -2)) {
+            ok = false;
+            break;
           }
         }
         if (!ok) break;
       }
       if (lane == 0) {
         const unsigned e = tail % kQ;
-        if ((inst.opcode & VDC_F_WRITEBACK) || req >= kSlots) sh->st_insts[slot] = inst;
-        sh->ring[e] = inst;
+        if ((opcode & VDC_F_WRITEBACK) || req >= kSlots) *reinterpret_cast<uint4*>(&sh->st_insts[slot]) = w;
+        *reinterpret_cast<uint4*>(&sh->ring[e]) = w;
         sh->ring_word[e] = word;
         __threadfence_block();
         sh->ring_tail = tail + 1;
-        if (opid == 28) sh->demand_pos = demand + inst.size;
+        if (opid == 28) sh->demand_pos = demand + size;
       }
-      if (opid == 28) demand += inst.size;
+      if (opid == 28) demand += size;
       tail++;
-      t_pub += clock64() - tp0;
 
-      if ((inst.opcode & VDC_F_JUMP) && loop_counter > 0) {
+      if ((opcode & VDC_F_JUMP) && loop_counter > 0) {
         --loop_counter;
         if (loop_counter > 0) next_pc = (uint32_t)loop_start;
         accum += delta;
       }
     } else {
+      const uint64_t address = ((uint64_t)w.w << 32) | w.z;
+      const uint32_t arg = w.y >> 16;
       switch (opid) {
         case 1: {  // TERMINATE: an end marker travels through the ring to both load ports
           running = false;
           bool ok = true;
           uint32_t it = 0;
+          uint64_t t0 = 0;
           while (tail - head_cache >= (unsigned)kQ) {
             head_cache = ring_head(sh, lane);
-            if ((++it & 1023u) == 0 && __shfl_sync(0xffffffffu, ld_relaxed_gpu(&c.status->abort), 0)) {
+            if (control_backoff(c, lane, it, t0, pc, opcode, -3)) {
               ok = false;
               break;
             }
           }
           if (ok && lane == 0) {
-            sh->ring[tail % kQ] = inst;
+            *reinterpret_cast<uint4*>(&sh->ring[tail % kQ]) = w;
             __threadfence_block();
             sh->ring_tail = tail + 1;
           }
           break;
         }
         case 2: {  // REPEAT: per-lane address deltas for the following body
-          int count = inst.size;
+          int count = (int)size;
           if (count == 0xFFFF) count = dyn;
-          const int reg_start = inst.num_slots & 0xFF, reg_end = inst.num_slots >> 8;
+          const int reg_start = (int)(num_slots & 0xFF), reg_end = (int)(num_slots >> 8);
           if (lane >= reg_start && lane < reg_end) {
-            delta = inst.address;
+            delta = address;
             accum = 0;
           }
           loop_counter = count;
           loop_start = (int)pc + 1;
-          if (inst.size == 0xFFFF && count == 0) next_pc = pc + 1 + inst.arg;  // empty dynamic loop: skip body
+          if (size == 0xFFFF && count == 0) {
+            next_pc = pc + 1 + arg;  // empty dynamic loop: skip body
+            break;
+          }
+          // Fast path for the dominant case, a body of one plain 1-D load (a weight
+          // stream): lane 0 runs the whole loop alone, without warp-wide votes.
+          if (count > 0 && pc + 1 - ic_base < 64u && !ind_pending) {
+            const uint4 b = *reinterpret_cast<const uint4*>(&sh->icache[pc + 1 - ic_base]);
+            const uint32_t bop = b.x & 0xFFFFu, bid = bop >> VDC_FLAG_BITS;
+            const int breq = (int)(b.y & 63u);
+            if ((bid == 9 || bid == 28) && (bop & VDC_F_JUMP) && !(bop & (VDC_F_GROUP | VDC_F_BARRIER)) && breq > 0 &&
+                breq < kSlots && reg_start == 0 && reg_end >= 1) {
+              int ok = 1;
+              if (lane == 0) {
+                uint64_t addr = ((uint64_t)b.w << 32) | b.z;
+                const uint32_t bsize = b.x >> 16;
+                const uint32_t unit = (1u << breq) - 1u;
+                int pos = 0;  // where the previous allocation ended: frees come back in the same order
+                for (int k = 0; k < count && ok; ++k) {
+                  uint32_t it = 0;
+                  uint64_t t0 = 0;
+                  uint32_t mask;
+                  while (true) {
+                    const uint32_t avail = *reinterpret_cast<volatile uint32_t*>(&sh->slot_avail);
+                    if (pos + breq > kSlots) pos = 0;
+                    mask = unit << pos;
+                    if ((avail & mask) == mask) break;
+                    bool found = false;
+                    for (int p2 = 0; p2 + breq <= kSlots; ++p2) {
+                      mask = unit << p2;
+                      if ((avail & mask) == mask) {
+                        pos = p2;
+                        found = true;
+                        break;
+                      }
+                    }
+                    if (found) break;
+                    n_alloc_retry++;
+                    __nanosleep(20);
+                    if ((++it & 63u) == 0) {
+                      const uint64_t now = globaltimer_ns();
+                      if (t0 == 0) t0 = now;
+                      if (ld_relaxed_gpu(&c.status->abort) != 0) ok = 0;
+                      else if (now - t0 > 2 * c.timeout_ns) {
+                        raise_abort(c, VDC_ERR_TIMEOUT, 1, (int)pc + 1, (int)bop, -1, breq);
+                        ok = 0;
+                      }
+                      if (!ok) break;
+                    }
+                  }
+                  if (!ok) break;
+                  atomicAnd(&sh->slot_avail, ~mask);
+                  pos += breq;
+                  while (tail - head_cache >= (unsigned)kQ) {  // ring full: recompute the head alone
+                    unsigned h = sh->cta_head;
+                    __threadfence_block();
+                    for (int wv = 0; wv < kCW; ++wv) {
+                      const unsigned v = sh->warp_next[wv];
+                      h = v < h ? v : h;
+                    }
+                    head_cache = h;
+                    if ((++it & 1023u) == 0 && ld_relaxed_gpu(&c.status->abort) != 0) {
+                      ok = 0;
+                      break;
+                    }
+                  }
+                  if (!ok) break;
+                  const unsigned e = tail % kQ;
+                  *reinterpret_cast<uint4*>(&sh->ring[e]) = make_uint4(b.x, b.y, (uint32_t)addr, (uint32_t)(addr >> 32));
+                  sh->ring_word[e] = (int)mask;
+                  __threadfence_block();
+                  sh->ring_tail = ++tail;
+                  if (bid == 28) {
+                    demand += bsize;
+                    sh->demand_pos = demand;
+                  }
+                  addr += address;  // the REPEAT delta
+                }
+              }
+              ok = __shfl_sync(0xffffffffu, ok, 0);
+              tail = __shfl_sync(0xffffffffu, tail, 0);
+              head_cache = __shfl_sync(0xffffffffu, head_cache, 0);
+              demand = __shfl_sync(0xffffffffu, demand, 0);
+              n_inst += (unsigned)count;
+              loop_counter = 0;
+              next_pc = pc + 2;
+              if (!ok) running = false;
+            }
+          }
           break;
         }
         case 3: {  // LOOP: jump back `size-1` times, shifting GROUP-flagged bar/TMA ids each time
-          const int reg = inst.num_slots & 31;
+          const int reg = (int)(num_slots & 31u);
           if (lane == reg) {
-            if (++jmp_cnt < (int)inst.size) {
-              next_pc = inst.coords[0];
-              shift += (uint32_t)inst.coords[2] | ((uint32_t)inst.coords[3] << 16);
+            if (++jmp_cnt < (int)size) {
+              next_pc = w.z & 0xFFFFu;  // coords[0]
+              shift += w.w;            // coords[2] | coords[3] << 16
             } else {
               jmp_cnt = 0;
               shift = 0;
@@ -214,7 +305,7 @@ __device__ void control_warp(const Ctx& c, const VdcMInst* __restrict__ insts, i
         }
         case 5: {  // ISSUE_BARRIER: stall the whole memory stream on a global barrier
           int ok = 1;
-          if (lane == 0) ok = wait_global_barrier(c, inst.num_slots >> 6, 1, (int)pc, inst.opcode);
+          if (lane == 0) ok = wait_global_barrier(c, (int)(num_slots >> 6), 1, (int)pc, (int)opcode);
           ok = __shfl_sync(0xffffffffu, ok, 0);
           if (!ok) running = false;
           break;
@@ -222,25 +313,25 @@ __device__ void control_warp(const Ctx& c, const VdcMInst* __restrict__ insts, i
         case 6:    // CC0: next allocating instruction's address += word << arg
         case 7: {  // CC0_ROW_BYTES:                        ... += word * size
           int word = 0;
-          if (lane == 0) word = ld_relaxed_gpu(reinterpret_cast<const int*>(inst.address));
+          if (lane == 0) word = ld_relaxed_gpu(reinterpret_cast<const int*>(address));
           word = __shfl_sync(0xffffffffu, word, 0);
-          ind_off = (opid == 6) ? ((uint64_t)(uint32_t)word << inst.arg) : ((uint64_t)(uint32_t)word * inst.size);
+          ind_off = (opid == 6) ? ((uint64_t)(uint32_t)word << arg) : ((uint64_t)(uint32_t)word * size);
           ind_pending = true;
           break;
         }
         case 25: {  // DYN_COUNT: dyn = clamp(word - base, 0, max)
           int word = 0;
-          if (lane == 0) word = ld_relaxed_gpu(reinterpret_cast<const int*>(inst.address));
+          if (lane == 0) word = ld_relaxed_gpu(reinterpret_cast<const int*>(address));
           word = __shfl_sync(0xffffffffu, word, 0);
-          int v = word - (int)inst.num_slots;
-          dyn = v < 0 ? 0 : (v > (int)inst.size ? (int)inst.size : v);
+          const int v = word - (int)num_slots;
+          dyn = v < 0 ? 0 : (v > (int)size ? (int)size : v);
           break;
         }
         case 27: {  // STREAM_LIST: hand the weight-stream segment list to the streamer warp
           if (lane == 0) {
-            sh->pf_list = inst.address;
-            sh->pf_n = inst.size;
-            sh->pf_window = (uint32_t)inst.num_slots << 10;  // KB
+            sh->pf_list = address;
+            sh->pf_n = size;
+            sh->pf_window = num_slots << 10;  // KB
             __threadfence_block();
             sh->pf_go = 1;
           }
@@ -248,8 +339,8 @@ __device__ void control_warp(const Ctx& c, const VdcMInst* __restrict__ insts, i
         }
         case 26: {  // PREFETCH_L2: pull [address, address + (arg << 16 | size)) into L2, no slot involved
           if (lane == 0) {
-            const uint32_t bytes = ((uint32_t)inst.arg << 16) | inst.size;
-            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(inst.address), "r"(bytes) : "memory");
+            const uint32_t bytes = (arg << 16) | size;
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(address), "r"(bytes) : "memory");
           }
           break;
         }
@@ -260,11 +351,10 @@ __device__ void control_warp(const Ctx& c, const VdcMInst* __restrict__ insts, i
   }
   if (lane == 0) {
     sh->pf_exit = 1;
-    uint64_t* pr = c.profile + c.sm * VDC_NUM_PROFILE_EVENTS;
-    pr[3] = (uint64_t)t_fetch;
-    pr[4] = (uint64_t)t_alloc;
-    pr[5] = (uint64_t)t_pub;
-    pr[6] = (uint64_t)n_inst;
+    c.profile[c.sm * VDC_NUM_PROFILE_EVENTS + 6] = n_inst;
+    c.profile[c.sm * VDC_NUM_PROFILE_EVENTS + 3] = (uint64_t)(clock64() - t_begin);
+    c.profile[c.sm * VDC_NUM_PROFILE_EVENTS + 4] = n_alloc_retry;
+    c.profile[c.sm * VDC_NUM_PROFILE_EVENTS + 5] = n_ring_wait;
   }
   // When the loop was left through an abort the load ports get no end marker:
   // their own waits observe the global abort flag and return.
@@ -308,41 +398,26 @@ __device__ void load_port(const Ctx& c, int port) {
   unsigned cursor = 0;  // next ring entry to look at (both ports walk every entry)
   int reg_file[4] = {0, 0, 0, 0};
   const int role = 3 + port;
-  long long t_idle = 0, t_bar = 0, t_issue = 0;
-  unsigned n_mine = 0;
-  uint64_t* pr = c.profile + c.sm * VDC_NUM_PROFILE_EVENTS + 8 + port * 4;
   unsigned seen_tail = 0;
   while (true) {
     if (seen_tail == cursor) {
-      const long long ti0 = clock64();
       if (!wait_until(c, [&] { return (seen_tail = sh->ring_tail) != cursor; }, role, (int)cursor, 0, -1, 0)) return;
-      t_idle += clock64() - ti0;
       __threadfence_block();
     }
     const unsigned e = cursor % kQ;
     const VdcMInst inst = sh->ring[e];
     cursor++;
     const uint16_t opcode = inst.opcode;
-    if ((opcode >> VDC_FLAG_BITS) == 1) {  // end marker
-      pr[0] = (uint64_t)t_idle;
-      pr[1] = (uint64_t)t_bar;
-      pr[2] = (uint64_t)t_issue;
-      pr[3] = n_mine;
-      return;
-    }
+    if ((opcode >> VDC_FLAG_BITS) == 1) return;  // end marker
     if (((opcode & VDC_F_PORT) ? 1 : 0) != port) continue;
-    n_mine++;
     const int word = sh->ring_word[e];
     const int req = inst.num_slots & 63;
     const int slot = req >= kSlots ? req : __ffs(word) - 1;
     uint64_t* bar = &sh->full[e];
 
     if ((opcode & VDC_F_BARRIER) && !(opcode & VDC_F_WRITEBACK)) {
-      const long long tb0 = clock64();
       if (!wait_global_barrier(c, inst.num_slots >> 6, role, (int)cursor, opcode)) return;
-      t_bar += clock64() - tb0;
     }
-    const long long ts0 = clock64();
     void* dst = slot < kSlots ? slot_ptr(c, slot) : nullptr;
     switch (opcode >> VDC_FLAG_BITS) {
       case 28:  // 1-D bulk load of weight-stream bytes (counted by the L2 streamer)
@@ -385,7 +460,6 @@ __device__ void load_port(const Ctx& c, int port) {
         mbar_arrive(bar);
         break;
     }
-    t_issue += clock64() - ts0;
   }
 }
 

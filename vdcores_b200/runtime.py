@@ -15,7 +15,7 @@ import types
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libvdcores_b200.so")
+LIB_PATH = os.environ.get("VDCORES_LIB") or os.path.join(_HERE, "libvdcores_b200.so")
 
 if not os.path.exists(LIB_PATH):
     raise ImportError(
