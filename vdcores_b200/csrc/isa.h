@@ -83,8 +83,13 @@
   X(OP_ATTN_DECODE_PAGED_G8, 0x7211)                                                   \
   X(OP_ATTN_MERGE, 0x7212)                                                             \
   X(OP_ARGMAX_FINAL, 0x7220)                                                          \
+  X(OP_L2_PREFETCH, 0x7230)                                                          \
   X(OP_EXT, 0x7FFF)
 
+// OP_L2_PREFETCH (two words): args = 48-bit address in three 16-bit pieces (low
+// first); second word args[0..1] = byte count (low, high).  All compute threads
+// issue L2 prefetches for the range and move on; nothing is popped.
+//
 // OP_EXT is never dispatched: it marks the second 8-byte word of a two-word
 // compute instruction (GEMV_ROWS, ATTN_DECODE_PAGED).
 //

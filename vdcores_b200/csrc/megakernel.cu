@@ -28,7 +28,7 @@ __device__ void compute_core(const Ctx& c, const VdcCInst* __restrict__ insts, i
     VdcCInst ci, ex;
     *reinterpret_cast<uint2*>(&ci) = w0;
     *reinterpret_cast<uint2*>(&ex) = w1;
-    const bool two_words = ci.opcode == 0x7200 || ci.opcode == 0x7210 || ci.opcode == 0x7211;
+    const bool two_words = ci.opcode == 0x7200 || ci.opcode == 0x7210 || ci.opcode == 0x7211 || ci.opcode == 0x7230;
     q.pc += two_words ? 2 : 1;
     if (two_words) {
       w0 = ld_word(q.pc);
@@ -106,6 +106,13 @@ __device__ void compute_core(const Ctx& c, const VdcCInst* __restrict__ insts, i
         compute_sync();
         if (ci.opcode == 0x7210) task_attn_decode<4>(q, ci.args[0], ci.args[1], ci.args[2]);
         else task_attn_decode<8>(q, ci.args[0], ci.args[1], ci.args[2]);
+        break;
+      }
+      case 0x7230: {  // L2_PREFETCH: every thread touches its share of the range, nobody waits
+        const uint64_t base = (uint64_t)ci.args[0] | ((uint64_t)ci.args[1] << 16) | ((uint64_t)ci.args[2] << 32);
+        const uint32_t bytes = (uint32_t)ex.args[0] | ((uint32_t)ex.args[1] << 16);
+        for (uint32_t off = (uint32_t)tid * 128u; off < bytes; off += kCT * 128u)
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(base + off));
         break;
       }
       case 0x7212: task_attn_merge(q, ci.args[0], ci.args[1], ci.args[2]); break;

@@ -225,7 +225,8 @@ __device__ __forceinline__ bool wait_until(const Ctx& c, Pred ready, int role, i
 
 __device__ __forceinline__ bool wait_global_barrier(const Ctx& c, int bar, int role, int pc, int opcode) {
   const int* p = c.bars + bar;
-  bool ok = wait_until(c, [&] { return ld_acquire_gpu(p) == 0; }, role, pc, opcode, bar, 32);
+  bool ok = wait_until(c, [&] { return ld_relaxed_gpu(p) == 0; }, role, pc, opcode, bar, 0);
+  asm volatile("fence.acq_rel.gpu;" ::: "memory");  // pairs with the releasing red of the producers
   fence_proxy_async();  // later bulk copies (async proxy) must observe what the releasing stores wrote
   return ok;
 }

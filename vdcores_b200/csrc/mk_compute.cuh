@@ -273,7 +273,9 @@ __device__ void task_gemv_rows(Compute& q, int n_chunks, int mode, bool accumula
       reinterpret_cast<int*>(sh->misc)[48 + q.warp] = best.idx;
     }
   }
-  __threadfence();  // output rows were written by lanes of every warp
+  // Output rows were written by lanes of every warp.  The CTA barrier inside
+  // warp_phase_end orders them before thread 0, whose gpu-scope fence in
+  // release() is cumulative, so no per-thread fence is needed here.
   q.warp_phase_end((unsigned)n_chunks);
   if (q.aborted) return;
   if (mode == VDC_GEMV_MODE_ARGMAX && q.tid == 0) {

@@ -19,6 +19,15 @@ __device__ __forceinline__ unsigned ring_head(const Shared* sh, int lane) {
   return __reduce_min_sync(0xffffffffu, v);
 }
 
+#ifndef VDC_CTRL_FASTPATH
+#define VDC_CTRL_FASTPATH 0
+#endif
+#ifndef VDC_FAST_SLEEP
+#define VDC_FAST_SLEEP 20
+#endif
+#ifndef VDC_FAST_FIRSTFIT
+#define VDC_FAST_FIRSTFIT 0
+#endif
 // The control warp keeps instructions as four 32-bit words in registers:
 //   w.x = opcode | size << 16,  w.y = num_slots | arg << 16 (the "shifter"),
 //   w.z / w.w = low / high half of the address (or the four 16-bit coordinates).
@@ -203,7 +212,10 @@ __device__ void control_warp(const Ctx& c, const VdcMInst* __restrict__ insts, i
           }
           // Fast path for the dominant case, a body of one plain 1-D load (a weight
           // stream): lane 0 runs the whole loop alone, without warp-wide votes.
-          if (count > 0 && pc + 1 - ic_base < 64u && !ind_pending) {
+          // (Measured on B200: issuing the chunk loads this fast makes them arrive in
+          // bursts, the warps then compute and free in lock-step, and a GEMV stage
+          // streams ~7 % slower than with the paced general path; off by default.)
+          if (VDC_CTRL_FASTPATH && count > 0 && pc + 1 - ic_base < 64u && !ind_pending) {
             const uint4 b = *reinterpret_cast<const uint4*>(&sh->icache[pc + 1 - ic_base]);
             const uint32_t bop = b.x & 0xFFFFu, bid = bop >> VDC_FLAG_BITS;
             const int breq = (int)(b.y & 63u);
@@ -221,7 +233,7 @@ __device__ void control_warp(const Ctx& c, const VdcMInst* __restrict__ insts, i
                   uint32_t mask;
                   while (true) {
                     const uint32_t avail = *reinterpret_cast<volatile uint32_t*>(&sh->slot_avail);
-                    if (pos + breq > kSlots) pos = 0;
+                    if (VDC_FAST_FIRSTFIT || pos + breq > kSlots) pos = 0;
                     mask = unit << pos;
                     if ((avail & mask) == mask) break;
                     bool found = false;
@@ -235,7 +247,7 @@ __device__ void control_warp(const Ctx& c, const VdcMInst* __restrict__ insts, i
                     }
                     if (found) break;
                     n_alloc_retry++;
-                    __nanosleep(20);
+                    __nanosleep(VDC_FAST_SLEEP);
                     if ((++it & 63u) == 0) {
                       const uint64_t now = globaltimer_ns();
                       if (t0 == 0) t0 = now;

@@ -91,7 +91,7 @@ def rows_per_chunk(K: int, even: bool = False) -> int:
 class DecodeEngine:
     def __init__(self, cfg: DecodeConfig, max_seq: int, device="cuda", num_sms: Optional[int] = None,
                  taps: bool = False, page_perm_seed: Optional[int] = None, max_steps: int = 4096,
-                 timeout_ns: int = 0, l2_prefetch_bytes: int = 384 * 1024):
+                 timeout_ns: int = 0, l2_prefetch_bytes: int = 0):
         assert cfg.head_dim == isa.HEAD_DIM, "the attention task is built for head_dim 128"
         assert cfg.group in (4, 8), "GQA group size must be 4 or 8"
         assert cfg.n_kv_heads & (cfg.n_kv_heads - 1) == 0, "n_kv_heads must be a power of two"
@@ -254,7 +254,7 @@ class DecodeEngine:
         plan = [[] for _ in range(S)]      # per SM: (emit(sm), weight segment or None)
 
         def add_gemv(sm, wseg, **kw):
-            plan[sm].append((lambda sm=sm, kw=kw: P.gemv(sm, stream=self.l2_prefetch_bytes > 0, **kw), wseg))
+            plan[sm].append((lambda sm=sm, kw=kw: P.gemv(sm, **kw), wseg))
 
         b_hid = None
         for l in range(L):
@@ -359,24 +359,41 @@ class DecodeEngine:
             sm, records=Src(self.argmax_rec.data_ptr(), len(lm_ranges) * 16, wait=b_logits), n=len(lm_ranges),
             state_addr=st, log_addr=self.token_log.data_ptr()), None))
 
-        # ---- emission; every SM first hands its weight-stream segment list to the L2 streamer
-        use_stream = self.l2_prefetch_bytes > 0
-        max_segs = max(sum(1 for _, w in plan[sm] if w is not None) for sm in range(S))
-        seg_tbl = np.zeros((S, max(max_segs, 1), 2), dtype=np.uint64)
+        # ---- emission.  Before every task the compute core is told to pull the next
+        # `l2_prefetch_bytes` of this SM's weight stream into L2 (beyond the part the
+        # memory core already holds in flight): it reaches that point exactly when it
+        # is about to wait for an activation from the other SMs, so HBM keeps streaming
+        # through the dependency bubble and the stalled stage later reads from L2.
+        in_flight = (isa.NUM_SLOTS - 4) * isa.SLOT_BYTES
         for sm in range(S):
-            k = 0
-            for _, w in plan[sm]:
-                if w is not None:
-                    seg_tbl[sm, k, 0] = w[0]
-                    seg_tbl[sm, k, 1] = w[1]          # low 32 bits: bytes, high 32 bits: pad
-                    k += 1
-        self.seg_table = torch.from_numpy(seg_tbl.view(np.int64)).to(self.dev)
-        for sm in range(S):
-            n_seg = sum(1 for _, w in plan[sm] if w is not None)
-            if use_stream and n_seg:
-                P.stream_list(sm, self.seg_table[sm].data_ptr(), n_seg, self.l2_prefetch_bytes)
-            for emit, _ in plan[sm]:
+            segs = [w for _, w in plan[sm] if w is not None]
+            seg_idx = 0          # segments before this index belong to tasks already emitted
+            pf_seg, pf_off = 0, 0
+            for emit, w in plan[sm]:
+                if self.l2_prefetch_bytes > 0:
+                    # frontier never behind the current task's start (+ what the memory core covers itself)
+                    if pf_seg < seg_idx:
+                        pf_seg, pf_off = seg_idx, 0
+                    ahead = sum(segs[j][1] for j in range(seg_idx, pf_seg)) + pf_off
+                    budget = in_flight + self.l2_prefetch_bytes - ahead
+                    while budget > 0 and pf_seg < len(segs):
+                        addr, nbytes = segs[pf_seg]
+                        n = min(budget, nbytes - pf_off)
+                        if n <= 0:
+                            break
+                        # the first `in_flight` bytes after the demand pointer are fetched by TMA anyway
+                        skip = max(0, in_flight - (ahead)) if pf_seg == seg_idx and pf_off == 0 else 0
+                        skip = min(skip, n)
+                        if n - skip >= 4096:
+                            P.l2_prefetch(sm, addr + pf_off + skip, n - skip)
+                        budget -= n
+                        ahead += n
+                        pf_off += n
+                        if pf_off >= nbytes:
+                            pf_seg, pf_off = pf_seg + 1, 0
                 emit()
+                if w is not None:
+                    seg_idx += 1
 
         st_ = P.stats()
         n_insts = max(st_["max_minsts"], st_["max_cinsts"]) + 2

@@ -199,6 +199,13 @@ class Program:
         op, size, _, arg, addr = self.m[sm][-1]
         self.m[sm][-1] = (op, size, window_bytes >> 10, arg, addr)
 
+    def l2_prefetch(self, sm, addr, nbytes):
+        """Compute-stream hint: when the compute core reaches this point all its
+        threads issue L2 prefetches for [addr, addr+nbytes) and continue."""
+        assert 0 <= addr < 1 << 48 and 0 < nbytes < 1 << 32
+        self.comp(sm, isa.OP_L2_PREFETCH, addr & 0xFFFF, (addr >> 16) & 0xFFFF, (addr >> 32) & 0xFFFF)
+        self.comp(sm, isa.OP_EXT, nbytes & 0xFFFF, nbytes >> 16, 0)
+
     def dyn_count(self, sm, word_addr, base, maximum):
         self.mem(sm, isa.OP_DYN_COUNT, size=maximum, address=word_addr, reg_range=None, nslot=0, bar=0)
         # base travels in the num_slots field
