@@ -189,7 +189,9 @@ def test_attention_split_merge_paged(cuda_device, G, n_kv, pos, qk_norm, pages_p
         kpool[table[p // 64], :, p % 64] = kc[p]
         vpool[table[p // 64], :, p % 64] = vc[p]
     kpool, vpool = kpool.to(dev), vpool.to(dev)
-    qkv = torch.cat((q, k_new, v_new)).to(dev)
+    # projection output stored per KV head group: [G query heads | key | value]
+    qkv = torch.cat([torch.cat((q.view(n_kv, G * D)[h], k_new.view(n_kv, D)[h], v_new.view(n_kv, D)[h]))
+                     for h in range(n_kv)]).to(dev)
     fr = torch.arange(max_pages * 64, dtype=torch.float32)[:, None] * O.rope_inv_freq(D, theta)[None]
     rope = torch.cat((fr.cos().to(BF16).float(), fr.sin().to(BF16).float()), 1).contiguous().to(dev)
     nw = torch.cat((qn, kn)).to(dev)
@@ -202,32 +204,30 @@ def test_attention_split_merge_paged(cuda_device, G, n_kv, pos, qk_norm, pages_p
     n_splits = (max_pages + pages_per_split - 1) // pages_per_split
     rec_floats = G * D + 16 * ((2 * G + 15) // 16)
     part = torch.zeros(n_kv, n_splits, rec_floats, dtype=torch.float32, device=dev)
+    cnt = torch.zeros(n_kv, dtype=torch.int32, device=dev)
     out = torch.zeros(n_q * D, dtype=BF16, device=dev)
 
     n_sms = 5
     P = Program(n_sms)
-    b_attn, b_out = P.new_barrier(), P.new_barrier()
+    b_out = P.new_barrier()
+    P.add_releases(b_out, n_kv)
     page_bytes = 64 * D * 2
     page_shift = int(math.log2(n_kv * page_bytes))
     sa = state.data_ptr()
+    grp = (G + 2) * D * 2
     units = [(h, s) for s in range(n_splits) for h in range(n_kv)]
     for i, (h, s) in enumerate(units):
         P.attn_decode(
             i % n_sms, G=G, state_addr=sa,
             rope=Src(rope.data_ptr(), 512, indirect=(sa + 4 * isa.ST_POS, 9, None)),
             norm_w=Src(nw.data_ptr(), 512) if qk_norm else None,
-            q=Src(qkv.data_ptr() + h * G * D * 2, G * D * 2),
-            k_new=Src(qkv.data_ptr() + (n_q + h) * D * 2, 256), v_new=Src(qkv.data_ptr() + (n_q + n_kv + h) * D * 2, 256),
-            k_row=Dst(kpool.data_ptr() + h * page_bytes, 256, indirect=(sa + 4 * isa.ST_NEWROW, 8, None)),
-            v_row=Dst(vpool.data_ptr() + h * page_bytes, 256, indirect=(sa + 4 * isa.ST_NEWROW, 8, None)),
+            qkv=Src(qkv.data_ptr() + h * grp, grp),
             k_page_addr=kpool.data_ptr() + h * page_bytes, v_page_addr=vpool.data_ptr() + h * page_bytes,
             page_shift=page_shift, base_page=s * pages_per_split, max_pages=pages_per_split,
-            out=Dst(part[h, s].data_ptr(), rec_floats * 4, release=b_attn), qk_eps=eps)
-    for h in range(n_kv):
-        P.attn_merge(h % n_sms, G=G, n_splits=n_splits,
-                     records=[Src(part[h].data_ptr(), n_splits * rec_floats * 4, wait=b_attn)], n_first=n_splits,
-                     out=Dst(out.data_ptr() + h * G * D * 2, G * D * 2, release=b_out))
+            records_addr=part[h].data_ptr(), counter_addr=cnt[h].data_ptr(),
+            out_addr=out.data_ptr() + h * G * D * 2, split=s, n_splits=n_splits, release=b_out, qk_eps=eps)
     run_program(P, dev)
+    assert int(cnt.abs().sum()) == 0, "the last arrival resets the head's counter"
     assert O.rel_l2(out.cpu(), ref) < 6e-3
     # the new K (normed + rotated) and V rows landed in the right page, nothing else changed
     page, row = int(table[pos // 64]), pos % 64

@@ -81,7 +81,6 @@
   X(OP_GEMV_ROWS_BF16, 0x7200)                                                         \
   X(OP_ATTN_DECODE_PAGED_G4, 0x7210)                                                   \
   X(OP_ATTN_DECODE_PAGED_G8, 0x7211)                                                   \
-  X(OP_ATTN_MERGE, 0x7212)                                                             \
   X(OP_ARGMAX_FINAL, 0x7220)                                                          \
   X(OP_L2_PREFETCH, 0x7230)                                                          \
   X(OP_EXT, 0x7FFF)
@@ -90,8 +89,13 @@
 // first); second word args[0..1] = byte count (low, high).  All compute threads
 // issue L2 prefetches for the range and move on; nothing is popped.
 //
-// OP_EXT is never dispatched: it marks the second 8-byte word of a two-word
-// compute instruction (GEMV_ROWS, ATTN_DECODE_PAGED).
+// OP_EXT is never dispatched: it marks the continuation words of a multi-word
+// compute instruction (GEMV_ROWS: 2 words, L2_PREFETCH: 2, ATTN_DECODE_PAGED: 9).
+//
+// ATTN_DECODE_PAGED words: [max_pages, base_page, flags] [qk-norm eps hi, lo, n_splits]
+// then six 48-bit addresses, low piece first: state block, this head's rows in K page 0,
+// same for V, the head's split records, its arrival counter, its slice of the output;
+// last word: [split index, barrier released by the merged output, 0].
 //
 // GEMV_ROWS args[1] layout: bits 0..4 rows per chunk (1,2,4,8,16), bits 8..10
 // epilogue mode, bit 11 accumulate into the output (residual add), bit 12 fused

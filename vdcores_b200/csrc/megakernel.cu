@@ -101,11 +101,30 @@ __device__ void compute_core(const Ctx& c, const VdcCInst* __restrict__ insts, i
         break;
       }
       case 0x7210:
-      case 0x7211: {
-        if (tid == 0) q.sh->misc[33] = __uint_as_float(((uint32_t)ex.args[0] << 16) | ex.args[1]);  // qk-norm eps
-        compute_sync();
-        if (ci.opcode == 0x7210) task_attn_decode<4>(q, ci.args[0], ci.args[1], ci.args[2]);
-        else task_attn_decode<8>(q, ci.args[0], ci.args[1], ci.args[2]);
+      case 0x7211: {  // ATTN_DECODE_PAGED (nine words; the first two are in registers already)
+        auto addr48 = [](const VdcCInst& w) {
+          return (uint64_t)w.args[0] | ((uint64_t)w.args[1] << 16) | ((uint64_t)w.args[2] << 32);
+        };
+        VdcCInst e[7];
+#pragma unroll
+        for (int k = 0; k < 7; ++k) *reinterpret_cast<uint2*>(&e[k]) = ld_word(q.pc + (uint32_t)k);
+        q.pc += 7;
+        AttnArgs a;
+        a.max_pages = ci.args[0];
+        a.base_page = ci.args[1];
+        a.flags = ci.args[2];
+        a.qk_eps = __uint_as_float(((uint32_t)ex.args[0] << 16) | ex.args[1]);
+        a.n_splits = ex.args[2];
+        a.state = reinterpret_cast<const int*>(addr48(e[0]));
+        a.k_rows = reinterpret_cast<uint8_t*>(addr48(e[1]));
+        a.v_rows = reinterpret_cast<uint8_t*>(addr48(e[2]));
+        a.records = reinterpret_cast<float*>(addr48(e[3]));
+        a.counter = reinterpret_cast<int*>(addr48(e[4]));
+        a.out = reinterpret_cast<__nv_bfloat16*>(addr48(e[5]));
+        a.split = e[6].args[0];
+        a.bar = e[6].args[1];
+        if (ci.opcode == 0x7210) task_attn_decode<4>(q, a);
+        else task_attn_decode<8>(q, a);
         break;
       }
       case 0x7230: {  // L2_PREFETCH: every thread touches its share of the range, nobody waits
@@ -115,7 +134,6 @@ __device__ void compute_core(const Ctx& c, const VdcCInst* __restrict__ insts, i
           asm volatile("prefetch.global.L2 [%0];" ::"l"(base + off));
         break;
       }
-      case 0x7212: task_attn_merge(q, ci.args[0], ci.args[1], ci.args[2]); break;
       case 0x7220: task_argmax_final(q, ci.args[0]); break;
       default:
         raise_abort(c, VDC_ERR_BAD_OPCODE, 0, (int)q.pc, ci.opcode, -1, 0);

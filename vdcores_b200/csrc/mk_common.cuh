@@ -159,12 +159,13 @@ struct __align__(16) Shared {
   volatile int pop_val[2];
   volatile uint32_t pop_meta[2];
   volatile uint64_t pop_addr[2];
-  float red[4096 + 64];                     // task scratch (reductions)
-  float scores[VDC_KV_PAGE * 8];
-  float probs[VDC_KV_PAGE * 8];
-  float wmax[kCW * 8];
-  float qrot[8 * VDC_HEAD_DIM];
-  float misc[64];
+  alignas(16) float red[4096 + 64];                     // task scratch (reductions)
+  alignas(16) float scores[VDC_KV_PAGE * 8];
+  alignas(16) float probs[VDC_KV_PAGE * 8];
+  alignas(16) float wmax[kCW * 8];
+  alignas(16) float qrot[8 * VDC_HEAD_DIM];
+  alignas(16) float misc[64];
+  uint4 newrows[32];                        // attention: rotated new key row, new value row (bf16)
 };
 
 struct Ctx {

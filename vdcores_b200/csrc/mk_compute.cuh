@@ -300,60 +300,75 @@ __device__ void task_gemv_rows(Compute& q, int n_chunks, int mode, bool accumula
 }
 
 // ------------------------------------------------------------------------- //
-// task: split-K GQA decode attention over 64-position KV pages
+// task: split-K GQA decode attention over 64-position KV pages, merge included
 // ------------------------------------------------------------------------- //
-// Pop order: state (raw address), rope row (cos[64] sin[64] fp32), [q/k norm
-// weights 2x128 bf16], q (G x 128 bf16, raw projection output), k_new, v_new
-// (128 bf16 each, raw projection output of the token being decoded), k_row_out,
-// v_row_out (write-back slots for the new cache rows), `count` x (K page, V page),
-// out (write-back: G x 128 fp32 unnormalised O, then m[G], l[G]).
-// count = clamp(n_pages - base, 0, max_pages) is read from the state block; the
-// memory stream uses the same rule (DYN_COUNT + REPEAT).
+// One task handles one KV head and one split (a range of pages) of the cache.
+// Pop order: rope row (cos[64] sin[64] fp32, gathered by position), [q/k norm
+// weights 2x128 bf16], the head group's projection output (G query heads, the
+// new key row, the new value row: (G+2) x 128 bf16, raw, contiguous), then
+// `count` x (K page, V page) with count = clamp(n_pages - base, 0, max_pages)
+// read from the state block (the memory stream applies the same rule through
+// DYN_COUNT + REPEAT).  Everything else travels in the instruction words:
+// addresses of the state block, of this head's K / V pages (for the new cache
+// rows), of the head's split records, of its arrival counter and of its slice
+// of the attention output, plus the barrier the merged output releases.
+//
+// Each task leaves {G x 128 fp32 unnormalised O, m[G], l[G]} in its record and
+// bumps the head's counter; the task that arrives last merges all records
+// (O = sum_s 2^(m_s-m) O_s / sum_s 2^(m_s-m) l_s), writes the bf16 output,
+// resets the counter and counts the barrier down.
 #ifdef VDC_TRACE_ATTN
 #define ATTN_STAMP(i) if (q.tid == 0) c.profile[c.sm * VDC_NUM_PROFILE_EVENTS + 100 + (i)] = globaltimer_ns()
 #else
 #define ATTN_STAMP(i)
 #endif
 
+struct AttnArgs {
+  int max_pages, base_page, flags;
+  float qk_eps;
+  int n_splits, split, bar;
+  const int* state;
+  uint8_t* k_rows;   // this head's rows inside K page 0 of the layer (new row = + NEWROW * 256)
+  uint8_t* v_rows;
+  float* records;    // [n_splits][rec_floats] of this head
+  int* counter;
+  __nv_bfloat16* out;  // G*128 outputs of this head
+};
+
 template <int G>
-__device__ void task_attn_decode(Compute& q, int max_pages, int base_page, int flags) {
+__device__ void task_attn_decode(Compute& q, const AttnArgs& a) {
   constexpr int D = VDC_HEAD_DIM;
   constexpr int LPP = (G == 4) ? 8 : 16;  // lanes per position in the QK phase
   constexpr int DPL = D / LPP;            // dims per lane: 16 or 8
   constexpr int PPW = 32 / LPP;           // positions per warp per round
   constexpr int ROUNDS = VDC_KV_PAGE / (PPW * kCW);
+  constexpr int REC = G * D + 16 * ((2 * G + 15) / 16);
   Shared* sh = q.sh;
   const Ctx& c = q.c;
-  const bool qk_norm = flags & VDC_ATTN_QKNORM_BIT;
+  const bool qk_norm = a.flags & VDC_ATTN_QKNORM_BIT;
 
   ATTN_STAMP(0);
-  q.pop();  // decode state block: raw address
-  const int* state = reinterpret_cast<const int*>(q.addr());
   const int rope_mask = q.pop();
   int nw_mask = 0;
   if (qk_norm) nw_mask = q.pop();
-  const int q_mask = q.pop();
-  const int kn_mask = q.pop();
-  const int vn_mask = q.pop();
-  const int kro_mask = q.pop();
-  const int vro_mask = q.pop();
+  const int qkv_mask = q.pop();
   if (q.aborted) return;
   ATTN_STAMP(1);
 
-  const int pos = ld_relaxed_gpu(state + VDC_ST_POS);
-  const int n_pages = ld_relaxed_gpu(state + VDC_ST_NPAGES);
-  int count = n_pages - base_page;
-  count = count < 0 ? 0 : (count > max_pages ? max_pages : count);
-  const bool owner = count > 0 && base_page + count == n_pages;
+  const int pos = ld_relaxed_gpu(a.state + VDC_ST_POS);
+  const int n_pages = ld_relaxed_gpu(a.state + VDC_ST_NPAGES);
+  int count = n_pages - a.base_page;
+  count = count < 0 ? 0 : (count > a.max_pages ? a.max_pages : count);
+  const bool owner = count > 0 && a.base_page + count == n_pages;
   const int tail_valid = (pos % VDC_KV_PAGE) + 1;  // valid rows of the last page, new row included
 
   const float* rope = (const float*)slot_ptr(c, first_slot(rope_mask));
   const __nv_bfloat16* nw = qk_norm ? (const __nv_bfloat16*)slot_ptr(c, first_slot(nw_mask)) : nullptr;
-  const __nv_bfloat16* qraw = (const __nv_bfloat16*)slot_ptr(c, first_slot(q_mask));
-  const __nv_bfloat16* knew = (const __nv_bfloat16*)slot_ptr(c, first_slot(kn_mask));
-  __nv_bfloat16* krow = (__nv_bfloat16*)slot_ptr(c, first_slot(kro_mask));
-  __nv_bfloat16* vrow = (__nv_bfloat16*)slot_ptr(c, first_slot(vro_mask));
-  const float eps = sh->misc[33];
+  const __nv_bfloat16* qraw = (const __nv_bfloat16*)slot_ptr(c, first_slot(qkv_mask));
+  const __nv_bfloat16* knew = qraw + G * D;
+  const __nv_bfloat16* vnew = knew + D;
+  __nv_bfloat16* krow = reinterpret_cast<__nv_bfloat16*>(sh->newrows);  // rotated new key row
+  __nv_bfloat16* vrow = krow + D;
 
   // --- prologue: optional per-head RMSNorm, then half-rotation RoPE.  One warp
   // per head: heads 0..G-1 are the queries, "head" G is the new key row.
@@ -365,7 +380,7 @@ __device__ void task_attn_decode(Compute& q, int max_pages, int base_page, int f
     float b0 = __bfloat162float(src[i0 + 64]), b1 = __bfloat162float(src[i0 + 65]);
     if (qk_norm) {
       float ss = warp_sum(a0 * a0 + a1 * a1 + b0 * b0 + b1 * b1);
-      const float rstd = rsqrtf(ss / (float)D + eps);
+      const float rstd = rsqrtf(ss / (float)D + a.qk_eps);
       const __nv_bfloat16* w = nw + (is_k ? D : 0);
       a0 = bf16_round(__bfloat162float(w[i0]) * bf16_round(a0 * rstd));
       a1 = bf16_round(__bfloat162float(w[i0 + 1]) * bf16_round(a1 * rstd));
@@ -392,12 +407,9 @@ __device__ void task_attn_decode(Compute& q, int max_pages, int base_page, int f
       dst[i0 + 65] = r65;
     }
   }
-  if (q.tid < D / 8) {  // v_new row copied as is (16 threads x 16 bytes)
-    reinterpret_cast<uint4*>(vrow)[q.tid] = reinterpret_cast<const uint4*>(slot_ptr(c, first_slot(vn_mask)))[q.tid];
-  }
-  fence_proxy_async_smem();
+  if (q.tid < D / 8) reinterpret_cast<uint4*>(vrow)[q.tid] = reinterpret_cast<const uint4*>(vnew)[q.tid];
   compute_sync();
-  q.free_slots(rope_mask | nw_mask | q_mask | kn_mask | vn_mask);
+  q.free_slots(rope_mask | nw_mask | qkv_mask);
   ATTN_STAMP(2);
 
   // per-lane slice of the rotated queries
@@ -406,9 +418,12 @@ __device__ void task_attn_decode(Compute& q, int max_pages, int base_page, int f
 #pragma unroll
   for (int g = 0; g < G; ++g)
 #pragma unroll
-    for (int h = 0; h < DPL / 8; ++h)
-#pragma unroll
-      for (int j = 0; j < 8; ++j) qreg[g][h * 8 + j] = sh->qrot[g * D + (sub + h * 8) * 8 + j];
+    for (int h = 0; h < DPL / 8; ++h) {
+      const float4 lo = *reinterpret_cast<const float4*>(sh->qrot + g * D + (sub + h * 8) * 8);
+      const float4 hi = *reinterpret_cast<const float4*>(sh->qrot + g * D + (sub + h * 8) * 8 + 4);
+      qreg[g][h * 8 + 0] = lo.x; qreg[g][h * 8 + 1] = lo.y; qreg[g][h * 8 + 2] = lo.z; qreg[g][h * 8 + 3] = lo.w;
+      qreg[g][h * 8 + 4] = hi.x; qreg[g][h * 8 + 5] = hi.y; qreg[g][h * 8 + 6] = hi.z; qreg[g][h * 8 + 7] = hi.w;
+    }
   const float scale_log2 = 1.4426950408889634f * rsqrtf((float)D);
 
   float m_run[G], l_run[G], acc[G][2];
@@ -419,7 +434,6 @@ __device__ void task_attn_decode(Compute& q, int max_pages, int base_page, int f
     acc[g][0] = acc[g][1] = 0.f;
   }
   const int pg = q.tid >> 6, dp = q.tid & 63;  // PV phase: position group, dim pair
-
   int v_prev = 0;
   for (int blk = 0; blk < count; ++blk) {
     const int k_mask = q.pop();  // its sync also ends the previous block's PV phase
@@ -525,12 +539,10 @@ __device__ void task_attn_decode(Compute& q, int max_pages, int base_page, int f
     ATTN_STAMP(6 + 4 * (blk & 1));
   }
 
-  const int out_mask = q.pop();  // sync: everyone is done with the last V page
-  if (q.aborted) return;
-  ATTN_STAMP(11);
+  compute_sync();  // everyone is done with the last V page
   q.free_slots(v_prev);
-  float* out = (float*)slot_ptr(c, first_slot(out_mask));
-  // cross position-group reduction: groups 1..3 publish, group 0 adds
+  ATTN_STAMP(11);
+  // cross position-group reduction: groups 1..3 publish, group 0 adds and writes the record
   float* red = sh->red;  // [3][G][128] then l: [3][G]
   if (pg > 0) {
 #pragma unroll
@@ -541,6 +553,7 @@ __device__ void task_attn_decode(Compute& q, int max_pages, int base_page, int f
     }
   }
   compute_sync();
+  float* rec = a.records + (size_t)a.split * REC;
   if (pg == 0) {
 #pragma unroll
     for (int g = 0; g < G; ++g) {
@@ -551,64 +564,54 @@ __device__ void task_attn_decode(Compute& q, int max_pages, int base_page, int f
         o1 += red[(r * G + g) * D + dp * 2 + 1];
         l += red[3 * G * D + r * G + g];
       }
-      out[g * D + dp * 2] = o0;
-      out[g * D + dp * 2 + 1] = o1;
+      *reinterpret_cast<float2*>(rec + g * D + dp * 2) = make_float2(o0, o1);
       if (dp == 0) {
-        out[G * D + g] = m_run[g];
-        out[G * D + G + g] = l;
+        rec[G * D + g] = m_run[g];
+        rec[G * D + G + g] = l;
       }
     }
   }
-  fence_proxy_async_smem();
+  if (owner && q.tid >= 64 && q.tid < 64 + 2 * (D / 8)) {
+    // the new cache rows go to HBM; the next step's page loads (a later launch) see them
+    const int t = q.tid - 64;
+    const size_t off = (size_t)ld_relaxed_gpu(a.state + VDC_ST_NEWROW) * (D * 2);
+    uint8_t* dst = (t < D / 8 ? a.k_rows : a.v_rows) + off;
+    reinterpret_cast<uint4*>(dst)[t % (D / 8)] = reinterpret_cast<const uint4*>(sh->newrows)[t];
+  }
+  // arrival: the record is complete once every writer passed the barrier; thread 0's
+  // gpu-scope fence before the counter bump makes it visible to whoever arrives last
+  compute_sync();
+  if (q.tid == 0) {
+    __threadfence();
+    const int old = atomicAdd(a.counter, 1);
+    __threadfence();
+    sh->misc[34] = (old == a.n_splits - 1) ? 1.f : 0.f;
+  }
   compute_sync();
   ATTN_STAMP(12);
-  q.push_store(out_mask);
-  if (owner) {
-    q.push_store(kro_mask);
-    q.push_store(vro_mask);
-  } else {
-    q.free_slots(kro_mask | vro_mask);
-  }
-}
+  if (sh->misc[34] == 0.f) return;
 
-// ------------------------------------------------------------------------- //
-// task: merge the split partials of one KV head:  O = sum_s 2^(m_s-m) O_s / sum_s 2^(m_s-m) l_s
-// ------------------------------------------------------------------------- //
-// Pop order: records part 1 (n1 records), [records part 2], out (G*128 bf16).
-// Record = G*128 fp32 O, G fp32 m, G fp32 l, padded to a multiple of 64 bytes.
-__device__ void task_attn_merge(Compute& q, int n_splits, int G, int n1) {
-  constexpr int D = VDC_HEAD_DIM;
-  const Ctx& c = q.c;
-  const int rec_floats = G * D + 16 * ((2 * G + 15) / 16);
-  const int m1 = q.pop();
-  int m2 = 0;
-  if (n_splits > n1) m2 = q.pop();
-  const int out_mask = q.pop();
-  if (q.aborted) return;
-  const float* r1 = (const float*)slot_ptr(c, first_slot(m1));
-  const float* r2 = m2 ? (const float*)slot_ptr(c, first_slot(m2)) : nullptr;
-  __nv_bfloat16* out = (__nv_bfloat16*)slot_ptr(c, first_slot(out_mask));
+  // ---- last arrival for this head: merge the split records (read past L1: other SMs wrote them)
   for (int o = q.tid; o < G * D; o += kCT) {
     const int g = o / D;
     float m = -INFINITY;
-    for (int s = 0; s < n_splits; ++s) {
-      const float* r = s < n1 ? r1 + s * rec_floats : r2 + (s - n1) * rec_floats;
-      m = fmaxf(m, r[G * D + g]);
-    }
+    for (int sidx = 0; sidx < a.n_splits; ++sidx) m = fmaxf(m, __ldcg(a.records + (size_t)sidx * REC + G * D + g));
     float num = 0.f, den = 0.f;
-    for (int s = 0; s < n_splits; ++s) {
-      const float* r = s < n1 ? r1 + s * rec_floats : r2 + (s - n1) * rec_floats;
-      const float ms = r[G * D + g];
+    for (int sidx = 0; sidx < a.n_splits; ++sidx) {
+      const float* r = a.records + (size_t)sidx * REC;
+      const float ms = __ldcg(r + G * D + g);
       const float w = (ms == -INFINITY) ? 0.f : exp2f(ms - m);
-      num = fmaf(w, r[o], num);
-      den = fmaf(w, r[G * D + G + g], den);
+      num = fmaf(w, __ldcg(r + o), num);
+      den = fmaf(w, __ldcg(r + G * D + G + g), den);
     }
-    out[o] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+    a.out[o] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
   }
-  fence_proxy_async_smem();
   compute_sync();
-  q.push_store(out_mask);
-  q.free_slots(m1 | m2);
+  if (q.tid == 0) {
+    *a.counter = 0;  // ready for the next layer / step; ordered before its use by the barrier chain
+    __threadfence();
+    red_release_gpu_add(c.bars + a.bar, -1);
+  }
 }
 
 // ------------------------------------------------------------------------- //

@@ -120,11 +120,22 @@ class DecodeEngine:
         G = cfg.group
         self.rec_floats = G * isa.HEAD_DIM + 16 * ((2 * G + 15) // 16)
         max_rec_per_load = 32768 // (self.rec_floats * 4)
-        self.n_splits = max(1, min(self.num_sms // cfg.n_kv_heads, self.max_pages, 2 * max_rec_per_load))
+        self.n_splits = max(1, min(self.num_sms // cfg.n_kv_heads, self.max_pages))
         self.pages_per_split = (self.max_pages + self.n_splits - 1) // self.n_splits
         self.n_splits = (self.max_pages + self.pages_per_split - 1) // self.pages_per_split
         self.max_rec_per_load = max_rec_per_load
         self.attn_part = z(cfg.n_kv_heads, self.n_splits, self.rec_floats, dt=torch.float32)
+        self.attn_cnt = z(L, cfg.n_kv_heads, dt=torch.int32)     # arrival counters, zero between steps
+        # projection rows are stored per KV head group: [G query heads | key | value] x 128
+        D_ = isa.HEAD_DIM
+        perm = []
+        for h in range(cfg.n_kv_heads):
+            perm += list(range(h * G * D_, (h + 1) * G * D_))
+            perm += list(range(cfg.q_width + h * D_, cfg.q_width + (h + 1) * D_))
+            perm += list(range(cfg.q_width + cfg.kv_width + h * D_, cfg.q_width + cfg.kv_width + (h + 1) * D_))
+        self.qkv_perm = torch.tensor(perm, dtype=torch.long)            # packed row -> standard row
+        self.qkv_inv = torch.empty_like(self.qkv_perm)
+        self.qkv_inv[self.qkv_perm] = torch.arange(len(perm))           # standard row -> packed row
         self.argmax_rec = z(self.num_sms, 4, dt=torch.float32)
         self.state = z(isa.ST_PAGETABLE + self.max_pages, dt=torch.int32)
         self.state_host = torch.zeros(isa.ST_PAGETABLE + self.max_pages, dtype=torch.int32).pin_memory()
@@ -159,7 +170,8 @@ class DecodeEngine:
         self.norm_w = to(w.norm)
         self.ln1 = torch.stack([to(t) for t in w.ln1])
         self.ln2 = torch.stack([to(t) for t in w.ln2])
-        self.wqkv = torch.stack([torch.cat((to(w.wq[l]), to(w.wk[l]), to(w.wv[l])), dim=0) for l in range(L)])
+        pm = self.qkv_perm.to(dev)
+        self.wqkv = torch.stack([torch.cat((to(w.wq[l]), to(w.wk[l]), to(w.wv[l])), dim=0)[pm] for l in range(L)])
         self.wo = torch.stack([to(w.wo[l]) for l in range(L)])
         # gate and up rows interleaved: row 2j = gate_j, row 2j+1 = up_j
         self.wgu = torch.stack([torch.stack((to(w.gate[l]), to(w.up[l])), dim=1).reshape(2 * cfg.ffn, cfg.hidden)
@@ -276,38 +288,25 @@ class DecodeEngine:
                 plan[sm].append((lambda sm=sm, b=b_qkv, bw=b_hid, t=self.taps[l - 1].data_ptr():
                                  P.copy(sm, Src(hid, H * 2, wait=bw), Dst(t, H * 2, release=b), H * 2), None))
 
-            # ---- split-K GQA decode attention over the paged cache
-            b_attn = P.new_barrier()
+            # ---- split-K GQA decode attention over the paged cache; the unit that finishes a
+            # head last merges its split records and releases the barrier
+            b_merge = P.new_barrier()
+            P.add_releases(b_merge, cfg.n_kv_heads)
             units = [(h, s) for s in range(self.n_splits) for h in range(cfg.n_kv_heads)]
             kp, vp = self.kpool[l].data_ptr(), self.vpool[l].data_ptr()
+            grp = (G + 2) * D * 2
             for (h, s), sm in zip(units, self._pick(load, len(units), 2 * page_bytes * self.pages_per_split)):
                 kw = dict(
                     G=G, state_addr=st,
                     rope=Src(self.rope.data_ptr(), D * 4, indirect=(st + 4 * isa.ST_POS, 9, None)),
                     norm_w=Src(self.qknorm[l].data_ptr(), 2 * D * 2) if cfg.qk_norm else None,
-                    q=Src(qkv + h * G * D * 2, G * D * 2, wait=b_qkv),
-                    k_new=Src(qkv + (cfg.q_width + h * D) * 2, D * 2),
-                    v_new=Src(qkv + (cfg.q_width + cfg.kv_width + h * D) * 2, D * 2),
-                    k_row=Dst(kp + h * page_bytes, D * 2, indirect=(st + 4 * isa.ST_NEWROW, 8, None)),
-                    v_row=Dst(vp + h * page_bytes, D * 2, indirect=(st + 4 * isa.ST_NEWROW, 8, None)),
+                    qkv=Src(qkv + h * grp, grp, wait=b_qkv),
                     k_page_addr=kp + h * page_bytes, v_page_addr=vp + h * page_bytes, page_shift=page_shift,
                     base_page=s * self.pages_per_split, max_pages=self.pages_per_split,
-                    out=Dst(self.attn_part[h, s].data_ptr(), self.rec_floats * 4, release=b_attn),
+                    records_addr=self.attn_part[h].data_ptr(), counter_addr=self.attn_cnt[l, h].data_ptr(),
+                    out_addr=ao + h * G * D * 2, split=s, n_splits=self.n_splits, release=b_merge,
                     qk_eps=cfg.qk_norm_eps)
                 plan[sm].append((lambda sm=sm, kw=kw: P.attn_decode(sm, **kw), None))
-
-            # ---- merge of the split partials, one task per KV head
-            b_merge = P.new_barrier()
-            n1 = min(self.n_splits, self.max_rec_per_load)
-            for h, sm in zip(range(cfg.n_kv_heads), self._pick(load, cfg.n_kv_heads, self.n_splits * self.rec_floats * 4)):
-                base = self.attn_part[h].data_ptr()
-                recs = [Src(base, n1 * self.rec_floats * 4, wait=b_attn)]
-                if self.n_splits > n1:
-                    recs.append(Src(base + n1 * self.rec_floats * 4, (self.n_splits - n1) * self.rec_floats * 4,
-                                    wait=b_attn))
-                kw = dict(G=G, n_splits=self.n_splits, records=recs, n_first=n1,
-                          out=Dst(ao + h * G * D * 2, G * D * 2, release=b_merge))
-                plan[sm].append((lambda sm=sm, kw=kw: P.attn_merge(sm, **kw), None))
 
             # ---- output projection, residual add into hidden
             b_o = P.new_barrier()
@@ -422,6 +421,7 @@ class DecodeEngine:
         s[isa.ST_MAXPAGES] = self.max_pages
         s[isa.ST_PAGETABLE:] = self.page_table
         self.state.copy_(s, non_blocking=True)
+        self.attn_cnt.zero_()
         self.pos = pos
         self.steps_done = 0
 
@@ -471,7 +471,7 @@ class DecodeEngine:
         ks, vs = [], []
         for l in range(cfg.n_layers):
             x = norm(h, self.ln1[l], cfg.eps)
-            qkv = x @ self.wqkv[l].t()
+            qkv = (x @ self.wqkv[l].t())[:, self.qkv_inv.to(dev)]
             q = qkv[:, :cfg.q_width].view(T, cfg.n_heads, D)
             k = qkv[:, cfg.q_width:cfg.q_width + cfg.kv_width].view(T, cfg.n_kv_heads, D)
             v = qkv[:, cfg.q_width + cfg.kv_width:].view(T, cfg.n_kv_heads, D)

@@ -253,19 +253,26 @@ class Program:
         self.comp(sm, isa.OP_GEMV_ROWS_BF16, n_chunks, a1, a2)
         self.comp(sm, isa.OP_EXT, e >> 16, e & 0xFFFF, rb8 & 0xFFFF)
 
-    def attn_decode(self, sm, *, G, state_addr, rope: Src, norm_w: Optional[Src], q: Src, k_new: Src, v_new: Src,
-                    k_row: Dst, v_row: Dst, k_page_addr, v_page_addr, page_shift, base_page, max_pages,
-                    out: Dst, qk_eps: float = 1e-6, state_slot=24):
+    def add_releases(self, bar: int, n: int):
+        """Declares n count-downs of `bar` that tasks perform themselves (not
+        through a store instruction), so that its initial value includes them."""
+        self.bar_counts[bar] += n
+
+    def attn_decode(self, sm, *, G, state_addr, rope: Src, norm_w: Optional[Src], qkv: Src, k_page_addr, v_page_addr,
+                    page_shift, base_page, max_pages, records_addr, counter_addr, out_addr, split, n_splits,
+                    release, qk_eps: float = 1e-6):
+        """One (KV head, split) unit of the decode attention.  k_page_addr /
+        v_page_addr: this head's rows inside page 0 of the layer's K / V pool;
+        the page table in the state block selects the page.  The unit that
+        completes the head last merges the n_splits records at records_addr,
+        writes G*128 bf16 to out_addr and counts `release` down once (declare it
+        with add_releases(release, 1) per head)."""
         page_bytes = isa.KV_PAGE * isa.HEAD_DIM * 2
-        self.raw_address(sm, state_addr, state_slot)
+        assert qkv.nbytes == (G + 2) * isa.HEAD_DIM * 2
         self.load(sm, rope, default_port=1)
         if norm_w is not None:
             self.load(sm, norm_w, default_port=1)
-        self.load(sm, q)
-        self.load(sm, k_new, default_port=1)
-        self.load(sm, v_new, default_port=1)
-        self.store(sm, k_row)
-        self.store(sm, v_row)
+        self.load(sm, qkv, default_port=1)
         tbl = state_addr + 4 * (isa.ST_PAGETABLE + base_page)
         self.dyn_count(sm, state_addr + 4 * isa.ST_NPAGES, base_page, max_pages)
         self.repeat(sm, 0, [4, 0, 4, 0], dynamic=True)
@@ -275,18 +282,14 @@ class Program:
         self.mem(sm, isa.OP_ALLOC_TMA_LOAD_1D, size=page_bytes, nslot=slots_for(page_bytes), address=v_page_addr,
                  flags=isa.F_JUMP)
         self.bytes_loaded[sm] += 2 * page_bytes * max_pages
-        self.store(sm, out)
         e = f32_bits(qk_eps)
         op = isa.OP_ATTN_DECODE_PAGED_G4 if G == 4 else isa.OP_ATTN_DECODE_PAGED_G8
         self.comp(sm, op, max_pages, base_page, isa.ATTN_QKNORM_BIT if norm_w is not None else 0)
-        self.comp(sm, isa.OP_EXT, e >> 16, e & 0xFFFF, 0)
-
-    def attn_merge(self, sm, *, G, n_splits, records: List[Src], n_first: int, out: Dst):
-        assert 1 <= len(records) <= 2
-        for r in records:
-            self.load(sm, r)
-        self.store(sm, out)
-        self.comp(sm, isa.OP_ATTN_MERGE, n_splits, G, n_first)
+        self.comp(sm, isa.OP_EXT, e >> 16, e & 0xFFFF, n_splits)
+        for addr in (state_addr, k_page_addr, v_page_addr, records_addr, counter_addr, out_addr):
+            assert 0 <= addr < 1 << 48
+            self.comp(sm, isa.OP_EXT, addr & 0xFFFF, (addr >> 16) & 0xFFFF, (addr >> 32) & 0xFFFF)
+        self.comp(sm, isa.OP_EXT, split, release, 0)
 
     def argmax_final(self, sm, *, records: Src, n: int, state_addr, log_addr, release=None):
         self.load(sm, records)
