@@ -103,6 +103,29 @@ int64_t vdc_config(const char* name);
  * time).  Replaces: compute_family_specs (src/torch_runtime.cu:266-277). */
 const char* vdc_family_specs(void);
 
+/* Launch for hosts that must not allocate device memory.  Some embedders hand
+ * every free byte of the GPU to their own pool at start-up (a serving engine
+ * that sizes its KV cache to whatever is left), or run under a memory budget
+ * that an outside allocator enforces; for them a cudaMalloc inside a library
+ * call fails or eats into that pool, so vdc_init (which allocates the status
+ * block) and scratch tensors are not an option.  This entry point runs the same
+ * megakernel as vdc_launch, synchronously on `stream`, with its scratch — status
+ * block, the VDC_MAX_BARS countdown barriers and the per-SM profile rows — in a
+ * 164 KB device array that is part of the library image.  It calls no
+ * cudaMalloc / cudaFree and no allocating library routine, and needs no vdc_init.
+ *   bars_init : device, int32[VDC_MAX_BARS], initial barrier counts (input, not modified)
+ *   other arguments as for vdc_launch; outputs are whatever the program's stores write.
+ * Limits: num_sms <= 160 (more is rejected with VDC_ERR_ARG).  The first call
+ * on a device does the one-time set-up (shared-memory attribute, address of the
+ * array): make that call before any stream capture.  All calls on a device share
+ * the one array: it keeps the last call's contents (status and barriers are
+ * re-initialised at the start of every call), and two calls that overlap on the
+ * GPU would race on it, so keep them on one stream or serialise them.
+ * No counterpart in the reference. */
+int vdc_launch_static(int num_sms, int insts_per_sm, const void* compute_insts, const void* memory_insts,
+                      const void* tma_descs, const int* bars_init, uint64_t stream, uint64_t timeout_ns,
+                      vdc_status* status);
+
 /* Text of the last CUDA error seen by this library on the calling thread. */
 const char* vdc_last_error(void);
 

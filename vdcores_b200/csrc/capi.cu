@@ -265,4 +265,80 @@ int64_t vdc_config(const char* name) {
 
 const char* vdc_family_specs(void) { return ""; }
 
+// ------------------------------------------------------------------------- //
+// launch without any allocation
+// ------------------------------------------------------------------------- //
+// Scratch of vdc_launch_static: status block, countdown barriers and per-SM
+// profile rows live in this file-scope device array, so the call needs neither
+// vdc_init's cudaMalloc nor caller-provided scratch.  Every GPU that loads the
+// library holds these 164 KB until the process exits.
+#define VDC_STATIC_MAX_SMS 160
+#define VDC_STATIC_STATUS_OFF 0
+#define VDC_STATIC_BARS_OFF 256
+#define VDC_STATIC_PROFILE_OFF (256 + 4 * VDC_MAX_BARS)
+#define VDC_STATIC_BYTES (VDC_STATIC_PROFILE_OFF + 8 * VDC_NUM_PROFILE_EVENTS * VDC_STATIC_MAX_SMS)
+static __device__ __align__(256) unsigned char g_static_scratch[VDC_STATIC_BYTES];
+
+namespace {
+unsigned char* g_static_ptr[kMaxDevices] = {nullptr};  // device address of g_static_scratch, per device
+int g_static_sms[kMaxDevices] = {0};
+}  // namespace
+
+int vdc_launch_static(int num_sms, int insts_per_sm, const void* compute_insts, const void* memory_insts,
+                      const void* tma_descs, const int* bars_init, uint64_t stream, uint64_t timeout_ns,
+                      vdc_status* status) {
+  int dev;
+  if (int r = current_device(&dev)) return r;
+  if (!g_static_ptr[dev]) {
+    // Set-up, once per device, with that device current.  In host code the
+    // array's name is only a stand-in; the device address comes from the runtime.
+    int sms = 0;
+    cudaError_t e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return fail_cuda(e, "cudaDeviceGetAttribute(MultiProcessorCount)");
+    e = vdc_megakernel_prepare();
+    if (e != cudaSuccess) return fail_cuda(e, "cudaFuncSetAttribute(MaxDynamicSharedMemorySize)");
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_static_scratch);
+    if (e != cudaSuccess || !p) return fail_cuda(e, "cudaGetSymbolAddress(static scratch)");
+    g_static_ptr[dev] = static_cast<unsigned char*>(p);
+    g_static_sms[dev] = sms;
+  }
+  if (num_sms > VDC_STATIC_MAX_SMS)
+    return fail_arg("vdc_launch_static: the static scratch holds profile rows for at most 160 SMs");
+  if (num_sms <= 0 || num_sms > g_static_sms[dev]) return fail_arg("num_sms must be in [1, SM count of the device]");
+  if (insts_per_sm <= 0 || insts_per_sm > 65536) return fail_arg("insts_per_sm out of range");
+  if (!compute_insts || !memory_insts || !bars_init) return fail_arg("null instruction or barrier-image pointer");
+  if (((uintptr_t)compute_insts & 7) || ((uintptr_t)memory_insts & 15) || ((uintptr_t)bars_init & 3))
+    return fail_arg("misaligned instruction or barrier-image pointer");
+  unsigned char* base = g_static_ptr[dev];
+  vdc_status* d_status = reinterpret_cast<vdc_status*>(base + VDC_STATIC_STATUS_OFF);
+  int* d_bars = reinterpret_cast<int*>(base + VDC_STATIC_BARS_OFF);
+  uint64_t* d_profile = reinterpret_cast<uint64_t*>(base + VDC_STATIC_PROFILE_OFF);
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  // the array keeps the previous call's contents: the status must start at zero,
+  // the barriers at the caller's counts; profile rows are fully rewritten by the kernel
+  cudaError_t e = cudaMemsetAsync(d_status, 0, sizeof(vdc_status), s);
+  if (e != cudaSuccess) return fail_cuda(e, "cudaMemsetAsync(status)");
+  e = cudaMemcpyAsync(d_bars, bars_init, sizeof(int) * VDC_MAX_BARS, cudaMemcpyDeviceToDevice, s);
+  if (e != cudaSuccess) return fail_cuda(e, "cudaMemcpyAsync(bars)");
+  if (timeout_ns == 0) timeout_ns = 2000000000ull;
+  e = vdc_megakernel_launch(num_sms, compute_insts, memory_insts, tma_descs, d_bars, d_profile, d_status, insts_per_sm,
+                            timeout_ns, s);
+  if (e != cudaSuccess) return fail_cuda(e, "megakernel launch");
+  vdc_status h{};
+  e = cudaMemcpyAsync(&h, d_status, sizeof(h), cudaMemcpyDeviceToHost, s);
+  if (e != cudaSuccess) return fail_cuda(e, "cudaMemcpyAsync(status)");
+  e = cudaStreamSynchronize(s);
+  if (e != cudaSuccess) return fail_cuda(e, "cudaStreamSynchronize");
+  if (status) *status = h;
+  if (h.abort) {
+    char buf[256];
+    snprintf(buf, sizeof buf, "megakernel gave up: code=%d sm=%d role=%d pc=%d opcode=0x%x bar=%d aux=%d", h.code, h.sm,
+             h.role, h.pc, h.opcode, h.bar, h.aux);
+    g_err = buf;
+    return h.code ? h.code : VDC_ERR_TIMEOUT;
+  }
+  return VDC_OK;
+}
+
 }  // extern "C"

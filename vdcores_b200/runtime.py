@@ -38,6 +38,7 @@ _lib.vdc_init.restype = _i32
 _lib.vdc_set_smem_size.argtypes = [_i32]
 _lib.vdc_launch.argtypes = [_i32, _i32, _vp, _vp, _vp, _vp, _vp, _u64, _u64, ctypes.POINTER(Status)]
 _lib.vdc_launch_async.argtypes = [_i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _u64, _u64]
+_lib.vdc_launch_static.argtypes = [_i32, _i32, _vp, _vp, _vp, _vp, _u64, _u64, ctypes.POINTER(Status)]
 _lib.vdc_read_status.argtypes = [_u64, ctypes.POINTER(Status), _i32]
 _lib.vdc_build_tma_desc.argtypes = [_vp, _vp, _i32, _i32, ctypes.POINTER(_u64), ctypes.POINTER(_u64),
                                     ctypes.POINTER(ctypes.c_uint32), ctypes.POINTER(ctypes.c_uint32), _i32, _i32]
@@ -52,7 +53,8 @@ _lib.vdc_family_specs.restype = ctypes.c_char_p
 _lib.vdc_last_error.restype = ctypes.c_char_p
 
 EXPORTED_SYMBOLS = [
-    "vdc_version", "vdc_init", "vdc_set_smem_size", "vdc_launch", "vdc_launch_async", "vdc_read_status",
+    "vdc_version", "vdc_init", "vdc_set_smem_size", "vdc_launch", "vdc_launch_async", "vdc_launch_static",
+    "vdc_read_status",
     "vdc_build_tma_desc", "vdc_set_cache_policy", "vdc_opcode_count", "vdc_opcode_name", "vdc_opcode_value",
     "vdc_opcode_is_compute", "vdc_config", "vdc_family_specs", "vdc_last_error",
 ]
@@ -140,6 +142,18 @@ def launch_async(num_sms, insts_per_sm, compute_insts, memory_insts, tma_descs, 
     init()
     _check(_lib.vdc_launch_async(num_sms, insts_per_sm, _ptr(compute_insts), _ptr(memory_insts), _ptr(tma_descs),
                                  _ptr(bars), _ptr(bars_init), _ptr(profile), int(stream), int(timeout_ns)))
+
+
+def launch_static(num_sms, insts_per_sm, compute_insts, memory_insts, tma_descs, bars_init, stream=0, timeout_ns=0):
+    """Synchronous launch whose scratch (status, barriers, profile) is a static
+    device array inside the library: for hosts that cannot let a library call
+    allocate device memory.  Needs no init(); at most 160 SMs; calls on one device
+    share the array, so do not overlap them."""
+    st = Status()
+    rc = _lib.vdc_launch_static(num_sms, insts_per_sm, _ptr(compute_insts), _ptr(memory_insts), _ptr(tma_descs),
+                                _ptr(bars_init), int(stream), int(timeout_ns), ctypes.byref(st))
+    _check(rc, st)
+    return st.as_dict()
 
 
 def read_status(stream=0, clear=True):
