@@ -1,0 +1,94 @@
+"""Host-side logic of the tensor-parallel split, with two gloo ranks on the CPU:
+each rank evaluates one decode layer on its shard of the weights (plain torch
+math on the shard tensors), partial hidden-state updates are all-reduced, and
+the result must equal the oracle's full layer."""
+import os
+import socket
+
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import decode_oracle as O
+from tests.helpers import dense_weights, engine_config, perturb_norms, small_cfg
+
+
+def _port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _rank(rank, world, port, q):
+    from vdcores_b200.tp import shard_dense_weights
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    try:
+        cfg = small_cfg("llama")
+        w = perturb_norms(O.ModelWeights.random(cfg, seed=5))
+        ecfg = engine_config(cfg)
+        sh = shard_dense_weights(ecfg, dense_weights(w), rank, world)
+        g = torch.Generator().manual_seed(9)
+        hidden = torch.randn(cfg.hidden, generator=g).to(torch.bfloat16)
+        T, pos, d = 40, 40, cfg.head_dim
+        kc = torch.randn(T + 1, cfg.n_kv_heads, d, generator=g).to(torch.bfloat16)
+        vc = torch.randn(T + 1, cfg.n_kv_heads, d, generator=g).to(torch.bfloat16)
+        nkv, nq = cfg.n_kv_heads // world, cfg.n_heads // world
+        # --- this rank's half layer, on shard tensors only
+        x = O.rms_norm(hidden, sh.ln1[0], cfg.eps)
+        q_ = O.linear(x[None], sh.wq[0])[0].view(nq, d)
+        k_ = O.linear(x[None], sh.wk[0])[0].view(nkv, d)
+        v_ = O.linear(x[None], sh.wv[0])[0].view(nkv, d)
+        cos, sin = O.rope_cos_sin(torch.tensor([pos]), d, cfg.theta)
+        q_, k_ = O.apply_rope(q_, cos, sin), O.apply_rope(k_, cos, sin)
+        kl = kc[:, rank * nkv:(rank + 1) * nkv].clone()
+        vl = vc[:, rank * nkv:(rank + 1) * nkv].clone()
+        kl[pos], vl[pos] = k_, v_
+        attn = O.gqa_decode_attention(q_, kl, vl)
+        part = attn.float() @ sh.wo[0].float().t()                 # fp32 partial over the local columns
+        dist.all_reduce(part)
+        h1 = hidden + part.to(torch.bfloat16)
+        x2 = O.rms_norm(h1, sh.ln2[0], cfg.eps)
+        a = O.silu_mul(O.linear(x2[None], sh.gate[0]), O.linear(x2[None], sh.up[0]))[0]
+        part2 = a.float() @ sh.down[0].float().t()
+        dist.all_reduce(part2)
+        h2 = h1 + part2.to(torch.bfloat16)
+        # --- the oracle's full layer
+        kf, vf = kc.clone(), vc.clone()
+        ref = O.decode_layer(cfg, w.layers[0], hidden, pos, kf, vf)
+        q.put((rank, O.rel_l2(h2, ref), float((h2.float() - ref.float()).abs().max())))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_split_reproduces_the_full_layer():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _port()
+    procs = [ctx.Process(target=_rank, args=(r, 2, port, q), daemon=True) for r in range(2)]
+    for p in procs:
+        p.start()
+    try:
+        res = [q.get(timeout=120) for _ in range(2)]
+    finally:
+        for p in procs:
+            p.join(10)
+            if p.is_alive():
+                p.kill()
+    for rank, r, mx in res:
+        assert r < 3e-3, (rank, r, mx)
+
+
+def test_shard_shapes():
+    from vdcores_b200.tp import shard_dense_weights
+    cfg = small_cfg("llama")
+    w = O.ModelWeights.random(cfg, seed=1)
+    ecfg = engine_config(cfg)
+    for world in (1, 2):
+        parts = [shard_dense_weights(ecfg, dense_weights(w), r, world) for r in range(world)]
+        assert torch.equal(torch.cat([p.wq[0] for p in parts], 0), w.layers[0].wq.w)
+        assert torch.equal(torch.cat([p.wo[1] for p in parts], 1), w.layers[1].wo.w)
+        assert torch.equal(torch.cat([p.down[2] for p in parts], 1), w.layers[2].down.w)
+        assert torch.equal(torch.cat([p.lm_head for p in parts], 0), w.lm_head)
+        assert parts[0].gate[0].shape == (cfg.ffn // world, cfg.hidden)

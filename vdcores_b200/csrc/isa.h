@@ -105,6 +105,7 @@
 #define VDC_GEMV_MODE_STORE 0
 #define VDC_GEMV_MODE_SILU_PAIRS 1
 #define VDC_GEMV_MODE_ARGMAX 2
+#define VDC_GEMV_MODE_STORE_F32 3   // fp32 partial results (tensor-parallel row-split projections)
 #define VDC_GEMV_ACC_BIT 0x0800
 #define VDC_GEMV_NORM_BIT 0x1000
 

@@ -134,7 +134,7 @@ __device__ void compute_core(const Ctx& c, const VdcCInst* __restrict__ insts, i
           asm volatile("prefetch.global.L2 [%0];" ::"l"(base + off));
         break;
       }
-      case 0x7220: task_argmax_final(q, ci.args[0]); break;
+      case 0x7220: task_argmax_final(q, ci.args[0], ci.args[1]); break;
       default:
         raise_abort(c, VDC_ERR_BAD_OPCODE, 0, (int)q.pc, ci.opcode, -1, 0);
         q.aborted = true;

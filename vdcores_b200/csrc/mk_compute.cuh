@@ -243,7 +243,9 @@ __device__ void task_gemv_rows(Compute& q, int n_chunks, int mode, bool accumula
 #pragma unroll
       for (int r = 0; r < R; ++r)
         if (q.lane == r) v = acc[r];
-      if (q.lane < R) {
+      if (q.lane < R && mode == VDC_GEMV_MODE_STORE_F32) {
+        reinterpret_cast<float*>(outg)[row0 + q.lane] = v;
+      } else if (q.lane < R) {
         const __nv_bfloat16 bq = __float2bfloat16_rn(v);
         if (accumulate) atomicAdd(outg + row0 + q.lane, bq);  // residual add: bf16(old + bf16(W x))
         else outg[row0 + q.lane] = bq;
@@ -620,7 +622,7 @@ __device__ void task_attn_decode(Compute& q, const AttnArgs& a) {
 // Pop order: candidate records (n x {f32 val, i32 idx, pad, pad}), state (raw
 // address), token log (raw address, int32 per step), done (raw address slot that
 // is pushed back so the store warp can release a barrier).
-__device__ void task_argmax_final(Compute& q, int n) {
+__device__ void task_argmax_final(Compute& q, int n, int local_only) {
   const Ctx& c = q.c;
   const int rec_mask = q.pop();
   q.pop();
@@ -650,7 +652,15 @@ __device__ void task_argmax_final(Compute& q, int n) {
         bi = oi;
       }
     }
-    if (q.lane == 0) {
+    if (q.lane == 0 && local_only) {
+      // tensor-parallel vocabulary shard: leave this rank's best candidate as one
+      // record; the ranks' records are reduced by a second, global call
+      reinterpret_cast<float*>(log)[0] = bv;
+      log[1] = bi;
+      log[2] = 0;
+      log[3] = 0;
+      __threadfence();
+    } else if (q.lane == 0) {
       const int step = state[VDC_ST_STEP];
       const int pos = state[VDC_ST_POS] + 1;
       log[step] = bi;

@@ -230,6 +230,7 @@ class Program:
         assert n_rows % R == 0 and n_rows > 0
         assert mode != isa.GEMV_MODE_SILU_PAIRS or R % 2 == 0
         assert out.kind in ("store", "add_bf16") and out.addr % 2 == 0
+        assert mode != isa.GEMV_MODE_STORE_F32 or (out.kind == "store" and out.addr % 4 == 0)
         n_chunks = n_rows // R
         assert n_chunks < 0xFFFF
         chunk_bytes = R * K * 2
@@ -291,11 +292,14 @@ class Program:
             self.comp(sm, isa.OP_EXT, addr & 0xFFFF, (addr >> 16) & 0xFFFF, (addr >> 32) & 0xFFFF)
         self.comp(sm, isa.OP_EXT, split, release, 0)
 
-    def argmax_final(self, sm, *, records: Src, n: int, state_addr, log_addr, release=None):
+    def argmax_final(self, sm, *, records: Src, n: int, state_addr, log_addr, release=None, local_only=False):
+        """Reduces n candidate records {f32 value, i32 index, pad, pad}.  Normally
+        the winner is logged as the next token and the state block advances;
+        with local_only the winner is written to log_addr as one more record."""
         self.load(sm, records)
         self.raw_address(sm, state_addr, 25)
         self.raw_address(sm, log_addr, 26, release=release)
-        self.comp(sm, isa.OP_ARGMAX_FINAL, n)
+        self.comp(sm, isa.OP_ARGMAX_FINAL, n, 1 if local_only else 0)
 
     # ------------------------------------------------------------------ output
     def finalize(self):

@@ -1,0 +1,366 @@
+"""Tensor-parallel batch-1 decode: one process per GPU, the model split the
+Megatron way — QKV and gate/up by output rows (heads / FFN columns), O and down
+by input columns, vocabulary rows of the lm_head — with an all-reduce (sum) of
+the fp32 partial hidden-state update after the O projection and after the down
+projection of every layer, over NCCL (`torch.distributed`).
+
+The reference has no multi-GPU path at all; this is new.  Each rank runs the
+same megakernel tasks as the single-GPU engine on its shard.  A layer becomes
+two launches (attention half, MLP half) separated by the collectives; the whole
+step is replayed as one CUDA graph when capture is available.
+"""
+from __future__ import annotations
+
+import math
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+from . import isa, runtime
+from .decode import BF16, DecodeConfig, DecodeEngine, DenseWeights, rows_per_chunk
+from .program import Dst, Program, Src
+
+
+def shard_rows(t: torch.Tensor, rank: int, world: int) -> torch.Tensor:
+    n = t.shape[0] // world
+    return t[rank * n:(rank + 1) * n].contiguous()
+
+
+def shard_cols(t: torch.Tensor, rank: int, world: int) -> torch.Tensor:
+    n = t.shape[1] // world
+    return t[:, rank * n:(rank + 1) * n].contiguous()
+
+
+def shard_dense_weights(cfg: DecodeConfig, w: DenseWeights, rank: int, world: int) -> DenseWeights:
+    """The rank's shard in the usual [out, in] layout: q/k/v by heads, gate/up by
+    FFN rows, o/down by input columns, lm_head by vocabulary rows; embedding and
+    norms replicated."""
+    assert cfg.n_kv_heads % world == 0 and cfg.ffn % world == 0 and cfg.vocab % world == 0
+    L = cfg.n_layers
+    return DenseWeights(
+        embed=w.embed, lm_head=shard_rows(w.lm_head, rank, world), norm=w.norm, ln1=w.ln1, ln2=w.ln2,
+        wq=[shard_rows(w.wq[l], rank, world) for l in range(L)],
+        wk=[shard_rows(w.wk[l], rank, world) for l in range(L)],
+        wv=[shard_rows(w.wv[l], rank, world) for l in range(L)],
+        wo=[shard_cols(w.wo[l], rank, world) for l in range(L)],
+        gate=[shard_rows(w.gate[l], rank, world) for l in range(L)],
+        up=[shard_rows(w.up[l], rank, world) for l in range(L)],
+        down=[shard_cols(w.down[l], rank, world) for l in range(L)],
+        q_norm=w.q_norm, k_norm=w.k_norm)
+
+
+class TPDecodeEngine:
+    def __init__(self, cfg: DecodeConfig, max_seq: int, rank: int, world: int, device, group=None,
+                 max_steps: int = 4096, timeout_ns: int = 0, use_graph: bool = True):
+        assert cfg.n_kv_heads % world == 0 and cfg.ffn % world == 0 and cfg.vocab % world == 0
+        self.cfg, self.rank, self.world, self.group = cfg, rank, world, group
+        self.dev = torch.device(device)
+        self.max_seq = max_seq
+        self.max_pages = (max_seq + isa.KV_PAGE - 1) // isa.KV_PAGE
+        self.max_steps, self.timeout_ns, self.use_graph = max_steps, timeout_ns, use_graph
+        self.num_sms = torch.cuda.get_device_properties(self.dev).multi_processor_count
+        self.stream = torch.cuda.current_stream(self.dev)
+        runtime.init()
+        D, G = isa.HEAD_DIM, cfg.group
+        self.nkv = cfg.n_kv_heads // world
+        self.nq = cfg.n_heads // world
+        self.F = cfg.ffn // world
+        self.V = cfg.vocab // world
+        self.qw, self.kvw = self.nq * D, self.nkv * D
+        assert self.nkv & (self.nkv - 1) == 0 and self.qw % 256 == 0 and self.F % 256 == 0
+        L, H = cfg.n_layers, cfg.hidden
+        z = lambda *s, dt=BF16: torch.zeros(*s, dtype=dt, device=self.dev)
+        self.hidden = z(H)
+        self.qkv = z(self.qw + 2 * self.kvw)
+        self.attn_out = z(self.qw)
+        self.act = z(self.F)
+        self.partial = z(H, dt=torch.float32)
+        self.logits = z(self.V)
+        self.rec_floats = G * D + 16 * ((2 * G + 15) // 16)
+        self.n_splits = max(1, min(self.num_sms // self.nkv, self.max_pages))
+        self.pages_per_split = (self.max_pages + self.n_splits - 1) // self.n_splits
+        self.n_splits = (self.max_pages + self.pages_per_split - 1) // self.pages_per_split
+        self.attn_part = z(self.nkv, self.n_splits, self.rec_floats, dt=torch.float32)
+        self.attn_cnt = z(L, self.nkv, dt=torch.int32)
+        self.argmax_rec = z(self.num_sms, 4, dt=torch.float32)
+        self.best_local = z(4, dt=torch.float32)
+        self.best_all = z(world, 4, dt=torch.float32)
+        self.state = z(isa.ST_PAGETABLE + self.max_pages, dt=torch.int32)
+        self.state_host = torch.zeros(isa.ST_PAGETABLE + self.max_pages, dtype=torch.int32).pin_memory()
+        self.token_log = z(max_steps, dt=torch.int32)
+        self.kpool = z(L, self.max_pages, self.nkv, isa.KV_PAGE, D)
+        self.vpool = z(L, self.max_pages, self.nkv, isa.KV_PAGE, D)
+        self.page_table = torch.arange(self.max_pages, dtype=torch.int32)
+        pos = torch.arange(max_seq, dtype=torch.float32)
+        inv = 1.0 / (cfg.theta ** (torch.arange(0, D, 2, dtype=torch.float32) / D))
+        fr = pos[:, None] * inv[None, :]
+        self.rope = torch.cat((fr.cos().to(BF16).float(), fr.sin().to(BF16).float()), dim=1).contiguous().to(self.dev)
+        self.bars = z(isa.MAX_BARS, dt=torch.int32)
+        self.profile = z(self.num_sms * isa.NUM_PROFILE_EVENTS, dt=torch.int64)
+        self.programs = []
+        self.graph = None
+        self.pos = 0
+        self.steps_done = 0
+        self.launches_per_step = 2 * L + 2
+
+    # ------------------------------------------------------------------ weights
+    def load_shard(self, w: DenseWeights):
+        """Takes this rank's shard (see shard_dense_weights) and builds the programs."""
+        cfg, dev = self.cfg, self.dev
+        L, G, D = cfg.n_layers, cfg.group, isa.HEAD_DIM
+        to = lambda t: t.to(device=dev, dtype=BF16).contiguous()
+        self.embed = to(w.embed)
+        self.lm_head = to(w.lm_head)
+        self.norm_w = to(w.norm)
+        self.ln1 = torch.stack([to(t) for t in w.ln1])
+        self.ln2 = torch.stack([to(t) for t in w.ln2])
+        perm = []
+        for h in range(self.nkv):
+            perm += list(range(h * G * D, (h + 1) * G * D))
+            perm += list(range(self.qw + h * D, self.qw + (h + 1) * D))
+            perm += list(range(self.qw + self.kvw + h * D, self.qw + self.kvw + (h + 1) * D))
+        pm = torch.tensor(perm, dtype=torch.long, device=dev)
+        self.wqkv = torch.stack([torch.cat((to(w.wq[l]), to(w.wk[l]), to(w.wv[l])), dim=0)[pm] for l in range(L)])
+        self.wo = torch.stack([to(w.wo[l]) for l in range(L)])
+        self.wgu = torch.stack([torch.stack((to(w.gate[l]), to(w.up[l])), dim=1).reshape(2 * self.F, cfg.hidden)
+                                for l in range(L)])
+        self.wd = torch.stack([to(w.down[l]) for l in range(L)])
+        self.qknorm = (torch.stack([torch.cat((to(w.q_norm[l]), to(w.k_norm[l]))) for l in range(L)])
+                       if cfg.qk_norm else None)
+        self._build_programs()
+
+    def weight_bytes(self) -> int:
+        ts = [self.lm_head, self.norm_w, self.ln1, self.ln2, self.wqkv, self.wo, self.wgu, self.wd]
+        if self.qknorm is not None:
+            ts.append(self.qknorm)
+        return sum(t.numel() * t.element_size() for t in ts) + self.cfg.hidden * 2
+
+    def algorithmic_bytes(self, pos: int) -> int:
+        """Per-GPU HBM bytes of one step: this rank's weights once, one embedding
+        row, its share of the KV cache."""
+        return self.weight_bytes() + 2 * self.kvw * 2 * (pos + 1) * self.cfg.n_layers
+
+    # ------------------------------------------------------------------ programs
+    def _ranges(self, load, n_units: int, unit_bytes: int):
+        S = self.num_sms
+        base, rem = divmod(n_units, S)
+        order = sorted(range(S), key=lambda s: (load[s], s))
+        extra = set(order[:rem])
+        out, u = [], 0
+        for sm in range(S):
+            cnt = base + (1 if sm in extra else 0)
+            if cnt:
+                out.append((sm, u, cnt))
+                load[sm] += cnt * unit_bytes
+            u += cnt
+        return out
+
+    def _finish(self, P: Program):
+        n = max(max(len(x) for x in P.m), max(len(x) for x in P.c)) + 2
+        P.insts_per_sm = ((n + 15) // 16) * 16
+        c, m, bars = P.finalize()
+        self.programs.append((torch.from_numpy(c).to(self.dev), torch.from_numpy(m).to(self.dev),
+                              torch.from_numpy(bars).to(self.dev), P.insts_per_sm))
+
+    def _build_programs(self):
+        cfg = self.cfg
+        L, H, G, D, S = cfg.n_layers, cfg.hidden, cfg.group, isa.HEAD_DIM, self.num_sms
+        st = self.state.data_ptr()
+        page_bytes = isa.KV_PAGE * D * 2
+        page_shift = int(math.log2(self.nkv * page_bytes))
+        hid, qkv, ao, act, part = (t.data_ptr() for t in (self.hidden, self.qkv, self.attn_out, self.act, self.partial))
+        self.programs = []
+        load = [0] * S
+        for l in range(L):
+            # ---- attention half: QKV (local heads) -> attention -> O projection over the local columns
+            P = Program(S)
+            b_qkv, b_merge = P.new_barrier(), P.new_barrier()
+            R = rows_per_chunk(H)
+            rows = self.qw + 2 * self.kvw
+            for sm, u0, cnt in self._ranges(load, rows // R, R * H * 2):
+                r0, n = u0 * R, cnt * R
+                P.gemv(sm, w_addr=self.wqkv[l].data_ptr() + r0 * H * 2, n_rows=n, K=H, R=R, x=Src(hid, H * 2),
+                       out=Dst(qkv + r0 * 2, n * 2, "store", release=b_qkv),
+                       norm_w=Src(self.ln1[l].data_ptr(), H * 2), eps=cfg.eps)
+            P.add_releases(b_merge, self.nkv)
+            units = [(h, s) for s in range(self.n_splits) for h in range(self.nkv)]
+            order = sorted(range(S), key=lambda s: (load[s], s))
+            grp = (G + 2) * D * 2
+            for i, (h, s) in enumerate(units):
+                sm = order[i % S]
+                P.attn_decode(
+                    sm, G=G, state_addr=st,
+                    rope=Src(self.rope.data_ptr(), D * 4, indirect=(st + 4 * isa.ST_POS, 9, None)),
+                    norm_w=Src(self.qknorm[l].data_ptr(), 2 * D * 2) if cfg.qk_norm else None,
+                    qkv=Src(qkv + h * grp, grp, wait=b_qkv),
+                    k_page_addr=self.kpool[l].data_ptr() + h * page_bytes,
+                    v_page_addr=self.vpool[l].data_ptr() + h * page_bytes, page_shift=page_shift,
+                    base_page=s * self.pages_per_split, max_pages=self.pages_per_split,
+                    records_addr=self.attn_part[h].data_ptr(), counter_addr=self.attn_cnt[l, h].data_ptr(),
+                    out_addr=ao + h * G * D * 2, split=s, n_splits=self.n_splits, release=b_merge,
+                    qk_eps=cfg.qk_norm_eps)
+            K = self.qw
+            R = rows_per_chunk(K)
+            for sm, u0, cnt in self._ranges(load, H // R, R * K * 2):
+                r0, n = u0 * R, cnt * R
+                P.gemv(sm, w_addr=self.wo[l].data_ptr() + r0 * K * 2, n_rows=n, K=K, R=R,
+                       x=Src(ao, K * 2, wait=b_merge), out=Dst(part + r0 * 4, n * 4, "store"),
+                       mode=isa.GEMV_MODE_STORE_F32)
+            self._finish(P)
+            # ---- MLP half: gate/up over the local FFN rows -> down over the local columns
+            P = Program(S)
+            b_gu = P.new_barrier()
+            R = rows_per_chunk(H, even=True)
+            for sm, u0, cnt in self._ranges(load, 2 * self.F // R, R * H * 2):
+                r0, n = u0 * R, cnt * R
+                P.gemv(sm, w_addr=self.wgu[l].data_ptr() + r0 * H * 2, n_rows=n, K=H, R=R, x=Src(hid, H * 2),
+                       out=Dst(act + (r0 // 2) * 2, n, "store", release=b_gu), mode=isa.GEMV_MODE_SILU_PAIRS,
+                       norm_w=Src(self.ln2[l].data_ptr(), H * 2), eps=cfg.eps)
+            K = self.F
+            R = rows_per_chunk(K)
+            for sm, u0, cnt in self._ranges(load, H // R, R * K * 2):
+                r0, n = u0 * R, cnt * R
+                P.gemv(sm, w_addr=self.wd[l].data_ptr() + r0 * K * 2, n_rows=n, K=K, R=R,
+                       x=Src(act, K * 2, wait=b_gu), out=Dst(part + r0 * 4, n * 4, "store"),
+                       mode=isa.GEMV_MODE_STORE_F32)
+            self._finish(P)
+        # ---- vocabulary shard: candidates per SM, then this rank's best as one record
+        P = Program(S)
+        b_logits = P.new_barrier()
+        R = rows_per_chunk(H)
+        lm = self._ranges(load, self.V // R, R * H * 2)
+        for i, (sm, u0, cnt) in enumerate(lm):
+            r0, n = u0 * R, cnt * R
+            P.gemv(sm, w_addr=self.lm_head.data_ptr() + r0 * H * 2, n_rows=n, K=H, R=R, x=Src(hid, H * 2),
+                   out=Dst(self.logits.data_ptr() + r0 * 2, n * 2, "store", release=b_logits),
+                   mode=isa.GEMV_MODE_ARGMAX, norm_w=Src(self.norm_w.data_ptr(), H * 2), eps=cfg.eps,
+                   pair_out=Dst(self.argmax_rec[i].data_ptr(), 16, release=b_logits), row_base=self.rank * self.V + r0)
+        P.argmax_final(0, records=Src(self.argmax_rec.data_ptr(), len(lm) * 16, wait=b_logits), n=len(lm),
+                       state_addr=st, log_addr=self.best_local.data_ptr(), local_only=True)
+        self._finish(P)
+        # ---- global winner among the ranks' records, token log, state advance (identical on every rank)
+        P = Program(1)
+        P.argmax_final(0, records=Src(self.best_all.data_ptr(), self.world * 16), n=self.world, state_addr=st,
+                       log_addr=self.token_log.data_ptr())
+        self._finish(P)
+
+    # ------------------------------------------------------------------ state / cache
+    def set_state(self, pos: int, token: int):
+        s = self.state_host
+        s.zero_()
+        page = pos // isa.KV_PAGE
+        s[isa.ST_POS], s[isa.ST_NPAGES], s[isa.ST_TOKEN] = pos, page + 1, token
+        s[isa.ST_NEWROW] = int(self.page_table[page]) * isa.KV_PAGE * self.nkv + pos % isa.KV_PAGE
+        s[isa.ST_NKVH], s[isa.ST_MAXPAGES] = self.nkv, self.max_pages
+        s[isa.ST_PAGETABLE:] = self.page_table
+        self.state.copy_(s, non_blocking=True)
+        self.attn_cnt.zero_()
+        self.pos, self.steps_done = pos, 0
+
+    def load_kv(self, k: List[torch.Tensor], v: List[torch.Tensor]):
+        """Per-layer contiguous caches [T, n_kv_heads (all), 128]: keeps this rank's heads."""
+        h0 = self.rank * self.nkv
+        for l in range(self.cfg.n_layers):
+            for src, pool in ((k[l], self.kpool[l]), (v[l], self.vpool[l])):
+                T = src.shape[0]
+                n_pages = (T + isa.KV_PAGE - 1) // isa.KV_PAGE
+                pad = torch.zeros(n_pages * isa.KV_PAGE, self.nkv, isa.HEAD_DIM, dtype=BF16, device=self.dev)
+                pad[:T] = src[:, h0:h0 + self.nkv].to(self.dev)
+                pool[:n_pages] = pad.view(n_pages, isa.KV_PAGE, self.nkv, isa.HEAD_DIM).permute(0, 2, 1, 3)
+
+    # ------------------------------------------------------------------ decode
+    def _launch(self, i: int):
+        c, m, b0, n = self.programs[i]
+        num_sms = 1 if i == len(self.programs) - 1 else self.num_sms
+        # the stream that is current now: inside a graph capture that is the capturing stream
+        runtime.launch_async(num_sms, n, c, m, None, self.bars, b0, self.profile,
+                             torch.cuda.current_stream(self.dev).cuda_stream, self.timeout_ns)
+
+    def _all_reduce_add(self):
+        dist.all_reduce(self.partial, group=self.group)
+        self.hidden.add_(self.partial)           # bf16(hidden + fp32 sum of the ranks' partial products)
+
+    def _step_body(self):
+        L = self.cfg.n_layers
+        tok = self.state[isa.ST_TOKEN:isa.ST_TOKEN + 1].long()
+        torch.index_select(self.embed, 0, tok, out=self.hidden.view(1, -1))
+        for l in range(L):
+            self._launch(2 * l)
+            self._all_reduce_add()
+            self._launch(2 * l + 1)
+            self._all_reduce_add()
+        self._launch(2 * L)
+        dist.all_gather_into_tensor(self.best_all.view(-1), self.best_local, group=self.group)
+        self._launch(2 * L + 1)
+
+    def step_async(self):
+        if self.pos >= self.max_seq or self.steps_done >= self.max_steps:
+            raise RuntimeError("out of KV pages or token-log space")
+        if self.use_graph and self.graph is None and self.steps_done >= 2:
+            # two eager steps first (NCCL sets up its channels on first use), then capture one step
+            try:
+                torch.cuda.synchronize(self.dev)
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    self._step_body()
+                self.graph = g
+                # the captured step has not run: fall through and replay it below
+            except Exception as e:           # capture not available: stay eager
+                self.use_graph = False
+                self.graph_error = repr(e)
+                torch.cuda.synchronize(self.dev)
+        if self.graph is not None:
+            self.graph.replay()
+        else:
+            self._step_body()
+        self.pos += 1
+        self.steps_done += 1
+
+    def step_host(self, token: int) -> int:
+        """One step from host buffers: token id up, next id down (synchronous)."""
+        if not hasattr(self, "_tok_in"):
+            self._tok_in = torch.zeros(1, dtype=torch.int32).pin_memory()
+            self._tok_out = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self._tok_in[0] = token
+        self.state[isa.ST_TOKEN:isa.ST_TOKEN + 1].copy_(self._tok_in, non_blocking=True)
+        idx = self.steps_done
+        self.step_async()
+        self._tok_out.copy_(self.token_log[idx:idx + 1], non_blocking=True)
+        torch.cuda.synchronize(self.dev)
+        return int(self._tok_out[0])
+
+    def load_from_full(self, full: DecodeEngine, cached_positions: int):
+        """Takes this rank's shard out of a single-GPU engine that holds the whole
+        model (packed layout) and its KV cache for `cached_positions` positions."""
+        r, cfg = self.rank, self.cfg
+        rows = self.qw + 2 * self.kvw
+        self.embed, self.norm_w, self.ln1, self.ln2 = full.embed, full.norm_w, full.ln1, full.ln2
+        self.lm_head = full.lm_head[r * self.V:(r + 1) * self.V].contiguous()
+        self.wqkv = full.wqkv[:, r * rows:(r + 1) * rows].contiguous()
+        self.wo = full.wo[:, :, r * self.qw:(r + 1) * self.qw].contiguous()
+        self.wgu = full.wgu[:, r * 2 * self.F:(r + 1) * 2 * self.F].contiguous()
+        self.wd = full.wd[:, :, r * self.F:(r + 1) * self.F].contiguous()
+        self.qknorm = full.qknorm
+        ks, vs = [], []
+        for l in range(cfg.n_layers):
+            k, v = full.read_kv(l, cached_positions)
+            ks.append(k)
+            vs.append(v)
+        self.load_kv(ks, vs)
+        self._build_programs()
+
+    def close(self):
+        """Drops the captured step (it holds NCCL kernels) before the process group
+        is destroyed; call on every rank, then barrier, then destroy."""
+        torch.cuda.synchronize(self.dev)
+        self.graph = None
+        torch.cuda.synchronize(self.dev)
+
+    def generate(self, n_steps: int) -> List[int]:
+        first = self.steps_done
+        for _ in range(n_steps):
+            self.step_async()
+        torch.cuda.synchronize(self.dev)
+        runtime.read_status(self.stream.cuda_stream)
+        return self.token_log[first:first + n_steps].tolist()
