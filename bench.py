@@ -170,7 +170,7 @@ def run_gpu(args):
     g = torch.Generator().manual_seed(0)
     prompt = torch.randint(0, cfg.vocab, (PROMPT_LEN,), generator=g)
     if world == 1:
-        eng = DecodeEngine(cfg, max_seq=max_seq, device=dev, max_steps=W + K + 8)
+        eng = DecodeEngine(cfg, max_seq=max_seq, device=dev, max_steps=W + K + 8, wkind=args.wkind)
         eng.init_random_weights(seed=0)
         first = eng.prefill(prompt)
         tokens_per_step, scaling, parallelism = 1, "strong", "single GPU"
@@ -252,7 +252,7 @@ def run_gpu(args):
     line = {
         "metric": METRIC, "value": tokens_per_step * K / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": K,
         "warmup": W, "ms_per_step": ms / K, "higher_is_better": True, "scaling": scaling, "vs_baseline": None,
-        "dtype": "bf16", "data": "synthetic",
+        "dtype": args.wkind, "data": "synthetic",
         "config": {"workload": "Llama-3.1-8B shape (32 layers, hidden 4096, 32q/8kv heads, FFN 14336, vocab 128256), "
                                "bf16, batch 1, 2048-token prompt prefilled, greedy decode",
                    "l2": "inputs larger than L2: every step streams ~15 GB of weights through a 126 MB L2",
@@ -284,6 +284,8 @@ def main():
     ap.add_argument("--impl", default="vdcores_b200", choices=["vdcores_b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer arm (profiling runs)")
+    ap.add_argument("--wkind", default="bf16", choices=["bf16", "fp8"],
+                    help="storage of the layer projections (fp8: e4m3 + per-row fp32 scales; reported, not the headline)")
     ap.add_argument("--layers", type=int, default=32,
                     help="profiling only: a model with fewer layers of the same shape (the JSON line says so)")
     args = ap.parse_args()

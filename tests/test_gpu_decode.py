@@ -81,3 +81,47 @@ def test_torch_prefill_then_decode(cuda_device):
         if gap > GAP:
             assert got == ref_next
         tok = ref_next
+
+
+def test_decode_fp8_matches_oracle(cuda_device):
+    """FP8-e4m3 projections (per-output-channel fp32 scales; embedding, norms and
+    lm_head stay bf16): per-layer hidden states within rel-L2 3e-2 of the oracle
+    that dequantises the same codes."""
+    import copy
+    import dataclasses
+    from vdcores_b200.decode import DecodeEngine
+    cfg_b = small_cfg("llama")
+    w_b = perturb_norms(O.ModelWeights.random(cfg_b, seed=6))
+    cfg = dataclasses.replace(cfg_b, wkind="fp8")
+    w = copy.copy(w_b)
+    w.cfg = cfg
+    w.layers = []
+    for lw in w_b.layers:
+        q = copy.copy(lw)
+        for name in ("wq", "wk", "wv", "wo", "gate", "up", "down"):
+            setattr(q, name, O.QLinear.make(getattr(lw, name).w, "fp8"))
+        w.layers.append(q)
+    g = torch.Generator().manual_seed(13)
+    prompt = torch.randint(0, cfg.vocab, (50,), generator=g)
+    orc = O.DecodeOracle(w, 128)
+    orc.prefill(prompt[:-1].tolist())
+    # the engine quantises the same bf16 weights with the same rule (codes checked in test_gemv_fp8_store)
+    eng = DecodeEngine(engine_config(cfg), max_seq=128, device=cuda_device, taps=True, wkind="fp8",
+                       timeout_ns=500_000_000)
+    eng.load_weights(dense_weights(w_b))
+    eng.load_kv([k[:49] for k in orc.k], [v[:49] for v in orc.v])
+    tok = int(prompt[-1])
+    eng.set_state(49, tok)
+    for step in range(4):
+        caps = []
+        logits_ref, nxt_ref, gap = orc.step(tok, caps)
+        got = eng.generate(1)[0]
+        taps = eng.taps.cpu()
+        for l in range(cfg.n_layers):
+            r = O.rel_l2(taps[l], caps[l]["hidden_state_out"])
+            assert r < 3e-2, f"step {step} layer {l}: rel-L2 {r:.3e}"
+        if gap > GAP:
+            assert got == nxt_ref
+        tok = nxt_ref
+        if got != nxt_ref:
+            eng.state[2:3].copy_(torch.tensor([tok], dtype=torch.int32))

@@ -276,3 +276,26 @@ def test_wait_budget_returns_status_instead_of_hanging(cuda_device):
     assert ei.value.code == isa.ERR_TIMEOUT and ei.value.status["bar"] == b
     # the context is still healthy
     assert float((torch.ones(8, device=dev) * 2).sum()) == 16.0
+
+
+@pytest.mark.parametrize("M,K,R,n_sms", [(256, 4096, 8, 4), (64, 14336, 2, 2), (128, 512, 16, 1)])
+def test_gemv_fp8_store(cuda_device, M, K, R, n_sms):
+    """e4m3 weights with per-row fp32 scales, dequantised in registers; the oracle
+    multiplies the same codes and scales in fp32."""
+    from vdcores_b200.decode import quantize_fp8_rows
+    from vdcores_b200.program import Dst, Program, Src
+    dev = cuda_device
+    w, x = seeded((M, K), 31, 0.02), seeded((K,), 32)
+    lin = O.QLinear.make(w, "fp8")
+    q, sc = quantize_fp8_rows(w)             # on the CPU: the same conversion the oracle used
+    assert torch.equal(q, lin.q.view(torch.uint8)) and torch.equal(sc, lin.scale)
+    q, sc, xd = q.to(dev), sc.to(dev), x.to(dev)
+    y = torch.zeros(M, dtype=BF16, device=dev)
+    P = Program(n_sms)
+    per = M // n_sms
+    for sm in range(n_sms):
+        r0 = sm * per
+        P.gemv(sm, w_addr=q.data_ptr() + r0 * K, n_rows=per, K=K, R=R, x=Src(xd.data_ptr(), K * 2),
+               out=Dst(y.data_ptr() + r0 * 2, per * 2, "store"), fp8_scales=sc.data_ptr() + 4 * r0)
+    run_program(P, dev)
+    assert O.rel_l2(y.cpu(), lin(x[None])[0]) < 3e-3

@@ -79,6 +79,7 @@
   X(OP_DUMMY, 0x7002)                                                                  \
   X(OP_COPY, 0x7003)                                                                   \
   X(OP_GEMV_ROWS_BF16, 0x7200)                                                         \
+  X(OP_GEMV_ROWS_FP8, 0x7201)                                                          \
   X(OP_ATTN_DECODE_PAGED_G4, 0x7210)                                                   \
   X(OP_ATTN_DECODE_PAGED_G8, 0x7211)                                                   \
   X(OP_ARGMAX_FINAL, 0x7220)                                                          \
@@ -91,6 +92,9 @@
 //
 // OP_EXT is never dispatched: it marks the continuation words of a multi-word
 // compute instruction (GEMV_ROWS: 2 words, L2_PREFETCH: 2, ATTN_DECODE_PAGED: 9).
+//
+// GEMV_ROWS_FP8 (3 words): as GEMV_ROWS_BF16 for e4m3 weights (K a multiple of 512, one byte per
+// weight), third word = 48-bit address of the fp32 per-row scales of the task's first row.
 //
 // ATTN_DECODE_PAGED words: [max_pages, base_page, flags] [qk-norm eps hi, lo, n_splits]
 // then six 48-bit addresses, low piece first: state block, this head's rows in K page 0,

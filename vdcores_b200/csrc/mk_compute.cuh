@@ -1,5 +1,7 @@
 // Compute virtual core of the megakernel: queue access and the decode tasks.
 #pragma once
+#include <cuda_fp8.h>
+
 #include "mk_common.cuh"
 
 namespace vdc {
@@ -166,8 +168,51 @@ __device__ __forceinline__ void gemv_chunk(const uint8_t* w, const uint8_t* x, i
   }
 }
 
+// Same for e4m3 weights (one byte each, per-row fp32 scale applied by the caller):
+// 16 weights per lane and step, converted two at a time to fp16 and widened to
+// fp32 in registers; products accumulate in fp32.
+__device__ __forceinline__ float2 e4m3x2_to_float2(uint32_t pair16) {
+  const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)pair16, __NV_E4M3);
+  return __half22float2(*reinterpret_cast<const __half2*>(&h));
+}
+
 template <int R>
-__device__ void task_gemv_rows(Compute& q, int n_chunks, int mode, bool accumulate, bool norm, int K, int row_base) {
+__device__ __forceinline__ void gemv_chunk_fp8(const uint8_t* w, const uint8_t* x, int K, int lane, float (&out)[R]) {
+  constexpr int NA = R >= 8 ? 1 : (R == 4 ? 2 : 4);
+  float2 acc[R][NA];
+#pragma unroll
+  for (int r = 0; r < R; ++r)
+#pragma unroll
+    for (int a = 0; a < NA; ++a) acc[r][a] = make_float2(0.f, 0.f);
+  const int iters = K >> 9;  // 512 weights per warp step
+  for (int it = 0; it < iters; ++it) {
+    const int e0 = (it << 9) + (lane << 4);  // first element of this lane
+    const uint4 xa = lds128(x + e0 * 2), xb = lds128(x + e0 * 2 + 16);
+    const float2 xf[8] = {bf2(xa.x), bf2(xa.y), bf2(xa.z), bf2(xa.w), bf2(xb.x), bf2(xb.y), bf2(xb.z), bf2(xb.w)};
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const uint4 wv = lds128(w + (size_t)r * K + e0);
+      const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        acc[r][(2 * j) % NA] = __ffma2_rn(e4m3x2_to_float2(ww[j] & 0xFFFFu), xf[2 * j], acc[r][(2 * j) % NA]);
+        acc[r][(2 * j + 1) % NA] = __ffma2_rn(e4m3x2_to_float2(ww[j] >> 16), xf[2 * j + 1], acc[r][(2 * j + 1) % NA]);
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    float v = acc[r][0].x + acc[r][0].y;
+#pragma unroll
+    for (int a = 1; a < NA; ++a) v += acc[r][a].x + acc[r][a].y;
+    out[r] = warp_sum(v);
+  }
+}
+
+// scales: nullptr for bf16 weights; for e4m3 weights the fp32 per-row scales of the task's rows.
+template <int R>
+__device__ void task_gemv_rows(Compute& q, int n_chunks, int mode, bool accumulate, bool norm, int K, int row_base,
+                               const float* scales = nullptr) {
   Shared* sh = q.sh;
   const Ctx& c = q.c;
   int normw_mask = 0;
@@ -221,9 +266,15 @@ __device__ void task_gemv_rows(Compute& q, int n_chunks, int mode, bool accumula
     if (w_mask == kPopAbort) break;
     const uint8_t* w = (const uint8_t*)slot_ptr(c, first_slot(w_mask));
     float acc[R];
-    gemv_chunk<R>(w, x, K, q.lane, acc);
-    q.warp_done((unsigned)i, (unsigned)n_chunks, w_mask);
     const int row0 = i * R;
+    if (scales) {
+      gemv_chunk_fp8<R>(w, x, K, q.lane, acc);
+#pragma unroll
+      for (int r = 0; r < R; ++r) acc[r] *= __ldg(scales + row0 + r);
+    } else {
+      gemv_chunk<R>(w, x, K, q.lane, acc);
+    }
+    q.warp_done((unsigned)i, (unsigned)n_chunks, w_mask);
     if (mode == VDC_GEMV_MODE_SILU_PAIRS) {
       float g = 0.f, u = 0.f;
 #pragma unroll

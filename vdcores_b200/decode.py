@@ -78,25 +78,42 @@ class DenseWeights:
     k_norm: Optional[List[torch.Tensor]] = None
 
 
-def rows_per_chunk(K: int, even: bool = False) -> int:
-    """Largest power-of-two row count whose bf16 rows fit one 32 KB bulk copy."""
+def rows_per_chunk(K: int, even: bool = False, wbytes: int = 2) -> int:
+    """Largest power-of-two row count whose rows (wbytes per weight) fit one 32 KB bulk copy."""
     r = 16
-    while r > 1 and r * K * 2 > 32768:
+    while r > 1 and r * K * wbytes > 32768:
         r //= 2
-    if r * K * 2 > 32768 or (even and r < 2):
+    if r * K * wbytes > 32768 or (even and r < 2):
         raise ValueError(f"K={K} rows do not fit the 32 KB chunk limit")
     return r
+
+
+FP8_MAX = 448.0
+
+
+def quantize_fp8_rows(w: torch.Tensor):
+    """Per-output-channel e4m3: scale[row] = max|w[row]| / 448 (fp32), q = e4m3(w / scale).
+    Works on [..., rows, K]; returns (uint8 view of the codes, fp32 scales)."""
+    wf = w.float()
+    scale = wf.abs().amax(dim=-1).clamp_min(1e-12) / FP8_MAX
+    q = (wf / scale[..., None]).to(torch.float8_e4m3fn)
+    return q.view(torch.uint8), scale.contiguous()
 
 
 class DecodeEngine:
     def __init__(self, cfg: DecodeConfig, max_seq: int, device="cuda", num_sms: Optional[int] = None,
                  taps: bool = False, page_perm_seed: Optional[int] = None, max_steps: int = 4096,
-                 timeout_ns: int = 0, l2_prefetch_bytes: int = 0):
+                 timeout_ns: int = 0, l2_prefetch_bytes: int = 0, wkind: str = "bf16"):
         assert cfg.head_dim == isa.HEAD_DIM, "the attention task is built for head_dim 128"
         assert cfg.group in (4, 8), "GQA group size must be 4 or 8"
         assert cfg.n_kv_heads & (cfg.n_kv_heads - 1) == 0, "n_kv_heads must be a power of two"
         assert cfg.hidden % 256 == 0 and cfg.ffn % 256 == 0 and cfg.q_width % 256 == 0
+        assert wkind in ("bf16", "fp8")
         self.cfg = cfg
+        self.wkind = wkind                  # storage of the layer projections; embed / norms / lm_head stay bf16
+        self.wbytes = 1 if wkind == "fp8" else 2
+        if wkind == "fp8":
+            assert cfg.hidden % 512 == 0 and cfg.ffn % 512 == 0 and cfg.q_width % 512 == 0
         self.dev = torch.device(device)
         props = torch.cuda.get_device_properties(self.dev)
         self.num_sms = num_sms or props.multi_processor_count
@@ -162,27 +179,51 @@ class DecodeEngine:
 
     # ------------------------------------------------------------------ weights
     def load_weights(self, w: DenseWeights):
+        """Packs (and for fp8 quantises) on the device the weights arrive on, then
+        moves the result to the GPU: CPU weights give the exact CPU conversion
+        (torch's fp8 cast is not bit-identical between CPU and CUDA)."""
         cfg, dev = self.cfg, self.dev
         L = cfg.n_layers
-        to = lambda t: t.to(device=dev, dtype=BF16).contiguous()
-        self.embed = to(w.embed)
-        self.lm_head = to(w.lm_head)
-        self.norm_w = to(w.norm)
-        self.ln1 = torch.stack([to(t) for t in w.ln1])
-        self.ln2 = torch.stack([to(t) for t in w.ln2])
-        pm = self.qkv_perm.to(dev)
+        to = lambda t: t.to(dtype=BF16).contiguous()
+        pm = self.qkv_perm.to(w.wq[0].device)
         self.wqkv = torch.stack([torch.cat((to(w.wq[l]), to(w.wk[l]), to(w.wv[l])), dim=0)[pm] for l in range(L)])
         self.wo = torch.stack([to(w.wo[l]) for l in range(L)])
         # gate and up rows interleaved: row 2j = gate_j, row 2j+1 = up_j
         self.wgu = torch.stack([torch.stack((to(w.gate[l]), to(w.up[l])), dim=1).reshape(2 * cfg.ffn, cfg.hidden)
                                 for l in range(L)])
         self.wd = torch.stack([to(w.down[l]) for l in range(L)])
+        self._quantize()
+        for name in ("wqkv", "wo", "wgu", "wd"):
+            setattr(self, name, getattr(self, name).to(dev))
+        self.scales = {k: v.to(dev) for k, v in self.scales.items()}
+        self.embed = to(w.embed).to(dev)
+        self.lm_head = to(w.lm_head).to(dev)
+        self.norm_w = to(w.norm).to(dev)
+        self.ln1 = torch.stack([to(t) for t in w.ln1]).to(dev)
+        self.ln2 = torch.stack([to(t) for t in w.ln2]).to(dev)
         if cfg.qk_norm:
-            self.qknorm = torch.stack([torch.cat((to(w.q_norm[l]), to(w.k_norm[l]))) for l in range(L)])
+            self.qknorm = torch.stack([torch.cat((to(w.q_norm[l]), to(w.k_norm[l]))) for l in range(L)]).to(dev)
         else:
             self.qknorm = None
         self.w = True
         self._build_program()
+
+    def _quantize(self):
+        """fp8: replaces the packed projection matrices by e4m3 codes + fp32 row scales."""
+        self.scales = {}
+        if self.wkind != "fp8":
+            return
+        for name in ("wqkv", "wo", "wgu", "wd"):
+            q, sc = quantize_fp8_rows(getattr(self, name))
+            setattr(self, name, q)
+            self.scales[name] = sc
+
+    def _dense(self, name: str, l: int) -> torch.Tensor:
+        """Layer l's projection as a bf16 matrix (PyTorch prefill path)."""
+        w = getattr(self, name)[l]
+        if self.wkind == "fp8":
+            return (w.view(torch.float8_e4m3fn).float() * self.scales[name][l][:, None]).to(BF16)
+        return w
 
     def init_random_weights(self, seed: int = 0, std: float = 0.02):
         """Random N(0, std) weights generated on the device (benchmarks)."""
@@ -205,10 +246,12 @@ class DecodeEngine:
         self.wd = rnd(L, H, F)
         self.qknorm = torch.ones(L, 2 * isa.HEAD_DIM, dtype=BF16, device=dev) if cfg.qk_norm else None
         self.w = True
+        self._quantize()
         self._build_program()
 
     def weight_bytes(self) -> int:
         ts = [self.lm_head, self.norm_w, self.ln1, self.ln2, self.wqkv, self.wo, self.wgu, self.wd]
+        ts += list(self.scales.values())
         if self.qknorm is not None:
             ts.append(self.qknorm)
         return sum(t.numel() * t.element_size() for t in ts) + self.cfg.hidden * 2
@@ -262,6 +305,8 @@ class DecodeEngine:
         assert 1 << page_shift == page_stride
         hid, qkv, ao, act = (t.data_ptr() for t in (self.hidden, self.qkv, self.attn_out, self.act))
         embed_src = lambda: Src(self.embed.data_ptr(), H * 2, indirect=(st + 4 * isa.ST_TOKEN, None, H * 2))
+        wb = self.wbytes
+        sc = lambda name, l, r0: (self.scales[name][l].data_ptr() + 4 * r0) if self.wkind == 'fp8' else None
         load = [0] * S
         plan = [[] for _ in range(S)]      # per SM: (emit(sm), weight segment or None)
 
@@ -272,12 +317,12 @@ class DecodeEngine:
         for l in range(L):
             # ---- QKV projection with fused input RMSNorm
             b_qkv = P.new_barrier()
-            R = rows_per_chunk(H)
-            for sm, u0, cnt in self._ranges(load, self.qkv_rows // R, R * H * 2):
+            R = rows_per_chunk(H, wbytes=wb)
+            for sm, u0, cnt in self._ranges(load, self.qkv_rows // R, R * H * wb):
                 r0, n = u0 * R, cnt * R
                 x = Src(hid, H * 2, wait=b_hid) if l > 0 else embed_src()
-                wa = self.wqkv[l].data_ptr() + r0 * H * 2
-                add_gemv(sm, (wa, n * H * 2), w_addr=wa, n_rows=n, K=H, R=R, x=x,
+                wa = self.wqkv[l].data_ptr() + r0 * H * wb
+                add_gemv(sm, (wa, n * H * wb), w_addr=wa, n_rows=n, K=H, R=R, x=x, fp8_scales=sc('wqkv', l, r0),
                          out=Dst(qkv + r0 * 2, n * 2, "store", release=b_qkv),
                          norm_w=Src(self.ln1[l].data_ptr(), H * 2), eps=cfg.eps)
             if l == 0:
@@ -311,30 +356,33 @@ class DecodeEngine:
             # ---- output projection, residual add into hidden
             b_o = P.new_barrier()
             K = cfg.q_width
-            R = rows_per_chunk(K)
-            for sm, u0, cnt in self._ranges(load, H // R, R * K * 2):
+            R = rows_per_chunk(K, wbytes=wb)
+            for sm, u0, cnt in self._ranges(load, H // R, R * K * wb):
                 r0, n = u0 * R, cnt * R
-                wa = self.wo[l].data_ptr() + r0 * K * 2
-                add_gemv(sm, (wa, n * K * 2), w_addr=wa, n_rows=n, K=K, R=R, x=Src(ao, K * 2, wait=b_merge),
+                wa = self.wo[l].data_ptr() + r0 * K * wb
+                add_gemv(sm, (wa, n * K * wb), w_addr=wa, n_rows=n, K=K, R=R, x=Src(ao, K * 2, wait=b_merge),
+                         fp8_scales=sc('wo', l, r0),
                          out=Dst(hid + r0 * 2, n * 2, "add_bf16", release=b_o))
 
             # ---- gate/up projection with fused post-attention RMSNorm and SiLU·mul
             b_gu = P.new_barrier()
-            R = rows_per_chunk(H, even=True)
-            for sm, u0, cnt in self._ranges(load, 2 * F // R, R * H * 2):
+            R = rows_per_chunk(H, even=True, wbytes=wb)
+            for sm, u0, cnt in self._ranges(load, 2 * F // R, R * H * wb):
                 r0, n = u0 * R, cnt * R
-                wa = self.wgu[l].data_ptr() + r0 * H * 2
-                add_gemv(sm, (wa, n * H * 2), w_addr=wa, n_rows=n, K=H, R=R, x=Src(hid, H * 2, wait=b_o),
+                wa = self.wgu[l].data_ptr() + r0 * H * wb
+                add_gemv(sm, (wa, n * H * wb), w_addr=wa, n_rows=n, K=H, R=R, x=Src(hid, H * 2, wait=b_o),
+                         fp8_scales=sc('wgu', l, r0),
                          out=Dst(act + (r0 // 2) * 2, n, "store", release=b_gu), mode=isa.GEMV_MODE_SILU_PAIRS,
                          norm_w=Src(self.ln2[l].data_ptr(), H * 2), eps=cfg.eps)
 
             # ---- down projection, residual add into hidden
             b_hid = P.new_barrier()
-            R = rows_per_chunk(F)
-            for sm, u0, cnt in self._ranges(load, H // R, R * F * 2):
+            R = rows_per_chunk(F, wbytes=wb)
+            for sm, u0, cnt in self._ranges(load, H // R, R * F * wb):
                 r0, n = u0 * R, cnt * R
-                wa = self.wd[l].data_ptr() + r0 * F * 2
-                add_gemv(sm, (wa, n * F * 2), w_addr=wa, n_rows=n, K=F, R=R, x=Src(act, F * 2, wait=b_gu),
+                wa = self.wd[l].data_ptr() + r0 * F * wb
+                add_gemv(sm, (wa, n * F * wb), w_addr=wa, n_rows=n, K=F, R=R, x=Src(act, F * 2, wait=b_gu),
+                         fp8_scales=sc('wd', l, r0),
                          out=Dst(hid + r0 * 2, n * 2, "add_bf16", release=b_hid))
 
         # ---- final norm + vocabulary projection + per-SM argmax candidates
@@ -471,7 +519,7 @@ class DecodeEngine:
         ks, vs = [], []
         for l in range(cfg.n_layers):
             x = norm(h, self.ln1[l], cfg.eps)
-            qkv = (x @ self.wqkv[l].t())[:, self.qkv_inv.to(dev)]
+            qkv = (x @ self._dense('wqkv', l).t())[:, self.qkv_inv.to(dev)]
             q = qkv[:, :cfg.q_width].view(T, cfg.n_heads, D)
             k = qkv[:, cfg.q_width:cfg.q_width + cfg.kv_width].view(T, cfg.n_kv_heads, D)
             v = qkv[:, cfg.q_width + cfg.kv_width:].view(T, cfg.n_kv_heads, D)
@@ -485,11 +533,11 @@ class DecodeEngine:
             o = torch.nn.functional.scaled_dot_product_attention(
                 q.transpose(0, 1)[None], k.transpose(0, 1)[None], v.transpose(0, 1)[None], is_causal=True,
                 enable_gqa=True)[0].transpose(0, 1).reshape(T, cfg.q_width)
-            h = h + o @ self.wo[l].t()
+            h = h + o @ self._dense('wo', l).t()
             x = norm(h, self.ln2[l], cfg.eps)
-            gu = x @ self.wgu[l].t()
+            gu = x @ self._dense('wgu', l).t()
             a = torch.nn.functional.silu(gu[:, 0::2]) * gu[:, 1::2]
-            h = h + a @ self.wd[l].t()
+            h = h + a @ self._dense('wd', l).t()
         self.load_kv(ks, vs)
         hn = norm(h[-1], self.norm_w, cfg.eps)
         logits = hn @ self.lm_head.t()
