@@ -284,7 +284,7 @@ def main():
     ap.add_argument("--impl", default="vdcores_b200", choices=["vdcores_b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer arm (profiling runs)")
-    ap.add_argument("--wkind", default="bf16", choices=["bf16", "fp8"],
+    ap.add_argument("--wkind", default="bf16", choices=["bf16", "fp8", "nvfp4"],
                     help="storage of the layer projections (fp8: e4m3 + per-row fp32 scales; reported, not the headline)")
     ap.add_argument("--layers", type=int, default=32,
                     help="profiling only: a model with fewer layers of the same shape (the JSON line says so)")

@@ -12,6 +12,9 @@ def small_cfg(kind: str) -> O.DecodeConfig:
     if kind == "qwen3":
         return O.DecodeConfig(hidden=512, n_heads=8, n_kv_heads=1, head_dim=128, ffn=768, vocab=1024,
                               n_layers=2, eps=1e-6, theta=1e6, qk_norm=True)
+    if kind == "qwen3_1k":      # K multiples of 1024, as the NVFP4 rows need
+        return O.DecodeConfig(hidden=1024, n_heads=8, n_kv_heads=1, head_dim=128, ffn=1024, vocab=1024,
+                              n_layers=2, eps=1e-6, theta=1e6, qk_norm=True)
     raise ValueError(kind)
 
 

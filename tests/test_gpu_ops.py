@@ -299,3 +299,28 @@ def test_gemv_fp8_store(cuda_device, M, K, R, n_sms):
                out=Dst(y.data_ptr() + r0 * 2, per * 2, "store"), fp8_scales=sc.data_ptr() + 4 * r0)
     run_program(P, dev)
     assert O.rel_l2(y.cpu(), lin(x[None])[0]) < 3e-3
+
+
+@pytest.mark.parametrize("M,K,R,n_sms", [(128, 4096, 8, 2), (32, 12288, 4, 2), (64, 1024, 16, 1)])
+def test_gemv_nvfp4_store(cuda_device, M, K, R, n_sms):
+    """NVFP4 rows (e2m1 pairs + e4m3 block scales per 16 + fp32 tensor scale); block
+    dots in half precision, fp32 across blocks.  Against the oracle's fp32 dequantised product."""
+    from vdcores_b200.decode import quantize_nvfp4_rows
+    from vdcores_b200.program import Dst, Program, Src
+    dev = cuda_device
+    w, x = seeded((M, K), 41, 0.02), seeded((K,), 42)
+    lin = O.QLinear.make(w, "nvfp4")
+    rows, ts = quantize_nvfp4_rows(w)
+    assert torch.equal(rows[:, :K // 2], lin.q)
+    rows, xd = rows.to(dev), x.to(dev)
+    sc = ts.expand(M).contiguous().to(dev)
+    rb = K // 2 + K // 16
+    y = torch.zeros(M, dtype=BF16, device=dev)
+    P = Program(n_sms)
+    per = M // n_sms
+    for sm in range(n_sms):
+        r0 = sm * per
+        P.gemv(sm, w_addr=rows.data_ptr() + r0 * rb, n_rows=per, K=K, R=R, x=Src(xd.data_ptr(), K * 2),
+               out=Dst(y.data_ptr() + r0 * 2, per * 2, "store"), nvfp4_scales=sc.data_ptr() + 4 * r0)
+    run_program(P, dev)
+    assert O.rel_l2(y.cpu(), lin(x[None])[0]) < 5e-3

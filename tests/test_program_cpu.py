@@ -83,3 +83,21 @@ def test_ring_overflow_is_reported():
         P.load(0, Src(0x1000, 256))
     with pytest.raises(ValueError):
         P.finalize()
+
+
+def test_engine_quantisers_match_the_oracle_codecs():
+    """The engine's own FP8 / NVFP4 encoders (product code) produce exactly the
+    oracle's codes, block scales and tensor scales on the CPU."""
+    import torch
+    from oracle import decode_oracle as O
+    from vdcores_b200.decode import quantize_fp8_rows, quantize_nvfp4_rows
+    g = torch.Generator().manual_seed(3)
+    w = (torch.randn(48, 1024, generator=g) * 0.02).to(torch.bfloat16)
+    w[5, 100:116] = 0                                  # an all-zero block
+    q, s = quantize_fp8_rows(w)
+    oq, os_ = O.fp8_quantize(w)
+    assert torch.equal(q, oq.view(torch.uint8)) and torch.equal(s, os_)
+    rows, ts = quantize_nvfp4_rows(w)
+    op, obs, ots = O.nvfp4_quantize(w)
+    assert torch.equal(rows[:, :512], op) and torch.equal(rows[:, 512:], obs.view(torch.uint8))
+    assert float(ts) == float(ots)

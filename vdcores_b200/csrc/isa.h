@@ -80,6 +80,7 @@
   X(OP_COPY, 0x7003)                                                                   \
   X(OP_GEMV_ROWS_BF16, 0x7200)                                                         \
   X(OP_GEMV_ROWS_FP8, 0x7201)                                                          \
+  X(OP_GEMV_ROWS_NVFP4, 0x7202)                                                        \
   X(OP_ATTN_DECODE_PAGED_G4, 0x7210)                                                   \
   X(OP_ATTN_DECODE_PAGED_G8, 0x7211)                                                   \
   X(OP_ARGMAX_FINAL, 0x7220)                                                          \
@@ -95,6 +96,9 @@
 //
 // GEMV_ROWS_FP8 (3 words): as GEMV_ROWS_BF16 for e4m3 weights (K a multiple of 512, one byte per
 // weight), third word = 48-bit address of the fp32 per-row scales of the task's first row.
+//
+// GEMV_ROWS_NVFP4 (3 words): rows of K/2 bytes e2m1 pairs + K/16 e4m3 block scales (K a multiple
+// of 1024); third word as for FP8 (fp32 per-row scale = the tensor scale of the row's matrix).
 //
 // ATTN_DECODE_PAGED words: [max_pages, base_page, flags] [qk-norm eps hi, lo, n_splits]
 // then six 48-bit addresses, low piece first: state block, this head's rows in K page 0,

@@ -1,5 +1,6 @@
 // Compute virtual core of the megakernel: queue access and the decode tasks.
 #pragma once
+#include <cuda_fp4.h>
 #include <cuda_fp8.h>
 
 #include "mk_common.cuh"
@@ -209,10 +210,63 @@ __device__ __forceinline__ void gemv_chunk_fp8(const uint8_t* w, const uint8_t* 
   }
 }
 
-// scales: nullptr for bf16 weights; for e4m3 weights the fp32 per-row scales of the task's rows.
+// NVFP4 rows: K/2 bytes of e2m1 pairs (element 2i in the low nibble) followed by
+// K/16 e4m3 block scales, one per 16 weights.  The activation vector has been
+// converted to fp16 in place.  Each lane takes 32 weights (two blocks) per step:
+// the 16 products of a block are accumulated with half2 FMAs, the block sum is
+// widened, multiplied by the block scale and accumulated in fp32.  The per-row
+// fp32 scale (the tensor scale) is applied by the caller.
+__device__ __forceinline__ __half2 e2m1x2_to_half2(uint32_t byte) {
+  const __half2_raw h = __nv_cvt_fp4x2_to_halfraw2((__nv_fp4x2_storage_t)byte, __NV_E2M1);
+  return *reinterpret_cast<const __half2*>(&h);
+}
+__device__ __forceinline__ float e4m3_to_float(uint32_t byte) {
+  const __half_raw h = __nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)byte, __NV_E4M3);
+  return __half2float(*reinterpret_cast<const __half*>(&h));
+}
+
+template <int R>
+__device__ __forceinline__ void gemv_chunk_nvfp4(const uint8_t* w, const uint8_t* x16, int K, int lane,
+                                                 float (&out)[R]) {
+  const int row_bytes = (K >> 1) + (K >> 4);
+  float acc[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) acc[r] = 0.f;
+  const int iters = K >> 10;  // 1024 weights per warp step
+  for (int it = 0; it < iters; ++it) {
+    const int e0 = (it << 10) + (lane << 5);  // first element of this lane
+    uint4 xv[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) xv[j] = lds128(x16 + e0 * 2 + 16 * j);
+    const __half2* xh = reinterpret_cast<const __half2*>(xv);  // 16 half2 = 32 activations
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const uint8_t* row = w + (size_t)r * row_bytes;
+      const uint4 cv = lds128(row + (e0 >> 1));
+      const uint32_t sc2 = *reinterpret_cast<const uint16_t*>(row + (K >> 1) + (e0 >> 4));
+      const uint32_t cw[4] = {cv.x, cv.y, cv.z, cv.w};
+#pragma unroll
+      for (int b = 0; b < 2; ++b) {  // two blocks of 16 weights = 8 bytes each
+        __half2 s0 = __float2half2_rn(0.f), s1 = s0;
+#pragma unroll
+        for (int j = 0; j < 8; j += 2) {
+          const uint32_t word = cw[b * 2 + (j >> 2)];
+          s0 = __hfma2(e2m1x2_to_half2((word >> (8 * (j & 3))) & 0xFFu), xh[b * 8 + j], s0);
+          s1 = __hfma2(e2m1x2_to_half2((word >> (8 * ((j + 1) & 3))) & 0xFFu), xh[b * 8 + j + 1], s1);
+        }
+        const float2 f = __half22float2(__hadd2(s0, s1));
+        acc[r] = fmaf(f.x + f.y, e4m3_to_float((sc2 >> (8 * b)) & 0xFFu), acc[r]);
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < R; ++r) out[r] = warp_sum(acc[r]);
+}
+
+// wfmt: 0 bf16, 1 e4m3 (scales = fp32 per-row scales of the task's rows), 2 NVFP4 (scales likewise).
 template <int R>
 __device__ void task_gemv_rows(Compute& q, int n_chunks, int mode, bool accumulate, bool norm, int K, int row_base,
-                               const float* scales = nullptr) {
+                               const float* scales = nullptr, int wfmt = 0) {
   Shared* sh = q.sh;
   const Ctx& c = q.c;
   int normw_mask = 0;
@@ -257,6 +311,15 @@ __device__ void task_gemv_rows(Compute& q, int n_chunks, int mode, bool accumula
     }
     // the sync inside warp_phase_begin publishes the normalised vector
   }
+  if (wfmt == 2) {
+    // NVFP4 block dots run in half precision: the activation vector becomes fp16 in place
+    if (norm) compute_sync();
+    for (int i = q.tid * 2; i < K; i += kCT * 2) {
+      const uint32_t xv = *reinterpret_cast<const uint32_t*>(x + i * 2);
+      const __half2 h = __floats2half2_rn(bf_lo(xv), bf_hi(xv));
+      *reinterpret_cast<__half2*>(x + i * 2) = h;
+    }
+  }
 
   ArgBest best = {-INFINITY, 0x7fffffff};
   q.warp_phase_begin((unsigned)n_chunks);  // its sync also publishes the normalised vector
@@ -267,7 +330,11 @@ __device__ void task_gemv_rows(Compute& q, int n_chunks, int mode, bool accumula
     const uint8_t* w = (const uint8_t*)slot_ptr(c, first_slot(w_mask));
     float acc[R];
     const int row0 = i * R;
-    if (scales) {
+    if (wfmt == 2) {
+      gemv_chunk_nvfp4<R>(w, x, K, q.lane, acc);
+#pragma unroll
+      for (int r = 0; r < R; ++r) acc[r] *= __ldg(scales + row0 + r);
+    } else if (wfmt == 1) {
       gemv_chunk_fp8<R>(w, x, K, q.lane, acc);
 #pragma unroll
       for (int r = 0; r < R; ++r) acc[r] *= __ldg(scales + row0 + r);

@@ -78,12 +78,13 @@ class DenseWeights:
     k_norm: Optional[List[torch.Tensor]] = None
 
 
-def rows_per_chunk(K: int, even: bool = False, wbytes: int = 2) -> int:
-    """Largest power-of-two row count whose rows (wbytes per weight) fit one 32 KB bulk copy."""
+def rows_per_chunk(K: int, even: bool = False, row_bytes: Optional[int] = None) -> int:
+    """Largest power-of-two row count whose rows (bf16 unless row_bytes is given) fit one 32 KB bulk copy."""
+    row_bytes = 2 * K if row_bytes is None else row_bytes
     r = 16
-    while r > 1 and r * K * wbytes > 32768:
+    while r > 1 and r * row_bytes > 32768:
         r //= 2
-    if r * K * wbytes > 32768 or (even and r < 2):
+    if r * row_bytes > 32768 or (even and r < 2):
         raise ValueError(f"K={K} rows do not fit the 32 KB chunk limit")
     return r
 
@@ -100,6 +101,34 @@ def quantize_fp8_rows(w: torch.Tensor):
     return q.view(torch.uint8), scale.contiguous()
 
 
+_E2M1 = [0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0]
+
+
+def quantize_nvfp4_rows(w: torch.Tensor):
+    """NVFP4 of one [M, K] matrix: e2m1 values (round to nearest, ties to the even
+    code), one e4m3 scale per 16 weights along K, one fp32 scale for the tensor.
+    Returns (uint8 rows [M, K/2 + K/16]: packed pairs with element 2i in the low
+    nibble, then the block scales; fp32 tensor scale)."""
+    wf = w.float()
+    M, K = wf.shape
+    assert K % 16 == 0
+    grid = torch.tensor(_E2M1, device=wf.device)
+    tscale = (wf.abs().max().clamp_min(1e-12) / (6.0 * FP8_MAX)).float()
+    blocks = wf.view(M, K // 16, 16)
+    bscale = (blocks.abs().amax(dim=-1) / 6.0 / tscale).to(torch.float8_e4m3fn)
+    v = blocks / (bscale.float() * tscale).clamp_min(1e-30)[..., None]
+    a = v.abs().clamp(max=6.0)
+    mids = (grid[1:] + grid[:-1]) / 2
+    idx = torch.zeros_like(a, dtype=torch.int64)
+    for i in range(7):
+        idx += ((a > mids[i]) | ((a == mids[i]) & ((i + 1) % 2 == 0))).long()
+    sign = (v < 0) | ((v == 0) & torch.signbit(v))
+    codes = (idx | (sign.long() << 3)).to(torch.uint8).view(M, K)
+    packed = codes[:, 0::2] | (codes[:, 1::2] << 4)
+    rows = torch.cat((packed, bscale.view(torch.uint8)), dim=1).contiguous()
+    return rows, tscale
+
+
 class DecodeEngine:
     def __init__(self, cfg: DecodeConfig, max_seq: int, device="cuda", num_sms: Optional[int] = None,
                  taps: bool = False, page_perm_seed: Optional[int] = None, max_steps: int = 4096,
@@ -108,12 +137,11 @@ class DecodeEngine:
         assert cfg.group in (4, 8), "GQA group size must be 4 or 8"
         assert cfg.n_kv_heads & (cfg.n_kv_heads - 1) == 0, "n_kv_heads must be a power of two"
         assert cfg.hidden % 256 == 0 and cfg.ffn % 256 == 0 and cfg.q_width % 256 == 0
-        assert wkind in ("bf16", "fp8")
+        assert wkind in ("bf16", "fp8", "nvfp4")
         self.cfg = cfg
         self.wkind = wkind                  # storage of the layer projections; embed / norms / lm_head stay bf16
-        self.wbytes = 1 if wkind == "fp8" else 2
-        if wkind == "fp8":
-            assert cfg.hidden % 512 == 0 and cfg.ffn % 512 == 0 and cfg.q_width % 512 == 0
+        kmult = {"bf16": 256, "fp8": 512, "nvfp4": 1024}[wkind]
+        assert cfg.hidden % kmult == 0 and cfg.ffn % kmult == 0 and cfg.q_width % kmult == 0
         self.dev = torch.device(device)
         props = torch.cuda.get_device_properties(self.dev)
         self.num_sms = num_sms or props.multi_processor_count
@@ -178,24 +206,60 @@ class DecodeEngine:
         self.steps_done = 0
 
     # ------------------------------------------------------------------ weights
+    def row_bytes(self, K: int) -> int:
+        """Bytes one weight row of K inputs occupies in the layer projections' storage."""
+        return {"bf16": 2 * K, "fp8": K, "nvfp4": K // 2 + K // 16}[self.wkind]
+
+    def _encode(self, w: torch.Tensor):
+        """One [M, K] bf16 matrix -> (stored rows, fp32 per-row scale or None), on w's device."""
+        if self.wkind == "bf16":
+            return w, None
+        if self.wkind == "fp8":
+            return quantize_fp8_rows(w)
+        rows, ts = quantize_nvfp4_rows(w)
+        return rows, ts.expand(w.shape[0]).contiguous()
+
+    def _dense(self, name: str, l: int) -> torch.Tensor:
+        """Layer l's projection as a bf16 matrix (PyTorch prefill path)."""
+        w = getattr(self, name)[l]
+        if self.wkind == "fp8":
+            return (w.view(torch.float8_e4m3fn).float() * self.scales[name][l][:, None]).to(BF16)
+        if self.wkind == "nvfp4":
+            K = w.shape[1] * 16 // 9
+            codes = w[:, :K // 2]
+            grid = torch.tensor(_E2M1 + [-x for x in _E2M1], device=w.device)
+            vals = torch.stack((grid[(codes & 0xF).long()], grid[(codes >> 4).long()]), dim=-1).view(w.shape[0], K)
+            bs = w[:, K // 2:].contiguous().view(torch.float8_e4m3fn).float()
+            return (vals.view(w.shape[0], K // 16, 16) * (bs * self.scales[name][l][:, None])[..., None]
+                    ).view(w.shape[0], K).to(BF16)
+        return w
+
     def load_weights(self, w: DenseWeights):
-        """Packs (and for fp8 quantises) on the device the weights arrive on, then
-        moves the result to the GPU: CPU weights give the exact CPU conversion
-        (torch's fp8 cast is not bit-identical between CPU and CUDA)."""
+        """Encodes (bf16 / fp8 / NVFP4, each source matrix on its own, like the
+        oracle) and packs on the device the weights arrive on, then moves the result
+        to the GPU: CPU weights give the exact CPU conversions (torch's fp8 cast is
+        not bit-identical between CPU and CUDA)."""
         cfg, dev = self.cfg, self.dev
         L = cfg.n_layers
         to = lambda t: t.to(dtype=BF16).contiguous()
         pm = self.qkv_perm.to(w.wq[0].device)
-        self.wqkv = torch.stack([torch.cat((to(w.wq[l]), to(w.wk[l]), to(w.wv[l])), dim=0)[pm] for l in range(L)])
-        self.wo = torch.stack([to(w.wo[l]) for l in range(L)])
-        # gate and up rows interleaved: row 2j = gate_j, row 2j+1 = up_j
-        self.wgu = torch.stack([torch.stack((to(w.gate[l]), to(w.up[l])), dim=1).reshape(2 * cfg.ffn, cfg.hidden)
-                                for l in range(L)])
-        self.wd = torch.stack([to(w.down[l]) for l in range(L)])
-        self._quantize()
-        for name in ("wqkv", "wo", "wgu", "wd"):
-            setattr(self, name, getattr(self, name).to(dev))
-        self.scales = {k: v.to(dev) for k, v in self.scales.items()}
+        cat = lambda parts: (torch.cat([p[0] for p in parts], 0),
+                             None if parts[0][1] is None else torch.cat([p[1] for p in parts], 0))
+        packed = {"wqkv": [], "wo": [], "wgu": [], "wd": []}
+        for l in range(L):
+            rows, sc = cat([self._encode(to(w.wq[l])), self._encode(to(w.wk[l])), self._encode(to(w.wv[l]))])
+            packed["wqkv"].append((rows[pm], None if sc is None else sc[pm]))
+            packed["wo"].append(self._encode(to(w.wo[l])))
+            # gate and up rows interleaved: row 2j = gate_j, row 2j+1 = up_j
+            (g, gs), (u, us) = self._encode(to(w.gate[l])), self._encode(to(w.up[l]))
+            packed["wgu"].append((torch.stack((g, u), dim=1).reshape(2 * cfg.ffn, g.shape[1]),
+                                  None if gs is None else torch.stack((gs, us), dim=1).reshape(-1)))
+            packed["wd"].append(self._encode(to(w.down[l])))
+        self.scales = {}
+        for name, parts in packed.items():
+            setattr(self, name, torch.stack([p[0] for p in parts]).to(dev))
+            if parts[0][1] is not None:
+                self.scales[name] = torch.stack([p[1] for p in parts]).to(dev)
         self.embed = to(w.embed).to(dev)
         self.lm_head = to(w.lm_head).to(dev)
         self.norm_w = to(w.norm).to(dev)
@@ -209,21 +273,16 @@ class DecodeEngine:
         self._build_program()
 
     def _quantize(self):
-        """fp8: replaces the packed projection matrices by e4m3 codes + fp32 row scales."""
+        """Random-weight path: replaces the packed bf16 projections by their stored form."""
         self.scales = {}
-        if self.wkind != "fp8":
+        if self.wkind == "bf16":
             return
         for name in ("wqkv", "wo", "wgu", "wd"):
-            q, sc = quantize_fp8_rows(getattr(self, name))
-            setattr(self, name, q)
-            self.scales[name] = sc
-
-    def _dense(self, name: str, l: int) -> torch.Tensor:
-        """Layer l's projection as a bf16 matrix (PyTorch prefill path)."""
-        w = getattr(self, name)[l]
-        if self.wkind == "fp8":
-            return (w.view(torch.float8_e4m3fn).float() * self.scales[name][l][:, None]).to(BF16)
-        return w
+            w = getattr(self, name)
+            parts = [self._encode(w[l]) for l in range(w.shape[0])]
+            setattr(self, name, torch.stack([p[0] for p in parts]))
+            self.scales[name] = torch.stack([p[1] for p in parts])
+            del w
 
     def init_random_weights(self, seed: int = 0, std: float = 0.02):
         """Random N(0, std) weights generated on the device (benchmarks)."""
@@ -305,8 +364,10 @@ class DecodeEngine:
         assert 1 << page_shift == page_stride
         hid, qkv, ao, act = (t.data_ptr() for t in (self.hidden, self.qkv, self.attn_out, self.act))
         embed_src = lambda: Src(self.embed.data_ptr(), H * 2, indirect=(st + 4 * isa.ST_TOKEN, None, H * 2))
-        wb = self.wbytes
-        sc = lambda name, l, r0: (self.scales[name][l].data_ptr() + 4 * r0) if self.wkind == 'fp8' else None
+        rb = self.row_bytes
+        rpc = lambda K, even=False: rows_per_chunk(K, even, row_bytes=rb(K))
+        skey = {'fp8': 'fp8_scales', 'nvfp4': 'nvfp4_scales'}.get(self.wkind)
+        sk = lambda name, l, r0: {skey: self.scales[name][l].data_ptr() + 4 * r0} if skey else {}
         load = [0] * S
         plan = [[] for _ in range(S)]      # per SM: (emit(sm), weight segment or None)
 
@@ -317,12 +378,12 @@ class DecodeEngine:
         for l in range(L):
             # ---- QKV projection with fused input RMSNorm
             b_qkv = P.new_barrier()
-            R = rows_per_chunk(H, wbytes=wb)
-            for sm, u0, cnt in self._ranges(load, self.qkv_rows // R, R * H * wb):
+            R = rpc(H)
+            for sm, u0, cnt in self._ranges(load, self.qkv_rows // R, R * rb(H)):
                 r0, n = u0 * R, cnt * R
                 x = Src(hid, H * 2, wait=b_hid) if l > 0 else embed_src()
-                wa = self.wqkv[l].data_ptr() + r0 * H * wb
-                add_gemv(sm, (wa, n * H * wb), w_addr=wa, n_rows=n, K=H, R=R, x=x, fp8_scales=sc('wqkv', l, r0),
+                wa = self.wqkv[l].data_ptr() + r0 * rb(H)
+                add_gemv(sm, (wa, n * rb(H)), w_addr=wa, n_rows=n, K=H, R=R, x=x, **sk('wqkv', l, r0),
                          out=Dst(qkv + r0 * 2, n * 2, "store", release=b_qkv),
                          norm_w=Src(self.ln1[l].data_ptr(), H * 2), eps=cfg.eps)
             if l == 0:
@@ -356,33 +417,33 @@ class DecodeEngine:
             # ---- output projection, residual add into hidden
             b_o = P.new_barrier()
             K = cfg.q_width
-            R = rows_per_chunk(K, wbytes=wb)
-            for sm, u0, cnt in self._ranges(load, H // R, R * K * wb):
+            R = rpc(K)
+            for sm, u0, cnt in self._ranges(load, H // R, R * rb(K)):
                 r0, n = u0 * R, cnt * R
-                wa = self.wo[l].data_ptr() + r0 * K * wb
-                add_gemv(sm, (wa, n * K * wb), w_addr=wa, n_rows=n, K=K, R=R, x=Src(ao, K * 2, wait=b_merge),
-                         fp8_scales=sc('wo', l, r0),
+                wa = self.wo[l].data_ptr() + r0 * rb(K)
+                add_gemv(sm, (wa, n * rb(K)), w_addr=wa, n_rows=n, K=K, R=R, x=Src(ao, K * 2, wait=b_merge),
+                         **sk('wo', l, r0),
                          out=Dst(hid + r0 * 2, n * 2, "add_bf16", release=b_o))
 
             # ---- gate/up projection with fused post-attention RMSNorm and SiLU·mul
             b_gu = P.new_barrier()
-            R = rows_per_chunk(H, even=True, wbytes=wb)
-            for sm, u0, cnt in self._ranges(load, 2 * F // R, R * H * wb):
+            R = rpc(H, True)
+            for sm, u0, cnt in self._ranges(load, 2 * F // R, R * rb(H)):
                 r0, n = u0 * R, cnt * R
-                wa = self.wgu[l].data_ptr() + r0 * H * wb
-                add_gemv(sm, (wa, n * H * wb), w_addr=wa, n_rows=n, K=H, R=R, x=Src(hid, H * 2, wait=b_o),
-                         fp8_scales=sc('wgu', l, r0),
+                wa = self.wgu[l].data_ptr() + r0 * rb(H)
+                add_gemv(sm, (wa, n * rb(H)), w_addr=wa, n_rows=n, K=H, R=R, x=Src(hid, H * 2, wait=b_o),
+                         **sk('wgu', l, r0),
                          out=Dst(act + (r0 // 2) * 2, n, "store", release=b_gu), mode=isa.GEMV_MODE_SILU_PAIRS,
                          norm_w=Src(self.ln2[l].data_ptr(), H * 2), eps=cfg.eps)
 
             # ---- down projection, residual add into hidden
             b_hid = P.new_barrier()
-            R = rows_per_chunk(F, wbytes=wb)
-            for sm, u0, cnt in self._ranges(load, H // R, R * F * wb):
+            R = rpc(F)
+            for sm, u0, cnt in self._ranges(load, H // R, R * rb(F)):
                 r0, n = u0 * R, cnt * R
-                wa = self.wd[l].data_ptr() + r0 * F * wb
-                add_gemv(sm, (wa, n * F * wb), w_addr=wa, n_rows=n, K=F, R=R, x=Src(act, F * 2, wait=b_gu),
-                         fp8_scales=sc('wd', l, r0),
+                wa = self.wd[l].data_ptr() + r0 * rb(F)
+                add_gemv(sm, (wa, n * rb(F)), w_addr=wa, n_rows=n, K=F, R=R, x=Src(act, F * 2, wait=b_gu),
+                         **sk('wd', l, r0),
                          out=Dst(hid + r0 * 2, n * 2, "add_bf16", release=b_hid))
 
         # ---- final norm + vocabulary projection + per-SM argmax candidates

@@ -221,21 +221,28 @@ class Program:
 
     def gemv(self, sm, *, w_addr, n_rows, K, R, x: Src, out: Dst, mode=isa.GEMV_MODE_STORE,
              norm_w: Optional[Src] = None, eps: float = 0.0, pair_out: Optional[Dst] = None, row_base: int = 0,
-             stream: bool = False, fp8_scales: Optional[int] = None):
+             stream: bool = False, fp8_scales: Optional[int] = None, nvfp4_scales: Optional[int] = None):
         """y[0:n_rows] = W[0:n_rows, :K] @ x for the contiguous row block at w_addr
-        (bf16, or e4m3 with fp8_scales = address of the block's fp32 per-row
-        scales), streamed as chunks of R rows.  The task writes y straight to
+        (bf16; e4m3 with fp8_scales = address of the block's fp32 per-row scales;
+        or NVFP4 rows — K/2 code bytes + K/16 block scales — with nvfp4_scales =
+        address of the fp32 per-row tensor scales), streamed as chunks of R rows.  The task writes y straight to
         out.addr (kind 'store') or adds it there (kind 'add_bf16'); in SILU_PAIRS
         mode rows (2j, 2j+1) are (gate_j, up_j) and n_rows/2 values are written."""
-        wbytes = 1 if fp8_scales is not None else 2       # bytes per weight
-        assert K % (512 if fp8_scales is not None else 256) == 0 and K * wbytes * R <= 32768 and R in (1, 2, 4, 8, 16)
+        assert fp8_scales is None or nvfp4_scales is None
+        if nvfp4_scales is not None:
+            row_bytes, kmult, op, scales = K // 2 + K // 16, 1024, isa.OP_GEMV_ROWS_NVFP4, nvfp4_scales
+        elif fp8_scales is not None:
+            row_bytes, kmult, op, scales = K, 512, isa.OP_GEMV_ROWS_FP8, fp8_scales
+        else:
+            row_bytes, kmult, op, scales = 2 * K, 256, isa.OP_GEMV_ROWS_BF16, None
+        assert K % kmult == 0 and row_bytes * R <= 32768 and R in (1, 2, 4, 8, 16)
         assert n_rows % R == 0 and n_rows > 0
         assert mode != isa.GEMV_MODE_SILU_PAIRS or R % 2 == 0
         assert out.kind in ("store", "add_bf16") and out.addr % 2 == 0
         assert mode != isa.GEMV_MODE_STORE_F32 or (out.kind == "store" and out.addr % 4 == 0)
         n_chunks = n_rows // R
         assert n_chunks < 0xFFFF
-        chunk_bytes = R * K * wbytes
+        chunk_bytes = R * row_bytes
         assert x.nbytes == K * 2
         if norm_w is not None:
             self.load(sm, norm_w, default_port=1)
@@ -253,11 +260,11 @@ class Program:
             (isa.GEMV_ACC_BIT if out.kind == "add_bf16" else 0)
         a2 = (K // 256) | ((rb8 >> 16) << 8)
         e = f32_bits(eps)
-        self.comp(sm, isa.OP_GEMV_ROWS_FP8 if fp8_scales is not None else isa.OP_GEMV_ROWS_BF16, n_chunks, a1, a2)
+        self.comp(sm, op, n_chunks, a1, a2)
         self.comp(sm, isa.OP_EXT, e >> 16, e & 0xFFFF, rb8 & 0xFFFF)
-        if fp8_scales is not None:
-            assert fp8_scales % 4 == 0 and 0 <= fp8_scales < 1 << 48
-            self.comp(sm, isa.OP_EXT, fp8_scales & 0xFFFF, (fp8_scales >> 16) & 0xFFFF, (fp8_scales >> 32) & 0xFFFF)
+        if scales is not None:
+            assert scales % 4 == 0 and 0 <= scales < 1 << 48
+            self.comp(sm, isa.OP_EXT, scales & 0xFFFF, (scales >> 16) & 0xFFFF, (scales >> 32) & 0xFFFF)
 
     def add_releases(self, bar: int, n: int):
         """Declares n count-downs of `bar` that tasks perform themselves (not
