@@ -162,9 +162,13 @@ def run_gpu(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     K, W = args.steps, max(args.warmup, 3)
-    cfg = LLAMA31_8B
+    import dataclasses
+    from vdcores_b200.decode import QWEN3_8B
+    cfg = LLAMA31_8B if args.model == "llama31-8b" else QWEN3_8B
+    global PROMPT_LEN
+    if args.model == "qwen3-8b":
+        PROMPT_LEN = 4096
     if args.layers != 32:
-        import dataclasses
         cfg = dataclasses.replace(cfg, n_layers=args.layers)
     max_seq = ((PROMPT_LEN + W + K + 8 + 63) // 64) * 64
     g = torch.Generator().manual_seed(0)
@@ -250,11 +254,13 @@ def run_gpu(args):
     bytes_per_launch = eng.algorithmic_bytes(mid_pos)
     achieved = bytes_per_launch / (ms / K * 1e-3) / 1e9
     line = {
-        "metric": METRIC, "value": tokens_per_step * K / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": K,
+        "metric": METRIC if args.model == "llama31-8b" else METRIC.replace("Llama-3.1-8B", "Qwen3-8B"),
+        "value": tokens_per_step * K / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": K,
         "warmup": W, "ms_per_step": ms / K, "higher_is_better": True, "scaling": scaling, "vs_baseline": None,
         "dtype": args.wkind, "data": "synthetic",
-        "config": {"workload": "Llama-3.1-8B shape (32 layers, hidden 4096, 32q/8kv heads, FFN 14336, vocab 128256), "
-                               "bf16, batch 1, 2048-token prompt prefilled, greedy decode",
+        "config": {"workload": (f"{args.model} shape ({cfg.n_layers} layers, hidden {cfg.hidden}, {cfg.n_heads}q/"
+                                f"{cfg.n_kv_heads}kv heads, FFN {cfg.ffn}, vocab {cfg.vocab}), {args.wkind} projections, "
+                                f"batch 1, {PROMPT_LEN}-token prompt prefilled, greedy decode"),
                    "l2": "inputs larger than L2: every step streams ~15 GB of weights through a 126 MB L2",
                    "parallelism": parallelism,
                    "num_sms": eng.num_sms, "kv_splits": eng.n_splits, "first_tokens": tokens[:4],
@@ -286,6 +292,8 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer arm (profiling runs)")
     ap.add_argument("--wkind", default="bf16", choices=["bf16", "fp8", "nvfp4"],
                     help="storage of the layer projections (fp8: e4m3 + per-row fp32 scales; reported, not the headline)")
+    ap.add_argument("--model", default="llama31-8b", choices=["llama31-8b", "qwen3-8b"],
+                    help="shape of the random-init model (qwen3-8b: 36 layers, FFN 12288, per-head QK norm, 4096-token prompt)")
     ap.add_argument("--layers", type=int, default=32,
                     help="profiling only: a model with fewer layers of the same shape (the JSON line says so)")
     args = ap.parse_args()
