@@ -164,10 +164,10 @@ def run_gpu(args):
     K, W = args.steps, max(args.warmup, 3)
     import dataclasses
     from vdcores_b200.decode import QWEN3_8B
-    cfg = LLAMA31_8B if args.model == "llama31-8b" else QWEN3_8B
+    from vdcores_b200.decode import QWEN3_30B_A3B
+    cfg = {"llama31-8b": LLAMA31_8B, "qwen3-8b": QWEN3_8B, "qwen3-30b-a3b": QWEN3_30B_A3B}[args.model]
     global PROMPT_LEN
-    if args.model == "qwen3-8b":
-        PROMPT_LEN = 4096
+    PROMPT_LEN = {"llama31-8b": 2048, "qwen3-8b": 4096, "qwen3-30b-a3b": 1024}[args.model]
     if args.layers != 32:
         cfg = dataclasses.replace(cfg, n_layers=args.layers)
     max_seq = ((PROMPT_LEN + W + K + 8 + 63) // 64) * 64
@@ -254,7 +254,7 @@ def run_gpu(args):
     bytes_per_launch = eng.algorithmic_bytes(mid_pos)
     achieved = bytes_per_launch / (ms / K * 1e-3) / 1e9
     line = {
-        "metric": METRIC if args.model == "llama31-8b" else METRIC.replace("Llama-3.1-8B", "Qwen3-8B"),
+        "metric": METRIC if args.model == "llama31-8b" else METRIC.replace("Llama-3.1-8B", {"qwen3-8b": "Qwen3-8B", "qwen3-30b-a3b": "Qwen3-30B-A3B"}[args.model]),
         "value": tokens_per_step * K / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": K,
         "warmup": W, "ms_per_step": ms / K, "higher_is_better": True, "scaling": scaling, "vs_baseline": None,
         "dtype": args.wkind, "data": "synthetic",
@@ -292,7 +292,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer arm (profiling runs)")
     ap.add_argument("--wkind", default="bf16", choices=["bf16", "fp8", "nvfp4"],
                     help="storage of the layer projections (fp8: e4m3 + per-row fp32 scales; reported, not the headline)")
-    ap.add_argument("--model", default="llama31-8b", choices=["llama31-8b", "qwen3-8b"],
+    ap.add_argument("--model", default="llama31-8b", choices=["llama31-8b", "qwen3-8b", "qwen3-30b-a3b"],
                     help="shape of the random-init model (qwen3-8b: 36 layers, FFN 12288, per-head QK norm, 4096-token prompt)")
     ap.add_argument("--layers", type=int, default=32,
                     help="profiling only: a model with fewer layers of the same shape (the JSON line says so)")

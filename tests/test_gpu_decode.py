@@ -14,7 +14,8 @@ REL_L2_BF16 = 1e-2
 GAP = 1e-2
 
 
-@pytest.mark.parametrize("kind,prompt_len,n_steps", [("llama", 70, 6), ("qwen3", 130, 4), ("llama", 1, 3)])
+@pytest.mark.parametrize("kind,prompt_len,n_steps", [("llama", 70, 6), ("qwen3", 130, 4), ("llama", 1, 3),
+                                                     ("moe", 70, 4)])
 def test_decode_matches_oracle(cuda_device, kind, prompt_len, n_steps):
     from vdcores_b200.decode import DecodeEngine
     cfg = small_cfg(kind)

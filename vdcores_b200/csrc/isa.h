@@ -68,7 +68,8 @@
   X(OP_DYN_COUNT, VDC_MOP(25, 0))                                                      \
   X(OP_PREFETCH_L2, VDC_MOP(26, 0))                                                    \
   X(OP_STREAM_LIST, VDC_MOP(27, 0))                                                    \
-  X(OP_ALLOC_TMA_LOAD_1D_STREAM, VDC_MOP(28, VDC_F_ALLOCATE))
+  X(OP_ALLOC_TMA_LOAD_1D_STREAM, VDC_MOP(28, VDC_F_ALLOCATE))                          \
+  X(OP_CC0_STRIDE32, VDC_MOP(29, 0))
 
 // Compute opcodes.  The first block keeps reference names (control ops and the
 // ops whose tile contracts this runtime still honours); the second block is
@@ -81,10 +82,12 @@
   X(OP_GEMV_ROWS_BF16, 0x7200)                                                         \
   X(OP_GEMV_ROWS_FP8, 0x7201)                                                          \
   X(OP_GEMV_ROWS_NVFP4, 0x7202)                                                        \
+  X(OP_GEMV_ROWS_MOE_DOWN, 0x7203)                                                     \
   X(OP_ATTN_DECODE_PAGED_G4, 0x7210)                                                   \
   X(OP_ATTN_DECODE_PAGED_G8, 0x7211)                                                   \
   X(OP_ARGMAX_FINAL, 0x7220)                                                          \
-  X(OP_L2_PREFETCH, 0x7230)                                                          \
+  X(OP_L2_PREFETCH, 0x7230)                                                           \
+  X(OP_MOE_ROUTE, 0x7240)                                                          \
   X(OP_EXT, 0x7FFF)
 
 // OP_L2_PREFETCH (two words): args = 48-bit address in three 16-bit pieces (low
@@ -100,6 +103,15 @@
 // GEMV_ROWS_NVFP4 (3 words): rows of K/2 bytes e2m1 pairs + K/16 e4m3 block scales (K a multiple
 // of 1024); third word as for FP8 (fp32 per-row scale = the tensor scale of the row's matrix).
 //
+// GEMV_ROWS_MOE_DOWN (5 words, bf16 weights): an expert's down projection.  Words 3..5 are 48-bit
+// addresses: the expert's routing weight (fp32), the fp32 accumulator and the int32 arrival counter of
+// the task's first output row.  Each row adds weight * bf16(W x) to its accumulator; the top_k-th
+// arrival (args of word 2: [eps hi, eps lo] unused, args[2] = top_k) folds bf16(sum) into the hidden
+// state (the output address) and clears both.
+//
+// MOE_ROUTE: args = [n_experts, top_k].  Pops the fp32 router logits and a raw address; writes
+// int32 ids[16] then fp32 weights[16] (softmax over all experts, top-k, renormalised, rounded to bf16).
+//
 // ATTN_DECODE_PAGED words: [max_pages, base_page, flags] [qk-norm eps hi, lo, n_splits]
 // then six 48-bit addresses, low piece first: state block, this head's rows in K page 0,
 // same for V, the head's split records, its arrival counter, its slice of the output;
@@ -114,6 +126,7 @@
 #define VDC_GEMV_MODE_SILU_PAIRS 1
 #define VDC_GEMV_MODE_ARGMAX 2
 #define VDC_GEMV_MODE_STORE_F32 3   // fp32 partial results (tensor-parallel row-split projections)
+#define VDC_GEMV_MODE_MOE_DOWN 4    // weighted fp32 accumulation over the selected experts
 #define VDC_GEMV_ACC_BIT 0x0800
 #define VDC_GEMV_NORM_BIT 0x1000
 

@@ -28,7 +28,7 @@ __device__ void compute_core(const Ctx& c, const VdcCInst* __restrict__ insts, i
     VdcCInst ci, ex;
     *reinterpret_cast<uint2*>(&ci) = w0;
     *reinterpret_cast<uint2*>(&ex) = w1;
-    const bool two_words = ci.opcode == 0x7200 || ci.opcode == 0x7201 || ci.opcode == 0x7202 || ci.opcode == 0x7210 || ci.opcode == 0x7211 || ci.opcode == 0x7230;
+    const bool two_words = ci.opcode == 0x7200 || ci.opcode == 0x7201 || ci.opcode == 0x7202 || ci.opcode == 0x7203 || ci.opcode == 0x7210 || ci.opcode == 0x7211 || ci.opcode == 0x7230;
     q.pc += two_words ? 2 : 1;
     if (two_words) {
       w0 = ld_word(q.pc);
@@ -85,7 +85,8 @@ __device__ void compute_core(const Ctx& c, const VdcCInst* __restrict__ insts, i
         break;
       case 0x7200:    // GEMV_ROWS_BF16 (two words)
       case 0x7201:    // GEMV_ROWS_FP8 (three words: + address of the per-row scales)
-      case 0x7202: {  // GEMV_ROWS_NVFP4 (three words, likewise)
+      case 0x7202:    // GEMV_ROWS_NVFP4 (three words, likewise)
+      case 0x7203: {  // GEMV_ROWS_MOE_DOWN (five words: + routing weight, accumulators, counters)
         const int R = ci.args[1] & 31, mode = (ci.args[1] >> 8) & 7;
         const bool accumulate = ci.args[1] & VDC_GEMV_ACC_BIT;
         const bool norm = ci.args[1] & VDC_GEMV_NORM_BIT;
@@ -93,7 +94,24 @@ __device__ void compute_core(const Ctx& c, const VdcCInst* __restrict__ insts, i
         if (tid == 0) q.sh->misc[32] = __uint_as_float(((uint32_t)ex.args[0] << 16) | ex.args[1]);  // norm eps
         const int row_base = ((int)ex.args[2] | ((int)(ci.args[2] >> 8) << 16)) * R;  // first output row (argmax)
         const float* scales = nullptr;
-        const int wfmt = ci.opcode - 0x7200;
+        auto addr48 = [](const VdcCInst& w) {
+          return (uint64_t)w.args[0] | ((uint64_t)w.args[1] << 16) | ((uint64_t)w.args[2] << 32);
+        };
+        MoeDown moe_args;
+        const MoeDown* moe = nullptr;
+        if (ci.opcode == 0x7203) {
+          VdcCInst e2, e3, e4;
+          *reinterpret_cast<uint2*>(&e2) = ld_word(q.pc);
+          *reinterpret_cast<uint2*>(&e3) = ld_word(q.pc + 1);
+          *reinterpret_cast<uint2*>(&e4) = ld_word(q.pc + 2);
+          q.pc += 3;
+          moe_args.weight = reinterpret_cast<const float*>(addr48(e2));
+          moe_args.acc = reinterpret_cast<float*>(addr48(e3));
+          moe_args.cnt = reinterpret_cast<int*>(addr48(e4));
+          moe_args.top_k = ex.args[2];
+          moe = &moe_args;
+        }
+        const int wfmt = ci.opcode == 0x7203 ? 0 : ci.opcode - 0x7200;
         if (wfmt != 0) {
           VdcCInst e2;
           *reinterpret_cast<uint2*>(&e2) = ld_word(q.pc);
@@ -102,11 +120,11 @@ __device__ void compute_core(const Ctx& c, const VdcCInst* __restrict__ insts, i
                                                   ((uint64_t)e2.args[2] << 32));
         }
         switch (R) {
-          case 1: task_gemv_rows<1>(q, ci.args[0], mode, accumulate, norm, K, row_base, scales, wfmt); break;
-          case 2: task_gemv_rows<2>(q, ci.args[0], mode, accumulate, norm, K, row_base, scales, wfmt); break;
-          case 4: task_gemv_rows<4>(q, ci.args[0], mode, accumulate, norm, K, row_base, scales, wfmt); break;
-          case 8: task_gemv_rows<8>(q, ci.args[0], mode, accumulate, norm, K, row_base, scales, wfmt); break;
-          case 16: task_gemv_rows<16>(q, ci.args[0], mode, accumulate, norm, K, row_base, scales, wfmt); break;
+          case 1: task_gemv_rows<1>(q, ci.args[0], mode, accumulate, norm, K, row_base, scales, wfmt, moe); break;
+          case 2: task_gemv_rows<2>(q, ci.args[0], mode, accumulate, norm, K, row_base, scales, wfmt, moe); break;
+          case 4: task_gemv_rows<4>(q, ci.args[0], mode, accumulate, norm, K, row_base, scales, wfmt, moe); break;
+          case 8: task_gemv_rows<8>(q, ci.args[0], mode, accumulate, norm, K, row_base, scales, wfmt, moe); break;
+          case 16: task_gemv_rows<16>(q, ci.args[0], mode, accumulate, norm, K, row_base, scales, wfmt, moe); break;
           default: raise_abort(c, VDC_ERR_BAD_OPCODE, 0, (int)q.pc, ci.opcode, -1, R); q.aborted = true; break;
         }
         break;
@@ -146,6 +164,7 @@ __device__ void compute_core(const Ctx& c, const VdcCInst* __restrict__ insts, i
         break;
       }
       case 0x7220: task_argmax_final(q, ci.args[0], ci.args[1]); break;
+      case 0x7240: task_moe_route(q, ci.args[0], ci.args[1]); break;
       default:
         raise_abort(c, VDC_ERR_BAD_OPCODE, 0, (int)q.pc, ci.opcode, -1, 0);
         q.aborted = true;

@@ -91,10 +91,9 @@ struct Compute {
   // that carries BARRIER|WRITEBACK.  Caller guarantees every writer executed
   // __threadfence() and a compute_sync() since its last global write.
   __device__ __forceinline__ void release(uint32_t m) {
-    if (tid == 0 && (m & VDC_F_BARRIER) && (m & VDC_F_WRITEBACK)) {
-      __threadfence();
-      red_release_gpu_add(c.bars + (m >> 22), -1);
-    }
+    // red.release.gpu is cumulative: it orders this thread's earlier writes and
+    // those it observed through the CTA barrier, so no separate fence is needed
+    if (tid == 0 && (m & VDC_F_BARRIER) && (m & VDC_F_WRITEBACK)) red_release_gpu_add(c.bars + (m >> 22), -1);
   }
   // Caller guarantees (with a compute_sync) that no thread still reads the slots.
   __device__ __forceinline__ void free_slots(int mask) {
@@ -264,9 +263,16 @@ __device__ __forceinline__ void gemv_chunk_nvfp4(const uint8_t* w, const uint8_t
 }
 
 // wfmt: 0 bf16, 1 e4m3 (scales = fp32 per-row scales of the task's rows), 2 NVFP4 (scales likewise).
+struct MoeDown {           // mode MOE_DOWN: per-row accumulation over the selected experts
+  const float* weight;     // this expert's routing weight
+  float* acc;              // fp32 accumulators of the task's rows
+  int* cnt;                // arrival counters of the task's rows
+  int top_k;
+};
+
 template <int R>
 __device__ void task_gemv_rows(Compute& q, int n_chunks, int mode, bool accumulate, bool norm, int K, int row_base,
-                               const float* scales = nullptr, int wfmt = 0) {
+                               const float* scales = nullptr, int wfmt = 0, const MoeDown* moe = nullptr) {
   Shared* sh = q.sh;
   const Ctx& c = q.c;
   int normw_mask = 0;
@@ -363,6 +369,17 @@ __device__ void task_gemv_rows(Compute& q, int n_chunks, int mode, bool accumula
         if (q.lane == r) v = acc[r];
       if (q.lane < R && mode == VDC_GEMV_MODE_STORE_F32) {
         reinterpret_cast<float*>(outg)[row0 + q.lane] = v;
+      } else if (q.lane < R && mode == VDC_GEMV_MODE_MOE_DOWN) {
+        const int row = row0 + q.lane;
+        atomicAdd(moe->acc + row, __ldg(moe->weight) * bf16_round(v));
+        __threadfence();
+        if (atomicAdd(moe->cnt + row, 1) == moe->top_k - 1) {
+          // every selected expert has added its share: fold the sum into the residual stream
+          __threadfence();
+          const float total = atomicExch(moe->acc + row, 0.f);
+          moe->cnt[row] = 0;
+          outg[row] = __float2bfloat16_rn(__bfloat162float(outg[row]) + bf16_round(total));
+        }
       } else if (q.lane < R) {
         const __nv_bfloat16 bq = __float2bfloat16_rn(v);
         if (accumulate) atomicAdd(outg + row0 + q.lane, bq);  // residual add: bf16(old + bf16(W x))
@@ -732,6 +749,79 @@ __device__ void task_attn_decode(Compute& q, const AttnArgs& a) {
     __threadfence();
     red_release_gpu_add(c.bars + a.bar, -1);
   }
+}
+
+// ------------------------------------------------------------------------- //
+// task: MoE routing — softmax over all experts, top-k, renormalise
+// ------------------------------------------------------------------------- //
+// Pop order: router logits (n_experts fp32), route record (raw address: int32
+// ids[16] followed by fp32 weights[16]).  One warp does the work.
+__device__ void task_moe_route(Compute& q, int n_experts, int top_k) {
+  const Ctx& c = q.c;
+  const int lg_mask = q.pop();
+  q.pop();
+  int* ids = reinterpret_cast<int*>(q.addr());
+  float* wts = reinterpret_cast<float*>(ids + 16);
+  const uint32_t meta = q.meta();
+  if (q.aborted) return;
+  if (q.warp == 0) {
+    const float* lg = (const float*)slot_ptr(c, first_slot(lg_mask));
+    constexpr int kMaxPerLane = 8;  // up to 256 experts
+    float v[kMaxPerLane];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < kMaxPerLane; ++j) {
+      const int e = q.lane + 32 * j;
+      v[j] = e < n_experts ? lg[e] : -INFINITY;
+      mx = fmaxf(mx, v[j]);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float sum = 0.f;
+#pragma unroll
+    for (int j = 0; j < kMaxPerLane; ++j) {
+      v[j] = (v[j] == -INFINITY) ? 0.f : __expf(v[j] - mx);  // unnormalised probabilities
+      sum += v[j];
+    }
+    sum = warp_sum(sum);
+    float sel_sum = 0.f, my_w = 0.f;
+    int my_id = 0;
+    for (int k = 0; k < top_k; ++k) {
+      float bv = -1.f;
+      int bi = 0x7fffffff;
+#pragma unroll
+      for (int j = 0; j < kMaxPerLane; ++j) {
+        const int e = q.lane + 32 * j;
+        if (e < n_experts && v[j] > bv) {  // ascending e within a lane: first maximum wins
+          bv = v[j];
+          bi = e;
+        }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) {
+          bv = ov;
+          bi = oi;
+        }
+      }
+      if ((bi & 31) == q.lane) v[bi >> 5] = -1.f;  // taken
+      const float p = bv / sum;
+      sel_sum += p;
+      if (q.lane == k) {
+        my_w = p;
+        my_id = bi;
+      }
+    }
+    if (q.lane < top_k) {
+      ids[q.lane] = my_id;
+      wts[q.lane] = bf16_round(my_w / sel_sum);
+    }
+  }
+  compute_sync();
+  q.release(meta);
+  q.free_slots(lg_mask);
 }
 
 // ------------------------------------------------------------------------- //

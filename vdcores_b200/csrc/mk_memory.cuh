@@ -107,7 +107,9 @@ __device__ void control_warp(const Ctx& c, const VdcMInst* __restrict__ insts, i
         const uint64_t addr = (((uint64_t)w.w << 32) | w.z) + ind_off;
         w.z = (uint32_t)addr;
         w.w = (uint32_t)(addr >> 32);
-        ind_pending = false;
+        // one shot, except for a loop body that is about to jump back: every trip of a
+        // weight-stream loop behind an indirection (an expert's rows) needs the offset
+        if (!((opcode & VDC_F_JUMP) && loop_counter > 1)) ind_pending = false;
       }
       const int req = (int)(num_slots & 63u);
       int slot, word;
@@ -322,12 +324,15 @@ __device__ void control_warp(const Ctx& c, const VdcMInst* __restrict__ insts, i
           if (!ok) running = false;
           break;
         }
+        case 29:   // CC0_STRIDE32:                         ... += word * (size | arg << 16)
         case 6:    // CC0: next allocating instruction's address += word << arg
         case 7: {  // CC0_ROW_BYTES:                        ... += word * size
           int word = 0;
           if (lane == 0) word = ld_relaxed_gpu(reinterpret_cast<const int*>(address));
           word = __shfl_sync(0xffffffffu, word, 0);
-          ind_off = (opid == 6) ? ((uint64_t)(uint32_t)word << arg) : ((uint64_t)(uint32_t)word * size);
+          ind_off = (opid == 6) ? ((uint64_t)(uint32_t)word << arg)
+                                : (opid == 7 ? (uint64_t)(uint32_t)word * size
+                                             : (uint64_t)(uint32_t)word * (uint64_t)(size | (arg << 16)));
           ind_pending = true;
           break;
         }

@@ -41,6 +41,8 @@ class DecodeConfig:
     theta: float = 500000.0
     qk_norm: bool = False
     qk_norm_eps: float = 1e-6
+    n_experts: int = 0          # > 0: every layer's FFN is a top-k mixture of experts of width `ffn`
+    top_k: int = 8
 
     @property
     def q_width(self):
@@ -57,6 +59,8 @@ class DecodeConfig:
 
 LLAMA31_8B = DecodeConfig()
 QWEN3_8B = DecodeConfig(ffn=12288, vocab=151936, n_layers=36, eps=1e-6, theta=1e6, qk_norm=True)
+QWEN3_30B_A3B = DecodeConfig(hidden=2048, n_heads=32, n_kv_heads=4, ffn=768, vocab=151936, n_layers=48, eps=1e-6,
+                             theta=1e6, qk_norm=True, n_experts=128, top_k=8)
 
 
 @dataclass
@@ -76,6 +80,8 @@ class DenseWeights:
     down: List[torch.Tensor]
     q_norm: Optional[List[torch.Tensor]] = None
     k_norm: Optional[List[torch.Tensor]] = None
+    # mixture of experts (gate/up/down then hold, per layer, a list with one matrix per expert)
+    router: Optional[List[torch.Tensor]] = None
 
 
 def rows_per_chunk(K: int, even: bool = False, row_bytes: Optional[int] = None) -> int:
@@ -160,8 +166,14 @@ class DecodeEngine:
         self.hidden = z(H)
         self.qkv = z(self.qkv_rows)
         self.attn_out = z(cfg.q_width)
-        self.act = z(F)
+        self.act = z(max(1, cfg.top_k if cfg.n_experts else 1), F)
         self.logits = z(V)
+        if cfg.n_experts:
+            assert wkind == "bf16", "expert weights are bf16 only"
+            self.router_logits = z(cfg.n_experts, dt=torch.float32)
+            self.route = z(32, dt=torch.int32)          # int32 ids[16] | fp32 weights[16]
+            self.moe_acc = z(H, dt=torch.float32)       # zero between layers: the last expert to arrive clears it
+            self.moe_cnt = z(H, dt=torch.int32)
         G = cfg.group
         self.rec_floats = G * isa.HEAD_DIM + 16 * ((2 * G + 15) // 16)
         max_rec_per_load = 32768 // (self.rec_floats * 4)
@@ -250,6 +262,12 @@ class DecodeEngine:
             rows, sc = cat([self._encode(to(w.wq[l])), self._encode(to(w.wk[l])), self._encode(to(w.wv[l]))])
             packed["wqkv"].append((rows[pm], None if sc is None else sc[pm]))
             packed["wo"].append(self._encode(to(w.wo[l])))
+            if cfg.n_experts:
+                # [E, 2F, H] with gate/up interleaved per expert, [E, H, F]
+                packed["wgu"].append((torch.stack([torch.stack((to(g), to(u)), dim=1).reshape(2 * cfg.ffn, cfg.hidden)
+                                                   for g, u in zip(w.gate[l], w.up[l])]), None))
+                packed["wd"].append((torch.stack([to(d) for d in w.down[l]]), None))
+                continue
             # gate and up rows interleaved: row 2j = gate_j, row 2j+1 = up_j
             (g, gs), (u, us) = self._encode(to(w.gate[l])), self._encode(to(w.up[l]))
             packed["wgu"].append((torch.stack((g, u), dim=1).reshape(2 * cfg.ffn, g.shape[1]),
@@ -260,6 +278,7 @@ class DecodeEngine:
             setattr(self, name, torch.stack([p[0] for p in parts]).to(dev))
             if parts[0][1] is not None:
                 self.scales[name] = torch.stack([p[1] for p in parts]).to(dev)
+        self.router = torch.stack([to(t) for t in w.router]).to(dev) if cfg.n_experts else None
         self.embed = to(w.embed).to(dev)
         self.lm_head = to(w.lm_head).to(dev)
         self.norm_w = to(w.norm).to(dev)
@@ -301,19 +320,31 @@ class DecodeEngine:
         self.ln2 = torch.ones(L, H, dtype=BF16, device=dev)
         self.wqkv = rnd(L, self.qkv_rows, H)
         self.wo = rnd(L, H, cfg.q_width)
-        self.wgu = rnd(L, 2 * F, H)
-        self.wd = rnd(L, H, F)
+        if cfg.n_experts:
+            self.wgu = rnd(L, cfg.n_experts, 2 * F, H)
+            self.wd = rnd(L, cfg.n_experts, H, F)
+            self.router = rnd(L, cfg.n_experts, H)
+        else:
+            self.wgu = rnd(L, 2 * F, H)
+            self.wd = rnd(L, H, F)
+            self.router = None
         self.qknorm = torch.ones(L, 2 * isa.HEAD_DIM, dtype=BF16, device=dev) if cfg.qk_norm else None
         self.w = True
         self._quantize()
         self._build_program()
 
     def weight_bytes(self) -> int:
-        ts = [self.lm_head, self.norm_w, self.ln1, self.ln2, self.wqkv, self.wo, self.wgu, self.wd]
+        ts = [self.lm_head, self.norm_w, self.ln1, self.ln2, self.wqkv, self.wo]
         ts += list(self.scales.values())
         if self.qknorm is not None:
             ts.append(self.qknorm)
-        return sum(t.numel() * t.element_size() for t in ts) + self.cfg.hidden * 2
+        n = sum(t.numel() * t.element_size() for t in ts) + self.cfg.hidden * 2
+        if self.cfg.n_experts:      # a token reads the router and top_k of the experts of every layer
+            n += self.router.numel() * 2
+            n += (self.wgu.numel() + self.wd.numel()) * 2 * self.cfg.top_k // self.cfg.n_experts
+        else:
+            n += sum(t.numel() * t.element_size() for t in (self.wgu, self.wd))
+        return n
 
     def algorithmic_bytes(self, pos: int) -> int:
         """HBM bytes one decode step at position `pos` has to read: every weight
@@ -425,6 +456,9 @@ class DecodeEngine:
                          **sk('wo', l, r0),
                          out=Dst(hid + r0 * 2, n * 2, "add_bf16", release=b_o))
 
+            if cfg.n_experts:
+                b_hid = self._plan_moe(P, plan, load, l, b_o, add_gemv)
+                continue
             # ---- gate/up projection with fused post-attention RMSNorm and SiLU·mul
             b_gu = P.new_barrier()
             R = rpc(H, True)
@@ -514,6 +548,63 @@ class DecodeEngine:
         self.bars_init = torch.from_numpy(bars).to(self.dev)
         self.launches_per_step = 1
 
+    def _plan_moe(self, P, plan, load, l, b_o, add_gemv):
+        """Router, top-k routing and the selected experts' gate/up and down projections of layer l."""
+        cfg = self.cfg
+        H, F, E, TK = cfg.hidden, cfg.ffn, cfg.n_experts, cfg.top_k
+        hid = self.hidden.data_ptr()
+        ids_addr = self.route.data_ptr()
+        wts_addr = ids_addr + 64
+        # ---- router logits (fp32) over all SMs that get a chunk
+        b_rl = P.new_barrier()
+        R = rows_per_chunk(H)
+        for sm, u0, cnt in self._ranges(load, E // R, R * H * 2):
+            r0, n = u0 * R, cnt * R
+            wa = self.router[l].data_ptr() + r0 * H * 2
+            add_gemv(sm, None, w_addr=wa, n_rows=n, K=H, R=R, x=Src(hid, H * 2, wait=b_o),
+                     out=Dst(self.router_logits.data_ptr() + r0 * 4, n * 4, "store", release=b_rl),
+                     mode=isa.GEMV_MODE_STORE_F32, norm_w=Src(self.ln2[l].data_ptr(), H * 2), eps=cfg.eps)
+        # ---- softmax / top-k on one SM
+        b_route = P.new_barrier()
+        sm = self._pick(load, 1)[0]
+        plan[sm].append((lambda sm=sm: P.moe_route(sm, logits=Src(self.router_logits.data_ptr(), E * 4, wait=b_rl),
+                                                   route_addr=ids_addr, n_experts=E, top_k=TK, release=b_route), None))
+        # ---- the selected experts' gate/up: units are (slot, chunk), contiguous per SM, split at slot borders
+        b_gu = P.new_barrier()
+        R = rows_per_chunk(H, even=True)
+        per = 2 * F // R
+        stride_gu = 2 * F * H * 2
+        for sm, u0, cnt in self._ranges(load, TK * per, R * H * 2):
+            u, end = u0, u0 + cnt
+            while u < end:
+                slot, c0 = divmod(u, per)
+                n_c = min(end - u, per - c0)
+                r0, n = c0 * R, n_c * R
+                add_gemv(sm, None, w_addr=self.wgu[l].data_ptr() + r0 * H * 2, n_rows=n, K=H, R=R,
+                         x=Src(hid, H * 2, wait=b_o), out=Dst(self.act[slot].data_ptr() + (r0 // 2) * 2, n, "store", release=b_gu),
+                         mode=isa.GEMV_MODE_SILU_PAIRS, norm_w=Src(self.ln2[l].data_ptr(), H * 2), eps=cfg.eps,
+                         w_indirect=(ids_addr + 4 * slot, stride_gu), wait_issue=b_route)
+                u += n_c
+        # ---- the selected experts' down projections, weighted and accumulated per output row;
+        # the last expert to reach a row folds the sum into the hidden state
+        b_hid = P.new_barrier()
+        R = rows_per_chunk(F)
+        per = H // R
+        stride_d = H * F * 2
+        for sm, u0, cnt in self._ranges(load, TK * per, R * F * 2):
+            u, end = u0, u0 + cnt
+            while u < end:
+                slot, c0 = divmod(u, per)
+                n_c = min(end - u, per - c0)
+                r0, n = c0 * R, n_c * R
+                add_gemv(sm, None, w_addr=self.wd[l].data_ptr() + r0 * F * 2, n_rows=n, K=F, R=R,
+                         x=Src(self.act[slot].data_ptr(), F * 2, wait=b_gu), out=Dst(hid + r0 * 2, n * 2, "store", release=b_hid),
+                         mode=isa.GEMV_MODE_MOE_DOWN, w_indirect=(ids_addr + 4 * slot, stride_d), wait_issue=b_route,
+                         moe=dict(weight_addr=wts_addr + 4 * slot, acc_addr=self.moe_acc.data_ptr() + 4 * r0,
+                                  cnt_addr=self.moe_cnt.data_ptr() + 4 * r0, top_k=TK))
+                u += n_c
+        return b_hid
+
     # ------------------------------------------------------------------ state
     def set_state(self, pos: int, token: int):
         """Positions [0, pos) are cached; `token` is decoded next at position pos."""
@@ -531,6 +622,9 @@ class DecodeEngine:
         s[isa.ST_PAGETABLE:] = self.page_table
         self.state.copy_(s, non_blocking=True)
         self.attn_cnt.zero_()
+        if self.cfg.n_experts:
+            self.moe_acc.zero_()
+            self.moe_cnt.zero_()
         self.pos = pos
         self.steps_done = 0
 
@@ -596,6 +690,18 @@ class DecodeEngine:
                 enable_gqa=True)[0].transpose(0, 1).reshape(T, cfg.q_width)
             h = h + o @ self._dense('wo', l).t()
             x = norm(h, self.ln2[l], cfg.eps)
+            if cfg.n_experts:
+                probs = torch.softmax(x.float() @ self.router[l].float().t(), dim=-1)
+                tw, ti = torch.topk(probs, cfg.top_k, dim=-1)
+                tw = (tw / tw.sum(-1, keepdim=True)).to(BF16)
+                y = torch.zeros(T, cfg.hidden, dtype=torch.float32, device=dev)
+                for e in ti.unique().tolist():
+                    rows, slots = (ti == e).nonzero(as_tuple=True)
+                    gu = x[rows] @ self.wgu[l, e].t()
+                    a = torch.nn.functional.silu(gu[:, 0::2]) * gu[:, 1::2]
+                    y.index_add_(0, rows, (a @ self.wd[l, e].t()).float() * tw[rows, slots].float()[:, None])
+                h = h + y.to(BF16)
+                continue
             gu = x @ self._dense('wgu', l).t()
             a = torch.nn.functional.silu(gu[:, 0::2]) * gu[:, 1::2]
             h = h + a @ self._dense('wd', l).t()

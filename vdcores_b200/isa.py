@@ -31,6 +31,7 @@ GEMV_MODE_STORE = _defs["GEMV_MODE_STORE"]
 GEMV_MODE_SILU_PAIRS = _defs["GEMV_MODE_SILU_PAIRS"]
 GEMV_MODE_ARGMAX = _defs["GEMV_MODE_ARGMAX"]
 GEMV_MODE_STORE_F32 = _defs["GEMV_MODE_STORE_F32"]
+GEMV_MODE_MOE_DOWN = _defs["GEMV_MODE_MOE_DOWN"]
 GEMV_NORM_BIT = _defs["GEMV_NORM_BIT"]
 GEMV_ACC_BIT = _defs["GEMV_ACC_BIT"]
 ATTN_QKNORM_BIT = _defs["ATTN_QKNORM_BIT"]

@@ -221,7 +221,8 @@ class Program:
 
     def gemv(self, sm, *, w_addr, n_rows, K, R, x: Src, out: Dst, mode=isa.GEMV_MODE_STORE,
              norm_w: Optional[Src] = None, eps: float = 0.0, pair_out: Optional[Dst] = None, row_base: int = 0,
-             stream: bool = False, fp8_scales: Optional[int] = None, nvfp4_scales: Optional[int] = None):
+             stream: bool = False, fp8_scales: Optional[int] = None, nvfp4_scales: Optional[int] = None,
+             w_indirect: Optional[tuple] = None, wait_issue: Optional[int] = None, moe: Optional[dict] = None):
         """y[0:n_rows] = W[0:n_rows, :K] @ x for the contiguous row block at w_addr
         (bf16; e4m3 with fp8_scales = address of the block's fp32 per-row scales;
         or NVFP4 rows — K/2 code bytes + K/16 block scales — with nvfp4_scales =
@@ -251,6 +252,14 @@ class Program:
         if mode == isa.GEMV_MODE_ARGMAX:
             assert pair_out is not None and row_base % R == 0
             self.raw_address(sm, pair_out.addr, 25, release=pair_out.release)
+        if wait_issue is not None:
+            # the weight address depends on data another SM produces (an expert id): the memory
+            # stream of this SM stops here until that barrier has opened
+            self.mem(sm, isa.OP_ISSUE_BARRIER, bar=wait_issue)
+        if w_indirect is not None:
+            waddr, stride = w_indirect
+            assert 0 < stride < 1 << 32
+            self.mem(sm, isa.OP_CC0_STRIDE32, size=stride & 0xFFFF, arg=stride >> 16, address=waddr)
         self.repeat(sm, n_chunks, [chunk_bytes])
         self.mem(sm, isa.OP_ALLOC_TMA_LOAD_1D_STREAM if stream else isa.OP_ALLOC_TMA_LOAD_1D, size=chunk_bytes,
                  nslot=slots_for(chunk_bytes), address=w_addr, flags=isa.F_JUMP)
@@ -260,6 +269,14 @@ class Program:
             (isa.GEMV_ACC_BIT if out.kind == "add_bf16" else 0)
         a2 = (K // 256) | ((rb8 >> 16) << 8)
         e = f32_bits(eps)
+        if moe is not None:
+            assert mode == isa.GEMV_MODE_MOE_DOWN and scales is None
+            self.comp(sm, isa.OP_GEMV_ROWS_MOE_DOWN, n_chunks, a1, a2)
+            self.comp(sm, isa.OP_EXT, e >> 16, e & 0xFFFF, moe["top_k"])
+            for addr in (moe["weight_addr"], moe["acc_addr"], moe["cnt_addr"]):
+                assert addr % 4 == 0 and 0 <= addr < 1 << 48
+                self.comp(sm, isa.OP_EXT, addr & 0xFFFF, (addr >> 16) & 0xFFFF, (addr >> 32) & 0xFFFF)
+            return
         self.comp(sm, op, n_chunks, a1, a2)
         self.comp(sm, isa.OP_EXT, e >> 16, e & 0xFFFF, rb8 & 0xFFFF)
         if scales is not None:
@@ -303,6 +320,14 @@ class Program:
             assert 0 <= addr < 1 << 48
             self.comp(sm, isa.OP_EXT, addr & 0xFFFF, (addr >> 16) & 0xFFFF, (addr >> 32) & 0xFFFF)
         self.comp(sm, isa.OP_EXT, split, release, 0)
+
+    def moe_route(self, sm, *, logits: Src, route_addr: int, n_experts: int, top_k: int, release=None):
+        """Softmax over n_experts fp32 router logits, top-k, renormalise: writes int32
+        ids[16] then fp32 weights[16] at route_addr."""
+        assert n_experts <= 256 and top_k <= 16 and logits.nbytes == n_experts * 4
+        self.load(sm, logits)
+        self.raw_address(sm, route_addr, 25, release=release)
+        self.comp(sm, isa.OP_MOE_ROUTE, n_experts, top_k)
 
     def argmax_final(self, sm, *, records: Src, n: int, state_addr, log_addr, release=None, local_only=False):
         """Reduces n candidate records {f32 value, i32 index, pad, pad}.  Normally
