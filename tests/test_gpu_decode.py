@@ -128,3 +128,35 @@ def test_decode_quantised_matches_oracle(cuda_device, wkind, tol, base):
         tok = nxt_ref
         if got != nxt_ref:
             eng.state[2:3].copy_(torch.tensor([tok], dtype=torch.int32))
+
+
+def test_full_size_llama_layer_matches_hf_fixture(cuda_device):
+    """BASELINE config 1 at full size: one Llama-3.1-8B-shaped layer (hidden 4096, 32q/8kv,
+    FFN 14336), seed-0 weights, 1024 cached positions, decode position 1024.  The device
+    output is compared with the stored Hugging Face result and with the oracle."""
+    import os
+    import numpy as np
+    from vdcores_b200.decode import DecodeEngine
+    z = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "llama8b_layer_pos1024.npz"))
+    cfg = O.DecodeConfig(n_layers=1, vocab=8)
+    gen = torch.Generator().manual_seed(0)
+    lw = O.LayerWeights.random(cfg, gen)
+    hidden = torch.randn(cfg.hidden, generator=gen).to(torch.bfloat16)
+    kc = torch.randn(1024, 8, 128, generator=gen).to(torch.bfloat16)
+    vc = torch.randn(1024, 8, 128, generator=gen).to(torch.bfloat16)
+    assert np.array_equal(hidden[:8].float().numpy(), z["hidden_in_head"])
+    # the layer input enters as the embedding row of token 0
+    embed = torch.zeros(8, cfg.hidden, dtype=torch.bfloat16)
+    embed[0] = hidden
+    w = O.ModelWeights(cfg, embed, [lw], torch.ones(cfg.hidden, dtype=torch.bfloat16),
+                       torch.zeros(8, cfg.hidden, dtype=torch.bfloat16))
+    eng = DecodeEngine(engine_config(cfg), max_seq=1088, device=cuda_device, taps=True, timeout_ns=500_000_000)
+    eng.load_weights(dense_weights(w))
+    eng.load_kv([kc], [vc])
+    eng.set_state(1024, 0)
+    eng.generate(1)
+    out = eng.taps[0].cpu()
+    k_dev, v_dev = eng.read_kv(0, 1025)
+    assert O.rel_l2(out, torch.from_numpy(z["hidden_out"])) < REL_L2_BF16
+    assert O.rel_l2(k_dev[1024].cpu(), torch.from_numpy(z["k_new"])) < REL_L2_BF16
+    assert O.rel_l2(v_dev[1024].cpu(), torch.from_numpy(z["v_new"])) < REL_L2_BF16
