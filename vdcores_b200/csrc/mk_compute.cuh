@@ -50,10 +50,11 @@ struct Compute {
   __device__ __forceinline__ uint64_t addr() const { return sh->pop_addr[(head - 1u) & 1u]; }
   __device__ __forceinline__ uint32_t meta() const { return sh->pop_meta[(head - 1u) & 1u]; }
 
-  // Per-warp phase: the next `n` ring entries are consumed by the warps
-  // independently, entry head+i by warp i % 8.  begin/end are CTA-wide.
-  __device__ __forceinline__ void warp_phase_begin(unsigned n) {
-    if (lane == 0) sh->warp_next[warp] = (unsigned)warp < n ? head + warp : 0xFFFFFFFFu;
+  // Per-warp phase: the next `n` ring entries are consumed by the warps on their own
+  // schedule (the GEMV task gives entry head+i to the warp pair i % 4).  begin/end are CTA-wide.
+  __device__ __forceinline__ void warp_phase_begin(unsigned n, unsigned first) {
+    // first: index of the first entry this warp will consume
+    if (lane == 0) sh->warp_next[warp] = first < n ? head + first : 0xFFFFFFFFu;
     compute_sync();
     if (tid == 0) sh->cta_head = head + n;
   }
@@ -136,7 +137,8 @@ __device__ __forceinline__ float2 bf2(uint32_t u) { return make_float2(bf_lo(u),
 // row keeps NA independent partial sums so the FMA chains stay short when R is
 // small (a single 28 KB row would otherwise be one long dependent chain).
 template <int R>
-__device__ __forceinline__ void gemv_chunk(const uint8_t* w, const uint8_t* x, int K, int lane, float (&out)[R]) {
+__device__ __forceinline__ void gemv_chunk(const uint8_t* w, const uint8_t* x, int K, int lane, int it0, int it1,
+                                           float (&out)[R]) {
   constexpr int NA = R >= 8 ? 1 : (R == 4 ? 2 : 4);
   constexpr int UNROLL = R >= 8 ? 1 : (R == 4 ? 2 : 4);
   float2 acc[R][NA];
@@ -144,9 +146,8 @@ __device__ __forceinline__ void gemv_chunk(const uint8_t* w, const uint8_t* x, i
   for (int r = 0; r < R; ++r)
 #pragma unroll
     for (int a = 0; a < NA; ++a) acc[r][a] = make_float2(0.f, 0.f);
-  const int iters = K >> 8;
 #pragma unroll UNROLL
-  for (int it = 0; it < iters; ++it) {
+  for (int it = it0; it < it1; ++it) {
     const int off = (it << 9) + (lane << 4);  // byte offset of this lane's 8 elements
     const uint4 xv = lds128(x + off);
     const float2 xf[4] = {bf2(xv.x), bf2(xv.y), bf2(xv.z), bf2(xv.w)};
@@ -177,15 +178,15 @@ __device__ __forceinline__ float2 e4m3x2_to_float2(uint32_t pair16) {
 }
 
 template <int R>
-__device__ __forceinline__ void gemv_chunk_fp8(const uint8_t* w, const uint8_t* x, int K, int lane, float (&out)[R]) {
+__device__ __forceinline__ void gemv_chunk_fp8(const uint8_t* w, const uint8_t* x, int K, int lane, int it0, int it1,
+                                               float (&out)[R]) {
   constexpr int NA = R >= 8 ? 1 : (R == 4 ? 2 : 4);
   float2 acc[R][NA];
 #pragma unroll
   for (int r = 0; r < R; ++r)
 #pragma unroll
     for (int a = 0; a < NA; ++a) acc[r][a] = make_float2(0.f, 0.f);
-  const int iters = K >> 9;  // 512 weights per warp step
-  for (int it = 0; it < iters; ++it) {
+  for (int it = it0; it < it1; ++it) {  // 512 weights per warp step
     const int e0 = (it << 9) + (lane << 4);  // first element of this lane
     const uint4 xa = lds128(x + e0 * 2), xb = lds128(x + e0 * 2 + 16);
     const float2 xf[8] = {bf2(xa.x), bf2(xa.y), bf2(xa.z), bf2(xa.w), bf2(xb.x), bf2(xb.y), bf2(xb.z), bf2(xb.w)};
@@ -225,14 +226,13 @@ __device__ __forceinline__ float e4m3_to_float(uint32_t byte) {
 }
 
 template <int R>
-__device__ __forceinline__ void gemv_chunk_nvfp4(const uint8_t* w, const uint8_t* x16, int K, int lane,
-                                                 float (&out)[R]) {
+__device__ __forceinline__ void gemv_chunk_nvfp4(const uint8_t* w, const uint8_t* x16, int K, int lane, int it0,
+                                                 int it1, float (&out)[R]) {
   const int row_bytes = (K >> 1) + (K >> 4);
   float acc[R];
 #pragma unroll
   for (int r = 0; r < R; ++r) acc[r] = 0.f;
-  const int iters = K >> 10;  // 1024 weights per warp step
-  for (int it = 0; it < iters; ++it) {
+  for (int it = it0; it < it1; ++it) {  // 1024 weights per warp step
     const int e0 = (it << 10) + (lane << 5);  // first element of this lane
     uint4 xv[4];
 #pragma unroll
@@ -328,26 +328,52 @@ __device__ void task_gemv_rows(Compute& q, int n_chunks, int mode, bool accumula
   }
 
   ArgBest best = {-INFINITY, 0x7fffffff};
-  q.warp_phase_begin((unsigned)n_chunks);  // its sync also publishes the normalised vector
+  // Chunk i belongs to the pair of warps (i % 4, i % 4 + 4): each member takes one half of K
+  // for all R rows, the halves meet in shared memory at a two-warp named barrier, and the
+  // lower warp finishes the chunk.  A chunk therefore stays resident for half the time one
+  // warp alone would need, which is what the in-flight window of 24 slots can afford.
+  const int pair = q.warp & 3, member = q.warp >> 2;
+  const int steps = wfmt == 2 ? K >> 10 : (wfmt == 1 ? K >> 9 : K >> 8);
+  const int it0 = member == 0 ? 0 : (steps + 1) / 2, it1 = member == 0 ? (steps + 1) / 2 : steps;
+  float* pair_part = sh->red + pair * (2 * 2 * 16);  // [buffer][member][row]
+  q.warp_phase_begin((unsigned)n_chunks, (unsigned)pair);  // its sync also publishes the normalised vector
   if (norm) q.free_slots(normw_mask);
-  for (int i = q.warp; i < n_chunks; i += kCW) {
+  for (int i = pair, trip = 0; i < n_chunks; i += 4, ++trip) {
     const int w_mask = q.warp_wait((unsigned)i);
-    if (w_mask == kPopAbort) break;
+    if (w_mask == kPopAbort) {
+      asm volatile("bar.arrive %0, 64;" ::"r"(2 + pair) : "memory");  // do not strand the partner
+      break;
+    }
     const uint8_t* w = (const uint8_t*)slot_ptr(c, first_slot(w_mask));
     float acc[R];
     const int row0 = i * R;
-    if (wfmt == 2) {
-      gemv_chunk_nvfp4<R>(w, x, K, q.lane, acc);
+    if (wfmt == 2) gemv_chunk_nvfp4<R>(w, x, K, q.lane, it0, it1, acc);
+    else if (wfmt == 1) gemv_chunk_fp8<R>(w, x, K, q.lane, it0, it1, acc);
+    else gemv_chunk<R>(w, x, K, q.lane, it0, it1, acc);
+    float* pp = pair_part + (trip & 1) * 32;
+    if (member == 1) {
+      float v = 0.f;
 #pragma unroll
-      for (int r = 0; r < R; ++r) acc[r] *= __ldg(scales + row0 + r);
-    } else if (wfmt == 1) {
-      gemv_chunk_fp8<R>(w, x, K, q.lane, acc);
-#pragma unroll
-      for (int r = 0; r < R; ++r) acc[r] *= __ldg(scales + row0 + r);
-    } else {
-      gemv_chunk<R>(w, x, K, q.lane, acc);
+      for (int r = 0; r < R; ++r)
+        if (q.lane == r) v = acc[r];
+      if (q.lane < R) pp[16 + q.lane] = v;
     }
-    q.warp_done((unsigned)i, (unsigned)n_chunks, w_mask);
+    asm volatile("bar.sync %0, 64;" ::"r"(2 + pair) : "memory");
+    if (member == 1) {  // the partner finishes the chunk; it also frees the slots
+      if (q.lane == 0) sh->warp_next[q.warp] = i + 4 < n_chunks ? q.head + i + 4 : 0xFFFFFFFFu;
+      continue;
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) acc[r] += pp[16 + r];
+    if (wfmt != 0) {
+#pragma unroll
+      for (int r = 0; r < R; ++r) acc[r] *= __ldg(scales + row0 + r);
+    }
+    __syncwarp();
+    if (q.lane == 0) {
+      atomicOr(&sh->slot_avail, (uint32_t)w_mask & kSlotMaskAll);
+      sh->warp_next[q.warp] = i + 4 < n_chunks ? q.head + i + 4 : 0xFFFFFFFFu;
+    }
     if (mode == VDC_GEMV_MODE_SILU_PAIRS) {
       float g = 0.f, u = 0.f;
 #pragma unroll
