@@ -88,6 +88,9 @@
   X(OP_ARGMAX_FINAL, 0x7220)                                                          \
   X(OP_L2_PREFETCH, 0x7230)                                                           \
   X(OP_MOE_ROUTE, 0x7240)                                                          \
+  X(OP_GEMM_TC_BF16, 0x7300)                                                           \
+  X(OP_EMBED_PACK, 0x7310)                                                             \
+  X(OP_BATCH_ADVANCE, 0x7320)                                                          \
   X(OP_EXT, 0x7FFF)
 
 // OP_L2_PREFETCH (two words): args = 48-bit address in three 16-bit pieces (low
@@ -122,6 +125,39 @@
 // RMSNorm of the activation vector.  args[2]: K/256 in the low byte.  Second
 // word: fp32 bits of the norm eps (hi, lo), index of the first chunk within the
 // whole matrix (argmax mode: candidate row = (first chunk + i) * R + r).
+// Batched decode (2 <= batch <= 128) keeps every activation matrix [Bpad, K] bf16 in the
+// "k-chunk major" layout the tensor cores read without swizzling: 16-byte pieces (8 consecutive k
+// of one sequence) ordered [K/8][Bpad/8][8 sequences]; byte offset of (b, k) =
+// ((k/8) * (Bpad/8) + b/8) * 128 + (b%8) * 16 + (k%8) * 2.  Bpad is 16, 32, 64 or 128.  Weights of
+// a projection unit (N rows, N a multiple of 16, at most 256) are stored the same way, [K/8][N/8][8 rows].
+// A K-range of either is one contiguous piece of memory, loaded with one 1-D bulk copy.
+//
+// GEMM_TC_BF16 (seven words): D[b, n] = sum_k X[b, k] W[n, k] on the tcgen05 tensor cores, the batch on
+// the accumulator's 128 lanes, the unit's N weight rows on its columns (fp32, in tensor memory).
+//   word 0: [n_chunks, N/16 | mode << 8 | norm << 12, k-steps of 16 per chunk]
+//   word 1: [norm eps hi, lo, batch]      word 2: 48-bit output address
+//   word 3: 48-bit address of the argmax keys (u64 per sequence; ARGMAX mode)
+//   word 4: [first output row low 16 bits, high bits, barrier to release (0xFFFF: none)]
+//   word 5: [row-major output leading dimension / 16, Bpad, 0]
+//   word 6: 48-bit address of fp32 per-sequence sums of squares: read by a norm task (the producers
+//           of its input left them there), accumulated by an ADD_PACKED task over the rows it updated
+// Pops [norm weights, K bf16], then n_chunks x (X chunk, W chunk).  With norm the X chunks become
+// bf16(w * bf16(x * rsqrt(sum/K + eps))) in shared memory before the tensor cores read them.
+#define VDC_GEMM_MODE_STORE_ROWS 0    // bf16 out[b * ld + row]
+#define VDC_GEMM_MODE_SILU_PAIRS 1    // rows (2j, 2j+1) = (gate_j, up_j): k-chunk-major act[b, j]
+#define VDC_GEMM_MODE_ARGMAX 2        // atomicMax of (orderable bf16 logit, ~row) per sequence
+#define VDC_GEMM_MODE_ADD_PACKED 3    // k-chunk-major out[b, row] += bf16(value)   (residual add)
+//
+// EMBED_PACK (six words): [first sequence, count, Bpad] [state stride in words, hidden/8, barrier]
+// then 48-bit addresses of the first state block, the embedding table, the k-chunk-major output and
+// the fp32 per-sequence sums of squares.  Copies embedding row state[b].TOKEN of each of its
+// sequences into the output and stores the row's sum of squares; pops nothing.
+//
+// BATCH_ADVANCE (five words): [batch, state stride in words, token-log stride] then 48-bit addresses
+// of the argmax keys, of the token log and of the sums of squares, then [count of those floats (lo, hi), 0]
+// (they are cleared for the next step).  Pops one raw address (the first state block; it carries
+// the wait on the vocabulary projection).  Thread b turns key b into the next token of sequence b,
+// logs it, advances that sequence's state block and clears the key.
 #define VDC_GEMV_MODE_STORE 0
 #define VDC_GEMV_MODE_SILU_PAIRS 1
 #define VDC_GEMV_MODE_ARGMAX 2
@@ -132,6 +168,7 @@
 
 // ATTN_DECODE args[2] bits
 #define VDC_ATTN_QKNORM_BIT 0x1
+#define VDC_ATTN_PACKED_BIT 0x2   // output goes to a k-chunk-major matrix; last word args[2] = b | Bpad/16 << 8
 
 // words of the per-sequence decode state block in device memory
 #define VDC_ST_POS 0        // number of cached positions = position of the token being decoded

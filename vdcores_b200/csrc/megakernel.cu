@@ -2,6 +2,7 @@
 #include "mk_common.cuh"
 #include "mk_memory.cuh"
 #include "mk_compute.cuh"
+#include "mk_tensor.cuh"
 
 namespace vdc {
 
@@ -28,7 +29,8 @@ __device__ void compute_core(const Ctx& c, const VdcCInst* __restrict__ insts, i
     VdcCInst ci, ex;
     *reinterpret_cast<uint2*>(&ci) = w0;
     *reinterpret_cast<uint2*>(&ex) = w1;
-    const bool two_words = ci.opcode == 0x7200 || ci.opcode == 0x7201 || ci.opcode == 0x7202 || ci.opcode == 0x7203 || ci.opcode == 0x7210 || ci.opcode == 0x7211 || ci.opcode == 0x7230;
+    const bool two_words = ci.opcode == 0x7200 || ci.opcode == 0x7201 || ci.opcode == 0x7202 || ci.opcode == 0x7203 || ci.opcode == 0x7210 || ci.opcode == 0x7211 || ci.opcode == 0x7230 ||
+                           ci.opcode == 0x7300 || ci.opcode == 0x7310 || ci.opcode == 0x7320;
     q.pc += two_words ? 2 : 1;
     if (two_words) {
       w0 = ld_word(q.pc);
@@ -152,6 +154,8 @@ __device__ void compute_core(const Ctx& c, const VdcCInst* __restrict__ insts, i
         a.out = reinterpret_cast<__nv_bfloat16*>(addr48(e[5]));
         a.split = e[6].args[0];
         a.bar = e[6].args[1];
+        a.b = (a.flags & VDC_ATTN_PACKED_BIT) ? (e[6].args[2] & 0xFF) : 0;
+        a.bpad = (a.flags & VDC_ATTN_PACKED_BIT) ? (e[6].args[2] >> 8) * 16 : 0;
         if (ci.opcode == 0x7210) task_attn_decode<4>(q, a);
         else task_attn_decode<8>(q, a);
         break;
@@ -161,6 +165,67 @@ __device__ void compute_core(const Ctx& c, const VdcCInst* __restrict__ insts, i
         const uint32_t bytes = (uint32_t)ex.args[0] | ((uint32_t)ex.args[1] << 16);
         for (uint32_t off = (uint32_t)tid * 128u; off < bytes; off += kCT * 128u)
           asm volatile("prefetch.global.L2 [%0];" ::"l"(base + off));
+        break;
+      }
+      case 0x7300: {  // GEMM_TC_BF16 (seven words)
+        auto addr48 = [](const VdcCInst& w) {
+          return (uint64_t)w.args[0] | ((uint64_t)w.args[1] << 16) | ((uint64_t)w.args[2] << 32);
+        };
+        VdcCInst e[5];
+#pragma unroll
+        for (int k = 0; k < 5; ++k) *reinterpret_cast<uint2*>(&e[k]) = ld_word(q.pc + (uint32_t)k);
+        q.pc += 5;
+        GemmTc g;
+        g.n_chunks = ci.args[0];
+        g.N = (ci.args[1] & 0xFF) * 16;
+        g.mode = (ci.args[1] >> 8) & 0xF;
+        g.norm = (ci.args[1] >> 12) & 1;
+        g.KS = ci.args[2];
+        g.eps = __uint_as_float(((uint32_t)ex.args[0] << 16) | ex.args[1]);
+        g.B = ex.args[2];
+        g.out = reinterpret_cast<uint8_t*>(addr48(e[0]));
+        g.keys = reinterpret_cast<unsigned long long*>(addr48(e[1]));
+        g.n0 = (int)e[2].args[0] | ((int)e[2].args[1] << 16);
+        g.bar = e[2].args[2];
+        g.ld = (int)e[3].args[0] * 16;
+        g.Bpad = e[3].args[1];
+        g.stats = reinterpret_cast<float*>(addr48(e[4]));
+        const bool ok = g.N >= 16 && g.N <= 256 && g.B >= 1 && g.B <= g.Bpad &&
+                        (g.Bpad == 16 || g.Bpad == 32 || g.Bpad == 64 || g.Bpad == 128) && g.KS >= 1 &&
+                        (!g.norm || g.stats != nullptr);
+        if (!ok) {
+          raise_abort(c, VDC_ERR_BAD_OPCODE, 0, (int)q.pc, ci.opcode, -1, g.N);
+          q.aborted = true;
+          break;
+        }
+        task_gemm_tc(q, g);
+        break;
+      }
+      case 0x7310: {  // EMBED_PACK (six words)
+        auto addr48 = [](const VdcCInst& w) {
+          return (uint64_t)w.args[0] | ((uint64_t)w.args[1] << 16) | ((uint64_t)w.args[2] << 32);
+        };
+        VdcCInst e[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) *reinterpret_cast<uint2*>(&e[k]) = ld_word(q.pc + (uint32_t)k);
+        q.pc += 4;
+        task_embed_pack(q, ci.args[0], ci.args[1], ci.args[2], ex.args[0], ex.args[1], ex.args[2],
+                        reinterpret_cast<const int*>(addr48(e[0])), reinterpret_cast<const uint8_t*>(addr48(e[1])),
+                        reinterpret_cast<uint8_t*>(addr48(e[2])), reinterpret_cast<float*>(addr48(e[3])));
+        break;
+      }
+      case 0x7320: {  // BATCH_ADVANCE (five words)
+        auto addr48 = [](const VdcCInst& w) {
+          return (uint64_t)w.args[0] | ((uint64_t)w.args[1] << 16) | ((uint64_t)w.args[2] << 32);
+        };
+        VdcCInst e2, e3, e4;
+        *reinterpret_cast<uint2*>(&e2) = ld_word(q.pc);
+        *reinterpret_cast<uint2*>(&e3) = ld_word(q.pc + 1);
+        *reinterpret_cast<uint2*>(&e4) = ld_word(q.pc + 2);
+        q.pc += 3;
+        task_batch_advance(q, ci.args[0], ci.args[1], ci.args[2], reinterpret_cast<unsigned long long*>(addr48(ex)),
+                           reinterpret_cast<int*>(addr48(e2)), reinterpret_cast<float*>(addr48(e3)),
+                           (int)e4.args[0] | ((int)e4.args[1] << 16));
         break;
       }
       case 0x7220: task_argmax_final(q, ci.args[0], ci.args[1]); break;
@@ -206,6 +271,7 @@ vdc_megakernel(const VdcCInst* __restrict__ cinsts, const VdcMInst* __restrict__
     sh.demand_pos = 0;
     sh.pf_go = 0;
     sh.pf_exit = 0;
+    sh.tmem_ready = 0;
     profile[c.sm * VDC_NUM_PROFILE_EVENTS + 0] = globaltimer_ns();
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -223,6 +289,17 @@ vdc_megakernel(const VdcCInst* __restrict__ cinsts, const VdcMInst* __restrict__
     else if (lane == 0) load_port(c, w - 2);
   }
   __syncthreads();
+  if (sh.tmem_ready && tid < 32) {
+    // Tensor memory goes back only after every tensor-core operation has finished (an
+    // aborted task may have left some in flight): bounded wait on one last commit.
+    if (tid == 0) {
+      umma_commit(&sh.mma_final);
+      const uint64_t t0 = globaltimer_ns();
+      while (!mbar_try_wait(&sh.mma_final, 0) && globaltimer_ns() - t0 < 2000000ull) __nanosleep(200);
+    }
+    __syncwarp();
+    tmem_dealloc(sh.tmem_base, kTmemCols);
+  }
   // After an abort some bulk loads may still be in flight towards this CTA's
   // shared memory: give them a bounded time to land before the CTA retires.
   if (tid == 0 && ld_relaxed_gpu(&status->abort) != 0) {

@@ -166,6 +166,11 @@ struct __align__(16) Shared {
   alignas(16) float qrot[8 * VDC_HEAD_DIM];
   alignas(16) float misc[64];
   uint4 newrows[32];                        // attention: rotated new key row, new value row (bf16)
+  // tensor cores (batched decode): tensor memory is allocated by the first task that needs it
+  uint32_t tmem_base;                       // written by tcgen05.alloc
+  volatile int tmem_ready;
+  uint64_t mma_bar[4];                      // completion of the tensor-core work of chunk i % 4
+  uint64_t mma_final;                       // used once, before the tensor memory is given back
 };
 
 struct Ctx {

@@ -19,6 +19,7 @@ struct Compute {
   uint32_t pc;
   bool aborted;
   uint64_t stall;    // cycles thread 0 spent waiting for data
+  unsigned mma_count;  // tensor-core commits issued so far (thread 0)
 
   // CTA-wide pop: thread 0 waits for the entry (bounded), everybody gets its
   // word after one compute_sync.  Returns kPopAbort once a wait was given up.
@@ -496,6 +497,7 @@ struct AttnArgs {
   float* records;    // [n_splits][rec_floats] of this head
   int* counter;
   __nv_bfloat16* out;  // G*128 outputs of this head
+  int b, bpad;         // bpad != 0: `out` is this head's first k group in a k-chunk-major [bpad, *] matrix, row b
 };
 
 template <int G>
@@ -767,7 +769,12 @@ __device__ void task_attn_decode(Compute& q, const AttnArgs& a) {
       num = fmaf(w, __ldcg(r + o), num);
       den = fmaf(w, __ldcg(r + G * D + G + g), den);
     }
-    a.out[o] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+    const __nv_bfloat16 res = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+    if (a.bpad)
+      *reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<uint8_t*>(a.out) + (size_t)(o >> 3) * a.bpad * 16 +
+                                        (a.b >> 3) * 128 + (a.b & 7) * 16 + (o & 7) * 2) = res;
+    else
+      a.out[o] = res;
   }
   compute_sync();
   if (q.tid == 0) {

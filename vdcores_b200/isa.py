@@ -35,6 +35,11 @@ GEMV_MODE_MOE_DOWN = _defs["GEMV_MODE_MOE_DOWN"]
 GEMV_NORM_BIT = _defs["GEMV_NORM_BIT"]
 GEMV_ACC_BIT = _defs["GEMV_ACC_BIT"]
 ATTN_QKNORM_BIT = _defs["ATTN_QKNORM_BIT"]
+ATTN_PACKED_BIT = _defs["ATTN_PACKED_BIT"]
+GEMM_MODE_STORE_ROWS = _defs["GEMM_MODE_STORE_ROWS"]
+GEMM_MODE_SILU_PAIRS = _defs["GEMM_MODE_SILU_PAIRS"]
+GEMM_MODE_ARGMAX = _defs["GEMM_MODE_ARGMAX"]
+GEMM_MODE_ADD_PACKED = _defs["GEMM_MODE_ADD_PACKED"]
 
 ST_POS, ST_NPAGES, ST_TOKEN, ST_STEP = _defs["ST_POS"], _defs["ST_NPAGES"], _defs["ST_TOKEN"], _defs["ST_STEP"]
 ST_NEWROW, ST_NKVH, ST_MAXPAGES, ST_ERR = _defs["ST_NEWROW"], _defs["ST_NKVH"], _defs["ST_MAXPAGES"], _defs["ST_ERR"]

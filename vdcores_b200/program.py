@@ -290,13 +290,15 @@ class Program:
 
     def attn_decode(self, sm, *, G, state_addr, rope: Src, norm_w: Optional[Src], qkv: Src, k_page_addr, v_page_addr,
                     page_shift, base_page, max_pages, records_addr, counter_addr, out_addr, split, n_splits,
-                    release, qk_eps: float = 1e-6):
+                    release, qk_eps: float = 1e-6, packed: Optional[tuple] = None):
         """One (KV head, split) unit of the decode attention.  k_page_addr /
         v_page_addr: this head's rows inside page 0 of the layer's K / V pool;
         the page table in the state block selects the page.  The unit that
         completes the head last merges the n_splits records at records_addr,
         writes G*128 bf16 to out_addr and counts `release` down once (declare it
-        with add_releases(release, 1) per head)."""
+        with add_releases(release, 1) per head).  packed=(b, Bpad): out_addr is the
+        head's first k group inside a k-chunk-major [Bpad, q_width] matrix and the
+        outputs go to its row b (batched decode)."""
         page_bytes = isa.KV_PAGE * isa.HEAD_DIM * 2
         assert qkv.nbytes == (G + 2) * isa.HEAD_DIM * 2
         self.load(sm, rope, default_port=1)
@@ -314,12 +316,85 @@ class Program:
         self.bytes_loaded[sm] += 2 * page_bytes * max_pages
         e = f32_bits(qk_eps)
         op = isa.OP_ATTN_DECODE_PAGED_G4 if G == 4 else isa.OP_ATTN_DECODE_PAGED_G8
-        self.comp(sm, op, max_pages, base_page, isa.ATTN_QKNORM_BIT if norm_w is not None else 0)
+        flags = (isa.ATTN_QKNORM_BIT if norm_w is not None else 0) | (isa.ATTN_PACKED_BIT if packed else 0)
+        self.comp(sm, op, max_pages, base_page, flags)
         self.comp(sm, isa.OP_EXT, e >> 16, e & 0xFFFF, n_splits)
         for addr in (state_addr, k_page_addr, v_page_addr, records_addr, counter_addr, out_addr):
             assert 0 <= addr < 1 << 48
             self.comp(sm, isa.OP_EXT, addr & 0xFFFF, (addr >> 16) & 0xFFFF, (addr >> 32) & 0xFFFF)
-        self.comp(sm, isa.OP_EXT, split, release, 0)
+        self.comp(sm, isa.OP_EXT, split, release, (packed[0] | (packed[1] // 16) << 8) if packed else 0)
+
+    # ------------------------------------------------------------------ batched decode (tensor cores)
+    def gemm_tc(self, sm, *, w_addr, N, K, Kc, x_addr, B, Bpad, out_addr, mode, x_wait: Optional[int] = None,
+                norm_w: Optional[Src] = None, eps: float = 0.0, n0: int = 0, ld: int = 0, keys_addr: int = 0,
+                stats_addr: int = 0, release: Optional[int] = None):
+        """D[b, n] = sum_k X[b, k] W[n, k] for one unit of N weight rows (k-chunk-major
+        [K/8][N/8][8][8] bf16 at w_addr) against the k-chunk-major activation matrix
+        [Bpad, K] at x_addr, streamed as K/Kc pairs of (X chunk, W chunk).  `mode`
+        selects the epilogue (isa.GEMM_MODE_*); n0 is the unit's first output row.
+        stats_addr: fp32 per-sequence sums of squares, read when norm_w is given (the
+        RMSNorm of the input rows), accumulated over the updated rows in ADD_PACKED mode."""
+        assert norm_w is None or stats_addr
+        assert N % 16 == 0 and 16 <= N <= 256 and Bpad in (16, 32, 64, 128) and 1 <= B <= Bpad
+        assert Kc % 16 == 0 and K % Kc == 0 and n0 % 16 == 0 and ld % 16 == 0
+        n_chunks = K // Kc
+        xbytes, wbytes = Bpad * Kc * 2, N * Kc * 2
+        assert xbytes <= 32768 and wbytes <= 32768 and n_chunks <= 0xFFFF
+        # the tensor cores read 128 lanes of X: the rows past Bpad fall behind the chunk's end
+        xslots = slots_for(xbytes + max(0, 2048 - Bpad * 16))
+        wslots = slots_for(wbytes)
+        if norm_w is not None:
+            assert norm_w.nbytes == K * 2
+            self.load(sm, norm_w, default_port=1)
+        flags = isa.F_PORT | (isa.F_BARRIER if x_wait is not None else 0)
+        self.mem(sm, isa.OP_ALLOC_TMA_LOAD_1D, size=xbytes, nslot=xslots, bar=x_wait or 0, address=x_addr, flags=flags)
+        self.mem(sm, isa.OP_ALLOC_TMA_LOAD_1D, size=wbytes, nslot=wslots, address=w_addr)
+        if n_chunks > 1:
+            self.repeat(sm, n_chunks - 1, [xbytes, wbytes])
+            self.mem(sm, isa.OP_ALLOC_TMA_LOAD_1D, size=xbytes, nslot=xslots, address=x_addr + xbytes, flags=isa.F_PORT)
+            self.mem(sm, isa.OP_ALLOC_TMA_LOAD_1D, size=wbytes, nslot=wslots, address=w_addr + wbytes, flags=isa.F_JUMP)
+        self.bytes_loaded[sm] += (xbytes + wbytes) * n_chunks
+        if release is not None:
+            self.bar_counts[release] += 1
+        e = f32_bits(eps)
+        a48 = lambda a: (a & 0xFFFF, (a >> 16) & 0xFFFF, (a >> 32) & 0xFFFF)
+        assert 0 <= out_addr < 1 << 48 and 0 <= keys_addr < 1 << 48 and out_addr % 16 == 0 and keys_addr % 8 == 0
+        self.comp(sm, isa.OP_GEMM_TC_BF16, n_chunks, (N // 16) | (mode << 8) | ((1 << 12) if norm_w is not None else 0),
+                  Kc // 16)
+        self.comp(sm, isa.OP_EXT, e >> 16, e & 0xFFFF, B)
+        self.comp(sm, isa.OP_EXT, *a48(out_addr))
+        self.comp(sm, isa.OP_EXT, *a48(keys_addr))
+        self.comp(sm, isa.OP_EXT, n0 & 0xFFFF, n0 >> 16, 0xFFFF if release is None else release)
+        self.comp(sm, isa.OP_EXT, ld // 16, Bpad, 0)
+        assert 0 <= stats_addr < 1 << 48 and stats_addr % 4 == 0
+        self.comp(sm, isa.OP_EXT, *a48(stats_addr))
+
+    def embed_pack(self, sm, *, b0, count, Bpad, state_addr, state_stride_words, hidden, table_addr, out_addr,
+                   stats_addr, release: Optional[int] = None):
+        """Copies embedding row state[b].TOKEN of sequences b0..b0+count-1 into row b
+        of the k-chunk-major [Bpad, hidden] matrix at out_addr."""
+        assert hidden % 8 == 0 and hidden // 8 <= 0xFFFF and state_stride_words <= 0xFFFF
+        if release is not None:
+            self.bar_counts[release] += 1
+        a48 = lambda a: (a & 0xFFFF, (a >> 16) & 0xFFFF, (a >> 32) & 0xFFFF)
+        self.comp(sm, isa.OP_EMBED_PACK, b0, count, Bpad)
+        self.comp(sm, isa.OP_EXT, state_stride_words, hidden // 8, 0xFFFF if release is None else release)
+        for a in (state_addr, table_addr, out_addr, stats_addr):
+            assert 0 <= a < 1 << 48
+            self.comp(sm, isa.OP_EXT, *a48(a))
+
+    def batch_advance(self, sm, *, batch, state_addr, state_stride_words, keys_addr, log_addr, log_stride, wait,
+                      stats_addr=0, n_stats=0):
+        """Turns the argmax keys into next tokens, logs them and advances every
+        sequence's state block, once barrier `wait` has opened."""
+        assert batch <= isa.COMPUTE_THREADS and log_stride <= 0xFFFF and state_stride_words <= 0xFFFF
+        self.raw_address(sm, state_addr, 25, wait=wait)
+        a48 = lambda a: (a & 0xFFFF, (a >> 16) & 0xFFFF, (a >> 32) & 0xFFFF)
+        self.comp(sm, isa.OP_BATCH_ADVANCE, batch, state_stride_words, log_stride)
+        self.comp(sm, isa.OP_EXT, *a48(keys_addr))
+        self.comp(sm, isa.OP_EXT, *a48(log_addr))
+        self.comp(sm, isa.OP_EXT, *a48(stats_addr))
+        self.comp(sm, isa.OP_EXT, n_stats & 0xFFFF, n_stats >> 16, 0)
 
     def moe_route(self, sm, *, logits: Src, route_addr: int, n_experts: int, top_k: int, release=None):
         """Softmax over n_experts fp32 router logits, top-k, renormalise: writes int32
