@@ -173,7 +173,16 @@ def run_gpu(args):
     max_seq = ((PROMPT_LEN + W + K + 8 + 63) // 64) * 64
     g = torch.Generator().manual_seed(0)
     prompt = torch.randint(0, cfg.vocab, (PROMPT_LEN,), generator=g)
-    if world == 1:
+    if world == 1 and args.batch > 1:
+        # batched decode: the projections run on the tensor cores, one state block per sequence
+        from vdcores_b200.batch import BatchDecodeEngine
+        assert args.wkind == "bf16", "batched decode is bf16 only"
+        eng = BatchDecodeEngine(cfg, args.batch, max_seq=max_seq, device=dev, max_steps=W + K + 8)
+        eng.init_random_weights(seed=0)
+        prompt = torch.randint(0, cfg.vocab, (args.batch, PROMPT_LEN), generator=g)
+        first = eng.prefill(prompt)
+        tokens_per_step, scaling, parallelism = args.batch, "strong", "single GPU"
+    elif world == 1:
         eng = DecodeEngine(cfg, max_seq=max_seq, device=dev, max_steps=W + K + 8, wkind=args.wkind)
         eng.init_random_weights(seed=0)
         first = eng.prefill(prompt)
@@ -199,8 +208,17 @@ def run_gpu(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    batched = world == 1 and args.batch > 1
+
+    def reset():
+        if batched:
+            for b in range(args.batch):
+                eng.set_state(PROMPT_LEN, first[b], b=b)
+        else:
+            eng.set_state(PROMPT_LEN, first)
+
     # ---- device-resident arm: K launches back to back, CUDA events on the launching stream
-    eng.set_state(PROMPT_LEN, first)
+    reset()
     for _ in range(W):
         eng.step_async()
     runtime.read_status(stream.cuda_stream)
@@ -220,11 +238,11 @@ def run_gpu(args):
     runtime.read_status(stream.cuda_stream)
     ms = e0.elapsed_time(e1)
     dbg(f'timed region done: {ms:.2f} ms')
-    tokens = eng.token_log[W:W + K].tolist()
+    tokens = eng.token_log[0, W:W + K].tolist() if batched else eng.token_log[W:W + K].tolist()
     # ---- end-to-end arm: host token in, host token out, every step
     e2e_ms = float("nan")
     if not args.no_e2e:
-        eng.set_state(PROMPT_LEN, first)
+        reset()
         tok = first
         for _ in range(W):
             tok = eng.step_host(tok)
@@ -254,13 +272,13 @@ def run_gpu(args):
     bytes_per_launch = eng.algorithmic_bytes(mid_pos)
     achieved = bytes_per_launch / (ms / K * 1e-3) / 1e9
     line = {
-        "metric": METRIC if args.model == "llama31-8b" else METRIC.replace("Llama-3.1-8B", {"qwen3-8b": "Qwen3-8B", "qwen3-30b-a3b": "Qwen3-30B-A3B"}[args.model]),
+        "metric": (METRIC if args.batch == 1 else METRIC.replace("batch 1", f"batch {args.batch}")) if args.model == "llama31-8b" else METRIC.replace("Llama-3.1-8B", {"qwen3-8b": "Qwen3-8B", "qwen3-30b-a3b": "Qwen3-30B-A3B"}[args.model]),
         "value": tokens_per_step * K / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": K,
         "warmup": W, "ms_per_step": ms / K, "higher_is_better": True, "scaling": scaling, "vs_baseline": None,
         "dtype": args.wkind, "data": "synthetic",
         "config": {"workload": (f"{args.model} shape ({cfg.n_layers} layers, hidden {cfg.hidden}, {cfg.n_heads}q/"
                                 f"{cfg.n_kv_heads}kv heads, FFN {cfg.ffn}, vocab {cfg.vocab}), {args.wkind} projections, "
-                                f"batch 1, {PROMPT_LEN}-token prompt prefilled, greedy decode"),
+                                f"batch {args.batch}, {PROMPT_LEN}-token prompt{'s' if args.batch > 1 else ''} prefilled, greedy decode"),
                    "l2": "inputs larger than L2: every step streams ~15 GB of weights through a 126 MB L2",
                    "parallelism": parallelism,
                    "num_sms": eng.num_sms, "kv_splits": eng.n_splits, "first_tokens": tokens[:4],
@@ -271,7 +289,8 @@ def run_gpu(args):
                      # 4-layer case of the same program (profiles/), scaled here by the bytes of this launch
                      "traffic": bytes_per_launch * 1.007 / 1e9, "traffic_unit": "GB", "peak_kind": f"of {peak_kind}", "frac_of_8TBs": achieved / 8000.0,
                      "bytes_per_launch": bytes_per_launch},
-        "e2e": ({"value": K / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4}
+        "e2e": ({"value": tokens_per_step * K / (e2e_ms * 1e-3), "unit": "tokens/s",
+                 "h2d_bytes_per_step": 4 * tokens_per_step, "d2h_bytes_per_step": 4 * tokens_per_step}
                 if not args.no_e2e else None),
         "gpu_launches": K * eng.launches_per_step,
         "clocks": clk.summary(),
@@ -294,6 +313,8 @@ def main():
                     help="storage of the layer projections (fp8: e4m3 + per-row fp32 scales; reported, not the headline)")
     ap.add_argument("--model", default="llama31-8b", choices=["llama31-8b", "qwen3-8b", "qwen3-30b-a3b"],
                     help="shape of the random-init model (qwen3-8b: 36 layers, FFN 12288, per-head QK norm, 4096-token prompt)")
+    ap.add_argument("--batch", type=int, default=1,
+                    help="sequences decoded in lock-step (> 1: tensor-core projections, bf16, one GPU)")
     ap.add_argument("--layers", type=int, default=32,
                     help="profiling only: a model with fewer layers of the same shape (the JSON line says so)")
     args = ap.parse_args()

@@ -230,6 +230,7 @@ class BatchDecodeEngine(DecodeEngine):
         self.minsts = torch.from_numpy(m).to(self.dev)
         self.bars_init = torch.from_numpy(bars).to(self.dev)
         self.bars.copy_(self.bars_init)
+        self.launches_per_step = 1
 
     # ------------------------------------------------------------------ state
     def set_state(self, pos: int, token: int, b: int = None):

@@ -80,6 +80,12 @@ __device__ void control_warp(const Ctx& c, const VdcMInst* __restrict__ insts, i
   uint32_t ic_base = 0;  // first instruction index held in the shared-memory window
   icache_fill(sh, insts, 0, n_insts, lane);
 
+#ifdef VDC_CTRL_PROFILE
+  long long tp_fetch = 0, tp_alloc = 0, tp_pub = 0, tp_ctl = 0, tp_mark = clock64();
+#define CTP(var) { const long long _n = clock64(); var += _n - tp_mark; tp_mark = _n; }
+#else
+#define CTP(var)
+#endif
   while (running) {
     pc = next_pc;
     if (pc - ic_base >= 64u) {
@@ -102,6 +108,7 @@ __device__ void control_warp(const Ctx& c, const VdcMInst* __restrict__ insts, i
     const uint32_t size = w.x >> 16;
     const uint32_t num_slots = w.y & 0xFFFFu;
 
+    CTP(tp_fetch);
     if (opcode & VDC_F_ALLOCATE) {
       if (ind_pending) {
         const uint64_t addr = (((uint64_t)w.w << 32) | w.z) + ind_off;
@@ -142,6 +149,7 @@ __device__ void control_warp(const Ctx& c, const VdcMInst* __restrict__ insts, i
         word = (int)mask;
       }
 
+      CTP(tp_alloc);
       // a ring entry is recycled only after every consumer moved past it
       if (tail - head_cache >= (unsigned)kQ) {
         uint32_t it = 0;
@@ -175,6 +183,7 @@ __device__ void control_warp(const Ctx& c, const VdcMInst* __restrict__ insts, i
         if (loop_counter > 0) next_pc = (uint32_t)loop_start;
         accum += delta;
       }
+      CTP(tp_pub);
     } else {
       const uint64_t address = ((uint64_t)w.w << 32) | w.z;
       const uint32_t arg = w.y >> 16;
@@ -364,8 +373,15 @@ __device__ void control_warp(const Ctx& c, const VdcMInst* __restrict__ insts, i
         default:
           break;  // OP_SHIFT_RESOURCE and unknown control ids are no-ops, as in the reference
       }
+      CTP(tp_ctl);
     }
   }
+#ifdef VDC_CTRL_PROFILE
+  if (lane == 0) {
+    uint64_t* pr = c.profile + c.sm * VDC_NUM_PROFILE_EVENTS;
+    pr[120] = tp_fetch; pr[121] = tp_alloc; pr[122] = tp_pub; pr[123] = tp_ctl;
+  }
+#endif
   if (lane == 0) {
     sh->pf_exit = 1;
     c.profile[c.sm * VDC_NUM_PROFILE_EVENTS + 6] = n_inst;

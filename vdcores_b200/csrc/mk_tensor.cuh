@@ -107,7 +107,8 @@ __device__ void task_gemm_tc(Compute& q, const GemmTc& g) {
     if (q.warp == 0) tmem_alloc(&sh->tmem_base, kTmemCols);
     if (q.tid >= 32 && q.tid < 36) mbar_init(&sh->mma_bar[q.tid - 32], 1);
     if (q.tid == 36) mbar_init(&sh->mma_final, 1);
-    if (q.tid >= 32 && q.tid <= 36) asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    if (q.tid >= 64 && q.tid < 80) mbar_init(&sh->x_ready[q.tid - 64], 1);
+    if (q.tid >= 32 && q.tid < 80) asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     tc_fence_before();
     compute_sync();
     tc_fence_after();
@@ -122,27 +123,34 @@ __device__ void task_gemm_tc(Compute& q, const GemmTc& g) {
   const uint32_t lbo_a = (uint32_t)g.Bpad * 16u, lbo_b = (uint32_t)g.N * 16u;
   const int pieces = g.KS * 2 * g.Bpad;  // 16-byte pieces of one X chunk
   const int K = g.n_chunks * g.KS * 16;
-  int prev_masks = 0;                    // thread 0: slots of the chunk whose tensor-core reads are in flight
+  const unsigned n_ent = 2u * (unsigned)g.n_chunks;  // ring entries of this task: X chunk, W chunk, X chunk, ...
 
-  for (int ch = 0; ch < g.n_chunks; ++ch) {
-    const int xm = q.pop();
-    const int wm = q.pop();
-    if (q.aborted) return;
-    uint8_t* xs = (uint8_t*)slot_ptr(c, first_slot(xm));
-    const uint8_t* ws = (const uint8_t*)slot_ptr(c, first_slot(wm));
-    if (g.norm) {
-      if (ch == 0) {
-        // The first X chunk waited for the producers of the input matrix, and with them for the
-        // sums of squares they left per sequence (read past L1: other SMs wrote them).
-        if (q.tid < g.Bpad) sh->red[q.tid] = rsqrtf(__ldcg(g.stats + q.tid) / (float)K + g.eps);
-        compute_sync();
+  // The streaming loop has no CTA-wide synchronisation.  Warp 0 consumes the ring entries in
+  // order: it waits for a chunk pair, one lane issues the tensor-core work and, once the
+  // previous pair's reads are done, recycles that pair's slots and ring entries.  With norm
+  // the other seven warps run ahead of it, each normalising every seventh X chunk in place
+  // and signalling that chunk's barrier.
+  q.warp_phase_begin(n_ent, q.warp == 0 ? 0u : n_ent);
+  if (q.warp > 0 && g.norm) {
+    float* rs = sh->red + q.warp * 128;  // this warp's copy of the per-sequence rsqrt(mean x^2 + eps)
+    bool have_rstd = false;
+    for (int ch = q.warp - 1; ch < g.n_chunks; ch += kCW - 1) {
+      const int xm = q.warp_wait(2u * (unsigned)ch);
+      if (xm == kPopAbort) break;
+      if (!have_rstd) {
+        // Any X chunk of this task was loaded after the producers of the input matrix had
+        // finished, and with them the sums of squares they left (read past L1).
+        for (int bb = q.lane; bb < g.Bpad; bb += 32) rs[bb] = rsqrtf(__ldcg(g.stats + bb) / (float)K + g.eps);
+        __syncwarp();
+        have_rstd = true;
       }
-      // RMSNorm in place, rounded like a bf16 tensor expression: bf16(w * bf16(x * rstd))
+      uint8_t* xs = (uint8_t*)slot_ptr(c, first_slot(xm));
       const int kc0 = ch * g.KS * 2;  // index of the chunk's first 8-element k group
-      for (int p = q.tid; p < pieces; p += kCT) {
+      // RMSNorm in place, rounded like a bf16 tensor expression: bf16(w * bf16(x * rstd))
+      for (int p = q.lane; p < pieces; p += 32) {
         const uint4 v = lds128(xs + p * 16);
         const uint4 w = lds128(nw + (kc0 + p / g.Bpad) * 16);
-        const float rstd = sh->red[p & (g.Bpad - 1)];
+        const float rstd = rs[p & (g.Bpad - 1)];
         const uint32_t xv[4] = {v.x, v.y, v.z, v.w}, wv[4] = {w.x, w.y, w.z, w.w};
         uint32_t o[4];
 #pragma unroll
@@ -151,34 +159,90 @@ __device__ void task_gemm_tc(Compute& q, const GemmTc& g) {
         *reinterpret_cast<uint4*>(xs + p * 16) = make_uint4(o[0], o[1], o[2], o[3]);
       }
       fence_proxy_async_smem();  // the tensor cores read shared memory through the async proxy
-      compute_sync();
-    }
-    if (q.tid == 0) {
-      tc_fence_after();
-      const uint32_t xa = smem_u32(xs), wa = smem_u32(ws);
-      for (int kk = 0; kk < g.KS; ++kk)
-        umma_bf16(tmem, umma_desc(xa + (uint32_t)kk * 2u * lbo_a, lbo_a, 128u),
-                  umma_desc(wa + (uint32_t)kk * 2u * lbo_b, lbo_b, 128u), idesc, (uint32_t)((ch | kk) != 0));
-      umma_commit(&sh->mma_bar[q.mma_count & 3u]);
-      // the previous chunk's reads are certainly done once its commit arrived: recycle its slots
-      if (ch > 0) {
-        if (!mma_wait(q, q.mma_count - 1)) prev_masks = 0;
-        if (prev_masks) atomicOr(&sh->slot_avail, (uint32_t)prev_masks & kSlotMaskAll);
-      }
-      prev_masks = (xm | wm) & (int)kSlotMaskAll;
-      q.mma_count++;
+      __syncwarp();
+      if (q.lane == 0) mbar_arrive(&sh->x_ready[(q.xr_count + (unsigned)ch) & 15u]);
     }
   }
-  if (q.tid == 0) {
-    if (mma_wait(q, q.mma_count - 1) && prev_masks) atomicOr(&sh->slot_avail, (uint32_t)prev_masks & kSlotMaskAll);
+  if (q.warp == 0) {
+    int prev_masks = 0;  // lane 0: slots of the chunk pair whose tensor-core reads are in flight
+#ifdef VDC_TC_PROFILE
+    long long t_data = 0, t_xr = 0, t_mma = 0, t_wait = 0;
+#endif
+    for (int ch = 0; ch < g.n_chunks; ++ch) {
+#ifdef VDC_TC_PROFILE
+      const long long td0 = clock64();
+#endif
+      const int xm = q.warp_wait(2u * (unsigned)ch);
+      const int wm = q.warp_wait(2u * (unsigned)ch + 1u);
+      if (xm == kPopAbort || wm == kPopAbort) break;
+#ifdef VDC_TC_PROFILE
+      t_data += clock64() - td0;
+      const long long tx0 = clock64();
+#endif
+      if (g.norm) {
+        int ok = 1;
+        if (q.lane == 0) {
+          const unsigned gch = q.xr_count + (unsigned)ch;
+          uint64_t* bar = &sh->x_ready[gch & 15u];
+          const uint32_t parity = (gch >> 4) & 1u;
+          if (!mbar_try_wait(bar, parity)) {
+            ok = wait_until(c, [&] { return mbar_try_wait(bar, parity); }, 0, (int)q.pc, 0x7300, -1, 0);
+            if (!ok) sh->aborted = 1;
+          }
+        }
+        if (!__shfl_sync(0xffffffffu, ok, 0)) break;
+      }
+#ifdef VDC_TC_PROFILE
+      t_xr += clock64() - tx0;
+      const long long tm0 = clock64();
+#endif
+      if (q.lane == 0) {
+        tc_fence_after();
+        uint64_t adesc = umma_desc(smem_u32(slot_ptr(c, first_slot(xm))), lbo_a, 128u);
+        uint64_t bdesc = umma_desc(smem_u32(slot_ptr(c, first_slot(wm))), lbo_b, 128u);
+        const uint64_t step_a = (uint64_t)((2u * lbo_a) >> 4), step_b = (uint64_t)((2u * lbo_b) >> 4);
+        umma_bf16(tmem, adesc, bdesc, idesc, (uint32_t)(ch != 0));
+#pragma unroll 4
+        for (int kk = 1; kk < g.KS; ++kk) {
+          adesc += step_a;  // the start-address field: 16 k further in both operands
+          bdesc += step_b;
+          umma_bf16(tmem, adesc, bdesc, idesc, 1u);
+        }
+        umma_commit(&sh->mma_bar[q.mma_count & 3u]);
+#ifdef VDC_TC_PROFILE
+        t_mma += clock64() - tm0;
+        const long long tw0 = clock64();
+#endif
+        // the previous pair's reads are certainly done once its commit arrived
+        if (ch > 0) {
+          if (!mma_wait(q, q.mma_count - 1)) prev_masks = 0;
+          if (prev_masks) atomicOr(&sh->slot_avail, (uint32_t)prev_masks & kSlotMaskAll);
+          sh->warp_next[0] = q.head + 2u * (unsigned)ch;  // its ring entries may be recycled too
+        }
+        prev_masks = (xm | wm) & (int)kSlotMaskAll;
+        q.mma_count++;
+#ifdef VDC_TC_PROFILE
+        t_wait += clock64() - tw0;
+#endif
+      }
+      __syncwarp();
+    }
+    if (q.lane == 0) {
+      if (q.mma_count > 0 && mma_wait(q, q.mma_count - 1) && prev_masks)
+        atomicOr(&sh->slot_avail, (uint32_t)prev_masks & kSlotMaskAll);
+      sh->warp_next[0] = 0xFFFFFFFFu;
+#ifdef VDC_TC_PROFILE
+      uint64_t* pr = c.profile + c.sm * VDC_NUM_PROFILE_EVENTS;
+      pr[8] += t_data; pr[9] += t_xr; pr[10] += t_mma; pr[11] += t_wait; pr[12] += g.n_chunks;
+      pr[13] += (uint64_t)g.n_chunks * g.KS;
+#endif
+    }
   }
   tc_fence_before();
-  compute_sync();  // accumulator complete: thread 0 saw the last commit
+  q.warp_phase_end(n_ent);  // CTA barrier: accumulator complete (lane 0 saw the last commit)
   tc_fence_after();
-  if (sh->aborted) {
-    q.aborted = true;
-    return;
-  }
+  if (g.norm) q.xr_count += (unsigned)g.n_chunks;
+  if (q.aborted) return;
 
   // ---- epilogue: lane b of the accumulator belongs to sequence b; warps w and w+4 share the
   // lane quarter w % 4 and split the columns
