@@ -20,55 +20,47 @@ def _bpad(B):
     return next(p for p in (16, 32, 64, 128) if B <= p)
 
 
-def _units(M, n_sms):
-    """Contiguous row ranges per SM (multiples of 16), cut into units of at most 256 rows."""
-    groups = M // 16
-    out, g0 = [], 0
-    for sm in range(n_sms):
-        cnt = groups // n_sms + (1 if sm < groups % n_sms else 0)
-        while cnt > 0:
-            n = min(cnt, 16)
-            out.append((sm, g0 * 16, n * 16))
-            g0 += n
-            cnt -= n
-    return out
-
-
 def _gemm_program(dev, x, w, n_sms, mode, out, norm_w=None, eps=1e-5, ld=0, keys=None, stats=None):
-    from vdcores_b200.batch import BatchDecodeEngine, choose_kc, pack_kc
-    from vdcores_b200.program import Program, Src
+    from vdcores_b200.batch import BLOCK_ROWS, emit_projection, pack_blocks, pack_kc, projection_blocks
+    from vdcores_b200.program import Program
     B, K = x.shape
     Bp = _bpad(B)
     xp = torch.zeros(Bp, K, dtype=BF16)
     xp[:B] = x
     xd = pack_kc(xp.to(dev))
-    units = _units(w.shape[0], n_sms)
-    wd = BatchDecodeEngine._pack_units(w.to(dev), units)
+    wd = pack_blocks(w.to(dev))
     nwd = norm_w.to(dev) if norm_w is not None else None
     if norm_w is not None:      # the producers of a normed input leave its per-row sums of squares
         stats = torch.zeros(128, dtype=torch.float32)
         stats[:B] = x.float().pow(2).sum(-1)
         stats = stats.to(dev)
+    n_blocks = len(projection_blocks(w.shape[0]))
+    scr = torch.zeros(n_blocks * B * BLOCK_ROWS, dtype=torch.float32, device=dev)
+    cnt = torch.zeros(n_blocks, dtype=torch.int32, device=dev)
     P = Program(n_sms)
-    for sm, r0, N in units:
-        P.gemm_tc(sm, w_addr=wd.data_ptr() + r0 * K * 2, N=N, K=K, Kc=choose_kc(N, Bp, K), x_addr=xd.data_ptr(), B=B,
-                  Bpad=Bp, out_addr=out.data_ptr() if out is not None else 0, mode=mode,
-                  norm_w=Src(nwd.data_ptr(), K * 2) if nwd is not None else None, eps=eps, n0=r0, ld=ld,
-                  keys_addr=keys.data_ptr() if keys is not None else 0,
-                  stats_addr=stats.data_ptr() if stats is not None else 0)
+    units = emit_projection(P, sms=list(range(n_sms)), load=[0] * n_sms, w_addr=wd.data_ptr(), M=w.shape[0], K=K,
+                            x_addr=xd.data_ptr(), B=B, Bpad=Bp, mode=mode, out_addr=out.data_ptr() if out is not None else 0,
+                            scratch_addr=scr.data_ptr(), counter_addr=cnt.data_ptr(),
+                            norm_addr=nwd.data_ptr() if nwd is not None else None, eps=eps, ld=ld,
+                            keys_addr=keys.data_ptr() if keys is not None else 0,
+                            stats_addr=stats.data_ptr() if stats is not None else 0)
     run_program(P, dev)
-    return xd, wd, nwd
+    assert float(scr.abs().max()) == 0.0 and int(cnt.abs().max()) == 0, "scratch and counters are left clear"
+    return units
 
 
-@pytest.mark.parametrize("B,K,M,n_sms,norm", [(5, 512, 96, 2, False), (16, 4096, 640, 2, True),
-                                             (40, 1024, 256, 1, True), (100, 256, 64, 3, False)])
+@pytest.mark.parametrize("B,K,M,n_sms,norm", [(5, 512, 96, 2, False), (16, 4096, 640, 5, True),
+                                             (40, 1024, 256, 1, True), (100, 256, 64, 3, False),
+                                             (16, 14336, 512, 7, False)])
 def test_gemm_tc_store_rows(cuda_device, B, K, M, n_sms, norm):
     from vdcores_b200 import isa
     dev = cuda_device
     x, w = seeded((B, K), 21), seeded((M, K), 22, 0.05)
     nw = (1 + 0.1 * torch.randn(K, generator=torch.Generator().manual_seed(23))).to(BF16) if norm else None
     y = torch.zeros(B, M, dtype=BF16, device=dev)
-    _gemm_program(dev, x, w, n_sms, isa.GEMM_MODE_STORE_ROWS, y, norm_w=nw, ld=M)
+    units = _gemm_program(dev, x, w, n_sms, isa.GEMM_MODE_STORE_ROWS, y, norm_w=nw, ld=M)
+    if n_sms > 1:
+        assert len(units) > len({u[1] for u in units}), "some block's K is shared by several units"
     xin = O.rms_norm(x, nw, 1e-5) if norm else x
     ref = O.linear(xin, w)
     assert O.rel_l2(y.cpu(), ref) < 4e-3

@@ -32,20 +32,83 @@ def unpack_kc(flat: torch.Tensor, R: int, K: int) -> torch.Tensor:
     return flat.view(K // 8, R // 8, 8, 8).permute(1, 2, 0, 3).reshape(R, K)
 
 
-def choose_kc(N: int, Bpad: int, K: int, max_slots: int = 6) -> int:
-    """Largest K-range per chunk (a multiple of 16 dividing K) whose X and W chunks fit in
-    max_slots shared-memory slots together, so that at least three pairs are in flight."""
-    best = 0
-    for kc in range(16, K + 1, 16):
-        if K % kc:
-            continue
-        xb, wb = Bpad * kc * 2, N * kc * 2
-        if xb > 32768 or wb > 32768:
-            break
-        if slots_for(xb + max(0, 2048 - Bpad * 16)) + slots_for(wb) <= max_slots:
-            best = kc
-    assert best, (N, Bpad, K)
-    return best
+BLOCK_ROWS = 256    # weight rows per projection block = accumulator columns of one tensor-core task
+
+
+def projection_blocks(M: int):
+    """[(first row, rows)] of a projection with M output rows (a multiple of 16)."""
+    assert M % 16 == 0
+    return [(r, min(BLOCK_ROWS, M - r)) for r in range(0, M, BLOCK_ROWS)]
+
+
+def pack_blocks(w: torch.Tensor) -> torch.Tensor:
+    """[M, K] -> flat: every block of 256 rows (the last one may be smaller) k-chunk-major, so
+    that any K-range of a block is one contiguous piece; block (r0, N) starts at element r0 * K."""
+    M, K = w.shape
+    out = torch.empty(M * K, dtype=w.dtype, device=w.device)
+    full = M // BLOCK_ROWS
+    if full:
+        out[:full * BLOCK_ROWS * K] = (w[:full * BLOCK_ROWS].reshape(full, BLOCK_ROWS // 8, 8, K // 8, 8)
+                                       .permute(0, 3, 1, 2, 4).reshape(-1))
+    if M % BLOCK_ROWS:
+        out[full * BLOCK_ROWS * K:] = pack_kc(w[full * BLOCK_ROWS:])
+    return out
+
+
+def chunk_geometry(N: int, Bpad: int, K: int):
+    """(Kc, G): inputs per W chunk (N * Kc * 2 bytes <= 32 KB, Kc divides K) and W chunks per X chunk
+    (the X chunk fills at most one 8 KB slot when it can)."""
+    kc = 256 if N <= 64 else 128 if N <= 128 else 64
+    while K % kc or Bpad * kc * 2 > 16384:
+        kc //= 2
+    assert kc >= 16
+    return kc, max(1, min(4, 8192 // (Bpad * kc * 2)))
+
+
+def plan_units(blocks, steps: int, sms, load, step_bytes_per_row: int):
+    """Deals the (block, W chunk) steps of a projection to the SMs, in `sms` order, as contiguous
+    ranges of about equal bytes.  Returns [(sm, block index, first chunk, chunk count)]."""
+    remaining = sum(n for _, n in blocks) * steps     # in rows x steps
+    units, bi, ci = [], 0, 0
+    for i, sm in enumerate(sms):
+        quota = -(-remaining // (len(sms) - i))
+        got = 0
+        while bi < len(blocks) and got < quota:
+            n = blocks[bi][1]
+            take = min(max(1, round((quota - got) / n)), steps - ci)
+            units.append((sm, bi, ci, take))
+            got += take * n
+            ci += take
+            if ci == steps:
+                bi, ci = bi + 1, 0
+        remaining -= got
+        load[sm] += got * step_bytes_per_row
+    assert bi == len(blocks) and remaining == 0
+    return units
+
+
+def emit_projection(P: Program, *, sms, load, w_addr, M, K, x_addr, B, Bpad, mode, out_addr, scratch_addr,
+                    counter_addr, x_wait=None, release=None, norm_addr=None, eps=0.0, ld=0, keys_addr=0, stats_addr=0):
+    """Emits every unit of the projection y[B, M] = x[B, K] W^T (W packed by pack_blocks at w_addr,
+    x k-chunk-major at x_addr).  scratch_addr: fp32 [blocks][B][256]; counter_addr: int32 [blocks]."""
+    blocks = projection_blocks(M)
+    Kc, G = chunk_geometry(blocks[0][1], Bpad, K)
+    units = plan_units(blocks, K // Kc, sms, load, Kc * 2)
+    slices = [0] * len(blocks)
+    for _, bi, _, _ in units:
+        slices[bi] += 1
+    if release is not None:
+        P.add_releases(release, len(blocks))
+    for sm, bi, c0, cnt in units:
+        r0, N = blocks[bi]
+        k0 = c0 * Kc
+        P.gemm_tc(sm, w_addr=w_addr + (r0 * K + k0 * N) * 2, N=N, K=K, k_len=cnt * Kc, Kc=Kc, G=G,
+                  x_addr=x_addr + k0 * Bpad * 2, B=B, Bpad=Bpad, out_addr=out_addr, mode=mode, x_wait=x_wait,
+                  norm_w=Src(norm_addr + k0 * 2, cnt * Kc * 2) if norm_addr is not None else None, eps=eps, n0=r0,
+                  ld=ld, keys_addr=keys_addr, stats_addr=stats_addr, release=release,
+                  scratch_addr=scratch_addr + bi * B * BLOCK_ROWS * 4, counter_addr=counter_addr + 4 * bi,
+                  n_slices=slices[bi])
+    return units
 
 
 class BatchDecodeEngine(DecodeEngine):
@@ -96,35 +159,6 @@ class BatchDecodeEngine(DecodeEngine):
         self.positions = [0] * B
 
     # ------------------------------------------------------------------ weights
-    def _units(self, load, n_rows: int, K: int):
-        """Deals the projection's groups of 16 rows to the SMs; returns [(sm, first row, N)], N <= 256."""
-        assert n_rows % 16 == 0
-        out = []
-        for sm, u0, cnt in self._ranges(load, n_rows // 16, 16 * K * 2):
-            while cnt > 0:
-                n = min(cnt, 16)
-                out.append((sm, u0 * 16, n * 16))
-                u0 += n
-                cnt -= n
-        return out
-
-    @staticmethod
-    def _pack_units(w: torch.Tensor, units) -> torch.Tensor:
-        """Rows of w regrouped unit by unit into k-chunk-major blocks; unit (r0, N) starts at element r0 * K."""
-        M, K = w.shape
-        out = torch.empty(M * K, dtype=w.dtype, device=w.device)
-        i = 0
-        while i < len(units):
-            j = i
-            while j + 1 < len(units) and units[j + 1][2] == units[i][2]:
-                j += 1
-            r0, N = units[i][1], units[i][2]
-            n_u = j - i + 1
-            blk = w[r0:r0 + n_u * N].reshape(n_u, N // 8, 8, K // 8, 8).permute(0, 3, 1, 2, 4)
-            out[r0 * K:(r0 + n_u * N) * K] = blk.reshape(-1)
-            i = j + 1
-        return out
-
     def weight_bytes(self) -> int:
         ts = [self.lm_head, self.norm_w, self.ln1, self.ln2, self.wqkv, self.wo, self.wgu, self.wd]
         return sum(t.numel() * t.element_size() for t in ts)
@@ -149,19 +183,26 @@ class BatchDecodeEngine(DecodeEngine):
         hid, qkv, ao, act = (t.data_ptr() for t in (self.hidden, self.qkv, self.attn_out, self.act))
         load = [0] * S
         packed = {"wqkv": [], "wo": [], "wgu": [], "wd": []}
+        self.scratch = {}
 
         stat = lambda i: self.stats[i].data_ptr()
 
         def gemm_stage(w, name, K, x_addr, x_wait, mode, out_addr, release, norm=None, ld=0, keys=0, stats=0):
-            units = self._units(load, w.shape[0], K)
-            pk = self._pack_units(w, units)
+            M = w.shape[0]
+            pk = pack_blocks(w)
             if name is not None:
                 packed[name].append(pk)
-            for sm, r0, N in units:
-                P.gemm_tc(sm, w_addr=pk.data_ptr() + r0 * K * 2, N=N, K=K, Kc=choose_kc(N, Bp, K), x_addr=x_addr, B=B,
-                          Bpad=Bp, out_addr=out_addr, mode=mode, x_wait=x_wait,
-                          norm_w=Src(norm.data_ptr(), K * 2) if norm is not None else None, eps=cfg.eps, n0=r0, ld=ld,
-                          keys_addr=keys, stats_addr=stats, release=release)
+            kind = name or "lm"
+            n_blocks = len(projection_blocks(M))
+            if kind not in self.scratch:      # fp32 partial sums and arrival counters, zero between uses
+                self.scratch[kind] = (torch.zeros(n_blocks * B * BLOCK_ROWS, dtype=torch.float32, device=self.dev),
+                                      torch.zeros(n_blocks, dtype=torch.int32, device=self.dev))
+            scr, cnt = self.scratch[kind]
+            sms = sorted(range(S), key=lambda i: (load[i], i))
+            emit_projection(P, sms=sms, load=load, w_addr=pk.data_ptr(), M=M, K=K, x_addr=x_addr, B=B, Bpad=Bp,
+                            mode=mode, out_addr=out_addr, scratch_addr=scr.data_ptr(), counter_addr=cnt.data_ptr(),
+                            x_wait=x_wait, release=release, norm_addr=norm.data_ptr() if norm is not None else None,
+                            eps=cfg.eps, ld=ld, keys_addr=keys, stats_addr=stats)
             return pk
 
         def tap(l, wait, release):

@@ -132,17 +132,22 @@
 // a projection unit (N rows, N a multiple of 16, at most 256) are stored the same way, [K/8][N/8][8 rows].
 // A K-range of either is one contiguous piece of memory, loaded with one 1-D bulk copy.
 //
-// GEMM_TC_BF16 (seven words): D[b, n] = sum_k X[b, k] W[n, k] on the tcgen05 tensor cores, the batch on
-// the accumulator's 128 lanes, the unit's N weight rows on its columns (fp32, in tensor memory).
-//   word 0: [n_chunks, N/16 | mode << 8 | norm << 12, k-steps of 16 per chunk]
+// GEMM_TC_BF16 (ten words): D[b, n] = sum_k X[b, k] W[n, k] on the tcgen05 tensor cores for one unit =
+// a block of N weight rows times a K-range; the batch sits on the accumulator's 128 lanes, the rows on
+// its columns (fp32, in tensor memory).
+//   word 0: [W chunks, N/16 | mode << 8 | norm << 12, k-steps of 16 per W chunk | W chunks per X chunk << 8]
 //   word 1: [norm eps hi, lo, batch]      word 2: 48-bit output address
 //   word 3: 48-bit address of the argmax keys (u64 per sequence; ARGMAX mode)
 //   word 4: [first output row low 16 bits, high bits, barrier to release (0xFFFF: none)]
-//   word 5: [row-major output leading dimension / 16, Bpad, 0]
+//   word 5: [row-major output leading dimension / 16, Bpad, whole K / 16]
 //   word 6: 48-bit address of fp32 per-sequence sums of squares: read by a norm task (the producers
-//           of its input left them there), accumulated by an ADD_PACKED task over the rows it updated
-// Pops [norm weights, K bf16], then n_chunks x (X chunk, W chunk).  With norm the X chunks become
-// bf16(w * bf16(x * rsqrt(sum/K + eps))) in shared memory before the tensor cores read them.
+//           of its input left them there), accumulated by an ADD_PACKED epilogue over the rows it updated
+//   word 7, 8: 48-bit addresses of the block's fp32 scratch sums [batch][N] and of its arrival counter
+//   word 9: [units the block's K is cut into, 0, 0]
+// Pops [norm weights of the K-range], then per group one X chunk and its W chunks.  With norm the X
+// chunks become bf16(w * bf16(x * rsqrt(sum/K + eps))) in shared memory before the tensor cores read
+// them.  With several units per block each adds its partial sums to the scratch area; the unit that
+// arrives last applies the epilogue, clears scratch and counter, and releases the barrier.
 #define VDC_GEMM_MODE_STORE_ROWS 0    // bf16 out[b * ld + row]
 #define VDC_GEMM_MODE_SILU_PAIRS 1    // rows (2j, 2j+1) = (gate_j, up_j): k-chunk-major act[b, j]
 #define VDC_GEMM_MODE_ARGMAX 2        // atomicMax of (orderable bf16 logit, ~row) per sequence

@@ -167,20 +167,21 @@ __device__ void compute_core(const Ctx& c, const VdcCInst* __restrict__ insts, i
           asm volatile("prefetch.global.L2 [%0];" ::"l"(base + off));
         break;
       }
-      case 0x7300: {  // GEMM_TC_BF16 (seven words)
+      case 0x7300: {  // GEMM_TC_BF16 (ten words)
         auto addr48 = [](const VdcCInst& w) {
           return (uint64_t)w.args[0] | ((uint64_t)w.args[1] << 16) | ((uint64_t)w.args[2] << 32);
         };
-        VdcCInst e[5];
+        VdcCInst e[8];
 #pragma unroll
-        for (int k = 0; k < 5; ++k) *reinterpret_cast<uint2*>(&e[k]) = ld_word(q.pc + (uint32_t)k);
-        q.pc += 5;
+        for (int k = 0; k < 8; ++k) *reinterpret_cast<uint2*>(&e[k]) = ld_word(q.pc + (uint32_t)k);
+        q.pc += 8;
         GemmTc g;
-        g.n_chunks = ci.args[0];
+        g.n_w = ci.args[0];
         g.N = (ci.args[1] & 0xFF) * 16;
         g.mode = (ci.args[1] >> 8) & 0xF;
         g.norm = (ci.args[1] >> 12) & 1;
-        g.KS = ci.args[2];
+        g.KS = ci.args[2] & 0xFF;
+        g.G = ci.args[2] >> 8;
         g.eps = __uint_as_float(((uint32_t)ex.args[0] << 16) | ex.args[1]);
         g.B = ex.args[2];
         g.out = reinterpret_cast<uint8_t*>(addr48(e[0]));
@@ -189,10 +190,15 @@ __device__ void compute_core(const Ctx& c, const VdcCInst* __restrict__ insts, i
         g.bar = e[2].args[2];
         g.ld = (int)e[3].args[0] * 16;
         g.Bpad = e[3].args[1];
+        g.Kfull = (int)e[3].args[2] * 16;
         g.stats = reinterpret_cast<float*>(addr48(e[4]));
+        g.scratch = reinterpret_cast<float*>(addr48(e[5]));
+        g.counter = reinterpret_cast<int*>(addr48(e[6]));
+        g.n_slices = e[7].args[0];
         const bool ok = g.N >= 16 && g.N <= 256 && g.B >= 1 && g.B <= g.Bpad &&
-                        (g.Bpad == 16 || g.Bpad == 32 || g.Bpad == 64 || g.Bpad == 128) && g.KS >= 1 &&
-                        (!g.norm || g.stats != nullptr);
+                        (g.Bpad == 16 || g.Bpad == 32 || g.Bpad == 64 || g.Bpad == 128) && g.KS >= 1 && g.G >= 1 &&
+                        g.n_w >= 1 && (!g.norm || g.stats != nullptr) &&
+                        (g.n_slices <= 1 || (g.scratch != nullptr && g.counter != nullptr));
         if (!ok) {
           raise_abort(c, VDC_ERR_BAD_OPCODE, 0, (int)q.pc, ci.opcode, -1, g.N);
           q.aborted = true;
@@ -314,7 +320,9 @@ vdc_megakernel(const VdcCInst* __restrict__ cinsts, const VdcMInst* __restrict__
 // ------------------------------------------------------------------------- //
 // host entry used by the C ABI
 // ------------------------------------------------------------------------- //
-extern "C" size_t vdc_megakernel_dynamic_smem() { return (size_t)VDC_NUM_SLOTS * VDC_SLOT_BYTES + 1024; }
+// Slots, 1 KB of alignment slack, and a 2 KB guard behind the last slot: the tensor cores read 128
+// operand rows of an X chunk whatever the batch, and the rows past the batch fall behind the chunk.
+extern "C" size_t vdc_megakernel_dynamic_smem() { return (size_t)VDC_NUM_SLOTS * VDC_SLOT_BYTES + 1024 + 2048; }
 
 extern "C" cudaError_t vdc_megakernel_prepare() {
   return cudaFuncSetAttribute(vdc::vdc_megakernel, cudaFuncAttributeMaxDynamicSharedMemorySize,

@@ -88,16 +88,85 @@ __device__ __forceinline__ bool mma_wait(Compute& q, unsigned commit_index) {
 // ------------------------------------------------------------------------- //
 // task: batched projection on the tensor cores
 // ------------------------------------------------------------------------- //
+// One unit = a block of N weight rows (N <= 256, the accumulator's columns) times a K-range.
+// The memory stream delivers groups of one X chunk (all sequences, G * KS * 16 inputs) and
+// the G W chunks that go with it.  A block whose K is cut into several units (n_slices > 1)
+// is summed in an fp32 scratch area in global memory; the unit that arrives last applies
+// the epilogue, clears the scratch and releases the barrier.
 struct GemmTc {
-  int n_chunks, N, KS, mode;
+  int n_w;       // W chunks of this unit
+  int N, KS, G;  // weight rows, k-steps of 16 per W chunk, W chunks per X chunk
+  int mode;
   bool norm;
   float eps;
-  int B, Bpad;
+  int B, Bpad, Kfull;
   uint8_t* out;
   unsigned long long* keys;
   float* stats;  // fp32 per sequence: sum of squares of the input rows (norm) / of the updated rows (ADD_PACKED)
   int n0, ld, bar;
+  float* scratch;  // [B][N] fp32 partial sums of this block (n_slices > 1)
+  int* counter;    // arrivals of this block's units
+  int n_slices;
 };
+
+struct EpiAcc {
+  float ssq;   // ADD_PACKED: squares of the new values
+  float best;  // ARGMAX
+  int best_row;
+};
+
+// Epilogue of 16 consecutive output rows (row .. row+15) of sequence b.
+__device__ __forceinline__ void gemm_epilogue16(const GemmTc& g, int b, int row, const float (&v)[16], EpiAcc& acc) {
+  if (g.mode == VDC_GEMM_MODE_STORE_ROWS) {
+    uint4* dst = reinterpret_cast<uint4*>(g.out + ((size_t)b * g.ld + row) * 2);
+    dst[0] = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
+    dst[1] = make_uint4(pack_bf16x2(v[8], v[9]), pack_bf16x2(v[10], v[11]), pack_bf16x2(v[12], v[13]),
+                        pack_bf16x2(v[14], v[15]));
+  } else if (g.mode == VDC_GEMM_MODE_SILU_PAIRS) {
+    float a[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float gt = bf16_round(v[2 * j]), up = bf16_round(v[2 * j + 1]);
+      a[j] = bf16_round(gt / (1.f + __expf(-gt))) * up;
+    }
+    *reinterpret_cast<uint4*>(g.out + kc_piece(g.Bpad, b, row >> 1)) =
+        make_uint4(pack_bf16x2(a[0], a[1]), pack_bf16x2(a[2], a[3]), pack_bf16x2(a[4], a[5]), pack_bf16x2(a[6], a[7]));
+  } else if (g.mode == VDC_GEMM_MODE_ADD_PACKED) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      __nv_bfloat162* dst = reinterpret_cast<__nv_bfloat162*>(g.out + kc_piece(g.Bpad, b, row + 8 * h));
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        // every element gets exactly one add per projection, so old + v is its final value
+        const __nv_bfloat162 add = __floats2bfloat162_rn(v[8 * h + 2 * j], v[8 * h + 2 * j + 1]);
+        const float2 nv = __bfloat1622float2(__hadd2(atomicAdd(dst + j, add), add));
+        acc.ssq = fmaf(nv.x, nv.x, fmaf(nv.y, nv.y, acc.ssq));
+      }
+    }
+  } else {  // ARGMAX over bf16-rounded logits, the lowest row wins ties
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const float l = bf16_round(v[j]);
+      if (l > acc.best) {
+        acc.best = l;
+        acc.best_row = row + j;
+      }
+    }
+  }
+}
+
+// Publishes what gemm_epilogue16 accumulated for sequence b and resets it.
+__device__ __forceinline__ void gemm_epilogue_flush(const GemmTc& g, int b, EpiAcc& acc) {
+  if (g.mode == VDC_GEMM_MODE_ARGMAX && acc.best_row != 0x7fffffff) {
+    uint32_t u = __float_as_uint(acc.best);
+    u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);  // order-preserving map of the float
+    atomicMax(g.keys + b, ((unsigned long long)u << 32) | (unsigned long long)(0xFFFFFFFFu - (uint32_t)acc.best_row));
+  }
+  if (g.mode == VDC_GEMM_MODE_ADD_PACKED && g.stats != nullptr) atomicAdd(g.stats + b, acc.ssq);
+  acc.ssq = 0.f;
+  acc.best = -INFINITY;
+  acc.best_row = 0x7fffffff;
+}
 
 __device__ void task_gemm_tc(Compute& q, const GemmTc& g) {
   Shared* sh = q.sh;
@@ -121,33 +190,43 @@ __device__ void task_gemm_tc(Compute& q, const GemmTc& g) {
   const uint32_t tmem = sh->tmem_base;
   const uint32_t idesc = umma_idesc_bf16_m128(g.N);
   const uint32_t lbo_a = (uint32_t)g.Bpad * 16u, lbo_b = (uint32_t)g.N * 16u;
-  const int pieces = g.KS * 2 * g.Bpad;  // 16-byte pieces of one X chunk
-  const int K = g.n_chunks * g.KS * 16;
-  const unsigned n_ent = 2u * (unsigned)g.n_chunks;  // ring entries of this task: X chunk, W chunk, X chunk, ...
+  const int n_x = (g.n_w + g.G - 1) / g.G;                      // X chunks = groups
+  const unsigned n_ent = (unsigned)(g.n_w + n_x);               // ring entries: X, G x W, X, G x W, ...
+  auto x_entry = [&](int grp) { return (unsigned)(grp * (g.G + 1)); };
+  auto w_entry = [&](int j) { return (unsigned)((j / g.G) * (g.G + 1) + 1 + j % g.G); };
 
   // The streaming loop has no CTA-wide synchronisation.  Warp 0 consumes the ring entries in
-  // order: it waits for a chunk pair, one lane issues the tensor-core work and, once the
-  // previous pair's reads are done, recycles that pair's slots and ring entries.  With norm
-  // the other seven warps run ahead of it, each normalising every seventh X chunk in place
-  // and signalling that chunk's barrier.
+  // order: it waits for the chunks, one lane issues the tensor-core work and, once the
+  // previous chunk's reads are done, recycles its slots.  With norm the other seven warps
+  // run ahead of it, normalising the X chunks in place and signalling each chunk's barrier.
   q.warp_phase_begin(n_ent, q.warp == 0 ? 0u : n_ent);
   if (q.warp > 0 && g.norm) {
-    float* rs = sh->red + q.warp * 128;  // this warp's copy of the per-sequence rsqrt(mean x^2 + eps)
-    bool have_rstd = false;
-    for (int ch = q.warp - 1; ch < g.n_chunks; ch += kCW - 1) {
-      const int xm = q.warp_wait(2u * (unsigned)ch);
+    // The seven warps normalise one X chunk after the other, together (224 threads).
+    constexpr int kTeam = (kCW - 1) * 32;
+    const int t = q.tid - 32;
+    float* rs = sh->red;  // per-sequence rsqrt(mean x^2 + eps)
+    int* xm_shared = reinterpret_cast<int*>(sh->misc) + 36;
+    for (int grp = 0; grp < n_x; ++grp) {
+      // one warp waits for the chunk (bounded) and tells the team, so that all leave together on an abort
+      if (q.warp == 1) {
+        const int m = q.warp_wait(x_entry(grp));
+        if (q.lane == 0) xm_shared[grp & 1] = m;
+      }
+      asm volatile("bar.sync 6, %0;" ::"n"(kTeam) : "memory");
+      const int xm = xm_shared[grp & 1];
       if (xm == kPopAbort) break;
-      if (!have_rstd) {
+      if (grp == 0) {
         // Any X chunk of this task was loaded after the producers of the input matrix had
         // finished, and with them the sums of squares they left (read past L1).
-        for (int bb = q.lane; bb < g.Bpad; bb += 32) rs[bb] = rsqrtf(__ldcg(g.stats + bb) / (float)K + g.eps);
-        __syncwarp();
-        have_rstd = true;
+        if (t < g.Bpad) rs[t] = rsqrtf(__ldcg(g.stats + t) / (float)g.Kfull + g.eps);
+        asm volatile("bar.sync 6, %0;" ::"n"(kTeam) : "memory");
       }
       uint8_t* xs = (uint8_t*)slot_ptr(c, first_slot(xm));
-      const int kc0 = ch * g.KS * 2;  // index of the chunk's first 8-element k group
+      const int w_in_grp = min(g.G, g.n_w - grp * g.G);
+      const int pieces = w_in_grp * g.KS * 2 * g.Bpad;  // 16-byte pieces of this X chunk
+      const int kc0 = grp * g.G * g.KS * 2;             // the chunk's first 8-element k group within the unit
       // RMSNorm in place, rounded like a bf16 tensor expression: bf16(w * bf16(x * rstd))
-      for (int p = q.lane; p < pieces; p += 32) {
+      for (int p = t; p < pieces; p += kTeam) {
         const uint4 v = lds128(xs + p * 16);
         const uint4 w = lds128(nw + (kc0 + p / g.Bpad) * 16);
         const float rstd = rs[p & (g.Bpad - 1)];
@@ -159,30 +238,37 @@ __device__ void task_gemm_tc(Compute& q, const GemmTc& g) {
         *reinterpret_cast<uint4*>(xs + p * 16) = make_uint4(o[0], o[1], o[2], o[3]);
       }
       fence_proxy_async_smem();  // the tensor cores read shared memory through the async proxy
-      __syncwarp();
-      if (q.lane == 0) mbar_arrive(&sh->x_ready[(q.xr_count + (unsigned)ch) & 15u]);
+      asm volatile("bar.sync 6, %0;" ::"n"(kTeam) : "memory");
+      if (t == 0) mbar_arrive(&sh->x_ready[(q.xr_count + (unsigned)grp) & 15u]);
     }
   }
   if (q.warp == 0) {
-    int prev_masks = 0;  // lane 0: slots of the chunk pair whose tensor-core reads are in flight
+    int w_prev = 0, x_prev = 0;  // lane 0: slots whose tensor-core reads may still be in flight
+    int xm = 0;
 #ifdef VDC_TC_PROFILE
     long long t_data = 0, t_xr = 0, t_mma = 0, t_wait = 0;
 #endif
-    for (int ch = 0; ch < g.n_chunks; ++ch) {
+    for (int j = 0; j < g.n_w; ++j) {
+      const int grp = j / g.G, jj = j % g.G;
 #ifdef VDC_TC_PROFILE
       const long long td0 = clock64();
 #endif
-      const int xm = q.warp_wait(2u * (unsigned)ch);
-      const int wm = q.warp_wait(2u * (unsigned)ch + 1u);
-      if (xm == kPopAbort || wm == kPopAbort) break;
+      int x_done = 0;
+      if (jj == 0) {
+        x_done = xm;  // the previous group's X chunk: its last W chunk is the previous chunk
+        xm = q.warp_wait(x_entry(grp));
+        if (xm == kPopAbort) break;
+      }
+      const int wm = q.warp_wait(w_entry(j));
+      if (wm == kPopAbort) break;
 #ifdef VDC_TC_PROFILE
       t_data += clock64() - td0;
       const long long tx0 = clock64();
 #endif
-      if (g.norm) {
+      if (g.norm && jj == 0) {
         int ok = 1;
         if (q.lane == 0) {
-          const unsigned gch = q.xr_count + (unsigned)ch;
+          const unsigned gch = q.xr_count + (unsigned)grp;
           uint64_t* bar = &sh->x_ready[gch & 15u];
           const uint32_t parity = (gch >> 4) & 1u;
           if (!mbar_try_wait(bar, parity)) {
@@ -198,10 +284,10 @@ __device__ void task_gemm_tc(Compute& q, const GemmTc& g) {
 #endif
       if (q.lane == 0) {
         tc_fence_after();
-        uint64_t adesc = umma_desc(smem_u32(slot_ptr(c, first_slot(xm))), lbo_a, 128u);
+        uint64_t adesc = umma_desc(smem_u32(slot_ptr(c, first_slot(xm))) + (uint32_t)(jj * g.KS) * 2u * lbo_a, lbo_a, 128u);
         uint64_t bdesc = umma_desc(smem_u32(slot_ptr(c, first_slot(wm))), lbo_b, 128u);
         const uint64_t step_a = (uint64_t)((2u * lbo_a) >> 4), step_b = (uint64_t)((2u * lbo_b) >> 4);
-        umma_bf16(tmem, adesc, bdesc, idesc, (uint32_t)(ch != 0));
+        umma_bf16(tmem, adesc, bdesc, idesc, (uint32_t)(j != 0));
 #pragma unroll 4
         for (int kk = 1; kk < g.KS; ++kk) {
           adesc += step_a;  // the start-address field: 16 k further in both operands
@@ -213,13 +299,14 @@ __device__ void task_gemm_tc(Compute& q, const GemmTc& g) {
         t_mma += clock64() - tm0;
         const long long tw0 = clock64();
 #endif
-        // the previous pair's reads are certainly done once its commit arrived
-        if (ch > 0) {
-          if (!mma_wait(q, q.mma_count - 1)) prev_masks = 0;
-          if (prev_masks) atomicOr(&sh->slot_avail, (uint32_t)prev_masks & kSlotMaskAll);
-          sh->warp_next[0] = q.head + 2u * (unsigned)ch;  // its ring entries may be recycled too
+        // the previous chunk's reads are certainly done once its commit arrived
+        if (j > 0) {
+          int done = w_prev | x_done;
+          if (!mma_wait(q, q.mma_count - 1)) done = 0;
+          if (done) atomicOr(&sh->slot_avail, (uint32_t)done & kSlotMaskAll);
+          sh->warp_next[0] = q.head + x_entry(grp);  // ring entries before this group may be recycled
         }
-        prev_masks = (xm | wm) & (int)kSlotMaskAll;
+        w_prev = wm & (int)kSlotMaskAll;
         q.mma_count++;
 #ifdef VDC_TC_PROFILE
         t_wait += clock64() - tw0;
@@ -228,90 +315,102 @@ __device__ void task_gemm_tc(Compute& q, const GemmTc& g) {
       __syncwarp();
     }
     if (q.lane == 0) {
-      if (q.mma_count > 0 && mma_wait(q, q.mma_count - 1) && prev_masks)
-        atomicOr(&sh->slot_avail, (uint32_t)prev_masks & kSlotMaskAll);
+      x_prev = xm == kPopAbort ? 0 : (xm & (int)kSlotMaskAll);
+      if (q.mma_count > 0 && mma_wait(q, q.mma_count - 1) && (w_prev | x_prev))
+        atomicOr(&sh->slot_avail, (uint32_t)(w_prev | x_prev) & kSlotMaskAll);
       sh->warp_next[0] = 0xFFFFFFFFu;
 #ifdef VDC_TC_PROFILE
       uint64_t* pr = c.profile + c.sm * VDC_NUM_PROFILE_EVENTS;
-      pr[8] += t_data; pr[9] += t_xr; pr[10] += t_mma; pr[11] += t_wait; pr[12] += g.n_chunks;
-      pr[13] += (uint64_t)g.n_chunks * g.KS;
+      pr[8] += t_data; pr[9] += t_xr; pr[10] += t_mma; pr[11] += t_wait; pr[12] += g.n_w;
+      pr[13] += (uint64_t)g.n_w * g.KS;
 #endif
     }
   }
   tc_fence_before();
   q.warp_phase_end(n_ent);  // CTA barrier: accumulator complete (lane 0 saw the last commit)
   tc_fence_after();
-  if (g.norm) q.xr_count += (unsigned)g.n_chunks;
+  if (g.norm) q.xr_count += (unsigned)n_x;
   if (q.aborted) return;
 
-  // ---- epilogue: lane b of the accumulator belongs to sequence b; warps w and w+4 share the
-  // lane quarter w % 4 and split the columns
+  // Lane b of the accumulator belongs to sequence b; warps w and w+4 share the lane quarter
+  // w % 4 and split the columns.
   const int quarter = q.warp & 3, half = q.warp >> 2;
   const int b = quarter * 32 + q.lane;
+  const int ng = g.N >> 4;
+  const int g0 = half ? (ng + 1) / 2 : 0, g1 = half ? ng : (ng + 1) / 2;
+  EpiAcc acc{0.f, -INFINITY, 0x7fffffff};
+  if (g.n_slices <= 1) {
+    // ---- the unit covers the whole K: epilogue straight from tensor memory
+    if (quarter * 32 < g.B) {
+      for (int gi = g0; gi < g1; ++gi) {
+        uint32_t r[16];
+        tmem_ld16(tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(gi * 16), r);
+        if (b >= g.B) continue;
+        float v[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
+        gemm_epilogue16(g, b, g.n0 + gi * 16, v, acc);
+      }
+      if (b < g.B) gemm_epilogue_flush(g, b, acc);
+      __threadfence();
+    }
+    tc_fence_before();
+    compute_sync();  // every lane read its columns: the next task may overwrite the accumulator
+    if (q.tid == 0 && g.bar != 0xFFFF) red_release_gpu_add(c.bars + g.bar, -1);
+    q.free_slots(normw_mask);
+    return;
+  }
+  // ---- a K-slice: add the partial sums to the block's fp32 scratch area
   if (quarter * 32 < g.B) {
-    float ssq = 0.f;  // ADD_PACKED: squares of the rows' new values over this thread's columns
-    const int ng = g.N >> 4;
-    const int g0 = half ? (ng + 1) / 2 : 0, g1 = half ? ng : (ng + 1) / 2;
-    float best = -INFINITY;
-    int best_row = 0x7fffffff;
     for (int gi = g0; gi < g1; ++gi) {
       uint32_t r[16];
       tmem_ld16(tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(gi * 16), r);
       if (b >= g.B) continue;
-      float v[16];
+      float* dst = g.scratch + (size_t)b * g.N + gi * 16;
 #pragma unroll
-      for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
-      const int row = g.n0 + gi * 16;  // first of the 16 output rows in v
-      if (g.mode == VDC_GEMM_MODE_STORE_ROWS) {
-        uint4* dst = reinterpret_cast<uint4*>(g.out + ((size_t)b * g.ld + row) * 2);
-        dst[0] = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]),
-                            pack_bf16x2(v[6], v[7]));
-        dst[1] = make_uint4(pack_bf16x2(v[8], v[9]), pack_bf16x2(v[10], v[11]), pack_bf16x2(v[12], v[13]),
-                            pack_bf16x2(v[14], v[15]));
-      } else if (g.mode == VDC_GEMM_MODE_SILU_PAIRS) {
-        float a[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const float gt = bf16_round(v[2 * j]), up = bf16_round(v[2 * j + 1]);
-          a[j] = bf16_round(gt / (1.f + __expf(-gt))) * up;
-        }
-        *reinterpret_cast<uint4*>(g.out + kc_piece(g.Bpad, b, row >> 1)) =
-            make_uint4(pack_bf16x2(a[0], a[1]), pack_bf16x2(a[2], a[3]), pack_bf16x2(a[4], a[5]), pack_bf16x2(a[6], a[7]));
-      } else if (g.mode == VDC_GEMM_MODE_ADD_PACKED) {
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          __nv_bfloat162* dst = reinterpret_cast<__nv_bfloat162*>(g.out + kc_piece(g.Bpad, b, row + 8 * h));
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            // every element gets exactly one add per projection, so old + v is its final value
-            const __nv_bfloat162 add = __floats2bfloat162_rn(v[8 * h + 2 * j], v[8 * h + 2 * j + 1]);
-            const float2 nv = __bfloat1622float2(__hadd2(atomicAdd(dst + j, add), add));
-            ssq = fmaf(nv.x, nv.x, fmaf(nv.y, nv.y, ssq));
-          }
-        }
-      } else {  // ARGMAX over bf16-rounded logits, the lowest row wins ties
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const float l = bf16_round(v[j]);
-          if (l > best) {
-            best = l;
-            best_row = row + j;
-          }
-        }
-      }
+      for (int j = 0; j < 16; j += 4)
+        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + j), "f"(__uint_as_float(r[j])),
+                     "f"(__uint_as_float(r[j + 1])), "f"(__uint_as_float(r[j + 2])), "f"(__uint_as_float(r[j + 3]))
+                     : "memory");
     }
-    if (g.mode == VDC_GEMM_MODE_ARGMAX && b < g.B && best_row != 0x7fffffff) {
-      uint32_t u = __float_as_uint(best);
-      u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);  // order-preserving map of the float
-      atomicMax(g.keys + b, ((unsigned long long)u << 32) | (unsigned long long)(0xFFFFFFFFu - (uint32_t)best_row));
-    }
-    if (g.mode == VDC_GEMM_MODE_ADD_PACKED && g.stats != nullptr && b < g.B) atomicAdd(g.stats + b, ssq);
     __threadfence();
   }
   tc_fence_before();
-  compute_sync();  // every lane read its columns: the next task may overwrite the accumulator
-  if (q.tid == 0 && g.bar != 0xFFFF) red_release_gpu_add(c.bars + g.bar, -1);
+  compute_sync();
+  if (q.tid == 0) {
+    // the sums are complete once every unit of the block arrived; the gpu-scope fences order
+    // this CTA's adds before the bump and the last arriver's reads after it
+    __threadfence();
+    const int old = atomicAdd(g.counter, 1);
+    __threadfence();
+    sh->misc[35] = (old == g.n_slices - 1) ? 1.f : 0.f;
+  }
+  compute_sync();
   q.free_slots(normw_mask);
+  if (sh->misc[35] == 0.f) return;
+  // ---- last arrival for this block: epilogue from the scratch area (read past L1), cleared for its next use
+  const int items = g.B * ng;
+  for (int item = q.tid; item < items; item += kCT) {
+    const int bb = item / ng, gi = item % ng;
+    float4* src = reinterpret_cast<float4*>(g.scratch + (size_t)bb * g.N + gi * 16);
+    float v[16];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float4 t = __ldcg(src + j);
+      v[4 * j] = t.x; v[4 * j + 1] = t.y; v[4 * j + 2] = t.z; v[4 * j + 3] = t.w;
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) src[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+    gemm_epilogue16(g, bb, g.n0 + gi * 16, v, acc);
+    gemm_epilogue_flush(g, bb, acc);
+  }
+  __threadfence();
+  compute_sync();
+  if (q.tid == 0) {
+    *g.counter = 0;  // ready for the block's next use; ordered before it by the barrier chain
+    __threadfence();
+    if (g.bar != 0xFFFF) red_release_gpu_add(c.bars + g.bar, -1);
+  }
 }
 
 // ------------------------------------------------------------------------- //

@@ -325,49 +325,71 @@ class Program:
         self.comp(sm, isa.OP_EXT, split, release, (packed[0] | (packed[1] // 16) << 8) if packed else 0)
 
     # ------------------------------------------------------------------ batched decode (tensor cores)
-    def gemm_tc(self, sm, *, w_addr, N, K, Kc, x_addr, B, Bpad, out_addr, mode, x_wait: Optional[int] = None,
+    def gemm_tc(self, sm, *, w_addr, N, K, k_len, Kc, G, x_addr, B, Bpad, out_addr, mode, x_wait: Optional[int] = None,
                 norm_w: Optional[Src] = None, eps: float = 0.0, n0: int = 0, ld: int = 0, keys_addr: int = 0,
-                stats_addr: int = 0, release: Optional[int] = None):
-        """D[b, n] = sum_k X[b, k] W[n, k] for one unit of N weight rows (k-chunk-major
-        [K/8][N/8][8][8] bf16 at w_addr) against the k-chunk-major activation matrix
-        [Bpad, K] at x_addr, streamed as K/Kc pairs of (X chunk, W chunk).  `mode`
-        selects the epilogue (isa.GEMM_MODE_*); n0 is the unit's first output row.
-        stats_addr: fp32 per-sequence sums of squares, read when norm_w is given (the
-        RMSNorm of the input rows), accumulated over the updated rows in ADD_PACKED mode."""
-        assert norm_w is None or stats_addr
+                stats_addr: int = 0, release: Optional[int] = None, scratch_addr: int = 0, counter_addr: int = 0,
+                n_slices: int = 1):
+        """One unit of a batched projection: D[b, n] = sum_k X[b, k] W[n, k] over a K-range
+        of k_len inputs for a block of N weight rows (k-chunk-major [K/8][N/8][8][8] bf16;
+        w_addr points at the range's first W chunk) against the k-chunk-major activation
+        matrix (x_addr points at the range's first k group).  The range is streamed as
+        W chunks of Kc inputs, G of them per X chunk.  `mode` selects the epilogue
+        (isa.GEMM_MODE_*); n0 is the block's first output row; K the projection's whole K.
+        stats_addr: fp32 per-sequence sums of squares, read when norm_w (the norm weights
+        of the range) is given, accumulated over the updated rows in ADD_PACKED mode.
+        With n_slices > 1 the block's K is shared by that many units: partial sums meet in
+        scratch_addr, counter_addr counts arrivals.  The caller declares `release` once per
+        block with add_releases."""
         assert N % 16 == 0 and 16 <= N <= 256 and Bpad in (16, 32, 64, 128) and 1 <= B <= Bpad
-        assert Kc % 16 == 0 and K % Kc == 0 and n0 % 16 == 0 and ld % 16 == 0
-        n_chunks = K // Kc
-        xbytes, wbytes = Bpad * Kc * 2, N * Kc * 2
-        assert xbytes <= 32768 and wbytes <= 32768 and n_chunks <= 0xFFFF
-        # the tensor cores read 128 lanes of X: the rows past Bpad fall behind the chunk's end
-        xslots = slots_for(xbytes + max(0, 2048 - Bpad * 16))
+        assert Kc % 16 == 0 and k_len % Kc == 0 and k_len > 0 and n0 % 16 == 0 and ld % 16 == 0 and K % 16 == 0
+        assert norm_w is None or stats_addr
+        assert n_slices == 1 or (scratch_addr and counter_addr)
+        n_w = k_len // Kc
+        wbytes = N * Kc * 2
+        assert wbytes <= 32768 and n_w <= 0xFFFF and 1 <= G <= 15 and Kc // 16 <= 255
+        assert Bpad * G * Kc * 2 <= 32768
         wslots = slots_for(wbytes)
         if norm_w is not None:
-            assert norm_w.nbytes == K * 2
+            assert norm_w.nbytes == k_len * 2
             self.load(sm, norm_w, default_port=1)
-        flags = isa.F_PORT | (isa.F_BARRIER if x_wait is not None else 0)
-        self.mem(sm, isa.OP_ALLOC_TMA_LOAD_1D, size=xbytes, nslot=xslots, bar=x_wait or 0, address=x_addr, flags=flags)
-        self.mem(sm, isa.OP_ALLOC_TMA_LOAD_1D, size=wbytes, nslot=wslots, address=w_addr)
-        if n_chunks > 1:
-            self.repeat(sm, n_chunks - 1, [xbytes, wbytes])
-            self.mem(sm, isa.OP_ALLOC_TMA_LOAD_1D, size=xbytes, nslot=xslots, address=x_addr + xbytes, flags=isa.F_PORT)
-            self.mem(sm, isa.OP_ALLOC_TMA_LOAD_1D, size=wbytes, nslot=wslots, address=w_addr + wbytes, flags=isa.F_JUMP)
-        self.bytes_loaded[sm] += (xbytes + wbytes) * n_chunks
-        if release is not None:
-            self.bar_counts[release] += 1
+
+        def group(first_w, count, wait=None, jump=False):
+            # one X chunk and the `count` W chunks that go with it
+            xb = Bpad * count * Kc * 2
+            flags = isa.F_PORT | (isa.F_BARRIER if wait is not None else 0)
+            self.mem(sm, isa.OP_ALLOC_TMA_LOAD_1D, size=xb, nslot=slots_for(xb), bar=wait or 0,
+                     address=x_addr + first_w * Kc * Bpad * 2, flags=flags)
+            for i in range(count):
+                self.mem(sm, isa.OP_ALLOC_TMA_LOAD_1D, size=wbytes, nslot=wslots, address=w_addr + (first_w + i) * wbytes,
+                         flags=isa.F_JUMP if (jump and i == count - 1) else 0)
+
+        n_full, tail = divmod(n_w, G)
+        if n_full == 0:
+            group(0, tail, wait=x_wait)
+        else:
+            group(0, G, wait=x_wait)          # the first X chunk carries the wait on the producers
+            if n_full > 1:
+                self.repeat(sm, n_full - 1, [Bpad * G * Kc * 2] + [G * wbytes] * G)
+                group(G, G, jump=True)
+            if tail:
+                group(n_full * G, tail)
+        self.bytes_loaded[sm] += (Bpad * Kc * 2 + wbytes) * n_w
         e = f32_bits(eps)
         a48 = lambda a: (a & 0xFFFF, (a >> 16) & 0xFFFF, (a >> 32) & 0xFFFF)
-        assert 0 <= out_addr < 1 << 48 and 0 <= keys_addr < 1 << 48 and out_addr % 16 == 0 and keys_addr % 8 == 0
-        self.comp(sm, isa.OP_GEMM_TC_BF16, n_chunks, (N // 16) | (mode << 8) | ((1 << 12) if norm_w is not None else 0),
-                  Kc // 16)
+        for a in (out_addr, keys_addr, stats_addr, scratch_addr, counter_addr):
+            assert 0 <= a < 1 << 48
+        assert out_addr % 16 == 0 and keys_addr % 8 == 0 and stats_addr % 4 == 0 and scratch_addr % 16 == 0
+        self.comp(sm, isa.OP_GEMM_TC_BF16, n_w, (N // 16) | (mode << 8) | ((1 << 12) if norm_w is not None else 0),
+                  (Kc // 16) | (G << 8))
         self.comp(sm, isa.OP_EXT, e >> 16, e & 0xFFFF, B)
         self.comp(sm, isa.OP_EXT, *a48(out_addr))
         self.comp(sm, isa.OP_EXT, *a48(keys_addr))
         self.comp(sm, isa.OP_EXT, n0 & 0xFFFF, n0 >> 16, 0xFFFF if release is None else release)
-        self.comp(sm, isa.OP_EXT, ld // 16, Bpad, 0)
-        assert 0 <= stats_addr < 1 << 48 and stats_addr % 4 == 0
+        self.comp(sm, isa.OP_EXT, ld // 16, Bpad, K // 16)
         self.comp(sm, isa.OP_EXT, *a48(stats_addr))
+        self.comp(sm, isa.OP_EXT, *a48(scratch_addr))
+        self.comp(sm, isa.OP_EXT, *a48(counter_addr))
+        self.comp(sm, isa.OP_EXT, n_slices, 0, 0)
 
     def embed_pack(self, sm, *, b0, count, Bpad, state_addr, state_stride_words, hidden, table_addr, out_addr,
                    stats_addr, release: Optional[int] = None):
