@@ -69,7 +69,9 @@
   X(OP_PREFETCH_L2, VDC_MOP(26, 0))                                                    \
   X(OP_STREAM_LIST, VDC_MOP(27, 0))                                                    \
   X(OP_ALLOC_TMA_LOAD_1D_STREAM, VDC_MOP(28, VDC_F_ALLOCATE))                          \
-  X(OP_CC0_STRIDE32, VDC_MOP(29, 0))
+  X(OP_CC0_STRIDE32, VDC_MOP(29, 0))                                                   \
+  X(OP_PT_LOAD32, VDC_MOP(30, 0))                                                      \
+  X(OP_PT_APPLY, VDC_MOP(31, 0))
 
 // Compute opcodes.  The first block keeps reference names (control ops and the
 // ops whose tile contracts this runtime still honours); the second block is

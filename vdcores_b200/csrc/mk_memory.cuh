@@ -68,6 +68,8 @@ __device__ void control_warp(const Ctx& c, const VdcMInst* __restrict__ insts, i
   uint64_t delta = 0, accum = 0;  // per-lane REPEAT registers
   int loop_counter = 0, loop_start = 0, jmp_cnt = 0;
   int dyn = 0;
+  int loop_iter = 0;     // trips of the current REPEAT completed so far
+  uint32_t tbl = 0;      // per-lane word of the table PT_LOAD32 fetched
   uint64_t ind_off = 0;
   bool ind_pending = false;
   unsigned tail = 0;        // ring entries published
@@ -180,6 +182,7 @@ __device__ void control_warp(const Ctx& c, const VdcMInst* __restrict__ insts, i
 
       if ((opcode & VDC_F_JUMP) && loop_counter > 0) {
         --loop_counter;
+        ++loop_iter;
         if (loop_counter > 0) next_pc = (uint32_t)loop_start;
         accum += delta;
       }
@@ -216,6 +219,7 @@ __device__ void control_warp(const Ctx& c, const VdcMInst* __restrict__ insts, i
             accum = 0;
           }
           loop_counter = count;
+          loop_iter = 0;
           loop_start = (int)pc + 1;
           if (size == 0xFFFF && count == 0) {
             next_pc = pc + 1 + arg;  // empty dynamic loop: skip body
@@ -342,6 +346,16 @@ __device__ void control_warp(const Ctx& c, const VdcMInst* __restrict__ insts, i
           ind_off = (opid == 6) ? ((uint64_t)(uint32_t)word << arg)
                                 : (opid == 7 ? (uint64_t)(uint32_t)word * size
                                              : (uint64_t)(uint32_t)word * (uint64_t)(size | (arg << 16)));
+          ind_pending = true;
+          break;
+        }
+        case 30: {  // PT_LOAD32: lane i keeps 32-bit word i of the table at `address` (size words, at most 32)
+          tbl = lane < (int)size ? (uint32_t)ld_relaxed_gpu(reinterpret_cast<const int*>(address) + lane) : 0u;
+          break;
+        }
+        case 31: {  // PT_APPLY: next allocating instruction's address += table word of this loop trip << arg
+          const uint32_t word = __shfl_sync(0xffffffffu, tbl, loop_iter & 31);
+          ind_off = (uint64_t)word << arg;
           ind_pending = true;
           break;
         }

@@ -305,14 +305,19 @@ class Program:
         if norm_w is not None:
             self.load(sm, norm_w, default_port=1)
         self.load(sm, qkv, default_port=1)
-        tbl = state_addr + 4 * (isa.ST_PAGETABLE + base_page)
-        self.dyn_count(sm, state_addr + 4 * isa.ST_NPAGES, base_page, max_pages)
-        self.repeat(sm, 0, [4, 0, 4, 0], dynamic=True)
-        self.mem(sm, isa.OP_CC0, arg=page_shift, address=tbl)
-        self.mem(sm, isa.OP_ALLOC_TMA_LOAD_1D, size=page_bytes, nslot=slots_for(page_bytes), address=k_page_addr)
-        self.mem(sm, isa.OP_CC0, arg=page_shift, address=tbl)
-        self.mem(sm, isa.OP_ALLOC_TMA_LOAD_1D, size=page_bytes, nslot=slots_for(page_bytes), address=v_page_addr,
-                 flags=isa.F_JUMP)
+        # The page ids of up to 32 pages are fetched with one load (a word per lane of the control
+        # warp); each trip of the loop then takes its page from there, so no load sits between
+        # two page copies.  Longer ranges are cut into segments of 32 pages.
+        for seg in range(0, max_pages, 32):
+            n = min(32, max_pages - seg)
+            self.dyn_count(sm, state_addr + 4 * isa.ST_NPAGES, base_page + seg, n)
+            self.mem(sm, isa.OP_PT_LOAD32, size=n, address=state_addr + 4 * (isa.ST_PAGETABLE + base_page + seg))
+            self.repeat(sm, 0, [0, 0, 0, 0], dynamic=True)
+            self.mem(sm, isa.OP_PT_APPLY, arg=page_shift)
+            self.mem(sm, isa.OP_ALLOC_TMA_LOAD_1D, size=page_bytes, nslot=slots_for(page_bytes), address=k_page_addr)
+            self.mem(sm, isa.OP_PT_APPLY, arg=page_shift)
+            self.mem(sm, isa.OP_ALLOC_TMA_LOAD_1D, size=page_bytes, nslot=slots_for(page_bytes), address=v_page_addr,
+                     flags=isa.F_JUMP)
         self.bytes_loaded[sm] += 2 * page_bytes * max_pages
         e = f32_bits(qk_eps)
         op = isa.OP_ATTN_DECODE_PAGED_G4 if G == 4 else isa.OP_ATTN_DECODE_PAGED_G8
