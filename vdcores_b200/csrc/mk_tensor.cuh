@@ -168,9 +168,17 @@ __device__ __forceinline__ void gemm_epilogue_flush(const GemmTc& g, int b, EpiA
   acc.best_row = 0x7fffffff;
 }
 
+#ifdef VDC_TC_PROFILE
+#define TCS(i) if (q.tid == 0) { const long long _n = clock64(); c.profile[c.sm * VDC_NUM_PROFILE_EVENTS + 100 + (i)] += _n - tcs_mark; tcs_mark = _n; }
+#else
+#define TCS(i)
+#endif
 __device__ void task_gemm_tc(Compute& q, const GemmTc& g) {
   Shared* sh = q.sh;
   const Ctx& c = q.c;
+#ifdef VDC_TC_PROFILE
+  long long tcs_mark = clock64();
+#endif
   // Tensor memory is taken the first time a program needs it and given back when the kernel ends.
   if (!sh->tmem_ready) {
     if (q.warp == 0) tmem_alloc(&sh->tmem_base, kTmemCols);
@@ -199,6 +207,7 @@ __device__ void task_gemm_tc(Compute& q, const GemmTc& g) {
   // order: it waits for the chunks, one lane issues the tensor-core work and, once the
   // previous chunk's reads are done, recycles its slots.  With norm the other seven warps
   // run ahead of it, normalising the X chunks in place and signalling each chunk's barrier.
+  TCS(0);
   q.warp_phase_begin(n_ent, q.warp == 0 ? 0u : n_ent);
   if (q.warp > 0 && g.norm) {
     // The seven warps normalise one X chunk after the other, together (224 threads).
@@ -331,6 +340,7 @@ __device__ void task_gemm_tc(Compute& q, const GemmTc& g) {
   tc_fence_after();
   if (g.norm) q.xr_count += (unsigned)n_x;
   if (q.aborted) return;
+  TCS(1);
 
   // Lane b of the accumulator belongs to sequence b; warps w and w+4 share the lane quarter
   // w % 4 and split the columns.
@@ -352,12 +362,12 @@ __device__ void task_gemm_tc(Compute& q, const GemmTc& g) {
         gemm_epilogue16(g, b, g.n0 + gi * 16, v, acc);
       }
       if (b < g.B) gemm_epilogue_flush(g, b, acc);
-      __threadfence();
     }
     tc_fence_before();
     compute_sync();  // every lane read its columns: the next task may overwrite the accumulator
     if (q.tid == 0 && g.bar != 0xFFFF) red_release_gpu_add(c.bars + g.bar, -1);
     q.free_slots(normw_mask);
+    TCS(2);
     return;
   }
   // ---- a K-slice: add the partial sums to the block's fp32 scratch area
@@ -373,20 +383,21 @@ __device__ void task_gemm_tc(Compute& q, const GemmTc& g) {
                      "f"(__uint_as_float(r[j + 1])), "f"(__uint_as_float(r[j + 2])), "f"(__uint_as_float(r[j + 3]))
                      : "memory");
     }
-    __threadfence();
   }
   tc_fence_before();
   compute_sync();
+  TCS(3);
   if (q.tid == 0) {
-    // the sums are complete once every unit of the block arrived; the gpu-scope fences order
-    // this CTA's adds before the bump and the last arriver's reads after it
-    __threadfence();
-    const int old = atomicAdd(g.counter, 1);
-    __threadfence();
+    // The sums are complete once every unit of the block arrived.  The bump releases this CTA's
+    // adds (ordered before it by the CTA barrier; a release is cumulative) and acquires the
+    // other units' for the reads of the last arriver.
+    int old;
+    asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(old) : "l"(g.counter) : "memory");
     sh->misc[35] = (old == g.n_slices - 1) ? 1.f : 0.f;
   }
   compute_sync();
   q.free_slots(normw_mask);
+  TCS(4);
   if (sh->misc[35] == 0.f) return;
   // ---- last arrival for this block: epilogue from the scratch area (read past L1), cleared for its next use
   const int items = g.B * ng;
@@ -404,13 +415,16 @@ __device__ void task_gemm_tc(Compute& q, const GemmTc& g) {
     gemm_epilogue16(g, bb, g.n0 + gi * 16, v, acc);
     gemm_epilogue_flush(g, bb, acc);
   }
-  __threadfence();
   compute_sync();
   if (q.tid == 0) {
     *g.counter = 0;  // ready for the block's next use; ordered before it by the barrier chain
-    __threadfence();
+    // the releasing count-down is cumulative: it publishes what the CTA barrier ordered before it
     if (g.bar != 0xFFFF) red_release_gpu_add(c.bars + g.bar, -1);
   }
+  TCS(5);
+#ifdef VDC_TC_PROFILE
+  if (q.tid == 0) c.profile[c.sm * VDC_NUM_PROFILE_EVENTS + 106] += 1;
+#endif
 }
 
 // ------------------------------------------------------------------------- //
