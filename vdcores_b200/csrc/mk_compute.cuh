@@ -600,18 +600,24 @@ __device__ void task_attn_decode(Compute& q, const AttnArgs& a) {
     acc[g][0] = acc[g][1] = 0.f;
   }
   const int pg = q.tid >> 6, dp = q.tid & 63;  // PV phase: position group, dim pair
+  // Every warp walks every page entry itself (no CTA-wide pop): the only CTA barriers of a page
+  // are the one after the scores and the one after the probabilities.  A warp whose wait was
+  // given up keeps joining the barriers; everybody leaves together at the next one.
+  const unsigned n_ent = 2u * (unsigned)count;  // ring entries: K page, V page, K page, ...
+  q.warp_phase_begin(n_ent, 0u);
   int v_prev = 0;
+  bool bail = false;
   for (int blk = 0; blk < count; ++blk) {
-    const int k_mask = q.pop();  // its sync also ends the previous block's PV phase
-    if (q.aborted) return;
+    const int k_mask = q.warp_wait(2u * (unsigned)blk);
+    const bool k_ok = k_mask != kPopAbort;
     ATTN_STAMP(3 + 4 * (blk & 1));
-    q.free_slots(v_prev);
-    uint8_t* kb = (uint8_t*)slot_ptr(c, first_slot(k_mask));
+    uint8_t* kb = (uint8_t*)slot_ptr(c, first_slot(k_ok ? k_mask : 1));  // a given-up wait computes on slot 0, unused
     const bool last = owner && blk == count - 1;
     const int valid = last ? tail_valid : VDC_KV_PAGE;
     if (last) {
-      // the page in HBM does not hold the new row yet: patch it in shared memory
-      if (q.tid < D / 8)
+      // the page in HBM does not hold the new row yet: patch it in shared memory (warp 0 has
+      // seen the page arrive; the barrier shows the row to the others, who have seen it too)
+      if (k_ok && q.tid < D / 8)
         reinterpret_cast<uint4*>(kb + (valid - 1) * D * 2)[q.tid] = reinterpret_cast<const uint4*>(krow)[q.tid];
       compute_sync();
     }
@@ -653,9 +659,14 @@ __device__ void task_attn_decode(Compute& q, const AttnArgs& a) {
       for (int o = LPP; o < 32; o <<= 1) wm[g] = fmaxf(wm[g], __shfl_xor_sync(0xffffffffu, wm[g], o));
       if (q.lane == 0) sh->wmax[q.warp * G + g] = wm[g];
     }
-    compute_sync();  // (A) scores and warp maxima visible; K page fully read
+    compute_sync();  // (A) scores and warp maxima visible; K page fully read; previous P V finished
+    if (sh->aborted) {
+      bail = true;
+      break;
+    }
     ATTN_STAMP(4 + 4 * (blk & 1));
-    q.free_slots(k_mask);
+    q.free_slots(k_mask | v_prev);
+    if (q.lane == 0) sh->warp_next[q.warp] = q.head + 2u * (unsigned)blk + 1u;
     // ---- phase 2: running max, rescale factors, probabilities
     float alpha[G], m_new[G];
 #pragma unroll
@@ -673,15 +684,16 @@ __device__ void task_attn_decode(Compute& q, const AttnArgs& a) {
       // HF rounds probabilities to bf16 after the softmax; here they stay fp32
       sh->probs[t] = (m_new[g] == -INFINITY) ? 0.f : exp2f(s - m_new[g]);
     }
-    const int v_mask = q.pop();  // (B) its sync publishes probs
-    if (q.aborted) return;
-    ATTN_STAMP(5 + 4 * (blk & 1));
-    uint8_t* vb = (uint8_t*)slot_ptr(c, first_slot(v_mask));
-    if (last) {
-      if (q.tid < D / 8)
-        reinterpret_cast<uint4*>(vb + (valid - 1) * D * 2)[q.tid] = reinterpret_cast<const uint4*>(vrow)[q.tid];
-      compute_sync();
+    const int v_mask = q.warp_wait(2u * (unsigned)blk + 1u);
+    uint8_t* vb = (uint8_t*)slot_ptr(c, first_slot(v_mask == kPopAbort ? 1 : v_mask));
+    if (last && v_mask != kPopAbort && q.tid < D / 8)
+      reinterpret_cast<uint4*>(vb + (valid - 1) * D * 2)[q.tid] = reinterpret_cast<const uint4*>(vrow)[q.tid];
+    compute_sync();  // (B) probabilities (and the patched V row) visible
+    if (sh->aborted) {
+      bail = true;
+      break;
     }
+    ATTN_STAMP(5 + 4 * (blk & 1));
     // ---- phase 3: O += P V over this thread's 16 positions, two dims per thread
 #pragma unroll
     for (int g = 0; g < G; ++g) {
@@ -702,10 +714,17 @@ __device__ void task_attn_decode(Compute& q, const AttnArgs& a) {
       }
     }
     v_prev = v_mask;
+    __syncwarp();
+    if (q.lane == 0) sh->warp_next[q.warp] = q.head + 2u * (unsigned)blk + 2u;
     ATTN_STAMP(6 + 4 * (blk & 1));
   }
-
-  compute_sync();  // everyone is done with the last V page
+  if (q.lane == 0) sh->warp_next[q.warp] = 0xFFFFFFFFu;
+  if (bail) {
+    q.aborted = true;
+    return;
+  }
+  q.warp_phase_end(n_ent);  // CTA barrier: everyone is done with the last V page
+  if (q.aborted) return;
   q.free_slots(v_prev);
   ATTN_STAMP(11);
   // cross position-group reduction: groups 1..3 publish, group 0 adds and writes the record
