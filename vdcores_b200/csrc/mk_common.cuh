@@ -156,6 +156,7 @@ struct __align__(16) Shared {
   volatile unsigned pf_n;
   volatile unsigned pf_window;              // bytes the frontier may run ahead
   volatile int pf_go, pf_exit;
+  uint32_t pt_words[32];                    // control warp: the table words PT_LOAD32 fetched (page loop)
   volatile int pop_val[2];
   volatile uint32_t pop_meta[2];
   volatile uint64_t pop_addr[2];

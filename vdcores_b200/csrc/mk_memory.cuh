@@ -22,6 +22,9 @@ __device__ __forceinline__ unsigned ring_head(const Shared* sh, int lane) {
 #ifndef VDC_CTRL_FASTPATH
 #define VDC_CTRL_FASTPATH 0
 #endif
+#ifndef VDC_CTRL_PAGELOOP
+#define VDC_CTRL_PAGELOOP 1   // lane-0 fast path for the attention page loop
+#endif
 #ifndef VDC_FAST_SLEEP
 #define VDC_FAST_SLEEP 20
 #endif
@@ -230,6 +233,98 @@ __device__ void control_warp(const Ctx& c, const VdcMInst* __restrict__ insts, i
           // (Measured on B200: issuing the chunk loads this fast makes them arrive in
           // bursts, the warps then compute and free in lock-step, and a GEMV stage
           // streams ~7 % slower than with the paced general path; off by default.)
+          // Page loop of the decode attention: a body of {PT_APPLY, page load, PT_APPLY, page load}.
+          // Lane 0 runs all its trips alone from the table words PT_LOAD32 fetched: per page copy
+          // one look at the slot mask, one ring entry, no warp-wide votes and no instruction fetch.
+          if (VDC_CTRL_PAGELOOP && count > 0 && pc + 4 - ic_base < 64u && !ind_pending) {
+            const uint4 a0 = *reinterpret_cast<const uint4*>(&sh->icache[pc + 1 - ic_base]);
+            const uint4 l0 = *reinterpret_cast<const uint4*>(&sh->icache[pc + 2 - ic_base]);
+            const uint4 a1 = *reinterpret_cast<const uint4*>(&sh->icache[pc + 3 - ic_base]);
+            const uint4 l1 = *reinterpret_cast<const uint4*>(&sh->icache[pc + 4 - ic_base]);
+            auto is_apply = [](const uint4& v) { return ((v.x & 0xFFFFu) >> VDC_FLAG_BITS) == 31u; };
+            auto is_load = [](const uint4& v, bool jump) {
+              const uint32_t op = v.x & 0xFFFFu;
+              const int rq = (int)(v.y & 63u);
+              return (op >> VDC_FLAG_BITS) == 9u && (op & VDC_F_ALLOCATE) && !(op & (VDC_F_GROUP | VDC_F_BARRIER)) &&
+                     ((op & VDC_F_JUMP) != 0) == jump && rq > 0 && rq < kSlots;
+            };
+            if (is_apply(a0) && is_load(l0, false) && is_apply(a1) && is_load(l1, true) && count <= 32 &&
+                reg_start == 0 && reg_end == 4 && address == 0) {
+              sh->pt_words[lane] = tbl;
+              __syncwarp();
+              int ok = 1;
+              if (lane == 0) {
+                const uint32_t sh0 = a0.y >> 16, sh1 = a1.y >> 16;
+                int pos = 0;
+                for (int k = 0; k < 2 * count && ok; ++k) {
+                  const uint4& b = (k & 1) ? l1 : l0;
+                  const int breq = (int)(b.y & 63u);
+                  const uint32_t unit = (1u << breq) - 1u;
+                  const uint64_t addr = (((uint64_t)b.w << 32) | b.z) + ((uint64_t)sh->pt_words[k >> 1] << ((k & 1) ? sh1 : sh0));
+                  uint32_t it = 0, mask;
+                  uint64_t t0 = 0;
+                  while (true) {
+                    const uint32_t avail = *reinterpret_cast<volatile uint32_t*>(&sh->slot_avail);
+                    if (pos + breq > kSlots) pos = 0;
+                    mask = unit << pos;
+                    if ((avail & mask) == mask) break;
+                    bool found = false;
+                    for (int p2 = 0; p2 + breq <= kSlots; ++p2) {
+                      mask = unit << p2;
+                      if ((avail & mask) == mask) {
+                        pos = p2;
+                        found = true;
+                        break;
+                      }
+                    }
+                    if (found) break;
+                    n_alloc_retry++;
+                    __nanosleep(20);
+                    if ((++it & 63u) == 0) {
+                      const uint64_t now = globaltimer_ns();
+                      if (t0 == 0) t0 = now;
+                      if (ld_relaxed_gpu(&c.status->abort) != 0) ok = 0;
+                      else if (now - t0 > 2 * c.timeout_ns) {
+                        raise_abort(c, VDC_ERR_TIMEOUT, 1, (int)pc + 2, (int)(b.x & 0xFFFFu), -1, breq);
+                        ok = 0;
+                      }
+                      if (!ok) break;
+                    }
+                  }
+                  if (!ok) break;
+                  atomicAnd(&sh->slot_avail, ~mask);
+                  pos += breq;
+                  while (tail - head_cache >= (unsigned)kQ) {  // ring full: recompute the head alone
+                    unsigned h = sh->cta_head;
+                    __threadfence_block();
+                    for (int wv = 0; wv < kCW; ++wv) {
+                      const unsigned v = sh->warp_next[wv];
+                      h = v < h ? v : h;
+                    }
+                    head_cache = h;
+                    if ((++it & 1023u) == 0 && ld_relaxed_gpu(&c.status->abort) != 0) {
+                      ok = 0;
+                      break;
+                    }
+                  }
+                  if (!ok) break;
+                  const unsigned e = tail % kQ;
+                  *reinterpret_cast<uint4*>(&sh->ring[e]) = make_uint4(b.x, b.y, (uint32_t)addr, (uint32_t)(addr >> 32));
+                  sh->ring_word[e] = (int)mask;
+                  __threadfence_block();
+                  sh->ring_tail = ++tail;
+                }
+              }
+              ok = __shfl_sync(0xffffffffu, ok, 0);
+              tail = __shfl_sync(0xffffffffu, tail, 0);
+              head_cache = __shfl_sync(0xffffffffu, head_cache, 0);
+              n_inst += 4u * (unsigned)count;
+              loop_counter = 0;
+              next_pc = pc + 5;
+              if (!ok) running = false;
+              break;
+            }
+          }
           if (VDC_CTRL_FASTPATH && count > 0 && pc + 1 - ic_base < 64u && !ind_pending) {
             const uint4 b = *reinterpret_cast<const uint4*>(&sh->icache[pc + 1 - ic_base]);
             const uint32_t bop = b.x & 0xFFFFu, bid = bop >> VDC_FLAG_BITS;
