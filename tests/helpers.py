@@ -15,6 +15,9 @@ def small_cfg(kind: str) -> O.DecodeConfig:
     if kind == "moe":           # Qwen3-MoE style: QK norm, group of 8, 16 experts of width 256, top-4
         return O.DecodeConfig(hidden=512, n_heads=8, n_kv_heads=1, head_dim=128, ffn=256, vocab=1024,
                               n_layers=2, eps=1e-6, theta=1e6, qk_norm=True, n_experts=16, top_k=4)
+    if kind == "moe2":          # the same with two KV heads, so that attention can be split over two ranks
+        return O.DecodeConfig(hidden=512, n_heads=8, n_kv_heads=2, head_dim=128, ffn=256, vocab=1024,
+                              n_layers=2, eps=1e-6, theta=1e6, qk_norm=True, n_experts=16, top_k=4)
     if kind == "qwen3_1k":      # K multiples of 1024, as the NVFP4 rows need
         return O.DecodeConfig(hidden=1024, n_heads=8, n_kv_heads=1, head_dim=128, ffn=1024, vocab=1024,
                               n_layers=2, eps=1e-6, theta=1e6, qk_norm=True)

@@ -23,7 +23,7 @@ def free_port():
     return p
 
 
-def run_rank(rank, world, port, n_steps, results):
+def run_rank(rank, world, port, n_steps, results, kind="llama"):
     import torch.distributed as dist
     from vdcores_b200.tp import TPDecodeEngine, shard_dense_weights
     torch.cuda.set_device(rank)
@@ -31,7 +31,7 @@ def run_rank(rank, world, port, n_steps, results):
     dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world,
                             device_id=dev)
     try:
-        cfg = small_cfg("llama")
+        cfg = small_cfg(kind)
         w = perturb_norms(O.ModelWeights.random(cfg, seed=3))
         g = torch.Generator().manual_seed(11)
         prompt = torch.randint(0, cfg.vocab, (70,), generator=g)
@@ -77,19 +77,30 @@ def test_tp_one_rank_group(cuda_device):
     check(results, 1)
 
 
-def _worker(rank, world, port, n_steps, q):
+def test_expert_parallel_one_rank_group(cuda_device):
+    """The mixture-of-experts model through the expert-parallel path with one rank: router,
+    selection, dynamically counted expert tasks, fp32 partial sum, collectives."""
+    results = {}
+    run_rank(0, 1, free_port(), 4, results, kind="moe")
+    check(results, 1)
+
+
+def _worker(rank, world, port, n_steps, q, kind="llama"):
     res = {}
-    run_rank(rank, world, port, n_steps, res)
+    run_rank(rank, world, port, n_steps, res, kind=kind)
     q.put((rank, res[rank]))
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_tp_two_ranks():
+@pytest.mark.parametrize("kind", ["llama", "moe2"])
+def test_tp_two_ranks(kind):
+    """Two ranks: tensor parallel for the dense model; attention tensor parallel and experts
+    expert parallel (8 of 16 experts per rank) for the mixture-of-experts model."""
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, 5, q), daemon=True) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, 4, q, kind), daemon=True) for r in range(2)]
     for p in procs:
         p.start()
     try:

@@ -92,3 +92,54 @@ def test_shard_shapes():
         assert torch.equal(torch.cat([p.down[2] for p in parts], 1), w.layers[2].down.w)
         assert torch.equal(torch.cat([p.lm_head for p in parts], 0), w.lm_head)
         assert parts[0].gate[0].shape == (cfg.ffn // world, cfg.hidden)
+
+
+def _ep_rank(rank, world, port, q):
+    """Expert parallelism: every rank routes on the replicated hidden state, evaluates only the
+    selected experts it owns and the weighted partial sums are all-reduced."""
+    from vdcores_b200.tp import shard_dense_weights
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    try:
+        cfg = small_cfg("moe2")
+        w = perturb_norms(O.ModelWeights.random(cfg, seed=5))
+        lw = w.layers[0]
+        sh = shard_dense_weights(engine_config(cfg), dense_weights(w), rank, world)
+        per = cfg.n_experts // world
+        assert len(sh.gate[0]) == per and torch.equal(sh.gate[0][0], lw.experts[rank * per][0].w)
+        g = torch.Generator().manual_seed(10)
+        x = torch.randn(cfg.hidden, generator=g).to(torch.bfloat16)
+        wts, idx = O.moe_route(x[None], sh.router[0], cfg.top_k)
+        part = torch.zeros(cfg.hidden, dtype=torch.float32)
+        n_local = 0
+        for slot in range(cfg.top_k):
+            e = int(idx[0, slot])
+            if e // per != rank:
+                continue                      # another rank's expert: this rank streams nothing for the slot
+            n_local += 1
+            le = e % per
+            a = O.silu_mul(O.linear(x[None], sh.gate[0][le]), O.linear(x[None], sh.up[0][le]))
+            part += O.linear(a, sh.down[0][le])[0].float() * wts[0, slot].float()
+        dist.all_reduce(part)
+        ref = O.moe_ffn(x, lw, cfg.top_k)
+        q.put((rank, n_local, O.rel_l2(part.to(torch.bfloat16), ref)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_expert_parallel_sum_reproduces_the_moe_block():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _port()
+    procs = [ctx.Process(target=_ep_rank, args=(r, 2, port, q), daemon=True) for r in range(2)]
+    for p in procs:
+        p.start()
+    try:
+        res = [q.get(timeout=120) for _ in range(2)]
+    finally:
+        for p in procs:
+            p.join(10)
+            if p.is_alive():
+                p.kill()
+    assert sum(n for _, n, _ in res) == small_cfg("moe2").top_k      # every selected expert has exactly one owner
+    for rank, n_local, r in res:
+        assert r < 3e-3, (rank, r)

@@ -114,8 +114,14 @@
 // arrival (args of word 2: [eps hi, eps lo] unused, args[2] = top_k) folds bf16(sum) into the hidden
 // state (the output address) and clears both.
 //
-// MOE_ROUTE: args = [n_experts, top_k].  Pops the fp32 router logits and a raw address; writes
-// int32 ids[16] then fp32 weights[16] (softmax over all experts, top-k, renormalised, rounded to bf16).
+// MOE_ROUTE: args = [n_experts, top_k, rank | world << 8].  Pops the fp32 router logits and a raw address;
+// writes int32 ids[16], fp32 weights[16] (softmax over all experts, top-k, renormalised, rounded to bf16),
+// int32 local[16] and int32 count[16]: with expert parallelism (world > 1, n_experts / world consecutive
+// experts per rank) local = id modulo the experts per rank and count = 0x7FFF for the slots whose expert
+// this rank owns, 0 / 0 for the others; without it local = id, count = 0x7FFF.  A GEMV_ROWS task with
+// VDC_GEMV_DYN_BIT takes min(n_chunks, count) chunks, i.e. it is skipped for experts of other ranks.
+// GEMV_ROWS_MOE_DOWN with a null accumulator address adds weight * bf16(W x) to the fp32 output
+// (the rank's partial sum, all-reduced afterwards) instead of counting arrivals.
 //
 // ATTN_DECODE_PAGED words: [max_pages, base_page, flags] [qk-norm eps hi, lo, n_splits]
 // then six 48-bit addresses, low piece first: state block, this head's rows in K page 0,
@@ -172,6 +178,7 @@
 #define VDC_GEMV_MODE_MOE_DOWN 4    // weighted fp32 accumulation over the selected experts
 #define VDC_GEMV_ACC_BIT 0x0800
 #define VDC_GEMV_NORM_BIT 0x1000
+#define VDC_GEMV_DYN_BIT 0x2000    // the chunk count is min(n_chunks, int32 word): one more pop (a raw address: the word)
 
 // ATTN_DECODE args[2] bits
 #define VDC_ATTN_QKNORM_BIT 0x1

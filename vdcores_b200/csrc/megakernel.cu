@@ -92,6 +92,7 @@ __device__ void compute_core(const Ctx& c, const VdcCInst* __restrict__ insts, i
         const int R = ci.args[1] & 31, mode = (ci.args[1] >> 8) & 7;
         const bool accumulate = ci.args[1] & VDC_GEMV_ACC_BIT;
         const bool norm = ci.args[1] & VDC_GEMV_NORM_BIT;
+        const bool dyn = ci.args[1] & VDC_GEMV_DYN_BIT;
         const int K = (ci.args[2] & 0xFF) << 8;
         if (tid == 0) q.sh->misc[32] = __uint_as_float(((uint32_t)ex.args[0] << 16) | ex.args[1]);  // norm eps
         const int row_base = ((int)ex.args[2] | ((int)(ci.args[2] >> 8) << 16)) * R;  // first output row (argmax)
@@ -122,11 +123,11 @@ __device__ void compute_core(const Ctx& c, const VdcCInst* __restrict__ insts, i
                                                   ((uint64_t)e2.args[2] << 32));
         }
         switch (R) {
-          case 1: task_gemv_rows<1>(q, ci.args[0], mode, accumulate, norm, K, row_base, scales, wfmt, moe); break;
-          case 2: task_gemv_rows<2>(q, ci.args[0], mode, accumulate, norm, K, row_base, scales, wfmt, moe); break;
-          case 4: task_gemv_rows<4>(q, ci.args[0], mode, accumulate, norm, K, row_base, scales, wfmt, moe); break;
-          case 8: task_gemv_rows<8>(q, ci.args[0], mode, accumulate, norm, K, row_base, scales, wfmt, moe); break;
-          case 16: task_gemv_rows<16>(q, ci.args[0], mode, accumulate, norm, K, row_base, scales, wfmt, moe); break;
+          case 1: task_gemv_rows<1>(q, ci.args[0], mode, accumulate, norm, K, row_base, scales, wfmt, moe, dyn); break;
+          case 2: task_gemv_rows<2>(q, ci.args[0], mode, accumulate, norm, K, row_base, scales, wfmt, moe, dyn); break;
+          case 4: task_gemv_rows<4>(q, ci.args[0], mode, accumulate, norm, K, row_base, scales, wfmt, moe, dyn); break;
+          case 8: task_gemv_rows<8>(q, ci.args[0], mode, accumulate, norm, K, row_base, scales, wfmt, moe, dyn); break;
+          case 16: task_gemv_rows<16>(q, ci.args[0], mode, accumulate, norm, K, row_base, scales, wfmt, moe, dyn); break;
           default: raise_abort(c, VDC_ERR_BAD_OPCODE, 0, (int)q.pc, ci.opcode, -1, R); q.aborted = true; break;
         }
         break;
@@ -235,7 +236,7 @@ __device__ void compute_core(const Ctx& c, const VdcCInst* __restrict__ insts, i
         break;
       }
       case 0x7220: task_argmax_final(q, ci.args[0], ci.args[1]); break;
-      case 0x7240: task_moe_route(q, ci.args[0], ci.args[1]); break;
+      case 0x7240: task_moe_route(q, ci.args[0], ci.args[1], ci.args[2] & 0xFF, ci.args[2] >> 8); break;
       default:
         raise_abort(c, VDC_ERR_BAD_OPCODE, 0, (int)q.pc, ci.opcode, -1, 0);
         q.aborted = true;

@@ -274,7 +274,8 @@ struct MoeDown {           // mode MOE_DOWN: per-row accumulation over the selec
 
 template <int R>
 __device__ void task_gemv_rows(Compute& q, int n_chunks, int mode, bool accumulate, bool norm, int K, int row_base,
-                               const float* scales = nullptr, int wfmt = 0, const MoeDown* moe = nullptr) {
+                               const float* scales = nullptr, int wfmt = 0, const MoeDown* moe = nullptr,
+                               bool dyn = false) {
   Shared* sh = q.sh;
   const Ctx& c = q.c;
   int normw_mask = 0;
@@ -289,6 +290,14 @@ __device__ void task_gemv_rows(Compute& q, int n_chunks, int mode, bool accumula
     q.pop();  // candidate record: raw address
     recg = reinterpret_cast<float*>(q.addr());
     rec_meta = q.meta();
+  }
+  if (dyn) {
+    // the count word was written by another SM; this hand-over was published only after the
+    // barrier that orders it had opened
+    q.pop();
+    if (q.aborted) return;
+    const int lim = ld_relaxed_gpu(reinterpret_cast<const int*>(q.addr()));
+    n_chunks = min(n_chunks, max(lim, 0));
   }
   if (q.aborted) return;
   uint8_t* x = (uint8_t*)slot_ptr(c, first_slot(x_mask));
@@ -397,6 +406,9 @@ __device__ void task_gemv_rows(Compute& q, int n_chunks, int mode, bool accumula
         if (q.lane == r) v = acc[r];
       if (q.lane < R && mode == VDC_GEMV_MODE_STORE_F32) {
         reinterpret_cast<float*>(outg)[row0 + q.lane] = v;
+      } else if (q.lane < R && mode == VDC_GEMV_MODE_MOE_DOWN && moe->acc == nullptr) {
+        // expert parallel: this rank's share of the weighted sum, fp32, all-reduced by the host side
+        atomicAdd(reinterpret_cast<float*>(outg) + row0 + q.lane, ld_relaxed_gpu_f32(moe->weight) * bf16_round(v));
       } else if (q.lane < R && mode == VDC_GEMV_MODE_MOE_DOWN) {
         const int row = row0 + q.lane;
         atomicAdd(moe->acc + row, __ldg(moe->weight) * bf16_round(v));
@@ -808,8 +820,8 @@ __device__ void task_attn_decode(Compute& q, const AttnArgs& a) {
 // task: MoE routing — softmax over all experts, top-k, renormalise
 // ------------------------------------------------------------------------- //
 // Pop order: router logits (n_experts fp32), route record (raw address: int32
-// ids[16] followed by fp32 weights[16]).  One warp does the work.
-__device__ void task_moe_route(Compute& q, int n_experts, int top_k) {
+// ids[16], fp32 weights[16], int32 local[16], int32 count[16]).  One warp does the work.
+__device__ void task_moe_route(Compute& q, int n_experts, int top_k, int rank, int world) {
   const Ctx& c = q.c;
   const int lg_mask = q.pop();
   q.pop();
@@ -870,6 +882,11 @@ __device__ void task_moe_route(Compute& q, int n_experts, int top_k) {
     if (q.lane < top_k) {
       ids[q.lane] = my_id;
       wts[q.lane] = bf16_round(my_w / sel_sum);
+      // expert parallelism: which of this rank's experts, and whether the slot is this rank's at all
+      const int per_rank = world > 1 ? n_experts / world : n_experts;
+      const bool mine = world <= 1 || my_id / per_rank == rank;
+      ids[32 + q.lane] = mine ? my_id % per_rank : 0;
+      ids[48 + q.lane] = mine ? 0x7FFF : 0;
     }
   }
   compute_sync();

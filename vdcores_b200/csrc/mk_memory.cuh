@@ -225,6 +225,7 @@ __device__ void control_warp(const Ctx& c, const VdcMInst* __restrict__ insts, i
           loop_iter = 0;
           loop_start = (int)pc + 1;
           if (size == 0xFFFF && count == 0) {
+            ind_pending = false;     // an indirection meant for the skipped body must not reach a later load
             next_pc = pc + 1 + arg;  // empty dynamic loop: skip body
             break;
           }

@@ -171,7 +171,7 @@ class DecodeEngine:
         if cfg.n_experts:
             assert wkind == "bf16", "expert weights are bf16 only"
             self.router_logits = z(cfg.n_experts, dt=torch.float32)
-            self.route = z(32, dt=torch.int32)          # int32 ids[16] | fp32 weights[16]
+            self.route = z(64, dt=torch.int32)          # int32 ids[16] | fp32 weights[16] | int32 local[16] | int32 count[16]
             self.moe_acc = z(H, dt=torch.float32)       # zero between layers: the last expert to arrive clears it
             self.moe_cnt = z(H, dt=torch.int32)
         G = cfg.group

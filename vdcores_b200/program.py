@@ -222,7 +222,8 @@ class Program:
     def gemv(self, sm, *, w_addr, n_rows, K, R, x: Src, out: Dst, mode=isa.GEMV_MODE_STORE,
              norm_w: Optional[Src] = None, eps: float = 0.0, pair_out: Optional[Dst] = None, row_base: int = 0,
              stream: bool = False, fp8_scales: Optional[int] = None, nvfp4_scales: Optional[int] = None,
-             w_indirect: Optional[tuple] = None, wait_issue: Optional[int] = None, moe: Optional[dict] = None):
+             w_indirect: Optional[tuple] = None, wait_issue: Optional[int] = None, moe: Optional[dict] = None,
+             dyn_count_addr: Optional[int] = None):
         """y[0:n_rows] = W[0:n_rows, :K] @ x for the contiguous row block at w_addr
         (bf16; e4m3 with fp8_scales = address of the block's fp32 per-row scales;
         or NVFP4 rows — K/2 code bytes + K/16 block scales — with nvfp4_scales =
@@ -256,24 +257,33 @@ class Program:
             # the weight address depends on data another SM produces (an expert id): the memory
             # stream of this SM stops here until that barrier has opened
             self.mem(sm, isa.OP_ISSUE_BARRIER, bar=wait_issue)
+        if dyn_count_addr is not None:
+            # the task takes min(n_chunks, word) chunks (an expert of another rank: none); the hand-over
+            # of the word's address follows the barrier that orders the word
+            assert wait_issue is not None
+            self.raw_address(sm, dyn_count_addr, 27)
         if w_indirect is not None:
             waddr, stride = w_indirect
             assert 0 < stride < 1 << 32
+            if dyn_count_addr is not None:
+                self.dyn_count(sm, dyn_count_addr, 0, n_chunks)
             self.mem(sm, isa.OP_CC0_STRIDE32, size=stride & 0xFFFF, arg=stride >> 16, address=waddr)
-        self.repeat(sm, n_chunks, [chunk_bytes])
+        elif dyn_count_addr is not None:
+            self.dyn_count(sm, dyn_count_addr, 0, n_chunks)
+        self.repeat(sm, n_chunks, [chunk_bytes], dynamic=dyn_count_addr is not None)
         self.mem(sm, isa.OP_ALLOC_TMA_LOAD_1D_STREAM if stream else isa.OP_ALLOC_TMA_LOAD_1D, size=chunk_bytes,
                  nslot=slots_for(chunk_bytes), address=w_addr, flags=isa.F_JUMP)
         self.bytes_loaded[sm] += chunk_bytes * n_chunks
         rb8 = row_base // R     # index of the first chunk within the whole matrix
         a1 = R | (mode << 8) | (isa.GEMV_NORM_BIT if norm_w is not None else 0) | \
-            (isa.GEMV_ACC_BIT if out.kind == "add_bf16" else 0)
+            (isa.GEMV_ACC_BIT if out.kind == "add_bf16" else 0) | (isa.GEMV_DYN_BIT if dyn_count_addr is not None else 0)
         a2 = (K // 256) | ((rb8 >> 16) << 8)
         e = f32_bits(eps)
         if moe is not None:
             assert mode == isa.GEMV_MODE_MOE_DOWN and scales is None
             self.comp(sm, isa.OP_GEMV_ROWS_MOE_DOWN, n_chunks, a1, a2)
             self.comp(sm, isa.OP_EXT, e >> 16, e & 0xFFFF, moe["top_k"])
-            for addr in (moe["weight_addr"], moe["acc_addr"], moe["cnt_addr"]):
+            for addr in (moe["weight_addr"], moe["acc_addr"], moe["cnt_addr"]):   # acc_addr 0: fp32 partial-sum output
                 assert addr % 4 == 0 and 0 <= addr < 1 << 48
                 self.comp(sm, isa.OP_EXT, addr & 0xFFFF, (addr >> 16) & 0xFFFF, (addr >> 32) & 0xFFFF)
             return
@@ -423,13 +433,17 @@ class Program:
         self.comp(sm, isa.OP_EXT, *a48(stats_addr))
         self.comp(sm, isa.OP_EXT, n_stats & 0xFFFF, n_stats >> 16, 0)
 
-    def moe_route(self, sm, *, logits: Src, route_addr: int, n_experts: int, top_k: int, release=None):
+    def moe_route(self, sm, *, logits: Src, route_addr: int, n_experts: int, top_k: int, release=None,
+                  rank: int = 0, world: int = 1):
         """Softmax over n_experts fp32 router logits, top-k, renormalise: writes int32
-        ids[16] then fp32 weights[16] at route_addr."""
+        ids[16], fp32 weights[16], int32 local[16], int32 count[16] at route_addr (256 bytes).
+        With world > 1 (expert parallelism, n_experts / world consecutive experts per rank)
+        local / count describe this rank's share of the selection (see isa.h)."""
         assert n_experts <= 256 and top_k <= 16 and logits.nbytes == n_experts * 4
+        assert 0 <= rank < max(world, 1) <= 255 and n_experts % max(world, 1) == 0
         self.load(sm, logits)
         self.raw_address(sm, route_addr, 25, release=release)
-        self.comp(sm, isa.OP_MOE_ROUTE, n_experts, top_k)
+        self.comp(sm, isa.OP_MOE_ROUTE, n_experts, top_k, rank | (world << 8))
 
     def argmax_final(self, sm, *, records: Src, n: int, state_addr, log_addr, release=None, local_only=False):
         """Reduces n candidate records {f32 value, i32 index, pad, pad}.  Normally

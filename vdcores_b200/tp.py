@@ -1,8 +1,14 @@
-"""Tensor-parallel batch-1 decode: one process per GPU, the model split the
+"""Tensor- and expert-parallel batch-1 decode: one process per GPU, the model split the
 Megatron way — QKV and gate/up by output rows (heads / FFN columns), O and down
 by input columns, vocabulary rows of the lm_head — with an all-reduce (sum) of
 the fp32 partial hidden-state update after the O projection and after the down
 projection of every layer, over NCCL (`torch.distributed`).
+
+Mixture-of-experts layers are expert parallel: every rank keeps n_experts / world
+consecutive experts whole, computes the router and the top-k selection on the
+replicated hidden state, runs only the selected experts it owns (the others'
+tasks see a chunk count of zero and stream nothing) and adds their weighted
+outputs into its fp32 partial sum, which the same all-reduce combines.
 
 The reference has no multi-GPU path at all; this is new.  Each rank runs the
 same megakernel tasks as the single-GPU engine on its shard.  A layer becomes
@@ -38,6 +44,18 @@ def shard_dense_weights(cfg: DecodeConfig, w: DenseWeights, rank: int, world: in
     norms replicated."""
     assert cfg.n_kv_heads % world == 0 and cfg.ffn % world == 0 and cfg.vocab % world == 0
     L = cfg.n_layers
+    if cfg.n_experts:
+        assert cfg.n_experts % world == 0
+        e0, e1 = rank * cfg.n_experts // world, (rank + 1) * cfg.n_experts // world
+        return DenseWeights(
+            embed=w.embed, lm_head=shard_rows(w.lm_head, rank, world), norm=w.norm, ln1=w.ln1, ln2=w.ln2,
+            wq=[shard_rows(w.wq[l], rank, world) for l in range(L)],
+            wk=[shard_rows(w.wk[l], rank, world) for l in range(L)],
+            wv=[shard_rows(w.wv[l], rank, world) for l in range(L)],
+            wo=[shard_cols(w.wo[l], rank, world) for l in range(L)],
+            gate=[w.gate[l][e0:e1] for l in range(L)], up=[w.up[l][e0:e1] for l in range(L)],
+            down=[w.down[l][e0:e1] for l in range(L)], router=w.router,
+            q_norm=w.q_norm, k_norm=w.k_norm)
     return DenseWeights(
         embed=w.embed, lm_head=shard_rows(w.lm_head, rank, world), norm=w.norm, ln1=w.ln1, ln2=w.ln2,
         wq=[shard_rows(w.wq[l], rank, world) for l in range(L)],
@@ -68,7 +86,7 @@ class TPDecodeEngine:
         self.F = cfg.ffn // world
         self.V = cfg.vocab // world
         self.qw, self.kvw = self.nq * D, self.nkv * D
-        assert self.nkv & (self.nkv - 1) == 0 and self.qw % 256 == 0 and self.F % 256 == 0
+        assert self.nkv & (self.nkv - 1) == 0 and self.qw % 256 == 0 and (cfg.n_experts or self.F % 256 == 0)
         L, H = cfg.n_layers, cfg.hidden
         z = lambda *s, dt=BF16: torch.zeros(*s, dtype=dt, device=self.dev)
         self.hidden = z(H)
@@ -77,6 +95,12 @@ class TPDecodeEngine:
         self.act = z(self.F)
         self.partial = z(H, dt=torch.float32)
         self.logits = z(self.V)
+        if cfg.n_experts:
+            assert cfg.n_experts % world == 0 and cfg.top_k <= 16
+            self.E_local = cfg.n_experts // world
+            self.act = z(cfg.top_k, cfg.ffn)
+            self.router_logits = z(cfg.n_experts, dt=torch.float32)
+            self.route = z(64, dt=torch.int32)      # int32 ids[16] | fp32 weights[16] | int32 local[16] | int32 count[16]
         self.rec_floats = G * D + 16 * ((2 * G + 15) // 16)
         self.n_splits = max(1, min(self.num_sms // self.nkv, self.max_pages))
         self.pages_per_split = (self.max_pages + self.n_splits - 1) // self.n_splits
@@ -123,6 +147,16 @@ class TPDecodeEngine:
         pm = torch.tensor(perm, dtype=torch.long, device=dev)
         self.wqkv = torch.stack([torch.cat((to(w.wq[l]), to(w.wk[l]), to(w.wv[l])), dim=0)[pm] for l in range(L)])
         self.wo = torch.stack([to(w.wo[l]) for l in range(L)])
+        if cfg.n_experts:
+            # this rank's experts: [L, E_local, 2F, H] with gate/up rows interleaved, [L, E_local, H, F]
+            self.wgu = torch.stack([torch.stack([torch.stack((to(g), to(u)), dim=1).reshape(2 * cfg.ffn, cfg.hidden)
+                                                 for g, u in zip(w.gate[l], w.up[l])]) for l in range(L)])
+            self.wd = torch.stack([torch.stack([to(d) for d in w.down[l]]) for l in range(L)])
+            self.router = torch.stack([to(t) for t in w.router])
+            self.qknorm = (torch.stack([torch.cat((to(w.q_norm[l]), to(w.k_norm[l]))) for l in range(L)])
+                           if cfg.qk_norm else None)
+            self._build_programs()
+            return
         self.wgu = torch.stack([torch.stack((to(w.gate[l]), to(w.up[l])), dim=1).reshape(2 * self.F, cfg.hidden)
                                 for l in range(L)])
         self.wd = torch.stack([to(w.down[l]) for l in range(L)])
@@ -131,10 +165,17 @@ class TPDecodeEngine:
         self._build_programs()
 
     def weight_bytes(self) -> int:
-        ts = [self.lm_head, self.norm_w, self.ln1, self.ln2, self.wqkv, self.wo, self.wgu, self.wd]
+        ts = [self.lm_head, self.norm_w, self.ln1, self.ln2, self.wqkv, self.wo]
         if self.qknorm is not None:
             ts.append(self.qknorm)
-        return sum(t.numel() * t.element_size() for t in ts) + self.cfg.hidden * 2
+        n = sum(t.numel() * t.element_size() for t in ts) + self.cfg.hidden * 2
+        if self.cfg.n_experts:
+            # a token reads the router and, on average over a uniform router, top_k / world of this rank's experts
+            n += self.router.numel() * 2
+            n += (self.wgu.numel() + self.wd.numel()) * 2 * self.cfg.top_k // self.cfg.n_experts
+        else:
+            n += sum(t.numel() * t.element_size() for t in (self.wgu, self.wd))
+        return n
 
     def algorithmic_bytes(self, pos: int) -> int:
         """Per-GPU HBM bytes of one step: this rank's weights once, one embedding
@@ -208,6 +249,9 @@ class TPDecodeEngine:
                        x=Src(ao, K * 2, wait=b_merge), out=Dst(part + r0 * 4, n * 4, "store"),
                        mode=isa.GEMV_MODE_STORE_F32)
             self._finish(P)
+            if cfg.n_experts:
+                self._build_moe_half(l, load)
+                continue
             # ---- MLP half: gate/up over the local FFN rows -> down over the local columns
             P = Program(S)
             b_gu = P.new_barrier()
@@ -243,6 +287,56 @@ class TPDecodeEngine:
         P = Program(1)
         P.argmax_final(0, records=Src(self.best_all.data_ptr(), self.world * 16), n=self.world, state_addr=st,
                        log_addr=self.token_log.data_ptr())
+        self._finish(P)
+
+    def _build_moe_half(self, l: int, load):
+        """Router and selection on the replicated hidden state, then the selected experts this
+        rank owns: gate/up with fused norm and SiLU-mul, down projections added (times the
+        routing weight) into the fp32 partial sum, which the host zeroes before the launch."""
+        cfg = self.cfg
+        H, F, E, TK, S = cfg.hidden, cfg.ffn, cfg.n_experts, cfg.top_k, self.num_sms
+        hid, part = self.hidden.data_ptr(), self.partial.data_ptr()
+        ids = self.route.data_ptr()
+        wts, lid, cnt = ids + 64, ids + 128, ids + 192
+        P = Program(S)
+        b_rl, b_route, b_gu = P.new_barrier(), P.new_barrier(), P.new_barrier()
+        R = rows_per_chunk(H)
+        for sm, u0, n_u in self._ranges(load, E // R, R * H * 2):
+            r0, n = u0 * R, n_u * R
+            P.gemv(sm, w_addr=self.router[l].data_ptr() + r0 * H * 2, n_rows=n, K=H, R=R, x=Src(hid, H * 2),
+                   out=Dst(self.router_logits.data_ptr() + r0 * 4, n * 4, "store", release=b_rl),
+                   mode=isa.GEMV_MODE_STORE_F32, norm_w=Src(self.ln2[l].data_ptr(), H * 2), eps=cfg.eps)
+        sm = min(range(S), key=lambda i: (load[i], i))
+        P.moe_route(sm, logits=Src(self.router_logits.data_ptr(), E * 4, wait=b_rl), route_addr=ids, n_experts=E,
+                    top_k=TK, release=b_route, rank=self.rank, world=self.world)
+        # units are (slot, chunk), contiguous per SM, split at slot borders
+        R = rows_per_chunk(H, even=True)
+        per = 2 * F // R
+        for sm, u0, n_u in self._ranges(load, TK * per, R * H * 2 // max(1, self.world)):
+            u, end = u0, u0 + n_u
+            while u < end:
+                slot, c0 = divmod(u, per)
+                n_c = min(end - u, per - c0)
+                r0, n = c0 * R, n_c * R
+                P.gemv(sm, w_addr=self.wgu[l].data_ptr() + r0 * H * 2, n_rows=n, K=H, R=R, x=Src(hid, H * 2),
+                       out=Dst(self.act[slot].data_ptr() + (r0 // 2) * 2, n, "store", release=b_gu),
+                       mode=isa.GEMV_MODE_SILU_PAIRS, norm_w=Src(self.ln2[l].data_ptr(), H * 2), eps=cfg.eps,
+                       w_indirect=(lid + 4 * slot, 2 * F * H * 2), wait_issue=b_route, dyn_count_addr=cnt + 4 * slot)
+                u += n_c
+        R = rows_per_chunk(F)
+        per = H // R
+        for sm, u0, n_u in self._ranges(load, TK * per, R * F * 2 // max(1, self.world)):
+            u, end = u0, u0 + n_u
+            while u < end:
+                slot, c0 = divmod(u, per)
+                n_c = min(end - u, per - c0)
+                r0, n = c0 * R, n_c * R
+                P.gemv(sm, w_addr=self.wd[l].data_ptr() + r0 * F * 2, n_rows=n, K=F, R=R,
+                       x=Src(self.act[slot].data_ptr(), F * 2, wait=b_gu), out=Dst(part + r0 * 4, n * 4, "store"),
+                       mode=isa.GEMV_MODE_MOE_DOWN, w_indirect=(lid + 4 * slot, H * F * 2), wait_issue=b_route,
+                       dyn_count_addr=cnt + 4 * slot,
+                       moe=dict(weight_addr=wts + 4 * slot, acc_addr=0, cnt_addr=0, top_k=TK))
+                u += n_c
         self._finish(P)
 
     # ------------------------------------------------------------------ state / cache
@@ -288,6 +382,8 @@ class TPDecodeEngine:
         for l in range(L):
             self._launch(2 * l)
             self._all_reduce_add()
+            if self.cfg.n_experts:
+                self.partial.zero_()         # the experts' down projections add into it
             self._launch(2 * l + 1)
             self._all_reduce_add()
         self._launch(2 * L)
@@ -339,8 +435,14 @@ class TPDecodeEngine:
         self.lm_head = full.lm_head[r * self.V:(r + 1) * self.V].contiguous()
         self.wqkv = full.wqkv[:, r * rows:(r + 1) * rows].contiguous()
         self.wo = full.wo[:, :, r * self.qw:(r + 1) * self.qw].contiguous()
-        self.wgu = full.wgu[:, r * 2 * self.F:(r + 1) * 2 * self.F].contiguous()
-        self.wd = full.wd[:, :, r * self.F:(r + 1) * self.F].contiguous()
+        if cfg.n_experts:
+            e0 = r * self.E_local
+            self.wgu = full.wgu[:, e0:e0 + self.E_local].contiguous()
+            self.wd = full.wd[:, e0:e0 + self.E_local].contiguous()
+            self.router = full.router
+        else:
+            self.wgu = full.wgu[:, r * 2 * self.F:(r + 1) * 2 * self.F].contiguous()
+            self.wd = full.wd[:, :, r * self.F:(r + 1) * self.F].contiguous()
         self.qknorm = full.qknorm
         ks, vs = [], []
         for l in range(cfg.n_layers):
