@@ -200,7 +200,8 @@ def run_gpu(args):
         dbg('shard loaded')
         del full
         torch.cuda.empty_cache()
-        tokens_per_step, scaling, parallelism = 1, "strong", f"tp{world}"
+        tokens_per_step, scaling = 1, "strong"
+        parallelism = f"tp{world}" if not cfg.n_experts else f"attention tp{world}, experts ep{world}"
     stream = torch.cuda.current_stream()
 
     def barrier():
