@@ -92,6 +92,16 @@ def test_shard_shapes():
         assert torch.equal(torch.cat([p.down[2] for p in parts], 1), w.layers[2].down.w)
         assert torch.equal(torch.cat([p.lm_head for p in parts], 0), w.lm_head)
         assert parts[0].gate[0].shape == (cfg.ffn // world, cfg.hidden)
+    # more ranks than KV heads: the KV head is replicated, its query heads are shared out
+    from vdcores_b200.tp import kv_layout
+    cfg = small_cfg("moe")          # 8 query heads on 1 KV head
+    w = O.ModelWeights.random(cfg, seed=2)
+    ecfg = engine_config(cfg)
+    parts = [shard_dense_weights(ecfg, dense_weights(w), r, 2) for r in range(2)]
+    assert [kv_layout(ecfg, r, 2) for r in range(2)] == [(0, 1, 4), (0, 1, 4)]
+    assert torch.equal(parts[0].wk[0], w.layers[0].wk.w) and torch.equal(parts[1].wv[1], w.layers[1].wv.w)
+    assert torch.equal(torch.cat([p.wq[0] for p in parts], 0), w.layers[0].wq.w)
+    assert len(parts[1].gate[0]) == cfg.n_experts // 2
 
 
 def _ep_rank(rank, world, port, q):

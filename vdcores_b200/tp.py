@@ -38,11 +38,30 @@ def shard_cols(t: torch.Tensor, rank: int, world: int) -> torch.Tensor:
     return t[:, rank * n:(rank + 1) * n].contiguous()
 
 
+def kv_layout(cfg: DecodeConfig, rank: int, world: int):
+    """(first KV head, KV heads, query heads per KV head) of a rank.  With more ranks than KV
+    heads a KV head is replicated over world / n_kv_heads consecutive ranks, each of which
+    takes a share of its query heads."""
+    if cfg.n_kv_heads % world == 0:
+        nkv = cfg.n_kv_heads // world
+        return rank * nkv, nkv, cfg.group
+    assert world % cfg.n_kv_heads == 0, "ranks must divide, or be a multiple of, the KV heads"
+    rep = world // cfg.n_kv_heads
+    assert cfg.group % rep == 0 and cfg.group // rep in (4, 8), "query heads per KV head and rank must be 4 or 8"
+    return rank // rep, 1, cfg.group // rep
+
+
+def shard_kv_rows(cfg: DecodeConfig, t: torch.Tensor, rank: int, world: int) -> torch.Tensor:
+    h0, nkv, _ = kv_layout(cfg, rank, world)
+    d = cfg.head_dim
+    return t[h0 * d:(h0 + nkv) * d].contiguous()
+
+
 def shard_dense_weights(cfg: DecodeConfig, w: DenseWeights, rank: int, world: int) -> DenseWeights:
     """The rank's shard in the usual [out, in] layout: q/k/v by heads, gate/up by
     FFN rows, o/down by input columns, lm_head by vocabulary rows; embedding and
     norms replicated."""
-    assert cfg.n_kv_heads % world == 0 and cfg.ffn % world == 0 and cfg.vocab % world == 0
+    assert cfg.n_heads % world == 0 and cfg.ffn % world == 0 and cfg.vocab % world == 0
     L = cfg.n_layers
     if cfg.n_experts:
         assert cfg.n_experts % world == 0
@@ -50,8 +69,8 @@ def shard_dense_weights(cfg: DecodeConfig, w: DenseWeights, rank: int, world: in
         return DenseWeights(
             embed=w.embed, lm_head=shard_rows(w.lm_head, rank, world), norm=w.norm, ln1=w.ln1, ln2=w.ln2,
             wq=[shard_rows(w.wq[l], rank, world) for l in range(L)],
-            wk=[shard_rows(w.wk[l], rank, world) for l in range(L)],
-            wv=[shard_rows(w.wv[l], rank, world) for l in range(L)],
+            wk=[shard_kv_rows(cfg, w.wk[l], rank, world) for l in range(L)],
+            wv=[shard_kv_rows(cfg, w.wv[l], rank, world) for l in range(L)],
             wo=[shard_cols(w.wo[l], rank, world) for l in range(L)],
             gate=[w.gate[l][e0:e1] for l in range(L)], up=[w.up[l][e0:e1] for l in range(L)],
             down=[w.down[l][e0:e1] for l in range(L)], router=w.router,
@@ -59,8 +78,8 @@ def shard_dense_weights(cfg: DecodeConfig, w: DenseWeights, rank: int, world: in
     return DenseWeights(
         embed=w.embed, lm_head=shard_rows(w.lm_head, rank, world), norm=w.norm, ln1=w.ln1, ln2=w.ln2,
         wq=[shard_rows(w.wq[l], rank, world) for l in range(L)],
-        wk=[shard_rows(w.wk[l], rank, world) for l in range(L)],
-        wv=[shard_rows(w.wv[l], rank, world) for l in range(L)],
+        wk=[shard_kv_rows(cfg, w.wk[l], rank, world) for l in range(L)],
+        wv=[shard_kv_rows(cfg, w.wv[l], rank, world) for l in range(L)],
         wo=[shard_cols(w.wo[l], rank, world) for l in range(L)],
         gate=[shard_rows(w.gate[l], rank, world) for l in range(L)],
         up=[shard_rows(w.up[l], rank, world) for l in range(L)],
@@ -71,7 +90,7 @@ def shard_dense_weights(cfg: DecodeConfig, w: DenseWeights, rank: int, world: in
 class TPDecodeEngine:
     def __init__(self, cfg: DecodeConfig, max_seq: int, rank: int, world: int, device, group=None,
                  max_steps: int = 4096, timeout_ns: int = 0, use_graph: bool = True):
-        assert cfg.n_kv_heads % world == 0 and cfg.ffn % world == 0 and cfg.vocab % world == 0
+        assert cfg.n_heads % world == 0 and cfg.ffn % world == 0 and cfg.vocab % world == 0
         self.cfg, self.rank, self.world, self.group = cfg, rank, world, group
         self.dev = torch.device(device)
         self.max_seq = max_seq
@@ -80,9 +99,13 @@ class TPDecodeEngine:
         self.num_sms = torch.cuda.get_device_properties(self.dev).multi_processor_count
         self.stream = torch.cuda.current_stream(self.dev)
         runtime.init()
-        D, G = isa.HEAD_DIM, cfg.group
-        self.nkv = cfg.n_kv_heads // world
+        D = isa.HEAD_DIM
+        # this rank's KV heads and the query heads it serves per KV head (a KV head is replicated
+        # when there are more ranks than KV heads)
+        self.kv0, self.nkv, self.G = kv_layout(cfg, rank, world)
+        G = self.G
         self.nq = cfg.n_heads // world
+        assert self.nq == self.nkv * G
         self.F = cfg.ffn // world
         self.V = cfg.vocab // world
         self.qw, self.kvw = self.nq * D, self.nkv * D
@@ -132,7 +155,7 @@ class TPDecodeEngine:
     def load_shard(self, w: DenseWeights):
         """Takes this rank's shard (see shard_dense_weights) and builds the programs."""
         cfg, dev = self.cfg, self.dev
-        L, G, D = cfg.n_layers, cfg.group, isa.HEAD_DIM
+        L, G, D = cfg.n_layers, self.G, isa.HEAD_DIM
         to = lambda t: t.to(device=dev, dtype=BF16).contiguous()
         self.embed = to(w.embed)
         self.lm_head = to(w.lm_head)
@@ -206,7 +229,7 @@ class TPDecodeEngine:
 
     def _build_programs(self):
         cfg = self.cfg
-        L, H, G, D, S = cfg.n_layers, cfg.hidden, cfg.group, isa.HEAD_DIM, self.num_sms
+        L, H, G, D, S = cfg.n_layers, cfg.hidden, self.G, isa.HEAD_DIM, self.num_sms
         st = self.state.data_ptr()
         page_bytes = isa.KV_PAGE * D * 2
         page_shift = int(math.log2(self.nkv * page_bytes))
@@ -354,7 +377,7 @@ class TPDecodeEngine:
 
     def load_kv(self, k: List[torch.Tensor], v: List[torch.Tensor]):
         """Per-layer contiguous caches [T, n_kv_heads (all), 128]: keeps this rank's heads."""
-        h0 = self.rank * self.nkv
+        h0 = self.kv0
         for l in range(self.cfg.n_layers):
             for src, pool in ((k[l], self.kpool[l]), (v[l], self.vpool[l])):
                 T = src.shape[0]
@@ -430,10 +453,19 @@ class TPDecodeEngine:
         """Takes this rank's shard out of a single-GPU engine that holds the whole
         model (packed layout) and its KV cache for `cached_positions` positions."""
         r, cfg = self.rank, self.cfg
-        rows = self.qw + 2 * self.kvw
+        D = isa.HEAD_DIM
         self.embed, self.norm_w, self.ln1, self.ln2 = full.embed, full.norm_w, full.ln1, full.ln2
         self.lm_head = full.lm_head[r * self.V:(r + 1) * self.V].contiguous()
-        self.wqkv = full.wqkv[:, r * rows:(r + 1) * rows].contiguous()
+        # the full engine stores [group's query heads | key | value] per KV head; this rank keeps, for each
+        # of its KV heads, its share of the query heads and the key / value rows
+        grp_rows = (cfg.group + 2) * D
+        q_share = (r % max(1, self.world // cfg.n_kv_heads)) * self.G * D if self.world > cfg.n_kv_heads else 0
+        idx = []
+        for h in range(self.kv0, self.kv0 + self.nkv):
+            base = h * grp_rows
+            idx += list(range(base + q_share, base + q_share + self.G * D))
+            idx += list(range(base + cfg.group * D, base + (cfg.group + 2) * D))
+        self.wqkv = full.wqkv[:, torch.tensor(idx, dtype=torch.long, device=full.wqkv.device)].contiguous()
         self.wo = full.wo[:, :, r * self.qw:(r + 1) * self.qw].contiguous()
         if cfg.n_experts:
             e0 = r * self.E_local
