@@ -20,15 +20,18 @@ def _bpad(B):
     return next(p for p in (16, 32, 64, 128) if B <= p)
 
 
-def _gemm_program(dev, x, w, n_sms, mode, out, norm_w=None, eps=1e-5, ld=0, keys=None, stats=None):
-    from vdcores_b200.batch import BLOCK_ROWS, emit_projection, pack_blocks, pack_kc, projection_blocks
+def _gemm_program(dev, x, w, n_sms, mode, out, norm_w=None, eps=1e-5, ld=0, keys=None, stats=None, scales=None):
+    """w: bf16 weights, or (with scales) uint8 e4m3 codes and their fp32 per-row scales."""
+    from vdcores_b200.batch import (BLOCK_ROWS, emit_projection, pack_blocks, pack_blocks_fp8, pack_kc,
+                                    projection_blocks)
     from vdcores_b200.program import Program
     B, K = x.shape
     Bp = _bpad(B)
     xp = torch.zeros(Bp, K, dtype=BF16)
     xp[:B] = x
     xd = pack_kc(xp.to(dev))
-    wd = pack_blocks(w.to(dev))
+    wd = pack_blocks_fp8(w.to(dev)) if scales is not None else pack_blocks(w.to(dev))
+    sd = scales.to(dev) if scales is not None else None
     nwd = norm_w.to(dev) if norm_w is not None else None
     if norm_w is not None:      # the producers of a normed input leave its per-row sums of squares
         stats = torch.zeros(128, dtype=torch.float32)
@@ -43,7 +46,8 @@ def _gemm_program(dev, x, w, n_sms, mode, out, norm_w=None, eps=1e-5, ld=0, keys
                             scratch_addr=scr.data_ptr(), counter_addr=cnt.data_ptr(),
                             norm_addr=nwd.data_ptr() if nwd is not None else None, eps=eps, ld=ld,
                             keys_addr=keys.data_ptr() if keys is not None else 0,
-                            stats_addr=stats.data_ptr() if stats is not None else 0)
+                            stats_addr=stats.data_ptr() if stats is not None else 0,
+                            wfmt="fp8" if sd is not None else "bf16", scales_addr=sd.data_ptr() if sd is not None else 0)
     run_program(P, dev)
     assert float(scr.abs().max()) == 0.0 and int(cnt.abs().max()) == 0, "scratch and counters are left clear"
     return units
@@ -63,6 +67,24 @@ def test_gemm_tc_store_rows(cuda_device, B, K, M, n_sms, norm):
         assert len(units) > len({u[1] for u in units}), "some block's K is shared by several units"
     xin = O.rms_norm(x, nw, 1e-5) if norm else x
     ref = O.linear(xin, w)
+    assert O.rel_l2(y.cpu(), ref) < 4e-3
+
+
+@pytest.mark.parametrize("B,K,M,n_sms,norm", [(7, 512, 256, 1, False), (16, 4096, 640, 5, True), (40, 1024, 96, 2, False)])
+def test_gemm_tc_fp8_weights(cuda_device, B, K, M, n_sms, norm):
+    """e4m3 weights with per-row scales: converted to bf16 in shared memory, scaled in the epilogue;
+    compared with the oracle's linear layer over the same codes."""
+    from vdcores_b200 import isa
+    from vdcores_b200.decode import quantize_fp8_rows
+    dev = cuda_device
+    x, w = seeded((B, K), 41), seeded((M, K), 42, 0.05)
+    codes, scales = quantize_fp8_rows(w)
+    nw = (1 + 0.1 * torch.randn(K, generator=torch.Generator().manual_seed(43))).to(BF16) if norm else None
+    y = torch.zeros(B, M, dtype=BF16, device=dev)
+    _gemm_program(dev, x, codes, n_sms, isa.GEMM_MODE_STORE_ROWS, y, norm_w=nw, ld=M, scales=scales)
+    wq = (codes.view(torch.float8_e4m3fn).float() * scales[:, None])
+    xin = O.rms_norm(x, nw, 1e-5) if norm else x
+    ref = (xin.float() @ wq.t()).to(BF16)
     assert O.rel_l2(y.cpu(), ref) < 4e-3
 
 
@@ -186,3 +208,55 @@ def test_batch_prefill_and_host_steps(cuda_device):
             if gap > GAP:
                 assert got[b] == ref_next
             toks[b] = ref_next
+
+
+def test_batch_decode_fp8_matches_oracle(cuda_device):
+    """Batched decode with e4m3 layer projections against one oracle per sequence that dequantises
+    the same codes: per-layer hidden states within rel-L2 3e-2."""
+    import copy
+    import dataclasses
+    from vdcores_b200.batch import BatchDecodeEngine
+    cfg_b = small_cfg("llama")
+    w_b = perturb_norms(O.ModelWeights.random(cfg_b, seed=6))
+    cfg = dataclasses.replace(cfg_b, wkind="fp8")
+    w = copy.copy(w_b)
+    w.cfg = cfg
+    w.layers = []
+    for lw in w_b.layers:
+        ql = copy.copy(lw)
+        for name in ("wq", "wk", "wv", "wo", "gate", "up", "down"):
+            setattr(ql, name, O.QLinear.make(getattr(lw, name).w, "fp8"))
+        w.layers.append(ql)
+    batch = 5
+    g = torch.Generator().manual_seed(33)
+    lens = [int(v) for v in torch.randint(2, 60, (batch,), generator=g)]
+    prompts = [torch.randint(0, cfg.vocab, (n,), generator=g) for n in lens]
+    eng = BatchDecodeEngine(engine_config(cfg), batch, max_seq=128, device=cuda_device, taps=True, wkind="fp8",
+                            timeout_ns=500_000_000)
+    eng.load_weights(dense_weights(w_b))       # the engine quantises the same bf16 weights with the same rule
+    orcs, toks = [], []
+    for b in range(batch):
+        orc = O.DecodeOracle(w, 128)
+        orc.prefill(prompts[b][:-1].tolist())
+        n = lens[b] - 1
+        eng.load_kv([k[:n] for k in orc.k], [v[:n] for v in orc.v], b=b)
+        eng.set_state(n, int(prompts[b][-1]), b=b)
+        orcs.append(orc)
+        toks.append(int(prompts[b][-1]))
+    for step in range(3):
+        got = eng.generate(1)[0]
+        taps = [eng.read_hidden(eng.taps[l]).cpu() for l in range(cfg.n_layers)]
+        fix = {}
+        for b in range(batch):
+            caps = []
+            _, nxt_ref, gap = orcs[b].step(toks[b], caps)
+            for l in range(cfg.n_layers):
+                r = O.rel_l2(taps[l][b], caps[l]["hidden_state_out"])
+                assert r < 3e-2, f"step {step} sequence {b} layer {l}: rel-L2 {r:.3e}"
+            if gap > GAP:
+                assert got[b] == nxt_ref
+            if got[b] != nxt_ref:
+                fix[b] = nxt_ref
+            toks[b] = nxt_ref
+        for b, t in fix.items():
+            eng.state[b, 2:3].copy_(torch.tensor([t], dtype=torch.int32))

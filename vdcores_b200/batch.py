@@ -55,6 +55,16 @@ def pack_blocks(w: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def pack_blocks_fp8(codes: torch.Tensor) -> torch.Tensor:
+    """[M, K] e4m3 bytes -> flat: per block of 256 rows the layout [K/16][N/8][8 rows][16 k],
+    which a 16-byte load turns into two adjacent bf16 pieces of the tensor-core operand layout."""
+    M, K = codes.shape
+    out = torch.empty(M * K, dtype=codes.dtype, device=codes.device)
+    for r0, n in projection_blocks(M):
+        out[r0 * K:(r0 + n) * K] = codes[r0:r0 + n].reshape(n // 8, 8, K // 16, 16).permute(2, 0, 1, 3).reshape(-1)
+    return out
+
+
 def chunk_geometry(N: int, Bpad: int, K: int):
     """(Kc, G): inputs per W chunk (N * Kc * 2 bytes <= 32 KB, Kc divides K) and W chunks per X chunk
     (the X chunk fills at most one 8 KB slot when it can)."""
@@ -88,12 +98,14 @@ def plan_units(blocks, steps: int, sms, load, step_bytes_per_row: int):
 
 
 def emit_projection(P: Program, *, sms, load, w_addr, M, K, x_addr, B, Bpad, mode, out_addr, scratch_addr,
-                    counter_addr, x_wait=None, release=None, norm_addr=None, eps=0.0, ld=0, keys_addr=0, stats_addr=0):
+                    counter_addr, x_wait=None, release=None, norm_addr=None, eps=0.0, ld=0, keys_addr=0, stats_addr=0,
+                    wfmt="bf16", scales_addr=0):
     """Emits every unit of the projection y[B, M] = x[B, K] W^T (W packed by pack_blocks at w_addr,
     x k-chunk-major at x_addr).  scratch_addr: fp32 [blocks][B][256]; counter_addr: int32 [blocks]."""
     blocks = projection_blocks(M)
     Kc, G = chunk_geometry(blocks[0][1], Bpad, K)
-    units = plan_units(blocks, K // Kc, sms, load, Kc * 2)
+    wbpe = 2 if wfmt == "bf16" else 1
+    units = plan_units(blocks, K // Kc, sms, load, Kc * wbpe)
     slices = [0] * len(blocks)
     for _, bi, _, _ in units:
         slices[bi] += 1
@@ -102,7 +114,8 @@ def emit_projection(P: Program, *, sms, load, w_addr, M, K, x_addr, B, Bpad, mod
     for sm, bi, c0, cnt in units:
         r0, N = blocks[bi]
         k0 = c0 * Kc
-        P.gemm_tc(sm, w_addr=w_addr + (r0 * K + k0 * N) * 2, N=N, K=K, k_len=cnt * Kc, Kc=Kc, G=G,
+        P.gemm_tc(sm, w_addr=w_addr + (r0 * K + k0 * N) * wbpe, N=N, K=K, k_len=cnt * Kc, Kc=Kc, G=G,
+                  wfmt=wfmt, scales_addr=scales_addr + 4 * r0 if scales_addr else 0,
                   x_addr=x_addr + k0 * Bpad * 2, B=B, Bpad=Bpad, out_addr=out_addr, mode=mode, x_wait=x_wait,
                   norm_w=Src(norm_addr + k0 * 2, cnt * Kc * 2) if norm_addr is not None else None, eps=eps, n0=r0,
                   ld=ld, keys_addr=keys_addr, stats_addr=stats_addr, release=release,
@@ -112,15 +125,16 @@ def emit_projection(P: Program, *, sms, load, w_addr, M, K, x_addr, B, Bpad, mod
 
 
 class BatchDecodeEngine(DecodeEngine):
-    """`batch` sequences decoded together, one kernel launch per step.  Dense bf16 models."""
+    """`batch` sequences decoded together, one kernel launch per step.  Dense models; the layer
+    projections are bf16 or e4m3 with per-row scales (wkind "fp8"), everything else bf16."""
 
     def __init__(self, cfg: DecodeConfig, batch: int, max_seq: int, device="cuda:0", num_sms=None, taps=False,
-                 page_perm_seed=None, max_steps: int = 256, timeout_ns: int = 2_000_000_000):
-        assert 1 <= batch <= 128 and not cfg.n_experts
+                 page_perm_seed=None, max_steps: int = 256, timeout_ns: int = 2_000_000_000, wkind: str = "bf16"):
+        assert 1 <= batch <= 128 and not cfg.n_experts and wkind in ("bf16", "fp8")
         self.batch = batch
         self.bpad = next(p for p in (16, 32, 64, 128) if batch <= p)
         super().__init__(cfg, max_seq, device=device, num_sms=num_sms, taps=False, page_perm_seed=None,
-                         max_steps=max_steps, timeout_ns=timeout_ns, wkind="bf16")
+                         max_steps=max_steps, timeout_ns=timeout_ns, wkind=wkind)
         B, Bp, L, H, F = batch, self.bpad, cfg.n_layers, cfg.hidden, cfg.ffn
         z = lambda *s, dt=BF16: torch.zeros(*s, dtype=dt, device=self.dev)
         self.hidden = z(Bp * H)                       # k-chunk-major [Bpad, H]
@@ -161,6 +175,7 @@ class BatchDecodeEngine(DecodeEngine):
     # ------------------------------------------------------------------ weights
     def weight_bytes(self) -> int:
         ts = [self.lm_head, self.norm_w, self.ln1, self.ln2, self.wqkv, self.wo, self.wgu, self.wd]
+        ts += list(self.scales.values())
         return sum(t.numel() * t.element_size() for t in ts)
 
     def algorithmic_bytes(self, pos: int) -> int:
@@ -189,7 +204,8 @@ class BatchDecodeEngine(DecodeEngine):
 
         def gemm_stage(w, name, K, x_addr, x_wait, mode, out_addr, release, norm=None, ld=0, keys=0, stats=0):
             M = w.shape[0]
-            pk = pack_blocks(w)
+            fp8 = name is not None and self.wkind == "fp8"      # the vocabulary projection stays bf16
+            pk = pack_blocks_fp8(w) if fp8 else pack_blocks(w)
             if name is not None:
                 packed[name].append(pk)
             kind = name or "lm"
@@ -202,7 +218,8 @@ class BatchDecodeEngine(DecodeEngine):
             emit_projection(P, sms=sms, load=load, w_addr=pk.data_ptr(), M=M, K=K, x_addr=x_addr, B=B, Bpad=Bp,
                             mode=mode, out_addr=out_addr, scratch_addr=scr.data_ptr(), counter_addr=cnt.data_ptr(),
                             x_wait=x_wait, release=release, norm_addr=norm.data_ptr() if norm is not None else None,
-                            eps=cfg.eps, ld=ld, keys_addr=keys, stats_addr=stats)
+                            eps=cfg.eps, ld=ld, keys_addr=keys, stats_addr=stats, wfmt="fp8" if fp8 else "bf16",
+                            scales_addr=self.scales[name][len(packed[name]) - 1].data_ptr() if fp8 else 0)
             return pk
 
         def tap(l, wait, release):

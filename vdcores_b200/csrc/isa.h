@@ -140,10 +140,10 @@
 // a projection unit (N rows, N a multiple of 16, at most 256) are stored the same way, [K/8][N/8][8 rows].
 // A K-range of either is one contiguous piece of memory, loaded with one 1-D bulk copy.
 //
-// GEMM_TC_BF16 (ten words): D[b, n] = sum_k X[b, k] W[n, k] on the tcgen05 tensor cores for one unit =
+// GEMM_TC_BF16 (eleven words): D[b, n] = sum_k X[b, k] W[n, k] on the tcgen05 tensor cores for one unit =
 // a block of N weight rows times a K-range; the batch sits on the accumulator's 128 lanes, the rows on
 // its columns (fp32, in tensor memory).
-//   word 0: [W chunks, N/16 | mode << 8 | norm << 12, k-steps of 16 per W chunk | W chunks per X chunk << 8]
+//   word 0: [W chunks, N/16 | mode << 8 | norm << 12 | e4m3 << 13, k-steps of 16 per W chunk | W chunks per X chunk << 8]
 //   word 1: [norm eps hi, lo, batch]      word 2: 48-bit output address
 //   word 3: 48-bit address of the argmax keys (u64 per sequence; ARGMAX mode)
 //   word 4: [first output row low 16 bits, high bits, barrier to release (0xFFFF: none)]
@@ -152,6 +152,10 @@
 //           of its input left them there), accumulated by an ADD_PACKED epilogue over the rows it updated
 //   word 7, 8: 48-bit addresses of the block's fp32 scratch sums [batch][N] and of its arrival counter
 //   word 9: [units the block's K is cut into, 0, 0]
+//   word 10: 48-bit address of the block's fp32 per-row scales (e4m3 weights), else 0
+// e4m3 weights (one byte each, chunk layout [Kc/16][N/8][8 rows][16 k]) are converted, exactly, to bf16
+// in shared memory by the seven non-issuing warps into two staging buffers (allocate-only entries popped
+// before the groups); the accumulator sums over the codes and the epilogue applies the row scale.
 // Pops [norm weights of the K-range], then per group one X chunk and its W chunks.  With norm the X
 // chunks become bf16(w * bf16(x * rsqrt(sum/K + eps))) in shared memory before the tensor cores read
 // them.  With several units per block each adds its partial sums to the scratch area; the unit that

@@ -168,14 +168,14 @@ __device__ void compute_core(const Ctx& c, const VdcCInst* __restrict__ insts, i
           asm volatile("prefetch.global.L2 [%0];" ::"l"(base + off));
         break;
       }
-      case 0x7300: {  // GEMM_TC_BF16 (ten words)
+      case 0x7300: {  // GEMM_TC_BF16 (eleven words)
         auto addr48 = [](const VdcCInst& w) {
           return (uint64_t)w.args[0] | ((uint64_t)w.args[1] << 16) | ((uint64_t)w.args[2] << 32);
         };
-        VdcCInst e[8];
+        VdcCInst e[9];
 #pragma unroll
-        for (int k = 0; k < 8; ++k) *reinterpret_cast<uint2*>(&e[k]) = ld_word(q.pc + (uint32_t)k);
-        q.pc += 8;
+        for (int k = 0; k < 9; ++k) *reinterpret_cast<uint2*>(&e[k]) = ld_word(q.pc + (uint32_t)k);
+        q.pc += 9;
         GemmTc g;
         g.n_w = ci.args[0];
         g.N = (ci.args[1] & 0xFF) * 16;
@@ -196,10 +196,13 @@ __device__ void compute_core(const Ctx& c, const VdcCInst* __restrict__ insts, i
         g.scratch = reinterpret_cast<float*>(addr48(e[5]));
         g.counter = reinterpret_cast<int*>(addr48(e[6]));
         g.n_slices = e[7].args[0];
+        g.wfmt = (ci.args[1] >> 13) & 1;
+        g.scales = reinterpret_cast<const float*>(addr48(e[8]));
         const bool ok = g.N >= 16 && g.N <= 256 && g.B >= 1 && g.B <= g.Bpad &&
                         (g.Bpad == 16 || g.Bpad == 32 || g.Bpad == 64 || g.Bpad == 128) && g.KS >= 1 && g.G >= 1 &&
                         g.n_w >= 1 && (!g.norm || g.stats != nullptr) &&
-                        (g.n_slices <= 1 || (g.scratch != nullptr && g.counter != nullptr));
+                        (g.n_slices <= 1 || (g.scratch != nullptr && g.counter != nullptr)) &&
+                        (g.wfmt == 0 || g.scales != nullptr);
         if (!ok) {
           raise_abort(c, VDC_ERR_BAD_OPCODE, 0, (int)q.pc, ci.opcode, -1, g.N);
           q.aborted = true;

@@ -178,6 +178,7 @@ struct __align__(16) Shared {
   uint64_t mma_bar[4];                      // completion of the tensor-core work of chunk i % 4
   uint64_t mma_final;                       // used once, before the tensor memory is given back
   uint64_t x_ready[16];                     // normalised X chunk i % 16 may be read by the tensor cores
+  uint64_t w_ready[16];                     // converted W chunk i % 16 (e4m3 weights) may be read by them
 };
 
 struct Ctx {

@@ -21,6 +21,7 @@ struct Compute {
   uint64_t stall;    // cycles thread 0 spent waiting for data
   unsigned mma_count;  // tensor-core commits issued so far (thread 0)
   unsigned xr_count;   // X chunks normalised by earlier tensor-core tasks (phase of the x_ready barriers)
+  unsigned wr_count;   // W chunks converted by earlier tensor-core tasks (phase of the w_ready barriers)
 
   // CTA-wide pop: thread 0 waits for the entry (bounded), everybody gets its
   // word after one compute_sync.  Returns kPopAbort once a wait was given up.

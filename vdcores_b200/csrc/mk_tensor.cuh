@@ -107,7 +107,11 @@ struct GemmTc {
   float* scratch;  // [B][N] fp32 partial sums of this block (n_slices > 1)
   int* counter;    // arrivals of this block's units
   int n_slices;
+  int wfmt;             // 0: bf16 weights, 1: e4m3 weights (converted to bf16 in shared memory)
+  const float* scales;  // e4m3: fp32 per-row scales of the block, applied in the epilogue
 };
+
+constexpr int kStages = 2;  // bf16 staging buffers of the e4m3 path
 
 struct EpiAcc {
   float ssq;   // ADD_PACKED: squares of the new values
@@ -116,7 +120,16 @@ struct EpiAcc {
 };
 
 // Epilogue of 16 consecutive output rows (row .. row+15) of sequence b.
-__device__ __forceinline__ void gemm_epilogue16(const GemmTc& g, int b, int row, const float (&v)[16], EpiAcc& acc) {
+__device__ __forceinline__ void gemm_epilogue16(const GemmTc& g, int b, int row, float (&v)[16], EpiAcc& acc) {
+  if (g.scales != nullptr) {
+    // e4m3 weights: the accumulator holds sums over the codes; one fp32 scale per output row
+    const float4* sc = reinterpret_cast<const float4*>(g.scales + (row - g.n0));
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float4 t = __ldg(sc + j);
+      v[4 * j] *= t.x; v[4 * j + 1] *= t.y; v[4 * j + 2] *= t.z; v[4 * j + 3] *= t.w;
+    }
+  }
   if (g.mode == VDC_GEMM_MODE_STORE_ROWS) {
     uint4* dst = reinterpret_cast<uint4*>(g.out + ((size_t)b * g.ld + row) * 2);
     dst[0] = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
@@ -185,7 +198,8 @@ __device__ void task_gemm_tc(Compute& q, const GemmTc& g) {
     if (q.tid >= 32 && q.tid < 36) mbar_init(&sh->mma_bar[q.tid - 32], 1);
     if (q.tid == 36) mbar_init(&sh->mma_final, 1);
     if (q.tid >= 64 && q.tid < 80) mbar_init(&sh->x_ready[q.tid - 64], 1);
-    if (q.tid >= 32 && q.tid < 80) asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    if (q.tid >= 96 && q.tid < 112) mbar_init(&sh->w_ready[q.tid - 96], 1);
+    if (q.tid >= 32 && q.tid < 112) asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     tc_fence_before();
     compute_sync();
     tc_fence_after();
@@ -193,7 +207,13 @@ __device__ void task_gemm_tc(Compute& q, const GemmTc& g) {
   }
   int normw_mask = 0;
   if (g.norm) normw_mask = q.pop();
+  int stage_mask[kStages] = {0, 0};
+  if (g.wfmt == 1) {
+#pragma unroll
+    for (int st = 0; st < kStages; ++st) stage_mask[st] = q.pop();  // allocate-only entries: bf16 staging buffers
+  }
   if (q.aborted) return;
+  const unsigned mma_base = q.mma_count;  // commits issued before this task (uniform across the CTA)
   const uint8_t* nw = g.norm ? (const uint8_t*)slot_ptr(c, first_slot(normw_mask)) : nullptr;
   const uint32_t tmem = sh->tmem_base;
   const uint32_t idesc = umma_idesc_bf16_m128(g.N);
@@ -209,46 +229,91 @@ __device__ void task_gemm_tc(Compute& q, const GemmTc& g) {
   // run ahead of it, normalising the X chunks in place and signalling each chunk's barrier.
   TCS(0);
   q.warp_phase_begin(n_ent, q.warp == 0 ? 0u : n_ent);
-  if (q.warp > 0 && g.norm) {
-    // The seven warps normalise one X chunk after the other, together (224 threads).
+  if (q.warp > 0 && (g.norm || g.wfmt == 1)) {
+    // The seven warps work as a team of 224 threads, ahead of the issuer: they normalise each X
+    // chunk in place and, for e4m3 weights, convert each W chunk into a bf16 staging buffer.
+    // One warp does the (bounded) waiting and tells the team, so that all leave together on an abort.
     constexpr int kTeam = (kCW - 1) * 32;
     const int t = q.tid - 32;
     float* rs = sh->red;  // per-sequence rsqrt(mean x^2 + eps)
-    int* xm_shared = reinterpret_cast<int*>(sh->misc) + 36;
-    for (int grp = 0; grp < n_x; ++grp) {
-      // one warp waits for the chunk (bounded) and tells the team, so that all leave together on an abort
-      if (q.warp == 1) {
-        const int m = q.warp_wait(x_entry(grp));
-        if (q.lane == 0) xm_shared[grp & 1] = m;
-      }
-      asm volatile("bar.sync 6, %0;" ::"n"(kTeam) : "memory");
-      const int xm = xm_shared[grp & 1];
-      if (xm == kPopAbort) break;
-      if (grp == 0) {
-        // Any X chunk of this task was loaded after the producers of the input matrix had
-        // finished, and with them the sums of squares they left (read past L1).
-        if (t < g.Bpad) rs[t] = rsqrtf(__ldcg(g.stats + t) / (float)g.Kfull + g.eps);
+    int* told = reinterpret_cast<int*>(sh->misc) + 36;
+    bool stop = false;
+    for (int j = 0; j < g.n_w && !stop; ++j) {
+      const int grp = j / g.G, jj = j % g.G;
+      if (g.norm && jj == 0) {
+        if (q.warp == 1) {
+          const int m = q.warp_wait(x_entry(grp));
+          if (q.lane == 0) told[0] = m;
+        }
         asm volatile("bar.sync 6, %0;" ::"n"(kTeam) : "memory");
-      }
-      uint8_t* xs = (uint8_t*)slot_ptr(c, first_slot(xm));
-      const int w_in_grp = min(g.G, g.n_w - grp * g.G);
-      const int pieces = w_in_grp * g.KS * 2 * g.Bpad;  // 16-byte pieces of this X chunk
-      const int kc0 = grp * g.G * g.KS * 2;             // the chunk's first 8-element k group within the unit
-      // RMSNorm in place, rounded like a bf16 tensor expression: bf16(w * bf16(x * rstd))
-      for (int p = t; p < pieces; p += kTeam) {
-        const uint4 v = lds128(xs + p * 16);
-        const uint4 w = lds128(nw + (kc0 + p / g.Bpad) * 16);
-        const float rstd = rs[p & (g.Bpad - 1)];
-        const uint32_t xv[4] = {v.x, v.y, v.z, v.w}, wv[4] = {w.x, w.y, w.z, w.w};
-        uint32_t o[4];
+        const int xm = told[0];
+        if (xm == kPopAbort) break;
+        if (grp == 0) {
+          // Any X chunk of this task was loaded after the producers of the input matrix had
+          // finished, and with them the sums of squares they left (read past L1).
+          if (t < g.Bpad) rs[t] = rsqrtf(__ldcg(g.stats + t) / (float)g.Kfull + g.eps);
+          asm volatile("bar.sync 6, %0;" ::"n"(kTeam) : "memory");
+        }
+        uint8_t* xs = (uint8_t*)slot_ptr(c, first_slot(xm));
+        const int w_in_grp = min(g.G, g.n_w - grp * g.G);
+        const int pieces = w_in_grp * g.KS * 2 * g.Bpad;  // 16-byte pieces of this X chunk
+        const int kc0 = grp * g.G * g.KS * 2;             // the chunk's first 8-element k group within the unit
+        // RMSNorm in place, rounded like a bf16 tensor expression: bf16(w * bf16(x * rstd))
+        for (int p = t; p < pieces; p += kTeam) {
+          const uint4 v = lds128(xs + p * 16);
+          const uint4 w = lds128(nw + (kc0 + p / g.Bpad) * 16);
+          const float rstd = rs[p & (g.Bpad - 1)];
+          const uint32_t xv[4] = {v.x, v.y, v.z, v.w}, wv[4] = {w.x, w.y, w.z, w.w};
+          uint32_t o[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
-          o[j] = pack_bf16x2(bf16_round(bf_lo(xv[j]) * rstd) * bf_lo(wv[j]), bf16_round(bf_hi(xv[j]) * rstd) * bf_hi(wv[j]));
-        *reinterpret_cast<uint4*>(xs + p * 16) = make_uint4(o[0], o[1], o[2], o[3]);
+          for (int i = 0; i < 4; ++i)
+            o[i] = pack_bf16x2(bf16_round(bf_lo(xv[i]) * rstd) * bf_lo(wv[i]), bf16_round(bf_hi(xv[i]) * rstd) * bf_hi(wv[i]));
+          *reinterpret_cast<uint4*>(xs + p * 16) = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+        fence_proxy_async_smem();  // the tensor cores read shared memory through the async proxy
+        asm volatile("bar.sync 6, %0;" ::"n"(kTeam) : "memory");
+        if (t == 0) mbar_arrive(&sh->x_ready[(q.xr_count + (unsigned)grp) & 15u]);
       }
-      fence_proxy_async_smem();  // the tensor cores read shared memory through the async proxy
-      asm volatile("bar.sync 6, %0;" ::"n"(kTeam) : "memory");
-      if (t == 0) mbar_arrive(&sh->x_ready[(q.xr_count + (unsigned)grp) & 15u]);
+      if (g.wfmt == 1) {
+        // W chunk j: [Kc/16][N/8][8 rows][16 k] e4m3 bytes -> staging buffer j % kStages as
+        // [Kc/8][N/8][8 rows][8 k] bf16 (exact), once the tensor cores are done with the
+        // buffer's previous occupant (chunk j - kStages)
+        if (q.warp == 1) {
+          int m = q.warp_wait(w_entry(j));
+          if (m != kPopAbort && j >= kStages) {
+            int ok = 1;
+            if (q.lane == 0) ok = mma_wait(q, mma_base + (unsigned)(j - kStages)) ? 1 : 0;
+            if (!__shfl_sync(0xffffffffu, ok, 0)) m = kPopAbort;
+          }
+          if (q.lane == 0) told[1] = m;
+        }
+        asm volatile("bar.sync 6, %0;" ::"n"(kTeam) : "memory");
+        const int wm = told[1];
+        if (wm == kPopAbort) break;
+        const uint8_t* src = (const uint8_t*)slot_ptr(c, first_slot(wm));
+        uint8_t* dst = (uint8_t*)slot_ptr(c, first_slot(stage_mask[j % kStages]));
+        const int pieces = g.KS * g.N;  // 16-byte pieces of the e4m3 chunk: (16-k group, row)
+        for (int p = t; p < pieces; p += kTeam) {
+          const uint4 v = lds128(src + p * 16);
+          const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
+          uint32_t o[8];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float2 lo = e4m3x2_to_float2(wv[i] & 0xFFFFu), hi = e4m3x2_to_float2(wv[i] >> 16);
+            o[2 * i] = pack_bf16x2(lo.x, lo.y);
+            o[2 * i + 1] = pack_bf16x2(hi.x, hi.y);
+          }
+          const int i16 = p / g.N, row = p - i16 * g.N;
+          *reinterpret_cast<uint4*>(dst + ((size_t)(2 * i16) * g.N + row) * 16) = make_uint4(o[0], o[1], o[2], o[3]);
+          *reinterpret_cast<uint4*>(dst + ((size_t)(2 * i16 + 1) * g.N + row) * 16) = make_uint4(o[4], o[5], o[6], o[7]);
+        }
+        fence_proxy_async_smem();
+        asm volatile("bar.sync 6, %0;" ::"n"(kTeam) : "memory");  // also: everybody has read told[] and the chunk
+        if (t == 0) {
+          atomicOr(&sh->slot_avail, (uint32_t)wm & kSlotMaskAll);  // the e4m3 chunk's slots are free already
+          mbar_arrive(&sh->w_ready[(q.wr_count + (unsigned)j) & 15u]);
+        }
+      }
     }
   }
   if (q.warp == 0) {
@@ -270,6 +335,20 @@ __device__ void task_gemm_tc(Compute& q, const GemmTc& g) {
       }
       const int wm = q.warp_wait(w_entry(j));
       if (wm == kPopAbort) break;
+      if (g.wfmt == 1) {
+        // the converted chunk, not the loaded one, is the operand
+        int ok = 1;
+        if (q.lane == 0) {
+          const unsigned gch = q.wr_count + (unsigned)j;
+          uint64_t* bar = &sh->w_ready[gch & 15u];
+          const uint32_t parity = (gch >> 4) & 1u;
+          if (!mbar_try_wait(bar, parity)) {
+            ok = wait_until(c, [&] { return mbar_try_wait(bar, parity); }, 0, (int)q.pc, 0x7300, -1, 0);
+            if (!ok) sh->aborted = 1;
+          }
+        }
+        if (!__shfl_sync(0xffffffffu, ok, 0)) break;
+      }
 #ifdef VDC_TC_PROFILE
       t_data += clock64() - td0;
       const long long tx0 = clock64();
@@ -294,7 +373,8 @@ __device__ void task_gemm_tc(Compute& q, const GemmTc& g) {
       if (q.lane == 0) {
         tc_fence_after();
         uint64_t adesc = umma_desc(smem_u32(slot_ptr(c, first_slot(xm))) + (uint32_t)(jj * g.KS) * 2u * lbo_a, lbo_a, 128u);
-        uint64_t bdesc = umma_desc(smem_u32(slot_ptr(c, first_slot(wm))), lbo_b, 128u);
+        const int b_slot = g.wfmt == 1 ? first_slot(stage_mask[j % kStages]) : first_slot(wm);
+        uint64_t bdesc = umma_desc(smem_u32(slot_ptr(c, b_slot)), lbo_b, 128u);
         const uint64_t step_a = (uint64_t)((2u * lbo_a) >> 4), step_b = (uint64_t)((2u * lbo_b) >> 4);
         umma_bf16(tmem, adesc, bdesc, idesc, (uint32_t)(j != 0));
 #pragma unroll 4
@@ -310,7 +390,7 @@ __device__ void task_gemm_tc(Compute& q, const GemmTc& g) {
 #endif
         // the previous chunk's reads are certainly done once its commit arrived
         if (j > 0) {
-          int done = w_prev | x_done;
+          int done = (g.wfmt == 1 ? 0 : w_prev) | x_done;  // e4m3 chunks were freed by the converting team
           if (!mma_wait(q, q.mma_count - 1)) done = 0;
           if (done) atomicOr(&sh->slot_avail, (uint32_t)done & kSlotMaskAll);
           sh->warp_next[0] = q.head + x_entry(grp);  // ring entries before this group may be recycled
@@ -325,6 +405,7 @@ __device__ void task_gemm_tc(Compute& q, const GemmTc& g) {
     }
     if (q.lane == 0) {
       x_prev = xm == kPopAbort ? 0 : (xm & (int)kSlotMaskAll);
+      if (g.wfmt == 1) w_prev = 0;
       if (q.mma_count > 0 && mma_wait(q, q.mma_count - 1) && (w_prev | x_prev))
         atomicOr(&sh->slot_avail, (uint32_t)(w_prev | x_prev) & kSlotMaskAll);
       sh->warp_next[0] = 0xFFFFFFFFu;
@@ -339,7 +420,10 @@ __device__ void task_gemm_tc(Compute& q, const GemmTc& g) {
   q.warp_phase_end(n_ent);  // CTA barrier: accumulator complete (lane 0 saw the last commit)
   tc_fence_after();
   if (g.norm) q.xr_count += (unsigned)n_x;
+  if (g.wfmt == 1) q.wr_count += (unsigned)g.n_w;
+  q.mma_count = mma_base + (unsigned)g.n_w;  // every thread keeps the count (thread 0 counted along)
   if (q.aborted) return;
+  if (g.wfmt == 1) q.free_slots(stage_mask[0] | stage_mask[1]);
   TCS(1);
 
   // Lane b of the accumulator belongs to sequence b; warps w and w+4 share the lane quarter

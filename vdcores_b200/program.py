@@ -343,7 +343,7 @@ class Program:
     def gemm_tc(self, sm, *, w_addr, N, K, k_len, Kc, G, x_addr, B, Bpad, out_addr, mode, x_wait: Optional[int] = None,
                 norm_w: Optional[Src] = None, eps: float = 0.0, n0: int = 0, ld: int = 0, keys_addr: int = 0,
                 stats_addr: int = 0, release: Optional[int] = None, scratch_addr: int = 0, counter_addr: int = 0,
-                n_slices: int = 1):
+                n_slices: int = 1, wfmt: str = "bf16", scales_addr: int = 0):
         """One unit of a batched projection: D[b, n] = sum_k X[b, k] W[n, k] over a K-range
         of k_len inputs for a block of N weight rows (k-chunk-major [K/8][N/8][8][8] bf16;
         w_addr points at the range's first W chunk) against the k-chunk-major activation
@@ -354,19 +354,26 @@ class Program:
         of the range) is given, accumulated over the updated rows in ADD_PACKED mode.
         With n_slices > 1 the block's K is shared by that many units: partial sums meet in
         scratch_addr, counter_addr counts arrivals.  The caller declares `release` once per
-        block with add_releases."""
+        block with add_releases.  wfmt "fp8": the weights are e4m3 bytes (chunk layout
+        [Kc/16][N/8][8][16]) with fp32 per-row scales at scales_addr; two bf16 staging
+        buffers are allocated for the task."""
+        assert wfmt in ("bf16", "fp8") and (wfmt == "bf16" or (scales_addr and scales_addr % 16 == 0))
+        wbpe = 2 if wfmt == "bf16" else 1
         assert N % 16 == 0 and 16 <= N <= 256 and Bpad in (16, 32, 64, 128) and 1 <= B <= Bpad
         assert Kc % 16 == 0 and k_len % Kc == 0 and k_len > 0 and n0 % 16 == 0 and ld % 16 == 0 and K % 16 == 0
         assert norm_w is None or stats_addr
         assert n_slices == 1 or (scratch_addr and counter_addr)
         n_w = k_len // Kc
-        wbytes = N * Kc * 2
-        assert wbytes <= 32768 and n_w <= 0xFFFF and 1 <= G <= 15 and Kc // 16 <= 255
+        wbytes = N * Kc * wbpe
+        assert N * Kc * 2 <= 32768 and n_w <= 0xFFFF and 1 <= G <= 15 and Kc // 16 <= 255
         assert Bpad * G * Kc * 2 <= 32768
         wslots = slots_for(wbytes)
         if norm_w is not None:
             assert norm_w.nbytes == k_len * 2
             self.load(sm, norm_w, default_port=1)
+        if wfmt == "fp8":
+            for _ in range(2):      # staging buffers: slots only, nothing is loaded or stored
+                self.mem(sm, isa.OP_ALLOC_WB_TMA_STORE_1D, size=0, nslot=slots_for(N * Kc * 2), address=0)
 
         def group(first_w, count, wait=None, jump=False):
             # one X chunk and the `count` W chunks that go with it
@@ -391,11 +398,11 @@ class Program:
         self.bytes_loaded[sm] += (Bpad * Kc * 2 + wbytes) * n_w
         e = f32_bits(eps)
         a48 = lambda a: (a & 0xFFFF, (a >> 16) & 0xFFFF, (a >> 32) & 0xFFFF)
-        for a in (out_addr, keys_addr, stats_addr, scratch_addr, counter_addr):
+        for a in (out_addr, keys_addr, stats_addr, scratch_addr, counter_addr, scales_addr):
             assert 0 <= a < 1 << 48
         assert out_addr % 16 == 0 and keys_addr % 8 == 0 and stats_addr % 4 == 0 and scratch_addr % 16 == 0
-        self.comp(sm, isa.OP_GEMM_TC_BF16, n_w, (N // 16) | (mode << 8) | ((1 << 12) if norm_w is not None else 0),
-                  (Kc // 16) | (G << 8))
+        self.comp(sm, isa.OP_GEMM_TC_BF16, n_w, (N // 16) | (mode << 8) | ((1 << 12) if norm_w is not None else 0) |
+                  ((1 << 13) if wfmt == "fp8" else 0), (Kc // 16) | (G << 8))
         self.comp(sm, isa.OP_EXT, e >> 16, e & 0xFFFF, B)
         self.comp(sm, isa.OP_EXT, *a48(out_addr))
         self.comp(sm, isa.OP_EXT, *a48(keys_addr))
@@ -405,6 +412,7 @@ class Program:
         self.comp(sm, isa.OP_EXT, *a48(scratch_addr))
         self.comp(sm, isa.OP_EXT, *a48(counter_addr))
         self.comp(sm, isa.OP_EXT, n_slices, 0, 0)
+        self.comp(sm, isa.OP_EXT, *a48(scales_addr))
 
     def embed_pack(self, sm, *, b0, count, Bpad, state_addr, state_stride_words, hidden, table_addr, out_addr,
                    stats_addr, release: Optional[int] = None):
