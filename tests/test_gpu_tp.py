@@ -23,9 +23,9 @@ def free_port():
     return p
 
 
-def run_rank(rank, world, port, n_steps, results, kind="llama"):
+def run_rank(rank, world, port, n_steps, results, kind="llama", fused=False):
     import torch.distributed as dist
-    from vdcores_b200.tp import TPDecodeEngine, shard_dense_weights
+    from vdcores_b200.tp import TPDecodeEngine, TPFusedEngine, shard_dense_weights
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world,
@@ -38,7 +38,8 @@ def run_rank(rank, world, port, n_steps, results, kind="llama"):
         orc = O.DecodeOracle(w, 256)
         orc.prefill(prompt[:-1].tolist())
         ecfg = engine_config(cfg)
-        eng = TPDecodeEngine(ecfg, max_seq=256, rank=rank, world=world, device=dev, timeout_ns=500_000_000)
+        cls = TPFusedEngine if fused else TPDecodeEngine
+        eng = cls(ecfg, max_seq=256, rank=rank, world=world, device=dev, timeout_ns=500_000_000)
         eng.load_shard(shard_dense_weights(ecfg, dense_weights(w), rank, world))
         eng.load_kv([k[:69] for k in orc.k], [v[:69] for v in orc.v])
         tok = int(prompt[-1])
@@ -77,6 +78,14 @@ def test_tp_one_rank_group(cuda_device):
     check(results, 1)
 
 
+def test_fused_exchange_one_rank(cuda_device):
+    """The in-kernel exchange (peer stores, arrival counters, XREDUCE) with a single rank:
+    one launch per step, no collective call in the step."""
+    results = {}
+    run_rank(0, 1, free_port(), 5, results, fused=True)
+    check(results, 1)
+
+
 def test_expert_parallel_one_rank_group(cuda_device):
     """The mixture-of-experts model through the expert-parallel path with one rank: router,
     selection, dynamically counted expert tasks, fp32 partial sum, collectives."""
@@ -87,16 +96,18 @@ def test_expert_parallel_one_rank_group(cuda_device):
 
 def _worker(rank, world, port, n_steps, q, kind="llama"):
     res = {}
-    run_rank(rank, world, port, n_steps, res, kind=kind)
+    fused = kind == "llama-fused"
+    run_rank(rank, world, port, n_steps, res, kind="llama" if fused else kind, fused=fused)
     q.put((rank, res[rank]))
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-@pytest.mark.parametrize("kind", ["llama", "moe2", "moe"])
+@pytest.mark.parametrize("kind", ["llama", "llama-fused", "moe2", "moe"])
 def test_tp_two_ranks(kind):
     """Two ranks: tensor parallel for the dense model; attention tensor parallel and experts
     expert parallel (8 of 16 experts per rank) for the mixture-of-experts models — "moe" has a
-    single KV head, which both ranks then hold, each serving four of its eight query heads."""
+    single KV head, which both ranks then hold, each serving four of its eight query heads.
+    "llama-fused": the dense model with the exchange inside the kernel (peer stores over NVLink)."""
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     q = ctx.Queue()

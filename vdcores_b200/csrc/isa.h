@@ -93,6 +93,8 @@
   X(OP_GEMM_TC_BF16, 0x7300)                                                           \
   X(OP_EMBED_PACK, 0x7310)                                                             \
   X(OP_BATCH_ADVANCE, 0x7320)                                                          \
+  X(OP_XREDUCE, 0x7330)                                                                \
+  X(OP_XWAIT, 0x7331)                                                                  \
   X(OP_EXT, 0x7FFF)
 
 // OP_L2_PREFETCH (two words): args = 48-bit address in three 16-bit pieces (low
@@ -113,6 +115,20 @@
 // the task's first output row.  Each row adds weight * bf16(W x) to its accumulator; the top_k-th
 // arrival (args of word 2: [eps hi, eps lo] unused, args[2] = top_k) folds bf16(sum) into the hidden
 // state (the output address) and clears both.
+//
+// In-kernel tensor parallelism (no collective library in the step).  Every rank owns an exchange block
+// that all ranks map (CUDA IPC): fp32 partial rows xbuf[parity][rank][hidden], argmax records
+// best[rank][4], int32 arrival counters that only ever grow.  A GEMV_ROWS task with VDC_GEMV_PEERS_BIT
+// (mode STORE_F32; its output "address" is the byte offset of its first row inside a block) stores its
+// rows into its slot of every rank's block and then adds 1 to every rank's counter with a system-scope
+// release; its two extra words are the 48-bit address of the table of block base addresses and
+// [ranks, counter byte offset low, high].  ARGMAX_FINAL with args[1] = 2 does the same with its record
+// (same two extra words).
+// XREDUCE (six words): [n elements, ranks, barrier] [48-bit address of xbuf[parity][0][first element]]
+// [hidden/16, arrivals per step low, high] [48-bit address of the first hidden element]
+// [48-bit state block] [48-bit local counter address]: waits (bounded) until the counter has reached
+// arrivals-per-step * (state.STEP + 1), then hidden[i] = bf16(hidden[i] + sum over ranks).
+// XWAIT (three words): [barrier, arrivals per step, 0] [48-bit counter address] [48-bit state block].
 //
 // MOE_ROUTE: args = [n_experts, top_k, rank | world << 8].  Pops the fp32 router logits and a raw address;
 // writes int32 ids[16], fp32 weights[16] (softmax over all experts, top-k, renormalised, rounded to bf16),
@@ -182,6 +198,7 @@
 #define VDC_GEMV_MODE_MOE_DOWN 4    // weighted fp32 accumulation over the selected experts
 #define VDC_GEMV_ACC_BIT 0x0800
 #define VDC_GEMV_NORM_BIT 0x1000
+#define VDC_GEMV_PEERS_BIT 0x4000  // STORE_F32 to every rank's exchange block; two more words (see below)
 #define VDC_GEMV_DYN_BIT 0x2000    // the chunk count is min(n_chunks, int32 word): one more pop (a raw address: the word)
 
 // ATTN_DECODE args[2] bits

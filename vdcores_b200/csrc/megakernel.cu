@@ -6,6 +6,19 @@
 
 namespace vdc {
 
+// The two trailing words of a task that writes to every rank's exchange block.
+#define VDC_LOAD_PEERS(dst)                                                                             \
+  {                                                                                                     \
+    VdcCInst p0, p1;                                                                                    \
+    *reinterpret_cast<uint2*>(&p0) = ld_word(q.pc);                                                     \
+    *reinterpret_cast<uint2*>(&p1) = ld_word(q.pc + 1);                                                 \
+    q.pc += 2;                                                                                          \
+    (dst).table = reinterpret_cast<const unsigned long long*>(                                          \
+        (uint64_t)p0.args[0] | ((uint64_t)p0.args[1] << 16) | ((uint64_t)p0.args[2] << 32));            \
+    (dst).n = p1.args[0];                                                                               \
+    (dst).cnt_off = (uint32_t)p1.args[1] | ((uint32_t)p1.args[2] << 16);                                \
+  }
+
 // ------------------------------------------------------------------------- //
 // compute virtual core: dispatch
 // ------------------------------------------------------------------------- //
@@ -30,7 +43,8 @@ __device__ void compute_core(const Ctx& c, const VdcCInst* __restrict__ insts, i
     *reinterpret_cast<uint2*>(&ci) = w0;
     *reinterpret_cast<uint2*>(&ex) = w1;
     const bool two_words = ci.opcode == 0x7200 || ci.opcode == 0x7201 || ci.opcode == 0x7202 || ci.opcode == 0x7203 || ci.opcode == 0x7210 || ci.opcode == 0x7211 || ci.opcode == 0x7230 ||
-                           ci.opcode == 0x7300 || ci.opcode == 0x7310 || ci.opcode == 0x7320;
+                           ci.opcode == 0x7300 || ci.opcode == 0x7310 || ci.opcode == 0x7320 || ci.opcode == 0x7330 ||
+                           ci.opcode == 0x7331;
     q.pc += two_words ? 2 : 1;
     if (two_words) {
       w0 = ld_word(q.pc);
@@ -93,6 +107,7 @@ __device__ void compute_core(const Ctx& c, const VdcCInst* __restrict__ insts, i
         const bool accumulate = ci.args[1] & VDC_GEMV_ACC_BIT;
         const bool norm = ci.args[1] & VDC_GEMV_NORM_BIT;
         const bool dyn = ci.args[1] & VDC_GEMV_DYN_BIT;
+        const bool to_peers = ci.args[1] & VDC_GEMV_PEERS_BIT;
         const int K = (ci.args[2] & 0xFF) << 8;
         if (tid == 0) q.sh->misc[32] = __uint_as_float(((uint32_t)ex.args[0] << 16) | ex.args[1]);  // norm eps
         const int row_base = ((int)ex.args[2] | ((int)(ci.args[2] >> 8) << 16)) * R;  // first output row (argmax)
@@ -122,12 +137,18 @@ __device__ void compute_core(const Ctx& c, const VdcCInst* __restrict__ insts, i
           scales = reinterpret_cast<const float*>((uint64_t)e2.args[0] | ((uint64_t)e2.args[1] << 16) |
                                                   ((uint64_t)e2.args[2] << 32));
         }
+        PeerOut peer_args;
+        const PeerOut* peers = nullptr;
+        if (to_peers) {
+          VDC_LOAD_PEERS(peer_args);
+          peers = &peer_args;
+        }
         switch (R) {
-          case 1: task_gemv_rows<1>(q, ci.args[0], mode, accumulate, norm, K, row_base, scales, wfmt, moe, dyn); break;
-          case 2: task_gemv_rows<2>(q, ci.args[0], mode, accumulate, norm, K, row_base, scales, wfmt, moe, dyn); break;
-          case 4: task_gemv_rows<4>(q, ci.args[0], mode, accumulate, norm, K, row_base, scales, wfmt, moe, dyn); break;
-          case 8: task_gemv_rows<8>(q, ci.args[0], mode, accumulate, norm, K, row_base, scales, wfmt, moe, dyn); break;
-          case 16: task_gemv_rows<16>(q, ci.args[0], mode, accumulate, norm, K, row_base, scales, wfmt, moe, dyn); break;
+          case 1: task_gemv_rows<1>(q, ci.args[0], mode, accumulate, norm, K, row_base, scales, wfmt, moe, dyn, peers); break;
+          case 2: task_gemv_rows<2>(q, ci.args[0], mode, accumulate, norm, K, row_base, scales, wfmt, moe, dyn, peers); break;
+          case 4: task_gemv_rows<4>(q, ci.args[0], mode, accumulate, norm, K, row_base, scales, wfmt, moe, dyn, peers); break;
+          case 8: task_gemv_rows<8>(q, ci.args[0], mode, accumulate, norm, K, row_base, scales, wfmt, moe, dyn, peers); break;
+          case 16: task_gemv_rows<16>(q, ci.args[0], mode, accumulate, norm, K, row_base, scales, wfmt, moe, dyn, peers); break;
           default: raise_abort(c, VDC_ERR_BAD_OPCODE, 0, (int)q.pc, ci.opcode, -1, R); q.aborted = true; break;
         }
         break;
@@ -238,7 +259,42 @@ __device__ void compute_core(const Ctx& c, const VdcCInst* __restrict__ insts, i
                            (int)e4.args[0] | ((int)e4.args[1] << 16));
         break;
       }
-      case 0x7220: task_argmax_final(q, ci.args[0], ci.args[1]); break;
+      case 0x7220: {
+        PeerOut peer_args;
+        if (ci.args[1] == 2) {
+          VDC_LOAD_PEERS(peer_args);
+          task_argmax_final(q, ci.args[0], 1, &peer_args);
+        } else {
+          task_argmax_final(q, ci.args[0], ci.args[1]);
+        }
+        break;
+      }
+      case 0x7330: {  // XREDUCE (six words)
+        auto addr48 = [](const VdcCInst& w) {
+          return (uint64_t)w.args[0] | ((uint64_t)w.args[1] << 16) | ((uint64_t)w.args[2] << 32);
+        };
+        VdcCInst e[5];
+        e[0] = ex;
+#pragma unroll
+        for (int k = 1; k < 5; ++k) *reinterpret_cast<uint2*>(&e[k]) = ld_word(q.pc + (uint32_t)(k - 1));
+        q.pc += 4;
+        task_xreduce(q, ci.args[0], ci.args[1], ci.args[2], reinterpret_cast<const float*>(addr48(e[0])),
+                     (size_t)e[1].args[0] * 4, (int)e[1].args[1] | ((int)e[1].args[2] << 16),
+                     reinterpret_cast<__nv_bfloat16*>(addr48(e[2])), reinterpret_cast<const int*>(addr48(e[3])),
+                     reinterpret_cast<const int*>(addr48(e[4])));
+        break;
+      }
+      case 0x7331: {  // XWAIT (three words)
+        auto addr48 = [](const VdcCInst& w) {
+          return (uint64_t)w.args[0] | ((uint64_t)w.args[1] << 16) | ((uint64_t)w.args[2] << 32);
+        };
+        VdcCInst e2;
+        *reinterpret_cast<uint2*>(&e2) = ld_word(q.pc);
+        q.pc += 1;
+        task_xwait(q, ci.args[0], ci.args[1], reinterpret_cast<const int*>(addr48(ex)),
+                   reinterpret_cast<const int*>(addr48(e2)));
+        break;
+      }
       case 0x7240: task_moe_route(q, ci.args[0], ci.args[1], ci.args[2] & 0xFF, ci.args[2] >> 8); break;
       default:
         raise_abort(c, VDC_ERR_BAD_OPCODE, 0, (int)q.pc, ci.opcode, -1, 0);

@@ -273,10 +273,19 @@ struct MoeDown {           // mode MOE_DOWN: per-row accumulation over the selec
   int top_k;
 };
 
+// Tensor parallel without a collective library: the exchange blocks of all ranks are mapped into
+// this process; a task writes its fp32 partial rows into its own slot of every rank's block with
+// plain peer stores and then bumps every rank's arrival counter (system-scope release).
+struct PeerOut {
+  const unsigned long long* table;  // base address of each rank's exchange block
+  int n;                            // ranks
+  uint32_t cnt_off;                 // byte offset of the arrival counter inside a block
+};
+
 template <int R>
 __device__ void task_gemv_rows(Compute& q, int n_chunks, int mode, bool accumulate, bool norm, int K, int row_base,
                                const float* scales = nullptr, int wfmt = 0, const MoeDown* moe = nullptr,
-                               bool dyn = false) {
+                               bool dyn = false, const PeerOut* peers = nullptr) {
   Shared* sh = q.sh;
   const Ctx& c = q.c;
   int normw_mask = 0;
@@ -405,7 +414,11 @@ __device__ void task_gemv_rows(Compute& q, int n_chunks, int mode, bool accumula
 #pragma unroll
       for (int r = 0; r < R; ++r)
         if (q.lane == r) v = acc[r];
-      if (q.lane < R && mode == VDC_GEMV_MODE_STORE_F32) {
+      if (q.lane < R && mode == VDC_GEMV_MODE_STORE_F32 && peers != nullptr) {
+        // `outg` is the byte offset of the task's first row inside an exchange block
+        const unsigned long long off = reinterpret_cast<unsigned long long>(outg) + (unsigned long long)(row0 + q.lane) * 4ull;
+        for (int pr = 0; pr < peers->n; ++pr) *reinterpret_cast<float*>(__ldg(peers->table + pr) + off) = v;
+      } else if (q.lane < R && mode == VDC_GEMV_MODE_STORE_F32) {
         reinterpret_cast<float*>(outg)[row0 + q.lane] = v;
       } else if (q.lane < R && mode == VDC_GEMV_MODE_MOE_DOWN && moe->acc == nullptr) {
         // expert parallel: this rank's share of the weighted sum, fp32, all-reduced by the host side
@@ -454,8 +467,11 @@ __device__ void task_gemv_rows(Compute& q, int n_chunks, int mode, bool accumula
   // Output rows were written by lanes of every warp.  The CTA barrier inside
   // warp_phase_end orders them before thread 0, whose gpu-scope fence in
   // release() is cumulative, so no per-thread fence is needed here.
+  if (peers != nullptr) __threadfence_system();  // the peer stores of this thread, before the arrival below
   q.warp_phase_end((unsigned)n_chunks);
   if (q.aborted) return;
+  if (peers != nullptr && q.tid < peers->n)
+    red_release_sys_add(reinterpret_cast<int*>(__ldg(peers->table + q.tid) + peers->cnt_off), 1);
   if (mode == VDC_GEMV_MODE_ARGMAX && q.tid == 0) {
     float bv = sh->misc[40];
     int bi = reinterpret_cast<int*>(sh->misc)[48];
@@ -901,7 +917,7 @@ __device__ void task_moe_route(Compute& q, int n_experts, int top_k, int rank, i
 // Pop order: candidate records (n x {f32 val, i32 idx, pad, pad}), state (raw
 // address), token log (raw address, int32 per step), done (raw address slot that
 // is pushed back so the store warp can release a barrier).
-__device__ void task_argmax_final(Compute& q, int n, int local_only) {
+__device__ void task_argmax_final(Compute& q, int n, int local_only, const PeerOut* peers = nullptr) {
   const Ctx& c = q.c;
   const int rec_mask = q.pop();
   q.pop();
@@ -931,7 +947,21 @@ __device__ void task_argmax_final(Compute& q, int n, int local_only) {
         bi = oi;
       }
     }
-    if (q.lane == 0 && local_only) {
+    if (q.lane == 0 && local_only && peers != nullptr) {
+      // vocabulary shard under in-kernel tensor parallelism: this rank's best candidate goes into
+      // its record of every rank's exchange block (`log` holds the record's byte offset)
+      const unsigned long long off = reinterpret_cast<unsigned long long>(log);
+      for (int pr = 0; pr < peers->n; ++pr) {
+        float* rec_p = reinterpret_cast<float*>(__ldg(peers->table + pr) + off);
+        rec_p[0] = bv;
+        reinterpret_cast<int*>(rec_p)[1] = bi;
+        rec_p[2] = 0.f;
+        rec_p[3] = 0.f;
+      }
+      __threadfence_system();
+      for (int pr = 0; pr < peers->n; ++pr)
+        red_release_sys_add(reinterpret_cast<int*>(__ldg(peers->table + pr) + peers->cnt_off), 1);
+    } else if (q.lane == 0 && local_only) {
       // tensor-parallel vocabulary shard: leave this rank's best candidate as one
       // record; the ranks' records are reduced by a second, global call
       reinterpret_cast<float*>(log)[0] = bv;
@@ -961,5 +991,47 @@ __device__ void task_argmax_final(Compute& q, int n, int local_only) {
   q.free_slots(rec_mask);
 }
 
+// ------------------------------------------------------------------------- //
+// tasks: in-kernel tensor-parallel exchange (peer stores instead of a collective library)
+// ------------------------------------------------------------------------- //
+// Bounded wait until the arrival counter `cnt` (bumped by tasks of every rank, never reset
+// within a run) has reached per_step * (steps completed + 1).  Thread 0 only.
+__device__ __forceinline__ bool xchg_wait(Compute& q, const int* cnt, const int* state, int per_step, int opcode) {
+  const int target = per_step * (ld_relaxed_gpu(state + VDC_ST_STEP) + 1);
+  const bool ok = wait_until(q.c, [&] { return ld_acquire_sys(cnt) >= target; }, 0, (int)q.pc, opcode, -1, 100);
+  if (!ok) q.sh->aborted = 1;
+  return ok;
+}
+
+// XREDUCE: hidden[i] = bf16(hidden[i] + sum over ranks of xbuf[rank][i]) for a slice of n elements,
+// once every rank's partial rows have arrived; counts `bar` down.  Pops nothing.
+__device__ void task_xreduce(Compute& q, int n, int n_ranks, int bar, const float* xbuf, size_t rank_stride,
+                             int per_step, __nv_bfloat16* hidden, const int* state, const int* cnt) {
+  if (q.tid == 0) xchg_wait(q, cnt, state, per_step, 0x7330);
+  compute_sync();
+  if (q.sh->aborted) {
+    q.aborted = true;
+    return;
+  }
+  for (int i = q.tid; i < n; i += kCT) {
+    float sum = 0.f;
+    for (int r = 0; r < n_ranks; ++r) sum += __ldcg(xbuf + (size_t)r * rank_stride + i);  // written by peers: read past L1
+    hidden[i] = __float2bfloat16_rn(__bfloat162float(hidden[i]) + sum);
+  }
+  compute_sync();
+  if (q.tid == 0 && bar != 0xFFFF) red_release_gpu_add(q.c.bars + bar, -1);
+}
+
+// XWAIT: counts `bar` down once the arrival counter has reached this step's target.  Pops nothing.
+__device__ void task_xwait(Compute& q, int bar, int per_step, const int* cnt, const int* state) {
+  if (q.tid == 0) {
+    if (xchg_wait(q, cnt, state, per_step, 0x7331)) {
+      asm volatile("fence.proxy.async;" ::: "memory");  // a bulk copy reads what the peers wrote
+      red_release_gpu_add(q.c.bars + bar, -1);
+    }
+  }
+  compute_sync();
+  if (q.sh->aborted) q.aborted = true;
+}
 
 }  // namespace vdc

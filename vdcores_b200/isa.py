@@ -35,6 +35,7 @@ GEMV_MODE_MOE_DOWN = _defs["GEMV_MODE_MOE_DOWN"]
 GEMV_NORM_BIT = _defs["GEMV_NORM_BIT"]
 GEMV_ACC_BIT = _defs["GEMV_ACC_BIT"]
 GEMV_DYN_BIT = _defs["GEMV_DYN_BIT"]
+GEMV_PEERS_BIT = _defs["GEMV_PEERS_BIT"]
 ATTN_QKNORM_BIT = _defs["ATTN_QKNORM_BIT"]
 ATTN_PACKED_BIT = _defs["ATTN_PACKED_BIT"]
 GEMM_MODE_STORE_ROWS = _defs["GEMM_MODE_STORE_ROWS"]

@@ -223,7 +223,7 @@ class Program:
              norm_w: Optional[Src] = None, eps: float = 0.0, pair_out: Optional[Dst] = None, row_base: int = 0,
              stream: bool = False, fp8_scales: Optional[int] = None, nvfp4_scales: Optional[int] = None,
              w_indirect: Optional[tuple] = None, wait_issue: Optional[int] = None, moe: Optional[dict] = None,
-             dyn_count_addr: Optional[int] = None):
+             dyn_count_addr: Optional[int] = None, peers: Optional[tuple] = None):
         """y[0:n_rows] = W[0:n_rows, :K] @ x for the contiguous row block at w_addr
         (bf16; e4m3 with fp8_scales = address of the block's fp32 per-row scales;
         or NVFP4 rows — K/2 code bytes + K/16 block scales — with nvfp4_scales =
@@ -276,7 +276,8 @@ class Program:
         self.bytes_loaded[sm] += chunk_bytes * n_chunks
         rb8 = row_base // R     # index of the first chunk within the whole matrix
         a1 = R | (mode << 8) | (isa.GEMV_NORM_BIT if norm_w is not None else 0) | \
-            (isa.GEMV_ACC_BIT if out.kind == "add_bf16" else 0) | (isa.GEMV_DYN_BIT if dyn_count_addr is not None else 0)
+            (isa.GEMV_ACC_BIT if out.kind == "add_bf16" else 0) | (isa.GEMV_DYN_BIT if dyn_count_addr is not None else 0) | \
+            (isa.GEMV_PEERS_BIT if peers is not None else 0)
         a2 = (K // 256) | ((rb8 >> 16) << 8)
         e = f32_bits(eps)
         if moe is not None:
@@ -292,6 +293,41 @@ class Program:
         if scales is not None:
             assert scales % 4 == 0 and 0 <= scales < 1 << 48
             self.comp(sm, isa.OP_EXT, scales & 0xFFFF, (scales >> 16) & 0xFFFF, (scales >> 32) & 0xFFFF)
+        if peers is not None:
+            # (table address, ranks, counter byte offset): out.addr is then the byte offset of the task's
+            # first row inside an exchange block, the rows go to every rank's block
+            assert mode == isa.GEMV_MODE_STORE_F32
+            self._peer_words(sm, peers)
+
+    def _peer_words(self, sm, peers):
+        table, n, cnt_off = peers
+        assert 0 <= table < 1 << 48 and table % 8 == 0 and 1 <= n <= 255 and 0 <= cnt_off < 1 << 32 and cnt_off % 4 == 0
+        self.comp(sm, isa.OP_EXT, table & 0xFFFF, (table >> 16) & 0xFFFF, (table >> 32) & 0xFFFF)
+        self.comp(sm, isa.OP_EXT, n, cnt_off & 0xFFFF, cnt_off >> 16)
+
+    def xreduce(self, sm, *, n, n_ranks, xbuf_addr, hidden_elems, per_step, hidden_addr, state_addr, cnt_addr,
+                release: Optional[int] = None):
+        """hidden[i] = bf16(hidden[i] + sum over ranks of xbuf[rank][i]) for n elements, once the
+        arrival counter at cnt_addr has reached per_step * (state.STEP + 1)."""
+        assert 0 < n <= 0xFFFF and hidden_elems % 16 == 0 and 0 < per_step < 1 << 32
+        if release is not None:
+            self.bar_counts[release] += 1
+        a48 = lambda a: (a & 0xFFFF, (a >> 16) & 0xFFFF, (a >> 32) & 0xFFFF)
+        self.comp(sm, isa.OP_XREDUCE, n, n_ranks, 0xFFFF if release is None else release)
+        self.comp(sm, isa.OP_EXT, *a48(xbuf_addr))
+        self.comp(sm, isa.OP_EXT, hidden_elems * 4 // 16, per_step & 0xFFFF, per_step >> 16)
+        for a in (hidden_addr, state_addr, cnt_addr):
+            assert 0 <= a < 1 << 48
+            self.comp(sm, isa.OP_EXT, *a48(a))
+
+    def xwait(self, sm, *, per_step, cnt_addr, state_addr, release: int):
+        """Counts `release` down once the arrival counter has reached per_step * (state.STEP + 1)."""
+        assert 0 < per_step <= 0xFFFF
+        self.bar_counts[release] += 1
+        a48 = lambda a: (a & 0xFFFF, (a >> 16) & 0xFFFF, (a >> 32) & 0xFFFF)
+        self.comp(sm, isa.OP_XWAIT, release, per_step, 0)
+        self.comp(sm, isa.OP_EXT, *a48(cnt_addr))
+        self.comp(sm, isa.OP_EXT, *a48(state_addr))
 
     def add_releases(self, bar: int, n: int):
         """Declares n count-downs of `bar` that tasks perform themselves (not
@@ -453,13 +489,19 @@ class Program:
         self.raw_address(sm, route_addr, 25, release=release)
         self.comp(sm, isa.OP_MOE_ROUTE, n_experts, top_k, rank | (world << 8))
 
-    def argmax_final(self, sm, *, records: Src, n: int, state_addr, log_addr, release=None, local_only=False):
+    def argmax_final(self, sm, *, records: Src, n: int, state_addr, log_addr, release=None, local_only=False,
+                     peers: Optional[tuple] = None):
         """Reduces n candidate records {f32 value, i32 index, pad, pad}.  Normally
         the winner is logged as the next token and the state block advances;
         with local_only the winner is written to log_addr as one more record."""
         self.load(sm, records)
         self.raw_address(sm, state_addr, 25)
         self.raw_address(sm, log_addr, 26, release=release)
+        if peers is not None:       # log_addr: byte offset of this rank's record inside an exchange block
+            assert local_only
+            self.comp(sm, isa.OP_ARGMAX_FINAL, n, 2)
+            self._peer_words(sm, peers)
+            return
         self.comp(sm, isa.OP_ARGMAX_FINAL, n, 1 if local_only else 0)
 
     # ------------------------------------------------------------------ output

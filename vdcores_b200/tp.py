@@ -498,3 +498,181 @@ class TPDecodeEngine:
         torch.cuda.synchronize(self.dev)
         runtime.read_status(self.stream.cuda_stream)
         return self.token_log[first:first + n_steps].tolist()
+
+
+class TPFusedEngine(TPDecodeEngine):
+    """Tensor-parallel decode of a dense model with the exchange inside the kernel: one launch
+    per step and rank, no collective library call in the step.  Every rank owns an exchange
+    block that all ranks map through CUDA IPC; the row-split projections (O, down) store
+    their fp32 partial rows into every rank's block with plain peer stores over NVLink and
+    bump every rank's arrival counter; an XREDUCE task per slice of the hidden state waits
+    for the counter and folds the ranks' partial sums into the replicated hidden state.
+    The vocabulary shard's best candidate travels the same way.  Bounded waits throughout:
+    a rank that never arrives makes the others time out and report, not hang."""
+
+    SLICE = 128     # hidden elements per XREDUCE task
+
+    def __init__(self, *args, **kw):
+        kw["use_graph"] = False
+        super().__init__(*args, **kw)
+        assert not self.cfg.n_experts, "the fused exchange covers dense models"
+        H, Pn, L = self.cfg.hidden, self.world, self.cfg.n_layers
+        # exchange block: xbuf[2][ranks][H] fp32 | best[ranks][4] fp32 | counters int32[2L + 1]
+        self.off_best = 2 * Pn * H * 4
+        self.off_cnt = self.off_best + Pn * 16
+        n_bytes = self.off_cnt + (2 * L + 1) * 4
+        self.xchg = torch.zeros((n_bytes + 255) // 256 * 64, dtype=torch.float32, device=self.dev)
+        self._peer_storages = []
+        bases = [0] * Pn
+        if Pn == 1:
+            bases[0] = self.xchg.data_ptr()
+        else:
+            handle = self.xchg.untyped_storage()._share_cuda_()
+            handles = [None] * Pn
+            dist.all_gather_object(handles, handle, group=self.group)
+            for r in range(Pn):
+                if r == self.rank:
+                    bases[r] = self.xchg.data_ptr()
+                    continue
+                assert torch.cuda.can_device_access_peer(self.dev.index, handles[r][0]), "peer access is required"
+                st = torch.UntypedStorage._new_shared_cuda(*handles[r])
+                self._peer_storages.append(st)      # keeps the mapping alive
+                bases[r] = st.data_ptr()
+                # one peer copy makes the runtime enable peer access from this device to rank r's
+                probe = torch.empty(4, dtype=torch.uint8, device=self.dev)
+                probe.copy_(torch.empty(0, dtype=torch.uint8, device=st.device).set_(st, 0, (4,)))
+            torch.cuda.synchronize(self.dev)
+            dist.barrier(group=self.group)
+        self.peer_table = torch.tensor(bases, dtype=torch.int64, device=self.dev)
+        self.launches_per_step = 1
+
+    # ------------------------------------------------------------------ program
+    def _build_programs(self):
+        cfg = self.cfg
+        L, H, G, D, S, Pn = cfg.n_layers, cfg.hidden, self.G, isa.HEAD_DIM, self.num_sms, self.world
+        st = self.state.data_ptr()
+        page_bytes = isa.KV_PAGE * D * 2
+        page_shift = int(math.log2(self.nkv * page_bytes))
+        hid, qkv, ao, act = (t.data_ptr() for t in (self.hidden, self.qkv, self.attn_out, self.act))
+        xb = self.xchg.data_ptr()
+        table = self.peer_table.data_ptr()
+        load = [0] * S
+        P = Program(S, insts_per_sm=isa.MAX_INSTS)
+
+        def exchange(half: int, n_tasks: int, release: int):
+            """XREDUCE tasks for exchange number `half` (two per layer): n_tasks row-split tasks per rank signal it."""
+            par = half & 1
+            order = sorted(range(S), key=lambda s: (load[s], s))
+            for i, e0 in enumerate(range(0, H, self.SLICE)):
+                n = min(self.SLICE, H - e0)
+                P.xreduce(order[i % S], n=n, n_ranks=Pn, xbuf_addr=xb + (par * Pn * H + e0) * 4, hidden_elems=H,
+                          per_step=Pn * n_tasks, hidden_addr=hid + e0 * 2, state_addr=st,
+                          cnt_addr=xb + self.off_cnt + 4 * half, release=release)
+
+        def peers(half: int):
+            return (table, Pn, self.off_cnt + 4 * half)
+
+        def my_slot(half: int, r0: int) -> int:
+            return (((half & 1) * Pn + self.rank) * H + r0) * 4      # byte offset inside an exchange block
+
+        # ---- embedding row of the current token into the hidden state
+        b_hid = P.new_barrier()
+        sm0 = 0
+        P.copy(sm0, Src(self.embed.data_ptr(), H * 2, indirect=(st + 4 * isa.ST_TOKEN, None, H * 2)),
+               Dst(hid, H * 2, release=b_hid), H * 2)
+        for l in range(L):
+            b_qkv, b_merge = P.new_barrier(), P.new_barrier()
+            R = rows_per_chunk(H)
+            rows = self.qw + 2 * self.kvw
+            for sm, u0, cnt in self._ranges(load, rows // R, R * H * 2):
+                r0, n = u0 * R, cnt * R
+                P.gemv(sm, w_addr=self.wqkv[l].data_ptr() + r0 * H * 2, n_rows=n, K=H, R=R, x=Src(hid, H * 2, wait=b_hid),
+                       out=Dst(qkv + r0 * 2, n * 2, "store", release=b_qkv),
+                       norm_w=Src(self.ln1[l].data_ptr(), H * 2), eps=cfg.eps)
+            P.add_releases(b_merge, self.nkv)
+            units = [(h, s) for s in range(self.n_splits) for h in range(self.nkv)]
+            order = sorted(range(S), key=lambda s: (load[s], s))
+            grp = (G + 2) * D * 2
+            for i, (h, s) in enumerate(units):
+                P.attn_decode(
+                    order[i % S], G=G, state_addr=st,
+                    rope=Src(self.rope.data_ptr(), D * 4, indirect=(st + 4 * isa.ST_POS, 9, None)),
+                    norm_w=Src(self.qknorm[l].data_ptr(), 2 * D * 2) if cfg.qk_norm else None,
+                    qkv=Src(qkv + h * grp, grp, wait=b_qkv),
+                    k_page_addr=self.kpool[l].data_ptr() + h * page_bytes,
+                    v_page_addr=self.vpool[l].data_ptr() + h * page_bytes, page_shift=page_shift,
+                    base_page=s * self.pages_per_split, max_pages=self.pages_per_split,
+                    records_addr=self.attn_part[h].data_ptr(), counter_addr=self.attn_cnt[l, h].data_ptr(),
+                    out_addr=ao + h * G * D * 2, split=s, n_splits=self.n_splits, release=b_merge,
+                    qk_eps=cfg.qk_norm_eps)
+            # ---- O projection over the local columns: partial rows to every rank, then the exchange
+            K = self.qw
+            R = rows_per_chunk(K)
+            tasks = self._ranges(load, H // R, R * K * 2)
+            for sm, u0, cnt in tasks:
+                r0, n = u0 * R, cnt * R
+                P.gemv(sm, w_addr=self.wo[l].data_ptr() + r0 * K * 2, n_rows=n, K=K, R=R, x=Src(ao, K * 2, wait=b_merge),
+                       out=Dst(my_slot(2 * l, r0), n * 4, "store"), mode=isa.GEMV_MODE_STORE_F32, peers=peers(2 * l))
+            b_h1 = P.new_barrier()
+            exchange(2 * l, len(tasks), b_h1)
+            # ---- gate/up over the local FFN rows, down over the local columns
+            b_gu = P.new_barrier()
+            R = rows_per_chunk(H, even=True)
+            for sm, u0, cnt in self._ranges(load, 2 * self.F // R, R * H * 2):
+                r0, n = u0 * R, cnt * R
+                P.gemv(sm, w_addr=self.wgu[l].data_ptr() + r0 * H * 2, n_rows=n, K=H, R=R, x=Src(hid, H * 2, wait=b_h1),
+                       out=Dst(act + (r0 // 2) * 2, n, "store", release=b_gu), mode=isa.GEMV_MODE_SILU_PAIRS,
+                       norm_w=Src(self.ln2[l].data_ptr(), H * 2), eps=cfg.eps)
+            K = self.F
+            R = rows_per_chunk(K)
+            tasks = self._ranges(load, H // R, R * K * 2)
+            for sm, u0, cnt in tasks:
+                r0, n = u0 * R, cnt * R
+                P.gemv(sm, w_addr=self.wd[l].data_ptr() + r0 * K * 2, n_rows=n, K=K, R=R, x=Src(act, K * 2, wait=b_gu),
+                       out=Dst(my_slot(2 * l + 1, r0), n * 4, "store"), mode=isa.GEMV_MODE_STORE_F32,
+                       peers=peers(2 * l + 1))
+            b_hid = P.new_barrier()
+            exchange(2 * l + 1, len(tasks), b_hid)
+        # ---- vocabulary shard, this rank's best candidate to every rank, global winner
+        b_logits = P.new_barrier()
+        R = rows_per_chunk(H)
+        lm = self._ranges(load, self.V // R, R * H * 2)
+        for i, (sm, u0, cnt) in enumerate(lm):
+            r0, n = u0 * R, cnt * R
+            P.gemv(sm, w_addr=self.lm_head.data_ptr() + r0 * H * 2, n_rows=n, K=H, R=R, x=Src(hid, H * 2, wait=b_hid),
+                   out=Dst(self.logits.data_ptr() + r0 * 2, n * 2, "store", release=b_logits),
+                   mode=isa.GEMV_MODE_ARGMAX, norm_w=Src(self.norm_w.data_ptr(), H * 2), eps=cfg.eps,
+                   pair_out=Dst(self.argmax_rec[i].data_ptr(), 16, release=b_logits), row_base=self.rank * self.V + r0)
+        last = 2 * L
+        P.argmax_final(0, records=Src(self.argmax_rec.data_ptr(), len(lm) * 16, wait=b_logits), n=len(lm),
+                       state_addr=st, log_addr=self.off_best + 16 * self.rank, local_only=True, peers=peers(last))
+        b_best = P.new_barrier()
+        P.xwait(0, per_step=Pn, cnt_addr=xb + self.off_cnt + 4 * last, state_addr=st, release=b_best)
+        P.argmax_final(0, records=Src(xb + self.off_best, Pn * 16, wait=b_best), n=Pn, state_addr=st,
+                       log_addr=self.token_log.data_ptr())
+        n = max(max(len(x) for x in P.m), max(len(x) for x in P.c)) + 2
+        P.insts_per_sm = ((n + 63) // 64) * 64
+        c, m, bars = P.finalize()
+        self.programs = [(torch.from_numpy(c).to(self.dev), torch.from_numpy(m).to(self.dev),
+                          torch.from_numpy(bars).to(self.dev), P.insts_per_sm)]
+
+    # ------------------------------------------------------------------ state / decode
+    def set_state(self, pos: int, token: int):
+        super().set_state(pos, token)
+        # the arrival counters count from step 0 again; nobody may still be writing
+        torch.cuda.synchronize(self.dev)
+        if self.world > 1:
+            dist.barrier(group=self.group)
+        self.xchg.zero_()
+        torch.cuda.synchronize(self.dev)
+        if self.world > 1:
+            dist.barrier(group=self.group)
+
+    def _step_body(self):
+        c, m, b0, n = self.programs[0]
+        runtime.launch_async(self.num_sms, n, c, m, None, self.bars, b0, self.profile,
+                             torch.cuda.current_stream(self.dev).cuda_stream, self.timeout_ns)
+
+    def close(self):
+        torch.cuda.synchronize(self.dev)
+        self._peer_storages = []
