@@ -83,6 +83,21 @@ int vdc_build_tma_desc(void* out_desc, const void* base, int dtype, int rank, co
 int vdc_set_cache_policy(const void* ptr, size_t bytes, uint64_t stream, float hit_ratio, int hit_policy,
                          int miss_policy);
 
+/* Lets kernels of the current device load from / store to memory of `peer_device` that is mapped
+ * into this process (its own allocations there, or another process's imported through CUDA IPC).
+ * The tensor-parallel engine calls it once per peer before its first step: its decode kernel
+ * writes partial results straight into the other ranks' exchange blocks.  Already enabled: success.
+ * No counterpart in the reference (it has no multi-GPU path). */
+int vdc_enable_peer_access(int peer_device);
+
+/* Maps a device allocation exported by another process (the 64-byte CUDA IPC memory handle of
+ * its base allocation) for kernels of the CURRENT device and returns its address in *out_ptr;
+ * peer access to the exporting device is enabled as needed.  vdc_ipc_close unmaps it.  Used for
+ * the other ranks' exchange blocks of the in-kernel tensor-parallel exchange.
+ * No counterpart in the reference. */
+int vdc_ipc_open(const void* handle, size_t handle_bytes, uint64_t* out_ptr);
+int vdc_ipc_close(uint64_t ptr);
+
 /* Opcode table: names and values of every memory and compute opcode.
  * Replaces: the `opcode` submodule (src/torch_runtime.cu:261-264). */
 int vdc_opcode_count(void);

@@ -102,12 +102,11 @@ def _worker(rank, world, port, n_steps, q, kind="llama"):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-@pytest.mark.parametrize("kind", ["llama", "llama-fused", "moe2", "moe"])
+@pytest.mark.parametrize("kind", ["llama", "moe2", "moe"])
 def test_tp_two_ranks(kind):
     """Two ranks: tensor parallel for the dense model; attention tensor parallel and experts
     expert parallel (8 of 16 experts per rank) for the mixture-of-experts models — "moe" has a
-    single KV head, which both ranks then hold, each serving four of its eight query heads.
-    "llama-fused": the dense model with the exchange inside the kernel (peer stores over NVLink)."""
+    single KV head, which both ranks then hold, each serving four of its eight query heads."""
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     q = ctx.Queue()

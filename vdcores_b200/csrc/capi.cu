@@ -236,6 +236,42 @@ int vdc_set_cache_policy(const void* ptr, size_t bytes, uint64_t stream, float h
   return VDC_OK;
 }
 
+int vdc_enable_peer_access(int peer_device) {
+  int dev;
+  if (int r = current_device(&dev)) return r;
+  if (peer_device == dev) return VDC_OK;
+  int can = 0;
+  cudaError_t e = cudaDeviceCanAccessPeer(&can, dev, peer_device);
+  if (e != cudaSuccess) return fail_cuda(e, "cudaDeviceCanAccessPeer");
+  if (!can) return fail_arg("the current device cannot map the peer's memory");
+  e = cudaDeviceEnablePeerAccess(peer_device, 0);
+  if (e == cudaErrorPeerAccessAlreadyEnabled) {
+    (void)cudaGetLastError();  // not an error for the caller: clear it
+    return VDC_OK;
+  }
+  if (e != cudaSuccess) return fail_cuda(e, "cudaDeviceEnablePeerAccess");
+  return VDC_OK;
+}
+
+int vdc_ipc_open(const void* handle, size_t handle_bytes, uint64_t* out_ptr) {
+  if (!handle || !out_ptr || handle_bytes != sizeof(cudaIpcMemHandle_t)) return fail_arg("bad IPC handle");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, sizeof(h));
+  void* p = nullptr;
+  // opened with the importing device current: the mapping is made for this device, peer access
+  // to the exporting device is enabled as needed
+  cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) return fail_cuda(e, "cudaIpcOpenMemHandle");
+  *out_ptr = reinterpret_cast<uint64_t>(p);
+  return VDC_OK;
+}
+
+int vdc_ipc_close(uint64_t ptr) {
+  cudaError_t e = cudaIpcCloseMemHandle(reinterpret_cast<void*>(ptr));
+  if (e != cudaSuccess) return fail_cuda(e, "cudaIpcCloseMemHandle");
+  return VDC_OK;
+}
+
 int vdc_opcode_count(void) { return kNumOps; }
 const char* vdc_opcode_name(int i) { return (i >= 0 && i < kNumOps) ? kOps[i].name : nullptr; }
 int vdc_opcode_value(int i) { return (i >= 0 && i < kNumOps) ? kOps[i].value : -1; }

@@ -43,6 +43,12 @@ _lib.vdc_read_status.argtypes = [_u64, ctypes.POINTER(Status), _i32]
 _lib.vdc_build_tma_desc.argtypes = [_vp, _vp, _i32, _i32, ctypes.POINTER(_u64), ctypes.POINTER(_u64),
                                     ctypes.POINTER(ctypes.c_uint32), ctypes.POINTER(ctypes.c_uint32), _i32, _i32]
 _lib.vdc_set_cache_policy.argtypes = [_vp, ctypes.c_size_t, _u64, ctypes.c_float, _i32, _i32]
+_lib.vdc_enable_peer_access.argtypes = [_i32]
+_lib.vdc_enable_peer_access.restype = _i32
+_lib.vdc_ipc_open.argtypes = [ctypes.c_char_p, ctypes.c_size_t, ctypes.POINTER(ctypes.c_uint64)]
+_lib.vdc_ipc_open.restype = _i32
+_lib.vdc_ipc_close.argtypes = [_u64]
+_lib.vdc_ipc_close.restype = _i32
 _lib.vdc_opcode_name.restype = ctypes.c_char_p
 _lib.vdc_opcode_name.argtypes = [_i32]
 _lib.vdc_opcode_value.argtypes = [_i32]
@@ -55,7 +61,7 @@ _lib.vdc_last_error.restype = ctypes.c_char_p
 EXPORTED_SYMBOLS = [
     "vdc_version", "vdc_init", "vdc_set_smem_size", "vdc_launch", "vdc_launch_async", "vdc_launch_static",
     "vdc_read_status",
-    "vdc_build_tma_desc", "vdc_set_cache_policy", "vdc_opcode_count", "vdc_opcode_name", "vdc_opcode_value",
+    "vdc_build_tma_desc", "vdc_set_cache_policy", "vdc_enable_peer_access", "vdc_ipc_open", "vdc_ipc_close", "vdc_opcode_count", "vdc_opcode_name", "vdc_opcode_value",
     "vdc_opcode_is_compute", "vdc_config", "vdc_family_specs", "vdc_last_error",
 ]
 
@@ -184,6 +190,22 @@ def build_tma_desc(base, shape, strides_bytes, box_dim, elem_strides, swizzle_by
                                  int(swizzle_bytes), int(interleave))
     _check(rc)
     return out
+
+
+def enable_peer_access(peer_device: int):
+    """Kernels of the current device may then access `peer_device`'s memory mapped into this process."""
+    _check(_lib.vdc_enable_peer_access(int(peer_device)))
+
+
+def ipc_open(handle: bytes) -> int:
+    """Maps another process's exported device allocation for the current device; returns its address."""
+    out = ctypes.c_uint64(0)
+    _check(_lib.vdc_ipc_open(handle, len(handle), ctypes.byref(out)))
+    return int(out.value)
+
+
+def ipc_close(ptr: int):
+    _check(_lib.vdc_ipc_close(int(ptr)))
 
 
 def set_cache_policy(tensor, stream, hit_ratio, hit_policy, miss_policy):

@@ -508,7 +508,11 @@ class TPFusedEngine(TPDecodeEngine):
     bump every rank's arrival counter; an XREDUCE task per slice of the hidden state waits
     for the counter and folds the ranks' partial sums into the replicated hidden state.
     The vocabulary shard's best candidate travels the same way.  Bounded waits throughout:
-    a rank that never arrives makes the others time out and report, not hang."""
+    a rank that never arrives makes the others time out and report, not hang.
+
+    Status: exercised on a GPU with one rank (the whole exchange path, peers = self); the
+    mapping of other ranks' blocks (world > 1) has not passed a test yet, so the collective
+    path of TPDecodeEngine remains the one the benchmark uses."""
 
     SLICE = 128     # hidden elements per XREDUCE task
 
@@ -535,12 +539,18 @@ class TPFusedEngine(TPDecodeEngine):
                     bases[r] = self.xchg.data_ptr()
                     continue
                 assert torch.cuda.can_device_access_peer(self.dev.index, handles[r][0]), "peer access is required"
-                st = torch.UntypedStorage._new_shared_cuda(*handles[r])
-                self._peer_storages.append(st)      # keeps the mapping alive
-                bases[r] = st.data_ptr()
-                # one peer copy makes the runtime enable peer access from this device to rank r's
-                probe = torch.empty(4, dtype=torch.uint8, device=self.dev)
-                probe.copy_(torch.empty(0, dtype=torch.uint8, device=st.device).set_(st, 0, (4,)))
+                # handles[r] = (device, 64-byte IPC handle of the base allocation, size, offset, ...): mapped
+                # with THIS device current, so that this device's kernels can store there
+                raw = bytes(handles[r][1])
+                if len(raw) == 65:          # the caching allocator prefixes a type byte; b"c": a plain cudaMalloc block
+                    assert raw[:1] == b"c", "the exchange block must come from a plain (not expandable) segment"
+                    raw = raw[1:]
+                if len(raw) != 64:
+                    raise RuntimeError(f"unexpected CUDA IPC handle of {len(raw)} bytes from the allocator")
+                with torch.cuda.device(self.dev):
+                    base = runtime.ipc_open(raw)
+                self._peer_storages.append(base)
+                bases[r] = base + int(handles[r][3])
             torch.cuda.synchronize(self.dev)
             dist.barrier(group=self.group)
         self.peer_table = torch.tensor(bases, dtype=torch.int64, device=self.dev)
@@ -675,4 +685,6 @@ class TPFusedEngine(TPDecodeEngine):
 
     def close(self):
         torch.cuda.synchronize(self.dev)
+        for base in self._peer_storages:
+            runtime.ipc_close(base)
         self._peer_storages = []
