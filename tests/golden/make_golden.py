@@ -274,11 +274,13 @@ def codec_fixture(path: str):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference-root", default="/root/reference")
+    ap.add_argument("--reference-root", default=os.environ.get("VDCORES_REFERENCE_ROOT", ""),
+                    help="checkout of the reference project (for its pure-torch attention helper); "
+                         "default: $VDCORES_REFERENCE_ROOT")
     args = ap.parse_args()
     ref_attn = None
     p = os.path.join(args.reference_root, "app/python/llama3/llama_attention_reference.py")
-    if os.path.exists(p):
+    if args.reference_root and os.path.exists(p):
         spec = importlib.util.spec_from_file_location("llama_attention_reference", p)
         ref_attn = importlib.util.module_from_spec(spec)
         sys.modules["llama_attention_reference"] = ref_attn

@@ -542,9 +542,11 @@ class TPFusedEngine(TPDecodeEngine):
                 # handles[r] = (device, 64-byte IPC handle of the base allocation, size, offset, ...): mapped
                 # with THIS device current, so that this device's kernels can store there
                 raw = bytes(handles[r][1])
-                if len(raw) == 65:          # the caching allocator prefixes a type byte; b"c": a plain cudaMalloc block
-                    assert raw[:1] == b"c", "the exchange block must come from a plain (not expandable) segment"
-                    raw = raw[1:]
+                # the caching allocator wraps the 64-byte driver handle: [format version][b"c": a plain
+                # cudaMalloc block][handle] (66 bytes), or [b"c"][handle] (65) in older releases
+                if len(raw) in (65, 66):
+                    assert raw[len(raw) - 65:len(raw) - 64] == b"c", "the exchange block must come from a plain (not expandable) segment"
+                    raw = raw[-64:]
                 if len(raw) != 64:
                     raise RuntimeError(f"unexpected CUDA IPC handle of {len(raw)} bytes from the allocator")
                 with torch.cuda.device(self.dev):
