@@ -101,3 +101,21 @@ def test_engine_quantisers_match_the_oracle_codecs():
     op, obs, ots = O.nvfp4_quantize(w)
     assert torch.equal(rows[:, :512], op) and torch.equal(rows[:, 512:], obs.view(torch.uint8))
     assert float(ts) == float(ots)
+
+
+def test_dynamic_expert_gemv_stream_order():
+    """An expert task of the expert-parallel path: the count word is handed over behind the
+    routing barrier, and the indirection sits directly in front of the dynamic loop, so that
+    a skipped loop (expert of another rank) drops it with the loop."""
+    P = Program(1)
+    b_route = P.new_barrier()
+    P.gemv(0, w_addr=1 << 30, n_rows=64, K=512, R=16, x=Src(1 << 20, 1024), out=Dst(1 << 21, 256, "store"),
+           mode=isa.GEMV_MODE_MOE_DOWN, w_indirect=(1 << 22, 512 * 64 * 2), wait_issue=b_route,
+           dyn_count_addr=(1 << 22) + 192, moe=dict(weight_addr=(1 << 22) + 64, acc_addr=0, cnt_addr=0, top_k=4))
+    ids = [isa.op_id(m[0]) for m in P.m[0]]
+    names = {isa.op_id(v): k for k, v in isa.OPCODES.items() if k in isa.MEMORY_OPS}
+    seq = [names[i] for i in ids]
+    assert seq == ["OP_ALLOC_TMA_LOAD_1D", "OP_ALLOC_WB_RAW_ADDRESS", "OP_ISSUE_BARRIER", "OP_ALLOC_WB_RAW_ADDRESS",
+                   "OP_DYN_COUNT", "OP_CC0_STRIDE32", "OP_REPEAT", "OP_ALLOC_TMA_LOAD_1D"], seq
+    assert P.m[0][6][1] == 0xFFFF                       # the loop count comes from DYN_COUNT
+    assert P.c[0][0][2] & isa.GEMV_DYN_BIT              # and the task clamps its chunk count the same way
