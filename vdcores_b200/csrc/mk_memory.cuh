@@ -25,6 +25,9 @@ __device__ __forceinline__ unsigned ring_head(const Shared* sh, int lane) {
 #ifndef VDC_CTRL_PAGELOOP
 #define VDC_CTRL_PAGELOOP 1   // lane-0 fast path for the attention page loop
 #endif
+#ifndef VDC_ALLOC_SLEEP
+#define VDC_ALLOC_SLEEP 20   // ns between two looks at the slot mask while no slot is free
+#endif
 #ifndef VDC_FAST_SLEEP
 #define VDC_FAST_SLEEP 20
 #endif
@@ -142,7 +145,7 @@ __device__ void control_warp(const Ctx& c, const VdcMInst* __restrict__ insts, i
             break;
           }
           n_alloc_retry++;
-          __nanosleep(20);
+          if (VDC_ALLOC_SLEEP) __nanosleep(VDC_ALLOC_SLEEP);
           if (control_backoff(c, lane, it, t0, pc, opcode, req)) {
             ok = false;
             break;
