@@ -150,8 +150,10 @@ def small_model_fixture(kind: str, path: str, ref_attn=None):
     for i in range(cfg.n_layers):
         store[f"{i}.k_cache"] = cache.layers[i].keys[0].float().numpy()      # [kv, T, d] post-RoPE
         store[f"{i}.v_cache"] = cache.layers[i].values[0].float().numpy()
-    # state dict so the test can rebuild the oracle weights without transformers
-    sd = {"w." + k: v.detach().float().numpy() for k, v in model.state_dict().items()}
+    # state dict so the test can rebuild the oracle weights without transformers: the model is
+    # bf16, so the bit patterns are stored ("wb." keys, uint16), half the size of fp32 and exact
+    sd = {"wb." + k: v.detach().to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16)
+          for k, v in model.state_dict().items()}
     np.savez_compressed(path, **store, **sd)
 
     # self-check: the oracle restatement agrees with HF on this fixture

@@ -18,7 +18,8 @@ def load(name):
 
 
 def weights_from_state_dict(z, cfg: O.DecodeConfig) -> O.ModelWeights:
-    g = lambda k: torch.from_numpy(z["w." + k]).to(BF16)
+    # weights are stored as bf16 bit patterns ("wb." keys): the Hugging Face models were bf16
+    g = lambda k: torch.from_numpy(z["wb." + k].view(np.int16)).view(BF16)
     layers = []
     for i in range(cfg.n_layers):
         p = f"model.layers.{i}."
