@@ -237,8 +237,7 @@ __device__ void task_gemm_tc(Compute& q, const GemmTc& g) {
     const int t = q.tid - 32;
     float* rs = sh->red;  // per-sequence rsqrt(mean x^2 + eps)
     int* told = reinterpret_cast<int*>(sh->misc) + 36;
-    bool stop = false;
-    for (int j = 0; j < g.n_w && !stop; ++j) {
+    for (int j = 0; j < g.n_w; ++j) {
       const int grp = j / g.G, jj = j % g.G;
       if (g.norm && jj == 0) {
         if (q.warp == 1) {
