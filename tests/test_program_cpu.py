@@ -119,3 +119,17 @@ def test_dynamic_expert_gemv_stream_order():
                    "OP_DYN_COUNT", "OP_CC0_STRIDE32", "OP_REPEAT", "OP_ALLOC_TMA_LOAD_1D"], seq
     assert P.m[0][6][1] == 0xFFFF                       # the loop count comes from DYN_COUNT
     assert P.c[0][0][2] & isa.GEMV_DYN_BIT              # and the task clamps its chunk count the same way
+
+
+def test_validate_catches_dead_barriers_and_oversized_loads():
+    P = Program(2)
+    b_in, b_out = P.new_barrier(), P.new_barrier()
+    P.gemv(0, w_addr=1 << 30, n_rows=64, K=512, R=16, x=Src(1 << 20, 1024, wait=b_in),
+           out=Dst(1 << 21, 128, "store", release=b_out))
+    with pytest.raises(ValueError, match="never released"):
+        P.validate()                                    # nobody counts b_in down
+    P.copy(1, Src(1 << 22, 1024), Dst(1 << 20, 1024, release=b_in), 1024)
+    assert P.validate()
+    P.mem(1, isa.OP_ALLOC_TMA_LOAD_1D, size=20000, nslot=2, address=1 << 23)
+    with pytest.raises(ValueError, match="into 2 slots"):
+        P.validate()

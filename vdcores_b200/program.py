@@ -529,6 +529,40 @@ class Program:
             bars[b] = cnt
         return (cm.view(np.uint8).reshape(self.num_sms * n, 8), mm.view(np.uint8).reshape(self.num_sms * n, 16), bars)
 
+    def validate(self):
+        """Static checks of the streams before they go to the device; raises ValueError.
+        * every allocation fits the slot pool, every load size fits its slots;
+        * every barrier some instruction waits for is counted down by somebody (a wait on a
+          barrier nobody releases would only end at the device-side timeout), and nobody
+          releases a barrier that was never declared."""
+        waited, released = set(), set(b for b, n in self.bar_counts.items() if n > 0)
+        op_id = isa.op_id
+        loads = {op_id(isa.OP_ALLOC_TMA_LOAD_1D), op_id(isa.OP_ALLOC_TMA_LOAD_1D_STREAM)}
+        for sm in range(self.num_sms):
+            for i, (op, size, num_slots, arg, addr) in enumerate(self.m[sm]):
+                oid = op_id(op)
+                if oid == op_id(isa.OP_REPEAT) or oid == op_id(isa.OP_DYN_COUNT) or oid == op_id(isa.OP_STREAM_LIST):
+                    continue
+                nslot, bar = num_slots & 63, num_slots >> 6
+                if op & isa.F_ALLOCATE and nslot < isa.NUM_SLOTS:
+                    if nslot == 0:
+                        raise ValueError(f"SM {sm} instruction {i}: allocation of zero slots")
+                    if oid in loads and size > nslot * SLOT:
+                        raise ValueError(f"SM {sm} instruction {i}: {size} bytes into {nslot} slots")
+                if op & isa.F_ALLOCATE and nslot >= isa.NUM_SLOTS + isa.NUM_SPECIAL_SLOTS:
+                    raise ValueError(f"SM {sm} instruction {i}: slot id {nslot} out of range")
+                if op & isa.F_BARRIER:
+                    if bar not in self.bar_counts:
+                        raise ValueError(f"SM {sm} instruction {i}: barrier {bar} was never declared")
+                    if not (op & isa.F_WRITEBACK):
+                        waited.add(bar)
+                if oid == op_id(isa.OP_ISSUE_BARRIER):
+                    waited.add(bar)
+        dead = sorted(waited - released)
+        if dead:
+            raise ValueError(f"barriers {dead} are waited for but never released")
+        return True
+
     def stats(self):
         return {"max_minsts": max(len(x) for x in self.m), "max_cinsts": max(len(x) for x in self.c),
                 "barriers": self._next_bar,
