@@ -153,3 +153,51 @@ def test_two_rank_expert_parallel_sum_reproduces_the_moe_block():
     assert sum(n for _, n, _ in res) == small_cfg("moe2").top_k      # every selected expert has exactly one owner
     for rank, n_local, r in res:
         assert r < 3e-3, (rank, r)
+
+
+def test_exchange_protocol_two_buffers_suffice():
+    """Model of the in-kernel tensor-parallel exchange (TPFusedEngine): every rank writes the partial
+    rows of exchange h into slot [h % 2][rank] of every rank's block, then bumps every rank's
+    counter h; a rank folds exchange h once its counter h is complete and only then produces
+    exchange h + 1.  Under random interleavings of the ranks (and of each rank's individual remote
+    writes) no rank may ever read a slot that already holds data of exchange h + 2."""
+    import random
+    for seed in range(200):
+        rng = random.Random(seed)
+        n_ranks, n_ex = rng.choice([2, 3, 4, 8]), 7
+        xbuf = [[[None] * n_ranks for _ in range(2)] for _ in range(n_ranks)]     # [owner][parity][writer] -> tag
+        cnt = [[0] * n_ex for _ in range(n_ranks)]
+        # per rank: list of pending micro-steps of the exchange it is in
+        state = [{"h": 0, "todo": None} for _ in range(n_ranks)]
+
+        def start(r):
+            h = state[r]["h"]
+            steps = [("write", p) for p in range(n_ranks)]
+            rng.shuffle(steps)
+            state[r]["todo"] = steps + [("signal", p) for p in range(n_ranks)] + [("fold", None)]
+
+        for r in range(n_ranks):
+            start(r)
+        live = set(range(n_ranks))
+        guard = 0
+        while live:
+            guard += 1
+            assert guard < 100000, "deadlock in the model"
+            r = rng.choice(sorted(live))
+            h = state[r]["h"]
+            kind, p = state[r]["todo"][0]
+            if kind == "write":
+                xbuf[p][h & 1][r] = h
+            elif kind == "signal":
+                cnt[p][h] += 1
+            else:
+                if cnt[r][h] < n_ranks:
+                    continue                         # bounded wait in the kernel; here: try another rank
+                assert all(tag == h for tag in xbuf[r][h & 1]), (seed, r, h, xbuf[r][h & 1])
+                state[r]["h"] = h + 1
+                if h + 1 == n_ex:
+                    live.discard(r)
+                    continue
+                start(r)
+                continue
+            state[r]["todo"].pop(0)
