@@ -19,10 +19,11 @@ def test_gemv_emission_matches_pop_order():
            out=Dst(0x3000, 128, "add_bf16", release=b_out), norm_w=Src(0x4000, 8192), eps=1e-5)
     c, m, bars = decode(P)
     ops = [int(x) for x in m[1]["opcode"][:7]]
-    # norm weight, x (port 1, waits on b_in), out (raw address, releases b_out), REPEAT header, chunk load, TERMINATE
+    # norm weight, x (slots + address handed to the task, which waits on b_in itself), out (raw address,
+    # releases b_out), REPEAT header, chunk load, TERMINATE
     assert ops[0] == isa.OP_ALLOC_TMA_LOAD_1D | isa.F_PORT
-    assert ops[1] == isa.OP_ALLOC_TMA_LOAD_1D | isa.F_PORT | isa.F_BARRIER
-    assert int(m[1]["num_slots"][1]) == 1 | (b_in << 6)
+    assert ops[1] == isa.OP_ALLOC_XVEC | isa.F_BARRIER
+    assert int(m[1]["num_slots"][1]) == 1 | (b_in << 6) and int(m[1]["address"][1]) == 0x2000
     assert ops[2] == isa.OP_ALLOC_WB_RAW_ADDRESS | isa.F_BARRIER | isa.F_WRITEBACK
     assert int(m[1]["num_slots"][2]) >> 6 == b_out
     assert ops[3] == isa.OP_REPEAT and int(m[1]["size"][3]) == 16 and int(m[1]["address"][3]) == 4 * 4096 * 2
@@ -115,7 +116,7 @@ def test_dynamic_expert_gemv_stream_order():
     ids = [isa.op_id(m[0]) for m in P.m[0]]
     names = {isa.op_id(v): k for k, v in isa.OPCODES.items() if k in isa.MEMORY_OPS}
     seq = [names[i] for i in ids]
-    assert seq == ["OP_ALLOC_TMA_LOAD_1D", "OP_ALLOC_WB_RAW_ADDRESS", "OP_ISSUE_BARRIER", "OP_ALLOC_WB_RAW_ADDRESS",
+    assert seq == ["OP_ALLOC_XVEC", "OP_ALLOC_WB_RAW_ADDRESS", "OP_ISSUE_BARRIER", "OP_ALLOC_WB_RAW_ADDRESS",
                    "OP_DYN_COUNT", "OP_CC0_STRIDE32", "OP_REPEAT", "OP_ALLOC_TMA_LOAD_1D"], seq
     assert P.m[0][6][1] == 0xFFFF                       # the loop count comes from DYN_COUNT
     assert P.c[0][0][2] & isa.GEMV_DYN_BIT              # and the task clamps its chunk count the same way
@@ -133,3 +134,30 @@ def test_validate_catches_dead_barriers_and_oversized_loads():
     P.mem(1, isa.OP_ALLOC_TMA_LOAD_1D, size=20000, nslot=2, address=1 << 23)
     with pytest.raises(ValueError, match="into 2 slots"):
         P.validate()
+
+
+def test_compute_word_counts_follow_the_table_in_the_header():
+    """Every emitter writes exactly the number of words isa.h declares for its opcode (optional
+    trailing words come on top): the kernel's dispatcher steps through the stream by that table."""
+    P = Program(1)
+    b = P.new_barrier()
+    P.add_releases(b, 1)
+    P.gemv(0, w_addr=1 << 30, n_rows=64, K=512, R=16, x=Src(1 << 20, 1024), out=Dst(1 << 21, 128, "store"))
+    P.gemv(0, w_addr=1 << 30, n_rows=64, K=512, R=16, x=Src(1 << 20, 1024), out=Dst(1 << 21, 128, "store"),
+           fp8_scales=1 << 22)
+    P.attn_decode(0, G=4, state_addr=1 << 16, rope=Src(1 << 17, 512), norm_w=None, qkv=Src(1 << 18, 6 * 256, wait=b),
+                  k_page_addr=1 << 24, v_page_addr=1 << 25, page_shift=15, base_page=0, max_pages=2,
+                  records_addr=1 << 19, counter_addr=1 << 20, out_addr=1 << 21, split=0, n_splits=1, release=b)
+    P.l2_prefetch(0, 1 << 30, 4096)
+    P.argmax_final(0, records=Src(1 << 20, 64), n=4, state_addr=1 << 16, log_addr=1 << 17)
+    i, stream = 0, P.c[0]
+    seen = []
+    while i < len(stream):
+        op = stream[i][0]
+        assert op != isa.OP_EXT, f"word {i}: a continuation word where an instruction must start"
+        n = isa.OP_WORDS[op]
+        assert all(stream[i + k][0] == isa.OP_EXT for k in range(1, n)), (hex(op), n)
+        seen.append(op)
+        i += n
+    assert seen == [isa.OP_GEMV_ROWS_BF16, isa.OP_GEMV_ROWS_FP8, isa.OP_ATTN_DECODE_PAGED_G4, isa.OP_L2_PREFETCH,
+                    isa.OP_ARGMAX_FINAL]

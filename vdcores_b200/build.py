@@ -16,7 +16,8 @@ def needs_build() -> bool:
     if not os.path.exists(LIB):
         return True
     t = os.path.getmtime(LIB)
-    deps = SOURCES + [os.path.join(HERE, "csrc", f) for f in ("isa.h", "mk_common.cuh", "mk_memory.cuh", "mk_compute.cuh")] + [os.path.join(HERE, "csrc", "isa.h"), os.path.join(HERE, "..", "include", "vdcores.h")]
+    csrc = os.path.join(HERE, "csrc")
+    deps = [os.path.join(csrc, f) for f in os.listdir(csrc)] + [os.path.join(HERE, "..", "include", "vdcores.h")]
     return any(os.path.getmtime(d) > t for d in deps)
 
 

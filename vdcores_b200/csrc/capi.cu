@@ -39,7 +39,7 @@ const OpEntry kOps[] = {
 #define X(name, value) {#name, (int)(value), 0},
     VDC_MEMORY_OPS(X)
 #undef X
-#define X(name, value) {#name, (int)(value), 1},
+#define X(name, value, words) {#name, (int)(value), 1},
         VDC_COMPUTE_OPS(X)
 #undef X
 };
@@ -293,7 +293,7 @@ int64_t vdc_config(const char* name) {
                    {"threads", VDC_THREADS},
                    {"kv_page", VDC_KV_PAGE},
                    {"head_dim", VDC_HEAD_DIM},
-                   {"dynamic_smem", (int64_t)((size_t)VDC_NUM_SLOTS * VDC_SLOT_BYTES + 1024)}};
+                   {"dynamic_smem", (int64_t)vdc_megakernel_dynamic_smem()}};
   for (auto& e : tbl)
     if (strcmp(e.k, name) == 0) return e.v;
   return -1;

@@ -71,38 +71,46 @@
   X(OP_ALLOC_TMA_LOAD_1D_STREAM, VDC_MOP(28, VDC_F_ALLOCATE))                          \
   X(OP_CC0_STRIDE32, VDC_MOP(29, 0))                                                   \
   X(OP_PT_LOAD32, VDC_MOP(30, 0))                                                      \
-  X(OP_PT_APPLY, VDC_MOP(31, 0))
+  X(OP_PT_APPLY, VDC_MOP(31, 0))                                                       \
+  X(OP_ALLOC_XVEC, VDC_MOP(32, VDC_F_ALLOCATE))
 
+// OP_ALLOC_XVEC: allocates slots for an activation vector and hands {address, size, barrier} to the
+// compute task, which waits for the barrier itself (BARRIER flag: the load port does NOT wait) and reads
+// the vector from global memory with ordinary loads.  It takes the copy engine, one ring hop and one
+// CTA barrier out of the path between "the producers' barrier opened" and "the stage computes".
+//
 // Compute opcodes.  The first block keeps reference names (control ops and the
 // ops whose tile contracts this runtime still honours); the second block is
 // the B200-native decode set.
+// X(name, value, words): `words` = 8-byte words the instruction occupies in the compute stream
+// before any optional trailing words (flags of the first word announce those).
 #define VDC_COMPUTE_OPS(X)                                                             \
-  X(OP_TERMINATEC, 0x7000)                                                             \
-  X(OP_LOOPC, 0x7001)                                                                  \
-  X(OP_DUMMY, 0x7002)                                                                  \
-  X(OP_COPY, 0x7003)                                                                   \
-  X(OP_GEMV_ROWS_BF16, 0x7200)                                                         \
-  X(OP_GEMV_ROWS_FP8, 0x7201)                                                          \
-  X(OP_GEMV_ROWS_NVFP4, 0x7202)                                                        \
-  X(OP_GEMV_ROWS_MOE_DOWN, 0x7203)                                                     \
-  X(OP_ATTN_DECODE_PAGED_G4, 0x7210)                                                   \
-  X(OP_ATTN_DECODE_PAGED_G8, 0x7211)                                                   \
-  X(OP_ARGMAX_FINAL, 0x7220)                                                          \
-  X(OP_L2_PREFETCH, 0x7230)                                                           \
-  X(OP_MOE_ROUTE, 0x7240)                                                          \
-  X(OP_GEMM_TC_BF16, 0x7300)                                                           \
-  X(OP_EMBED_PACK, 0x7310)                                                             \
-  X(OP_BATCH_ADVANCE, 0x7320)                                                          \
-  X(OP_XREDUCE, 0x7330)                                                                \
-  X(OP_XWAIT, 0x7331)                                                                  \
-  X(OP_EXT, 0x7FFF)
+  X(OP_TERMINATEC, 0x7000, 1)                                                          \
+  X(OP_LOOPC, 0x7001, 1)                                                               \
+  X(OP_DUMMY, 0x7002, 1)                                                               \
+  X(OP_COPY, 0x7003, 1)                                                                \
+  X(OP_GEMV_ROWS_BF16, 0x7200, 2)                                                      \
+  X(OP_GEMV_ROWS_FP8, 0x7201, 3)                                                       \
+  X(OP_GEMV_ROWS_NVFP4, 0x7202, 3)                                                     \
+  X(OP_GEMV_ROWS_MOE_DOWN, 0x7203, 5)                                                  \
+  X(OP_ATTN_DECODE_PAGED_G4, 0x7210, 13)                                               \
+  X(OP_ATTN_DECODE_PAGED_G8, 0x7211, 13)                                               \
+  X(OP_ARGMAX_FINAL, 0x7220, 1)                                                        \
+  X(OP_L2_PREFETCH, 0x7230, 2)                                                         \
+  X(OP_MOE_ROUTE, 0x7240, 1)                                                           \
+  X(OP_GEMM_TC_BF16, 0x7300, 11)                                                       \
+  X(OP_EMBED_PACK, 0x7310, 6)                                                          \
+  X(OP_BATCH_ADVANCE, 0x7320, 5)                                                       \
+  X(OP_XREDUCE, 0x7330, 6)                                                             \
+  X(OP_XWAIT, 0x7331, 3)                                                               \
+  X(OP_EXT, 0x7FFF, 1)
 
 // OP_L2_PREFETCH (two words): args = 48-bit address in three 16-bit pieces (low
 // first); second word args[0..1] = byte count (low, high).  All compute threads
 // issue L2 prefetches for the range and move on; nothing is popped.
 //
 // OP_EXT is never dispatched: it marks the continuation words of a multi-word
-// compute instruction (GEMV_ROWS: 2 words, L2_PREFETCH: 2, ATTN_DECODE_PAGED: 9).
+// compute instruction (the table above gives the counts).
 //
 // GEMV_ROWS_FP8 (3 words): as GEMV_ROWS_BF16 for e4m3 weights (K a multiple of 512, one byte per
 // weight), third word = 48-bit address of the fp32 per-row scales of the task's first row.
@@ -139,10 +147,13 @@
 // GEMV_ROWS_MOE_DOWN with a null accumulator address adds weight * bf16(W x) to the fp32 output
 // (the rank's partial sum, all-reduced afterwards) instead of counting arrivals.
 //
-// ATTN_DECODE_PAGED words: [max_pages, base_page, flags] [qk-norm eps hi, lo, n_splits]
+// ATTN_DECODE_PAGED (thirteen words): [max_pages, base_page, flags] [qk-norm eps hi, lo, n_splits]
 // then six 48-bit addresses, low piece first: state block, this head's rows in K page 0,
 // same for V, the head's split records, its arrival counter, its slice of the output;
-// last word: [split index, barrier released by the merged output, 0].
+// then [split index, barrier released by the merged output, packed-output info]; then three more
+// 48-bit addresses: the rope table ([position][cos 64 | sin 64] fp32), the q / k norm weights
+// (2 x 128 bf16, or 0) and the head group's projection output ((G + 2) x 128 bf16); last word
+// [barrier that orders that output (0xFFFF: none), 0, 0].  The memory stream delivers only the pages.
 //
 // GEMV_ROWS args[1] layout: bits 0..4 rows per chunk (1,2,4,8,16), bits 8..10
 // epilogue mode, bit 11 accumulate into the output (residual add), bit 12 fused

@@ -22,6 +22,20 @@ namespace vdc {
 // ------------------------------------------------------------------------- //
 // compute virtual core: dispatch
 // ------------------------------------------------------------------------- //
+// Words an instruction occupies before its optional trailing words: the one table in isa.h
+// that the host-side emitters read too.
+__device__ __forceinline__ int compute_op_words(uint16_t op) {
+  switch (op) {
+#define X(name, value, words) \
+  case value:                 \
+    return words;
+    VDC_COMPUTE_OPS(X)
+#undef X
+    default:
+      return 1;
+  }
+}
+
 __device__ void compute_core(const Ctx& c, const VdcCInst* __restrict__ insts, int n_insts, int tid) {
   Compute q{c, c.sh, tid, tid >> 5, tid & 31, 0u, 0u, 0u, false, 0ull};
   uint32_t count = 0;
@@ -42,9 +56,7 @@ __device__ void compute_core(const Ctx& c, const VdcCInst* __restrict__ insts, i
     VdcCInst ci, ex;
     *reinterpret_cast<uint2*>(&ci) = w0;
     *reinterpret_cast<uint2*>(&ex) = w1;
-    const bool two_words = ci.opcode == 0x7200 || ci.opcode == 0x7201 || ci.opcode == 0x7202 || ci.opcode == 0x7203 || ci.opcode == 0x7210 || ci.opcode == 0x7211 || ci.opcode == 0x7230 ||
-                           ci.opcode == 0x7300 || ci.opcode == 0x7310 || ci.opcode == 0x7320 || ci.opcode == 0x7330 ||
-                           ci.opcode == 0x7331;
+    const bool two_words = compute_op_words(ci.opcode) >= 2;
     q.pc += two_words ? 2 : 1;
     if (two_words) {
       w0 = ld_word(q.pc);
@@ -154,14 +166,14 @@ __device__ void compute_core(const Ctx& c, const VdcCInst* __restrict__ insts, i
         break;
       }
       case 0x7210:
-      case 0x7211: {  // ATTN_DECODE_PAGED (nine words; the first two are in registers already)
+      case 0x7211: {  // ATTN_DECODE_PAGED (thirteen words; the first two are in registers already)
         auto addr48 = [](const VdcCInst& w) {
           return (uint64_t)w.args[0] | ((uint64_t)w.args[1] << 16) | ((uint64_t)w.args[2] << 32);
         };
-        VdcCInst e[7];
+        VdcCInst e[11];
 #pragma unroll
-        for (int k = 0; k < 7; ++k) *reinterpret_cast<uint2*>(&e[k]) = ld_word(q.pc + (uint32_t)k);
-        q.pc += 7;
+        for (int k = 0; k < 11; ++k) *reinterpret_cast<uint2*>(&e[k]) = ld_word(q.pc + (uint32_t)k);
+        q.pc += 11;
         AttnArgs a;
         a.max_pages = ci.args[0];
         a.base_page = ci.args[1];
@@ -178,6 +190,10 @@ __device__ void compute_core(const Ctx& c, const VdcCInst* __restrict__ insts, i
         a.bar = e[6].args[1];
         a.b = (a.flags & VDC_ATTN_PACKED_BIT) ? (e[6].args[2] & 0xFF) : 0;
         a.bpad = (a.flags & VDC_ATTN_PACKED_BIT) ? (e[6].args[2] >> 8) * 16 : 0;
+        a.rope = reinterpret_cast<const float*>(addr48(e[7]));
+        a.nw = reinterpret_cast<const __nv_bfloat16*>(addr48(e[8]));
+        a.qkv = reinterpret_cast<const __nv_bfloat16*>(addr48(e[9]));
+        a.wait_bar = e[10].args[0];
         if (ci.opcode == 0x7210) task_attn_decode<4>(q, a);
         else task_attn_decode<8>(q, a);
         break;

@@ -172,7 +172,10 @@ struct __align__(16) Shared {
   uint32_t pt_words[32];                    // control warp: the table words PT_LOAD32 fetched (page loop)
   volatile int pop_val[2];
   volatile uint32_t pop_meta[2];
+  volatile uint32_t pop_size[2];
   volatile uint64_t pop_addr[2];
+  volatile int pair_ok[4][2][2];            // GEMV warp pairs: [pair][trip parity][member] chunk arrived
+  int att_done[8];                          // attention: warps finished with page pair i % 8
   alignas(16) float red[4096 + 64];                     // task scratch (reductions)
   alignas(16) float scores[VDC_KV_PAGE * 8];
   alignas(16) float probs[VDC_KV_PAGE * 8];
@@ -251,6 +254,23 @@ __device__ __forceinline__ bool wait_global_barrier(const Ctx& c, int bar, int r
   asm volatile("fence.acq_rel.gpu;" ::: "memory");  // pairs with the releasing red of the producers
   fence_proxy_async();  // later bulk copies (async proxy) must observe what the releasing stores wrote
   return ok;
+}
+// The same wait for a consumer that reads the produced data with ordinary loads (no bulk copy follows).
+__device__ __forceinline__ bool wait_global_barrier_generic(const Ctx& c, int bar, int role, int pc, int opcode) {
+  const int* p = c.bars + bar;
+  bool ok = wait_until(c, [&] { return ld_relaxed_gpu(p) == 0; }, role, pc, opcode, bar, 0);
+  asm volatile("fence.acq_rel.gpu;" ::: "memory");
+  return ok;
+}
+__device__ __forceinline__ uint4 ldcg128(const void* p) {  // 16 bytes past L1: another SM wrote them
+  uint4 v;
+  asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint32_t ldcg32(const void* p) {
+  uint32_t v;
+  asm volatile("ld.global.cg.u32 %0, [%1];" : "=r"(v) : "l"(p));
+  return v;
 }
 
 

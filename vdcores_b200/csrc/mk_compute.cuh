@@ -39,6 +39,7 @@ struct Compute {
       sh->pop_val[head & 1u] = ok ? sh->ring_word[e] : kPopAbort;
       sh->pop_addr[head & 1u] = sh->ring[e].address;
       sh->pop_meta[head & 1u] = (uint32_t)sh->ring[e].opcode | ((uint32_t)sh->ring[e].num_slots << 16);
+      sh->pop_size[head & 1u] = sh->ring[e].size;
       if (!ok) sh->aborted = 1;
       __threadfence_block();
       sh->cta_head = head + 1;
@@ -52,6 +53,15 @@ struct Compute {
   // Address / (opcode | num_slots << 16) of the instruction behind the last pop.
   __device__ __forceinline__ uint64_t addr() const { return sh->pop_addr[(head - 1u) & 1u]; }
   __device__ __forceinline__ uint32_t meta() const { return sh->pop_meta[(head - 1u) & 1u]; }
+  __device__ __forceinline__ uint32_t size() const { return sh->pop_size[(head - 1u) & 1u]; }
+  // CTA-wide wait on a global barrier by the compute core itself (thread 0 polls; the data it
+  // orders is then read with ordinary loads).  Returns false once a wait was given up.
+  __device__ __forceinline__ bool wait_barrier(int bar, int opcode) {
+    if (tid == 0 && !wait_global_barrier_generic(c, bar, 0, (int)pc, opcode)) sh->aborted = 1;
+    compute_sync();
+    if (sh->aborted) aborted = true;
+    return !aborted;
+  }
 
   // Per-warp phase: the next `n` ring entries are consumed by the warps on their own
   // schedule (the GEMV task gives entry head+i to the warp pair i % 4).  begin/end are CTA-wide.
@@ -67,9 +77,12 @@ struct Compute {
     uint64_t* bar = &sh->full[idx % kQ];
     const uint32_t parity = (idx / kQ) & 1u;
     int ok = 1;
-    if (lane == 0 && !mbar_try_wait(bar, parity)) {
-      ok = wait_until(c, [&] { return mbar_try_wait(bar, parity); }, 0, (int)pc, 0, -1, 0);
-      if (!ok) sh->aborted = 1;
+    if (lane == 0) {
+      if (!mbar_try_wait(bar, parity)) {
+        ok = wait_until(c, [&] { return mbar_try_wait(bar, parity); }, 0, (int)pc, 0, -1, 0);
+        if (!ok) sh->aborted = 1;
+      }
+      if (sh->aborted) ok = 0;  // another warp of this CTA gave up: stop consuming
     }
     ok = __shfl_sync(0xffffffffu, ok, 0);
     // lanes other than 0 did not observe the barrier themselves: order their
@@ -283,7 +296,7 @@ struct PeerOut {
 };
 
 template <int R>
-__device__ void task_gemv_rows(Compute& q, int n_chunks, int mode, bool accumulate, bool norm, int K, int row_base,
+__device__ __noinline__ void task_gemv_rows(Compute& q, int n_chunks, int mode, bool accumulate, bool norm, int K, int row_base,
                                const float* scales = nullptr, int wfmt = 0, const MoeDown* moe = nullptr,
                                bool dyn = false, const PeerOut* peers = nullptr) {
   Shared* sh = q.sh;
@@ -291,6 +304,8 @@ __device__ void task_gemv_rows(Compute& q, int n_chunks, int mode, bool accumula
   int normw_mask = 0;
   if (norm) normw_mask = q.pop();
   const int x_mask = q.pop();
+  const uint32_t x_meta = q.meta();
+  const uint64_t x_addr = q.addr();
   q.pop();  // output vector: raw address
   __nv_bfloat16* outg = reinterpret_cast<__nv_bfloat16*>(q.addr());
   const uint32_t out_meta = q.meta();
@@ -312,16 +327,32 @@ __device__ void task_gemv_rows(Compute& q, int n_chunks, int mode, bool accumula
   if (q.aborted) return;
   uint8_t* x = (uint8_t*)slot_ptr(c, first_slot(x_mask));
 
-  if (norm) {
-    // RMSNorm of the activation vector in place: bf16(w * bf16(x * rstd)), fp32 statistics
-    const uint8_t* nw = (const uint8_t*)slot_ptr(c, first_slot(normw_mask));
-    float ss = 0.f;
+  float ss = 0.f;
+  if (((x_meta & 0xFFFFu) >> VDC_FLAG_BITS) == 32u) {
+    // XVEC hand-over: the slots are empty.  Wait for the producers' barrier here, then every
+    // thread copies its share of the vector from global memory (past L1) into the slots.
+    if ((x_meta & VDC_F_BARRIER) && !q.wait_barrier((int)(x_meta >> 22), 0x7200)) return;
+    const uint8_t* xg = reinterpret_cast<const uint8_t*>(x_addr);
+    for (int i = q.tid * 8; i < K; i += kCT * 8) {
+      const uint4 v = ldcg128(xg + i * 2);
+      *reinterpret_cast<uint4*>(x + i * 2) = v;
+      if (norm) {
+        const float f[8] = {bf_lo(v.x), bf_hi(v.x), bf_lo(v.y), bf_hi(v.y), bf_lo(v.z), bf_hi(v.z), bf_lo(v.w), bf_hi(v.w)};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss = fmaf(f[j], f[j], ss);
+      }
+    }
+  } else if (norm) {
     for (int i = q.tid * 8; i < K; i += kCT * 8) {
       const uint4 v = lds128(x + i * 2);
       const float f[8] = {bf_lo(v.x), bf_hi(v.x), bf_lo(v.y), bf_hi(v.y), bf_lo(v.z), bf_hi(v.z), bf_lo(v.w), bf_hi(v.w)};
 #pragma unroll
       for (int j = 0; j < 8; ++j) ss = fmaf(f[j], f[j], ss);
     }
+  }
+  if (norm) {
+    // RMSNorm of the activation vector in place: bf16(w * bf16(x * rstd)), fp32 statistics
+    const uint8_t* nw = (const uint8_t*)slot_ptr(c, first_slot(normw_mask));
     ss = warp_sum(ss);
     if (q.lane == 0) sh->misc[q.warp] = ss;
     compute_sync();
@@ -361,16 +392,18 @@ __device__ void task_gemv_rows(Compute& q, int n_chunks, int mode, bool accumula
   if (norm) q.free_slots(normw_mask);
   for (int i = pair, trip = 0; i < n_chunks; i += 4, ++trip) {
     const int w_mask = q.warp_wait((unsigned)i);
-    if (w_mask == kPopAbort) {
-      asm volatile("bar.arrive %0, 64;" ::"r"(2 + pair) : "memory");  // do not strand the partner
-      break;
-    }
-    const uint8_t* w = (const uint8_t*)slot_ptr(c, first_slot(w_mask));
+    const bool arrived = w_mask != kPopAbort;
     float acc[R];
     const int row0 = i * R;
-    if (wfmt == 2) gemv_chunk_nvfp4<R>(w, x, K, q.lane, it0, it1, acc);
-    else if (wfmt == 1) gemv_chunk_fp8<R>(w, x, K, q.lane, it0, it1, acc);
-    else gemv_chunk<R>(w, x, K, q.lane, it0, it1, acc);
+    if (arrived) {
+      const uint8_t* w = (const uint8_t*)slot_ptr(c, first_slot(w_mask));
+      if (wfmt == 2) gemv_chunk_nvfp4<R>(w, x, K, q.lane, it0, it1, acc);
+      else if (wfmt == 1) gemv_chunk_fp8<R>(w, x, K, q.lane, it0, it1, acc);
+      else gemv_chunk<R>(w, x, K, q.lane, it0, it1, acc);
+    } else {
+#pragma unroll
+      for (int r = 0; r < R; ++r) acc[r] = 0.f;
+    }
     float* pp = pair_part + (trip & 1) * 32;
     if (member == 1) {
       float v = 0.f;
@@ -379,7 +412,11 @@ __device__ void task_gemv_rows(Compute& q, int n_chunks, int mode, bool accumula
         if (q.lane == r) v = acc[r];
       if (q.lane < R) pp[16 + q.lane] = v;
     }
+    // Both members always meet at the pair's barrier and decide together whether to go on: a
+    // member whose wait was given up must not leave its partner alone at a later barrier.
+    if (q.lane == 0) sh->pair_ok[pair][trip & 1][member] = arrived ? 1 : 0;
     asm volatile("bar.sync %0, 64;" ::"r"(2 + pair) : "memory");
+    if (!(sh->pair_ok[pair][trip & 1][0] && sh->pair_ok[pair][trip & 1][1])) break;
     if (member == 1) {  // the partner finishes the chunk; it also frees the slots
       if (q.lane == 0) sh->warp_next[q.warp] = i + 4 < n_chunks ? q.head + i + 4 : 0xFFFFFFFFu;
       continue;
@@ -425,7 +462,7 @@ __device__ void task_gemv_rows(Compute& q, int n_chunks, int mode, bool accumula
         atomicAdd(reinterpret_cast<float*>(outg) + row0 + q.lane, ld_relaxed_gpu_f32(moe->weight) * bf16_round(v));
       } else if (q.lane < R && mode == VDC_GEMV_MODE_MOE_DOWN) {
         const int row = row0 + q.lane;
-        atomicAdd(moe->acc + row, __ldg(moe->weight) * bf16_round(v));
+        atomicAdd(moe->acc + row, ld_relaxed_gpu_f32(moe->weight) * bf16_round(v));  // rewritten every layer: no read-only path
         __threadfence();
         if (atomicAdd(moe->cnt + row, 1) == moe->top_k - 1) {
           // every selected expert has added its share: fold the sum into the residual stream
@@ -497,15 +534,24 @@ __device__ void task_gemv_rows(Compute& q, int n_chunks, int mode, bool accumula
 // task: split-K GQA decode attention over 64-position KV pages, merge included
 // ------------------------------------------------------------------------- //
 // One task handles one KV head and one split (a range of pages) of the cache.
-// Pop order: rope row (cos[64] sin[64] fp32, gathered by position), [q/k norm
-// weights 2x128 bf16], the head group's projection output (G query heads, the
-// new key row, the new value row: (G+2) x 128 bf16, raw, contiguous), then
-// `count` x (K page, V page) with count = clamp(n_pages - base, 0, max_pages)
-// read from the state block (the memory stream applies the same rule through
-// DYN_COUNT + REPEAT).  Everything else travels in the instruction words:
-// addresses of the state block, of this head's K / V pages (for the new cache
-// rows), of the head's split records, of its arrival counter and of its slice
-// of the attention output, plus the barrier the merged output releases.
+// The memory stream delivers only the pages: `count` x (K page, V page) with
+// count = clamp(n_pages - base, 0, max_pages) read from the state block (the
+// memory stream applies the same rule through DYN_COUNT + REPEAT).  Everything
+// else travels in the instruction words and is read with ordinary loads: the
+// state block, the rope table, the q/k norm weights, the head group's
+// projection output (G query heads, the new key row, the new value row:
+// (G+2) x 128 bf16, contiguous) behind the barrier the task waits for itself,
+// this head's K / V pages (for the new cache rows), the head's split records,
+// its arrival counter, its slice of the attention output, and the barrier the
+// merged output releases.
+//
+// The page loop has no CTA-wide synchronisation: the eight warps share the 64
+// positions of a page (G = 4: eight each; G = 8: the warps form two groups of
+// four query heads, sixteen positions each), every warp waits for the page
+// entries itself, keeps its own online-softmax state (scores and probabilities
+// never leave registers; exp2 domain) and its own partial output, and the warp
+// that finishes a page last gives its slots back.  The warps' states meet once,
+// in shared memory, after the last page.
 //
 // Each task leaves {G x 128 fp32 unnormalised O, m[G], l[G]} in its record and
 // bumps the head's counter; the task that arrives last merges all records
@@ -528,26 +574,27 @@ struct AttnArgs {
   int* counter;
   __nv_bfloat16* out;  // G*128 outputs of this head
   int b, bpad;         // bpad != 0: `out` is this head's first k group in a k-chunk-major [bpad, *] matrix, row b
+  const float* rope;           // table [position][cos 64 | sin 64] fp32
+  const __nv_bfloat16* nw;     // q norm | k norm weights (2 x 128), or null
+  const __nv_bfloat16* qkv;    // the head group's projection output
+  int wait_bar;                // barrier that orders qkv (0xFFFF: none)
 };
 
 template <int G>
-__device__ void task_attn_decode(Compute& q, const AttnArgs& a) {
+__device__ __noinline__ void task_attn_decode(Compute& q, const AttnArgs& a) {
   constexpr int D = VDC_HEAD_DIM;
-  constexpr int LPP = (G == 4) ? 8 : 16;  // lanes per position in the QK phase
-  constexpr int DPL = D / LPP;            // dims per lane: 16 or 8
-  constexpr int PPW = 32 / LPP;           // positions per warp per round
-  constexpr int ROUNDS = VDC_KV_PAGE / (PPW * kCW);
+  constexpr int NG = G / 4;                  // groups of four query heads
+  constexpr int WPG = kCW / NG;              // warps per group
+  constexpr int PPW = VDC_KV_PAGE / WPG;     // positions of a page per warp: 8 or 16
+  constexpr int ROUNDS = PPW / 4;            // four positions per round (eight lanes each)
   constexpr int REC = G * D + 16 * ((2 * G + 15) / 16);
   Shared* sh = q.sh;
   const Ctx& c = q.c;
   const bool qk_norm = a.flags & VDC_ATTN_QKNORM_BIT;
 
   ATTN_STAMP(0);
-  const int rope_mask = q.pop();
-  int nw_mask = 0;
-  if (qk_norm) nw_mask = q.pop();
-  const int qkv_mask = q.pop();
-  if (q.aborted) return;
+  if (q.tid < 8) sh->att_done[q.tid] = 0;
+  if (a.wait_bar != 0xFFFF && !q.wait_barrier(a.wait_bar, 0x7210)) return;
   ATTN_STAMP(1);
 
   const int pos = ld_relaxed_gpu(a.state + VDC_ST_POS);
@@ -557,232 +604,215 @@ __device__ void task_attn_decode(Compute& q, const AttnArgs& a) {
   const bool owner = count > 0 && a.base_page + count == n_pages;
   const int tail_valid = (pos % VDC_KV_PAGE) + 1;  // valid rows of the last page, new row included
 
-  const float* rope = (const float*)slot_ptr(c, first_slot(rope_mask));
-  const __nv_bfloat16* nw = qk_norm ? (const __nv_bfloat16*)slot_ptr(c, first_slot(nw_mask)) : nullptr;
-  const __nv_bfloat16* qraw = (const __nv_bfloat16*)slot_ptr(c, first_slot(qkv_mask));
-  const __nv_bfloat16* knew = qraw + G * D;
+  const float* rope = a.rope + (size_t)pos * D;
+  const __nv_bfloat16* knew = a.qkv + G * D;
   const __nv_bfloat16* vnew = knew + D;
   __nv_bfloat16* krow = reinterpret_cast<__nv_bfloat16*>(sh->newrows);  // rotated new key row
   __nv_bfloat16* vrow = krow + D;
+  const float scale_log2 = 1.4426950408889634f * rsqrtf((float)D);
 
   // --- prologue: optional per-head RMSNorm, then half-rotation RoPE.  One warp
   // per head: heads 0..G-1 are the queries, "head" G is the new key row.
   for (int head = q.warp; head <= G; head += kCW) {
     const bool is_k = head == G;
-    const __nv_bfloat16* src = is_k ? knew : qraw + head * D;
+    const __nv_bfloat16* src = is_k ? knew : a.qkv + head * D;
     const int i0 = q.lane * 2;  // pairs (i0, i0+64), (i0+1, i0+65)
-    float a0 = __bfloat162float(src[i0]), a1 = __bfloat162float(src[i0 + 1]);
-    float b0 = __bfloat162float(src[i0 + 64]), b1 = __bfloat162float(src[i0 + 65]);
+    const uint32_t lo = ldcg32(src + i0), hi = ldcg32(src + i0 + 64);
+    float a0 = bf_lo(lo), a1 = bf_hi(lo), b0 = bf_lo(hi), b1 = bf_hi(hi);
     if (qk_norm) {
       float ss = warp_sum(a0 * a0 + a1 * a1 + b0 * b0 + b1 * b1);
       const float rstd = rsqrtf(ss / (float)D + a.qk_eps);
-      const __nv_bfloat16* w = nw + (is_k ? D : 0);
+      const __nv_bfloat16* w = a.nw + (is_k ? D : 0);
       a0 = bf16_round(__bfloat162float(w[i0]) * bf16_round(a0 * rstd));
       a1 = bf16_round(__bfloat162float(w[i0 + 1]) * bf16_round(a1 * rstd));
       b0 = bf16_round(__bfloat162float(w[i0 + 64]) * bf16_round(b0 * rstd));
       b1 = bf16_round(__bfloat162float(w[i0 + 65]) * bf16_round(b1 * rstd));
     }
-    const float c0 = rope[i0], c1 = rope[i0 + 1], s0 = rope[64 + i0], s1 = rope[64 + i0 + 1];
+    const float2 cs = __ldg(reinterpret_cast<const float2*>(rope + i0));
+    const float2 sn = __ldg(reinterpret_cast<const float2*>(rope + 64 + i0));
     // x*cos + rotate_half(x)*sin with every product and the sum rounded to bf16,
     // the way a bf16 tensor expression evaluates it
-    const float r0 = bf16_round(bf16_round(a0 * c0) - bf16_round(b0 * s0));
-    const float r1 = bf16_round(bf16_round(a1 * c1) - bf16_round(b1 * s1));
-    const float r64 = bf16_round(bf16_round(b0 * c0) + bf16_round(a0 * s0));
-    const float r65 = bf16_round(bf16_round(b1 * c1) + bf16_round(a1 * s1));
+    const float r0 = bf16_round(bf16_round(a0 * cs.x) - bf16_round(b0 * sn.x));
+    const float r1 = bf16_round(bf16_round(a1 * cs.y) - bf16_round(b1 * sn.y));
+    const float r64 = bf16_round(bf16_round(b0 * cs.x) + bf16_round(a0 * sn.x));
+    const float r65 = bf16_round(bf16_round(b1 * cs.y) + bf16_round(a1 * sn.y));
     if (is_k) {
       krow[i0] = __float2bfloat16_rn(r0);
       krow[i0 + 1] = __float2bfloat16_rn(r1);
       krow[i0 + 64] = __float2bfloat16_rn(r64);
       krow[i0 + 65] = __float2bfloat16_rn(r65);
     } else {
-      float* dst = sh->qrot + head * D;
-      dst[i0] = r0;
-      dst[i0 + 1] = r1;
-      dst[i0 + 64] = r64;
-      dst[i0 + 65] = r65;
+      float* dst = sh->qrot + head * D;  // pre-scaled: scores come out in the exp2 domain
+      dst[i0] = r0 * scale_log2;
+      dst[i0 + 1] = r1 * scale_log2;
+      dst[i0 + 64] = r64 * scale_log2;
+      dst[i0 + 65] = r65 * scale_log2;
     }
   }
-  if (q.tid < D / 8) reinterpret_cast<uint4*>(vrow)[q.tid] = reinterpret_cast<const uint4*>(vnew)[q.tid];
-  compute_sync();
-  q.free_slots(rope_mask | nw_mask | qkv_mask);
+  if (q.tid >= kCT - D / 8) {
+    const int t = q.tid - (kCT - D / 8);
+    reinterpret_cast<uint4*>(vrow)[t] = ldcg128(reinterpret_cast<const uint4*>(vnew) + t);
+  }
+  const unsigned n_ent = 2u * (unsigned)count;  // ring entries: K page, V page, K page, ...
+  q.warp_phase_begin(n_ent, 0u);              // its CTA barrier also publishes qrot / krow / vrow
   ATTN_STAMP(2);
 
-  // per-lane slice of the rotated queries
-  const int sub = q.lane % LPP, pl = q.lane / LPP;
-  float qreg[G][DPL];
+  // QK phase: eight lanes per position, each with two 8-dim pieces (sub, sub + 8) of the row;
+  // PV phase: lane l owns output dims 4l..4l+3 of the warp's four heads.
+  const int hg = q.warp / WPG, slice = (q.warp % WPG) * PPW;
+  const int sub = q.lane & 7, pl = q.lane >> 3;
+  float qreg[4][16];
 #pragma unroll
-  for (int g = 0; g < G; ++g)
+  for (int g = 0; g < 4; ++g)
 #pragma unroll
-    for (int h = 0; h < DPL / 8; ++h) {
-      const float4 lo = *reinterpret_cast<const float4*>(sh->qrot + g * D + (sub + h * 8) * 8);
-      const float4 hi = *reinterpret_cast<const float4*>(sh->qrot + g * D + (sub + h * 8) * 8 + 4);
+    for (int h = 0; h < 2; ++h) {
+      const float* src = sh->qrot + (hg * 4 + g) * D + (sub + h * 8) * 8;
+      const float4 lo = *reinterpret_cast<const float4*>(src);
+      const float4 hi = *reinterpret_cast<const float4*>(src + 4);
       qreg[g][h * 8 + 0] = lo.x; qreg[g][h * 8 + 1] = lo.y; qreg[g][h * 8 + 2] = lo.z; qreg[g][h * 8 + 3] = lo.w;
       qreg[g][h * 8 + 4] = hi.x; qreg[g][h * 8 + 5] = hi.y; qreg[g][h * 8 + 6] = hi.z; qreg[g][h * 8 + 7] = hi.w;
     }
-  const float scale_log2 = 1.4426950408889634f * rsqrtf((float)D);
-
-  float m_run[G], l_run[G], acc[G][2];
+  float m_run[4], l_run[4], acc[4][4];
 #pragma unroll
-  for (int g = 0; g < G; ++g) {
+  for (int g = 0; g < 4; ++g) {
     m_run[g] = -INFINITY;
     l_run[g] = 0.f;
-    acc[g][0] = acc[g][1] = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[g][j] = 0.f;
   }
-  const int pg = q.tid >> 6, dp = q.tid & 63;  // PV phase: position group, dim pair
-  // Every warp walks every page entry itself (no CTA-wide pop): the only CTA barriers of a page
-  // are the one after the scores and the one after the probabilities.  A warp whose wait was
-  // given up keeps joining the barriers; everybody leaves together at the next one.
-  const unsigned n_ent = 2u * (unsigned)count;  // ring entries: K page, V page, K page, ...
-  q.warp_phase_begin(n_ent, 0u);
-  int v_prev = 0;
-  bool bail = false;
   for (int blk = 0; blk < count; ++blk) {
     const int k_mask = q.warp_wait(2u * (unsigned)blk);
-    const bool k_ok = k_mask != kPopAbort;
-    ATTN_STAMP(3 + 4 * (blk & 1));
-    uint8_t* kb = (uint8_t*)slot_ptr(c, first_slot(k_ok ? k_mask : 1));  // a given-up wait computes on slot 0, unused
+    if (k_mask == kPopAbort) break;
+    ATTN_STAMP(3 + 3 * (blk & 1));
+    const uint8_t* kb = (const uint8_t*)slot_ptr(c, first_slot(k_mask));
     const bool last = owner && blk == count - 1;
     const int valid = last ? tail_valid : VDC_KV_PAGE;
-    if (last) {
-      // the page in HBM does not hold the new row yet: patch it in shared memory (warp 0 has
-      // seen the page arrive; the barrier shows the row to the others, who have seen it too)
-      if (k_ok && q.tid < D / 8)
-        reinterpret_cast<uint4*>(kb + (valid - 1) * D * 2)[q.tid] = reinterpret_cast<const uint4*>(krow)[q.tid];
-      compute_sync();
-    }
-    // ---- phase 1: scores = q . k for 64 positions
-    float wm[G];
-#pragma unroll
-    for (int g = 0; g < G; ++g) wm[g] = -INFINITY;
+    const int newpos = last ? tail_valid - 1 : -1;  // this row of the page is not in HBM yet
+    // ---- scores of this warp's positions
+    float s[ROUNDS][4];
 #pragma unroll
     for (int rd = 0; rd < ROUNDS; ++rd) {
-      const int p = rd * (PPW * kCW) + q.warp * PPW + pl;
-      float s[G];
+      const int p = slice + rd * 4 + pl;
+      const uint8_t* kr = (p == newpos) ? reinterpret_cast<const uint8_t*>(krow) : kb + p * (D * 2);
 #pragma unroll
-      for (int g = 0; g < G; ++g) s[g] = 0.f;
+      for (int g = 0; g < 4; ++g) s[rd][g] = 0.f;
 #pragma unroll
-      for (int h = 0; h < DPL / 8; ++h) {
-        const uint4 kv = lds128(kb + p * (D * 2) + (sub + h * 8) * 16);
+      for (int h = 0; h < 2; ++h) {
+        const uint4 kv = lds128(kr + (sub + h * 8) * 16);
         const float kf[8] = {bf_lo(kv.x), bf_hi(kv.x), bf_lo(kv.y), bf_hi(kv.y),
                              bf_lo(kv.z), bf_hi(kv.z), bf_lo(kv.w), bf_hi(kv.w)};
 #pragma unroll
-        for (int g = 0; g < G; ++g)
+        for (int g = 0; g < 4; ++g)
 #pragma unroll
-          for (int j = 0; j < 8; ++j) s[g] = fmaf(qreg[g][h * 8 + j], kf[j], s[g]);
+          for (int j = 0; j < 8; ++j) s[rd][g] = fmaf(qreg[g][h * 8 + j], kf[j], s[rd][g]);
       }
 #pragma unroll
-      for (int g = 0; g < G; ++g) {
-#pragma unroll
-        for (int o = 1; o < LPP; o <<= 1) s[g] += __shfl_xor_sync(0xffffffffu, s[g], o);
-        s[g] = (p < valid) ? s[g] * scale_log2 : -INFINITY;
-        wm[g] = fmaxf(wm[g], s[g]);
-      }
-      if (sub == 0) {
-#pragma unroll
-        for (int g = 0; g < G; ++g) sh->scores[p * G + g] = s[g];
+      for (int g = 0; g < 4; ++g) {
+        s[rd][g] += __shfl_xor_sync(0xffffffffu, s[rd][g], 1);
+        s[rd][g] += __shfl_xor_sync(0xffffffffu, s[rd][g], 2);
+        s[rd][g] += __shfl_xor_sync(0xffffffffu, s[rd][g], 4);
+        if (p >= valid) s[rd][g] = -INFINITY;
       }
     }
+    // ---- online softmax over the warp's positions (values are uniform over the eight lanes of a position)
+    float alpha[4];
 #pragma unroll
-    for (int g = 0; g < G; ++g) {
+    for (int g = 0; g < 4; ++g) {
+      float mx = s[0][g];
 #pragma unroll
-      for (int o = LPP; o < 32; o <<= 1) wm[g] = fmaxf(wm[g], __shfl_xor_sync(0xffffffffu, wm[g], o));
-      if (q.lane == 0) sh->wmax[q.warp * G + g] = wm[g];
-    }
-    compute_sync();  // (A) scores and warp maxima visible; K page fully read; previous P V finished
-    if (sh->aborted) {
-      bail = true;
-      break;
-    }
-    ATTN_STAMP(4 + 4 * (blk & 1));
-    q.free_slots(k_mask | v_prev);
-    if (q.lane == 0) sh->warp_next[q.warp] = q.head + 2u * (unsigned)blk + 1u;
-    // ---- phase 2: running max, rescale factors, probabilities
-    float alpha[G], m_new[G];
+      for (int rd = 1; rd < ROUNDS; ++rd) mx = fmaxf(mx, s[rd][g]);
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+      const float m_new = fmaxf(m_run[g], mx);
+      alpha[g] = (m_new == -INFINITY) ? 1.f : exp2f(m_run[g] - m_new);
+      m_run[g] = m_new;
+      float sum = 0.f;
 #pragma unroll
-    for (int g = 0; g < G; ++g) {
-      float mb = sh->wmax[g];
+      for (int rd = 0; rd < ROUNDS; ++rd) {
+        // HF rounds probabilities to bf16 after the softmax; here they stay fp32
+        s[rd][g] = (m_new == -INFINITY) ? 0.f : exp2f(s[rd][g] - m_new);
+        sum += s[rd][g];
+      }
+      sum += __shfl_xor_sync(0xffffffffu, sum, 8);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 16);
+      l_run[g] = l_run[g] * alpha[g] + sum;
 #pragma unroll
-      for (int w = 1; w < kCW; ++w) mb = fmaxf(mb, sh->wmax[w * G + g]);
-      m_new[g] = fmaxf(m_run[g], mb);
-      alpha[g] = (m_new[g] == -INFINITY) ? 1.f : exp2f(m_run[g] - m_new[g]);
-      m_run[g] = m_new[g];
+      for (int j = 0; j < 4; ++j) acc[g][j] *= alpha[g];
     }
-    for (int t = q.tid; t < VDC_KV_PAGE * G; t += kCT) {
-      const int g = t % G;
-      const float s = sh->scores[t];
-      // HF rounds probabilities to bf16 after the softmax; here they stay fp32
-      sh->probs[t] = (m_new[g] == -INFINITY) ? 0.f : exp2f(s - m_new[g]);
-    }
+    // ---- O += P V
     const int v_mask = q.warp_wait(2u * (unsigned)blk + 1u);
-    uint8_t* vb = (uint8_t*)slot_ptr(c, first_slot(v_mask == kPopAbort ? 1 : v_mask));
-    if (last && v_mask != kPopAbort && q.tid < D / 8)
-      reinterpret_cast<uint4*>(vb + (valid - 1) * D * 2)[q.tid] = reinterpret_cast<const uint4*>(vrow)[q.tid];
-    compute_sync();  // (B) probabilities (and the patched V row) visible
-    if (sh->aborted) {
-      bail = true;
-      break;
-    }
-    ATTN_STAMP(5 + 4 * (blk & 1));
-    // ---- phase 3: O += P V over this thread's 16 positions, two dims per thread
+    if (v_mask == kPopAbort) break;
+    ATTN_STAMP(4 + 3 * (blk & 1));
+    const uint8_t* vb = (const uint8_t*)slot_ptr(c, first_slot(v_mask));
 #pragma unroll
-    for (int g = 0; g < G; ++g) {
-      acc[g][0] *= alpha[g];
-      acc[g][1] *= alpha[g];
-      l_run[g] *= alpha[g];
-    }
-    const int p_end = min(pg * 16 + 16, valid);
-    for (int p = pg * 16; p < p_end; ++p) {
-      const uint32_t vv = *reinterpret_cast<const uint32_t*>(vb + p * (D * 2) + dp * 4);
-      const float v0 = bf_lo(vv), v1 = bf_hi(vv);
+    for (int rd = 0; rd < ROUNDS; ++rd)
 #pragma unroll
-      for (int g = 0; g < G; ++g) {
-        const float pr = sh->probs[p * G + g];
-        l_run[g] += pr;
-        acc[g][0] = fmaf(pr, v0, acc[g][0]);
-        acc[g][1] = fmaf(pr, v1, acc[g][1]);
+      for (int pp = 0; pp < 4; ++pp) {
+        const int p = slice + rd * 4 + pp;
+        float pr[4];
+#pragma unroll
+        for (int g = 0; g < 4; ++g) pr[g] = __shfl_sync(0xffffffffu, s[rd][g], pp * 8);
+        if (p < valid) {  // uniform over the warp
+          const uint8_t* vr = (p == newpos) ? reinterpret_cast<const uint8_t*>(vrow) : vb + p * (D * 2);
+          const uint2 vv = *reinterpret_cast<const uint2*>(vr + q.lane * 8);
+          const float vf[4] = {bf_lo(vv.x), bf_hi(vv.x), bf_lo(vv.y), bf_hi(vv.y)};
+#pragma unroll
+          for (int g = 0; g < 4; ++g)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[g][j] = fmaf(pr[g], vf[j], acc[g][j]);
+        }
       }
-    }
-    v_prev = v_mask;
+    // ---- the warp is done with this page pair; the last of the eight gives the slots back
     __syncwarp();
-    if (q.lane == 0) sh->warp_next[q.warp] = q.head + 2u * (unsigned)blk + 2u;
-    ATTN_STAMP(6 + 4 * (blk & 1));
+    if (q.lane == 0) {
+      if (atomicAdd(&sh->att_done[blk & 7], 1) == kCW - 1) {
+        sh->att_done[blk & 7] = 0;
+        atomicOr(&sh->slot_avail, (uint32_t)(k_mask | v_mask) & kSlotMaskAll);
+      }
+      sh->warp_next[q.warp] = q.head + 2u * (unsigned)blk + 2u;
+    }
+    ATTN_STAMP(5 + 3 * (blk & 1));
   }
   if (q.lane == 0) sh->warp_next[q.warp] = 0xFFFFFFFFu;
-  if (bail) {
-    q.aborted = true;
-    return;
+  // ---- the warps' states meet in shared memory: red[warp][4 heads][128], then m and l
+  float* red = sh->red;
+  *reinterpret_cast<float4*>(red + (q.warp * 4 + 0) * D + q.lane * 4) = make_float4(acc[0][0], acc[0][1], acc[0][2], acc[0][3]);
+  *reinterpret_cast<float4*>(red + (q.warp * 4 + 1) * D + q.lane * 4) = make_float4(acc[1][0], acc[1][1], acc[1][2], acc[1][3]);
+  *reinterpret_cast<float4*>(red + (q.warp * 4 + 2) * D + q.lane * 4) = make_float4(acc[2][0], acc[2][1], acc[2][2], acc[2][3]);
+  *reinterpret_cast<float4*>(red + (q.warp * 4 + 3) * D + q.lane * 4) = make_float4(acc[3][0], acc[3][1], acc[3][2], acc[3][3]);
+  if (q.lane < 4) {
+    float mv = m_run[0], lv = l_run[0];
+#pragma unroll
+    for (int g = 1; g < 4; ++g)
+      if (q.lane == g) {
+        mv = m_run[g];
+        lv = l_run[g];
+      }
+    red[kCW * 4 * D + q.warp * 8 + q.lane] = mv;
+    red[kCW * 4 * D + q.warp * 8 + 4 + q.lane] = lv;
   }
-  q.warp_phase_end(n_ent);  // CTA barrier: everyone is done with the last V page
+  q.warp_phase_end(n_ent);  // CTA barrier: every warp is done with the pages and has published its state
   if (q.aborted) return;
-  q.free_slots(v_prev);
   ATTN_STAMP(11);
-  // cross position-group reduction: groups 1..3 publish, group 0 adds and writes the record
-  float* red = sh->red;  // [3][G][128] then l: [3][G]
-  if (pg > 0) {
-#pragma unroll
-    for (int g = 0; g < G; ++g) {
-      red[((pg - 1) * G + g) * D + dp * 2] = acc[g][0];
-      red[((pg - 1) * G + g) * D + dp * 2 + 1] = acc[g][1];
-      if (dp == 0) red[3 * G * D + (pg - 1) * G + g] = l_run[g];
-    }
-  }
-  compute_sync();
   float* rec = a.records + (size_t)a.split * REC;
-  if (pg == 0) {
+  for (int o = q.tid; o < G * D; o += kCT) {
+    const int g = o / D, d = o % D, w0 = (g >> 2) * WPG, gg = g & 3;
+    const float* ml = red + kCW * 4 * D;
+    float m = -INFINITY;
 #pragma unroll
-    for (int g = 0; g < G; ++g) {
-      float o0 = acc[g][0], o1 = acc[g][1], l = l_run[g];
+    for (int k = 0; k < WPG; ++k) m = fmaxf(m, ml[(w0 + k) * 8 + gg]);
+    float num = 0.f, l = 0.f;
 #pragma unroll
-      for (int r = 0; r < 3; ++r) {
-        o0 += red[(r * G + g) * D + dp * 2];
-        o1 += red[(r * G + g) * D + dp * 2 + 1];
-        l += red[3 * G * D + r * G + g];
-      }
-      *reinterpret_cast<float2*>(rec + g * D + dp * 2) = make_float2(o0, o1);
-      if (dp == 0) {
-        rec[G * D + g] = m_run[g];
-        rec[G * D + G + g] = l;
-      }
+    for (int k = 0; k < WPG; ++k) {
+      const float mw = ml[(w0 + k) * 8 + gg];
+      const float wgt = (mw == -INFINITY) ? 0.f : exp2f(mw - m);
+      num = fmaf(wgt, red[((w0 + k) * 4 + gg) * D + d], num);
+      l = fmaf(wgt, ml[(w0 + k) * 8 + 4 + gg], l);
+    }
+    rec[o] = num;
+    if (d == 0) {
+      rec[G * D + g] = m;
+      rec[G * D + G + g] = l;
     }
   }
   if (owner && q.tid >= 64 && q.tid < 64 + 2 * (D / 8)) {

@@ -561,7 +561,8 @@ __device__ void load_port(const Ctx& c, int port) {
     const int slot = req >= kSlots ? req : __ffs(word) - 1;
     uint64_t* bar = &sh->full[e];
 
-    if ((opcode & VDC_F_BARRIER) && !(opcode & VDC_F_WRITEBACK)) {
+    // (an XVEC hand-over carries its barrier to the compute task, which waits for it itself)
+    if ((opcode & VDC_F_BARRIER) && !(opcode & VDC_F_WRITEBACK) && (opcode >> VDC_FLAG_BITS) != 32) {
       if (!wait_global_barrier(c, inst.num_slots >> 6, role, (int)cursor, opcode)) return;
     }
     void* dst = slot < kSlots ? slot_ptr(c, slot) : nullptr;

@@ -59,8 +59,10 @@ for _m in re.finditer(r"X\((OP_\w+),\s*VDC_MOP\((\d+),\s*([^)]*)\)\)", _src):
         _flags |= _flagval[_t.strip()]
     OPCODES[_m.group(1)] = (int(_m.group(2)) << FLAG_BITS) | _flags
     MEMORY_OPS.append(_m.group(1))
-for _m in re.finditer(r"X\((OP_\w+),\s*(0x[0-9A-Fa-f]+)\)", _src):
+OP_WORDS = {}      # compute opcode value -> 8-byte words it occupies before optional trailing words
+for _m in re.finditer(r"X\((OP_\w+),\s*(0x[0-9A-Fa-f]+),\s*(\d+)\)", _src):
     OPCODES[_m.group(1)] = int(_m.group(2), 16)
+    OP_WORDS[int(_m.group(2), 16)] = int(_m.group(3))
     COMPUTE_OPS.append(_m.group(1))
 globals().update(OPCODES)
 

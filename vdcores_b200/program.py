@@ -121,6 +121,19 @@ class Program:
                  address=src.addr, flags=flags)
         self.bytes_loaded[sm] += src.nbytes
 
+    def load_x(self, sm, src: Src):
+        """An activation vector for a compute task.  A plain source becomes an XVEC hand-over: slots are
+        allocated, the task waits for `src.wait` itself and copies the vector from global memory with
+        ordinary loads.  A gathered source (an embedding row) still goes through the copy engine."""
+        if src.indirect is not None:
+            return self.load(sm, src, default_port=1)
+        assert src.nbytes % 16 == 0 and src.addr % 16 == 0 and 0 < src.nbytes <= 32768
+        flags, bar = 0, 0
+        if src.wait is not None:
+            flags, bar = isa.F_BARRIER, src.wait
+        self.mem(sm, isa.OP_ALLOC_XVEC, size=src.nbytes, nslot=slots_for(src.nbytes), bar=bar, address=src.addr,
+                 flags=flags)
+
     def store(self, sm, dst: Dst):
         assert dst.nbytes % 16 == 0 and dst.addr % 16 == 0, (dst.nbytes, dst.addr)
         assert 0 < dst.nbytes <= SLOT * 4
@@ -248,7 +261,7 @@ class Program:
         assert x.nbytes == K * 2
         if norm_w is not None:
             self.load(sm, norm_w, default_port=1)
-        self.load(sm, x, default_port=1)
+        self.load_x(sm, x)
         self.raw_address(sm, out.addr, 24, release=out.release)
         if mode == isa.GEMV_MODE_ARGMAX:
             assert pair_out is not None and row_base % R == 0
@@ -346,11 +359,9 @@ class Program:
         head's first k group inside a k-chunk-major [Bpad, q_width] matrix and the
         outputs go to its row b (batched decode)."""
         page_bytes = isa.KV_PAGE * isa.HEAD_DIM * 2
-        assert qkv.nbytes == (G + 2) * isa.HEAD_DIM * 2
-        self.load(sm, rope, default_port=1)
-        if norm_w is not None:
-            self.load(sm, norm_w, default_port=1)
-        self.load(sm, qkv, default_port=1)
+        assert qkv.nbytes == (G + 2) * isa.HEAD_DIM * 2 and qkv.addr % 16 == 0 and qkv.indirect is None
+        # the rope row is table + position * 512 bytes: the task reads the position from the state block itself
+        assert rope.indirect is None or (rope.indirect[0] == state_addr + 4 * isa.ST_POS and rope.indirect[1] == 9)
         # The page ids of up to 32 pages are fetched with one load (a word per lane of the control
         # warp); each trip of the loop then takes its page from there, so no load sits between
         # two page copies.  Longer ranges are cut into segments of 32 pages.
@@ -370,10 +381,15 @@ class Program:
         flags = (isa.ATTN_QKNORM_BIT if norm_w is not None else 0) | (isa.ATTN_PACKED_BIT if packed else 0)
         self.comp(sm, op, max_pages, base_page, flags)
         self.comp(sm, isa.OP_EXT, e >> 16, e & 0xFFFF, n_splits)
+        a48 = lambda a: (a & 0xFFFF, (a >> 16) & 0xFFFF, (a >> 32) & 0xFFFF)
         for addr in (state_addr, k_page_addr, v_page_addr, records_addr, counter_addr, out_addr):
             assert 0 <= addr < 1 << 48
-            self.comp(sm, isa.OP_EXT, addr & 0xFFFF, (addr >> 16) & 0xFFFF, (addr >> 32) & 0xFFFF)
+            self.comp(sm, isa.OP_EXT, *a48(addr))
         self.comp(sm, isa.OP_EXT, split, release, (packed[0] | (packed[1] // 16) << 8) if packed else 0)
+        for addr in (rope.addr, norm_w.addr if norm_w is not None else 0, qkv.addr):
+            assert 0 <= addr < 1 << 48
+            self.comp(sm, isa.OP_EXT, *a48(addr))
+        self.comp(sm, isa.OP_EXT, 0xFFFF if qkv.wait is None else qkv.wait, 0, 0)
 
     # ------------------------------------------------------------------ batched decode (tensor cores)
     def gemm_tc(self, sm, *, w_addr, N, K, k_len, Kc, G, x_addr, B, Bpad, out_addr, mode, x_wait: Optional[int] = None,
