@@ -85,15 +85,29 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def cpu_oracle_tokens_per_s(n_layers_sample=2, steps=2, threads=None):
-    """Times the CPU oracle on a bounded sample of the workload: `n_layers_sample`
-    Llama-3.1-8B-shaped layers plus the final norm and vocabulary projection,
-    `steps` decode steps at context PROMPT_LEN, extrapolated linearly to 32 layers."""
+def oracle_cfg(model, wkind):
+    from oracle import decode_oracle as O
+    import dataclasses
+    base = {"llama31-8b": O.LLAMA31_8B, "qwen3-8b": O.QWEN3_8B, "qwen3-30b-a3b": O.QWEN3_30B_A3B}[model]
+    return dataclasses.replace(base, wkind=wkind)
+
+
+def cpu_oracle_tokens_per_s(model="llama31-8b", wkind="bf16", n_layers_sample=2, steps=2, threads=None,
+                            budget_s=25.0):
+    """Times the CPU oracle (the reference's PyTorch decode math) on a bounded sample of the workload:
+    `n_layers_sample` layers of the named shape plus the final norm and vocabulary projection, up to
+    `steps` decode steps at the prompt length, stopping early once `budget_s` is spent.  The layer
+    time is scaled to the model's depth.  Returns (tokens/s, threads, description, steps timed)."""
+    import dataclasses
     import torch
     from oracle import decode_oracle as O
     threads = threads or os.cpu_count()
     torch.set_num_threads(threads)
-    cfg = O.DecodeConfig(n_layers=n_layers_sample)
+    full = oracle_cfg(model, wkind)
+    n_layers_sample = min(n_layers_sample, full.n_layers)
+    cfg = dataclasses.replace(full, n_layers=n_layers_sample)
+    if cfg.n_experts:
+        cfg = dataclasses.replace(cfg, n_experts=max(cfg.top_k, 16))   # a token touches top_k experts: 16 are enough to draw from
     gen = torch.Generator().manual_seed(0)
     layers = [O.LayerWeights.random(cfg, gen) for _ in range(n_layers_sample)]
     lm_head = O.randn_bf16(gen, cfg.vocab, cfg.hidden)
@@ -116,27 +130,38 @@ def cpu_oracle_tokens_per_s(n_layers_sample=2, steps=2, threads=None):
         return t1 - t0, t2 - t1
     one(PROMPT_LEN)                                   # warm-up
     tl, th = [], []
+    t_start = time.perf_counter()
     for s in range(steps):
         a, b = one(PROMPT_LEN + 1 + s)
         tl.append(a)
         th.append(b)
-    per_token = statistics.mean(tl) / n_layers_sample * 32 + statistics.mean(th)
-    return 1.0 / per_token, threads, (f"{n_layers_sample} of 32 layers + final norm/lm_head/argmax, {steps} steps at "
-                                      f"context {PROMPT_LEN}, layer time scaled x{32 // n_layers_sample}")
+        if time.perf_counter() - t_start > budget_s:
+            break
+    per_token = statistics.mean(tl) / n_layers_sample * full.n_layers + statistics.mean(th)
+    desc = (f"{model} shape, {wkind}: {n_layers_sample} of {full.n_layers} layers + final norm/lm_head/argmax, "
+            f"{len(tl)} steps at context {PROMPT_LEN}, layer time scaled x{full.n_layers / n_layers_sample:g}, "
+            f"host BLAS bf16 linears (FAST_LINEAR)")
+    return 1.0 / per_token, threads, desc, len(tl)
 
 
 def run_reference(args):
-    """The reference arm: its PyTorch decode math on the host CPU (rank 0 only)."""
+    """The reference arm: its PyTorch decode math on the host CPU (rank 0 only).  Every step of the
+    arm is a bounded sample: `layers` of the model's layers are run and the layer time is scaled."""
     if int(os.environ.get("RANK", "0")) != 0:
         return
-    steps = max(1, min(args.steps, 3))
-    tps, cores, sample = cpu_oracle_tokens_per_s(n_layers_sample=2, steps=steps)
+    global PROMPT_LEN
+    PROMPT_LEN = {"llama31-8b": 2048, "qwen3-8b": 4096, "qwen3-30b-a3b": 1024}[args.model]
+    sample_layers = 8 if args.model == "llama31-8b" else 4
+    tps, cores, sample, timed = cpu_oracle_tokens_per_s(args.model, args.wkind, n_layers_sample=sample_layers,
+                                                        steps=max(1, args.steps), budget_s=60.0)
     line = {
         "impl": "reference", "metric": METRIC, "value": tps, "unit": "tokens/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 / tps, "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "Llama-3.1-8B shape, bf16, batch 1, 2048-token prompt, greedy decode",
-                   "timing": "CPU oracle of the reference's PyTorch decode math on a bounded sample"},
+        "steps": timed, "steps_requested": args.steps, "warmup": 1, "ms_per_step": 1000.0 / tps,
+        "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": args.wkind, "data": "synthetic",
+        "config": {"workload": f"{args.model} shape, {args.wkind}, batch 1, {PROMPT_LEN}-token prompt, greedy decode",
+                   "timing": "CPU oracle of the reference's PyTorch decode math; each step is a bounded sample "
+                             "(see cpu_baseline.sample), stopped after 60 s of timed steps"},
         "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -191,13 +216,17 @@ def run_gpu(args):
         # tensor parallel: every rank builds the same full model (same seed), prefills it with the
         # PyTorch path, keeps its shard of the weights and of the KV cache, and drops the rest
         from vdcores_b200.tp import TPDecodeEngine
-        full = DecodeEngine(cfg, max_seq=max_seq, device=dev, max_steps=8)
+        full = DecodeEngine(cfg, max_seq=max_seq, device=dev, max_steps=W + K + 8)
         full.init_random_weights(seed=0)
         first = full.prefill(prompt)
         eng = TPDecodeEngine(cfg, max_seq=max_seq, rank=rank, world=world, device=dev, max_steps=2 * (W + K) + 16)
         dbg('prefill done')
         eng.load_from_full(full, PROMPT_LEN)
         dbg('shard loaded')
+        # the single-GPU engine every rank still holds decodes the same W + K tokens: the sharded run
+        # is checked against them below (a correctness bit in the JSON line)
+        full.set_state(PROMPT_LEN, first)
+        single_gpu_tokens = full.generate(W + K)
         del full
         torch.cuda.empty_cache()
         tokens_per_step, scaling = 1, "strong"
@@ -268,6 +297,11 @@ def run_gpu(args):
         dbg('process group destroyed')
     if rank != 0:
         return
+    tokens_match, match_prefix = None, None
+    if world > 1:
+        ref_tokens = single_gpu_tokens[W:W + K]
+        tokens_match = tokens == ref_tokens
+        match_prefix = next((i for i, (a, b) in enumerate(zip(tokens, ref_tokens)) if a != b), len(tokens))
     peak, peak_kind = measured_peaks()
     mid_pos = pos0 + K // 2
     bytes_per_launch = eng.algorithmic_bytes(mid_pos)
@@ -280,7 +314,7 @@ def run_gpu(args):
         "config": {"workload": (f"{args.model} shape ({cfg.n_layers} layers, hidden {cfg.hidden}, {cfg.n_heads}q/"
                                 f"{cfg.n_kv_heads}kv heads, FFN {cfg.ffn}, vocab {cfg.vocab}), {args.wkind} projections, "
                                 f"batch {args.batch}, {PROMPT_LEN}-token prompt{'s' if args.batch > 1 else ''} prefilled, greedy decode"),
-                   "l2": "inputs larger than L2: every step streams ~15 GB of weights through a 126 MB L2",
+                   "l2": f"inputs larger than L2: every step streams {bytes_per_launch / 1e9:.2f} GB per GPU through a 126 MB L2",
                    "parallelism": parallelism,
                    "num_sms": eng.num_sms, "kv_splits": eng.n_splits, "first_tokens": tokens[:4],
                    **({"layers": args.layers, "note": "reduced-depth profiling case, not a benchmark result"}
@@ -294,10 +328,13 @@ def run_gpu(args):
                  "h2d_bytes_per_step": 4 * tokens_per_step, "d2h_bytes_per_step": 4 * tokens_per_step}
                 if not args.no_e2e else None),
         "gpu_launches": K * eng.launches_per_step,
+        # greedy ids of the sharded run against the single-GPU engine on the same weights and prompt; a random-init
+        # model has near-ties, after the first one the two trajectories differ legitimately (prefix = steps before it)
+        **({"tokens_match_single_gpu": tokens_match, "tokens_match_prefix": match_prefix} if tokens_match is not None else {}),
         "clocks": clk.summary(),
     }
     if not args.no_cpu_baseline:
-        tps, cores, sample = cpu_oracle_tokens_per_s(n_layers_sample=2, steps=2)
+        tps, cores, sample, _ = cpu_oracle_tokens_per_s(args.model, args.wkind, n_layers_sample=2, steps=3, budget_s=20.0)
         line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample}
     print(json.dumps(line))
 

@@ -278,6 +278,56 @@ def test_wait_budget_returns_status_instead_of_hanging(cuda_device):
     assert float((torch.ones(8, device=dev) * 2).sum()) == 16.0
 
 
+def test_gemv_gives_up_together_when_its_activation_never_arrives(cuda_device):
+    """A projection whose activation barrier nobody releases, next to one that streams normally:
+    the waiting task reports the barrier, the streaming task's warp pairs leave their loop together
+    (no member is left alone at a pair barrier), the kernel retires and the context stays usable."""
+    from vdcores_b200 import isa, runtime
+    from vdcores_b200.program import Dst, Program, Src
+    dev = cuda_device
+    K, M = 1024, 2048
+    w, x = seeded((M, K), 41, 0.02).to(dev), seeded((K,), 42).to(dev)
+    y = torch.zeros(2 * M, dtype=BF16, device=dev)
+    P = Program(2)
+    b = P.new_barrier()
+    P.bar_counts[b] = 1                                    # nobody counts it down
+    P.gemv(0, w_addr=w.data_ptr(), n_rows=M, K=K, R=16, x=Src(x.data_ptr(), K * 2, wait=b),
+           out=Dst(y.data_ptr(), M * 2, "store"))
+    for _ in range(8):                                      # SM 1 keeps streaming while SM 0 waits
+        P.gemv(1, w_addr=w.data_ptr(), n_rows=M, K=K, R=16, x=Src(x.data_ptr(), K * 2),
+               out=Dst(y.data_ptr() + M * 2, M * 2, "store"))
+    P.insts_per_sm = 64
+    c, m, bars = P.finalize()
+    prof = torch.zeros(2 * isa.NUM_PROFILE_EVENTS, dtype=torch.int64, device=dev)
+    with pytest.raises(runtime.VdcError) as ei:
+        runtime.launch_dae(2, 0, torch.from_numpy(c).to(dev), torch.from_numpy(m).to(dev), None,
+                           torch.from_numpy(bars).to(dev), prof, 0, timeout_ns=50_000_000, insts_per_sm=64)
+    assert ei.value.code == isa.ERR_TIMEOUT and ei.value.status["bar"] == b and ei.value.status["sm"] == 0
+    assert float((torch.ones(8, device=dev) * 2).sum()) == 16.0
+    # a task that expects one more weight chunk than its memory stream delivers: the pair that owns
+    # the missing chunk gives up inside the streaming loop, both of its warps together
+    P3 = Program(1)
+    P3.gemv(0, w_addr=w.data_ptr(), n_rows=M, K=K, R=16, x=Src(x.data_ptr(), K * 2), out=Dst(y.data_ptr(), M * 2, "store"))
+    op, n_chunks, a1, a2 = P3.c[0][0]
+    P3.c[0][0] = (op, n_chunks + 1, a1, a2)
+    P3.insts_per_sm = 16
+    c, m, bars = P3.finalize()
+    with pytest.raises(runtime.VdcError) as ei:
+        runtime.launch_dae(1, 0, torch.from_numpy(c).to(dev), torch.from_numpy(m).to(dev), None,
+                           torch.from_numpy(bars).to(dev), prof, 0, timeout_ns=20_000_000, insts_per_sm=16)
+    assert ei.value.code == isa.ERR_TIMEOUT
+    assert float((torch.ones(8, device=dev) * 2).sum()) == 16.0
+    # and the same streams run to completion once the barrier is released by a third SM
+    P2 = Program(3)
+    b2 = P2.new_barrier()
+    P2.gemv(0, w_addr=w.data_ptr(), n_rows=M, K=K, R=16, x=Src(x.data_ptr(), K * 2, wait=b2),
+            out=Dst(y.data_ptr(), M * 2, "store"))
+    P2.copy(2, Src(x.data_ptr(), 256), Dst(y.data_ptr() + M * 2, 256, release=b2), 256)
+    y.zero_()
+    run_program(P2, dev)
+    assert O.rel_l2(y[:M].cpu(), O.linear(x.cpu()[None], w.cpu())[0]) < 2e-3
+
+
 @pytest.mark.parametrize("M,K,R,n_sms", [(256, 4096, 8, 4), (64, 14336, 2, 2), (128, 512, 16, 1)])
 def test_gemv_fp8_store(cuda_device, M, K, R, n_sms):
     """e4m3 weights with per-row fp32 scales, dequantised in registers; the oracle

@@ -36,7 +36,7 @@ __device__ __forceinline__ int compute_op_words(uint16_t op) {
   }
 }
 
-__device__ void compute_core(const Ctx& c, const VdcCInst* __restrict__ insts, int n_insts, int tid) {
+__device__ __forceinline__ void compute_core(const Ctx& c, const VdcCInst* __restrict__ insts, int n_insts, int tid) {
   Compute q{c, c.sh, tid, tid >> 5, tid & 31, 0u, 0u, 0u, false, 0ull};
   uint32_t count = 0;
   int n_traced = 0;

@@ -7,6 +7,11 @@
 
 namespace vdc {
 
+// Tasks are inlined into the kernel: measured on B200, the same GEMV loop behind a real function call
+// (its queue state then lives in local memory, shared-memory accesses go through generic pointers)
+// streams at 3.5 TB/s instead of 6.4 TB/s.
+#define VDC_TASK __device__ __forceinline__
+
 // ------------------------------------------------------------------------- //
 // compute virtual core: queue access
 // ------------------------------------------------------------------------- //
@@ -296,7 +301,7 @@ struct PeerOut {
 };
 
 template <int R>
-__device__ __noinline__ void task_gemv_rows(Compute& q, int n_chunks, int mode, bool accumulate, bool norm, int K, int row_base,
+VDC_TASK void task_gemv_rows(Compute& q, int n_chunks, int mode, bool accumulate, bool norm, int K, int row_base,
                                const float* scales = nullptr, int wfmt = 0, const MoeDown* moe = nullptr,
                                bool dyn = false, const PeerOut* peers = nullptr) {
   Shared* sh = q.sh;
@@ -371,7 +376,7 @@ __device__ __noinline__ void task_gemv_rows(Compute& q, int n_chunks, int mode, 
   }
   if (wfmt == 2) {
     // NVFP4 block dots run in half precision: the activation vector becomes fp16 in place
-    if (norm) compute_sync();
+    compute_sync();  // the vector was written (copied or normalised) by other threads
     for (int i = q.tid * 2; i < K; i += kCT * 2) {
       const uint32_t xv = *reinterpret_cast<const uint32_t*>(x + i * 2);
       const __half2 h = __floats2half2_rn(bf_lo(xv), bf_hi(xv));
@@ -581,7 +586,7 @@ struct AttnArgs {
 };
 
 template <int G>
-__device__ __noinline__ void task_attn_decode(Compute& q, const AttnArgs& a) {
+VDC_TASK void task_attn_decode(Compute& q, const AttnArgs& a) {
   constexpr int D = VDC_HEAD_DIM;
   constexpr int NG = G / 4;                  // groups of four query heads
   constexpr int WPG = kCW / NG;              // warps per group

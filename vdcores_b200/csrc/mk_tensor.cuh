@@ -186,7 +186,7 @@ __device__ __forceinline__ void gemm_epilogue_flush(const GemmTc& g, int b, EpiA
 #else
 #define TCS(i)
 #endif
-__device__ __noinline__ void task_gemm_tc(Compute& q, const GemmTc& g) {
+VDC_TASK void task_gemm_tc(Compute& q, const GemmTc& g) {
   Shared* sh = q.sh;
   const Ctx& c = q.c;
 #ifdef VDC_TC_PROFILE

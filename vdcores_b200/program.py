@@ -226,6 +226,73 @@ class Program:
         assert 0 <= base <= 0xFFFF
         self.m[sm][-1] = (op, size, base, arg, addr)
 
+    # ------------------------------------------------------------------ tensor-map copies, registers, loops
+    @staticmethod
+    def _coords(coords):
+        assert 1 <= len(coords) <= 4 and all(0 <= c < 0xFFFF for c in coords)
+        c = list(coords) + [0] * (4 - len(coords))
+        return c[0] | (c[1] << 16) | (c[2] << 32) | (c[3] << 48)
+
+    def tensor_load(self, sm, *, tma_id, rank, coords, nbytes, wait=None, port=0, group=False, jump=False):
+        """Tiled `cp.async.bulk.tensor` load of one box of tensor map `tma_id` (rank 1..5; a rank-5 map takes
+        four coordinates, its innermost one is fixed to 0) at `coords` (innermost first) into fresh slots.
+        group: the map id and the barrier id shift with the enclosing LOOP (reference
+        python/dae/instructions.py TmaTensor, include/dae/pipeline/ldwarp.cuh:63-168)."""
+        op = {1: isa.OP_ALLOC_TMA_LOAD_TENSOR_1D, 2: isa.OP_ALLOC_TMA_LOAD_2D, 3: isa.OP_ALLOC_TMA_LOAD_3D,
+              4: isa.OP_ALLOC_TMA_LOAD_4D, 5: isa.OP_ALLOC_TMA_LOAD_5D_FIX0}[rank]
+        flags = (isa.F_PORT if port else 0) | (isa.F_GROUP if group else 0) | (isa.F_JUMP if jump else 0)
+        bar = 0
+        if wait is not None:
+            flags |= isa.F_BARRIER
+            bar = wait
+        self.mem(sm, op, size=nbytes, nslot=slots_for(nbytes), bar=bar, arg=tma_id, address=self._coords(coords),
+                 flags=flags)
+        self.bytes_loaded[sm] += nbytes
+
+    def tensor_store(self, sm, *, tma_id, rank, coords, nbytes, reduce=False, release=None, group=False, jump=False,
+                     n_releases=1):
+        """Tiled store (or reduce-add, ranks 2 and 3: the element type comes from the map) of the slots a task
+        writes back (reference include/dae/pipeline/stwarp.cuh:38-145).  n_releases: how many times the
+        instruction executes (a loop body), for the barrier's initial count."""
+        if reduce:
+            op = {2: isa.OP_ALLOC_WB_TMA_REDUCE_ADD_2D, 3: isa.OP_ALLOC_WB_TMA_REDUCE_ADD_3D}[rank]
+        else:
+            op = {2: isa.OP_ALLOC_WB_TMA_STORE_2D, 3: isa.OP_ALLOC_WB_TMA_STORE_3D, 4: isa.OP_ALLOC_WB_TMA_STORE_4D,
+                  5: isa.OP_ALLOC_WB_TMA_STORE_5D_FIX0}[rank]
+        flags = (isa.F_GROUP if group else 0) | (isa.F_JUMP if jump else 0)
+        bar = 0
+        if release is not None:
+            flags |= isa.F_BARRIER
+            bar = release
+            if not group:
+                self.bar_counts[bar] += n_releases
+        self.mem(sm, op, size=nbytes, nslot=slots_for(nbytes), bar=bar, arg=tma_id, address=self._coords(coords),
+                 flags=flags)
+
+    def reg_store(self, sm, reg, nbytes):
+        """Slots for a task's result that stays in shared memory: the producing task's write-back is skipped,
+        a later reg_load(reg) hands the same slots to the consuming task, which frees them (reference
+        python/dae/instructions.py RegStore / RegLoad, include/dae/pipeline/ldwarp.cuh:169-183)."""
+        assert 0 <= reg < 4
+        self.mem(sm, isa.OP_ALLOC_WB_REG_STORE, size=reg, nslot=slots_for(nbytes))
+
+    def reg_load(self, sm, reg, special_slot=None):
+        assert 0 <= reg < 4
+        slot = isa.NUM_SLOTS + (reg if special_slot is None else special_slot)
+        self.mem(sm, isa.OP_ALLOC_REG_LOAD, size=reg, nslot=slot)
+
+    def loop_m(self, sm, count, pc, *, bar_shift=0, tma_shift=0, reg=0):
+        """Memory-stream loop: jumps back to instruction `pc` count-1 times; before every further trip the
+        barrier ids and tensor-map ids of GROUP-flagged instructions move on by bar_shift / tma_shift
+        (reference python/dae/instructions.py LoopM, include/dae/pipeline/allocwarp.cuh:148-166)."""
+        assert 0 <= reg < 32 and 0 <= bar_shift < 1024 and 0 <= tma_shift < 1 << 16 and 0 <= pc < 0xFFFF
+        self.m[sm].append((isa.OP_LOOP, count, reg, 0, pc | ((bar_shift << 6) << 32) | (tma_shift << 48)))
+
+    def loop_c(self, sm, count, pc):
+        """Compute-stream loop: jumps back to compute instruction `pc` count-1 times (reference LoopC,
+        include/dae/compute_dispatch.cuh:311-321)."""
+        self.comp(sm, isa.OP_LOOPC, count, pc)
+
     # ------------------------------------------------------------------ tasks
     def copy(self, sm, src: Src, dst: Dst, nbytes: int):
         self.load(sm, src)
