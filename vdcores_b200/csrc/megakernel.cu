@@ -67,7 +67,11 @@ __device__ __forceinline__ void compute_core(const Ctx& c, const VdcCInst* __res
     }
     w_pc = q.pc;
     // task trace: (start, end) global-timer stamps of the first 56 tasks of this SM
+#ifdef VDC_TRACE_GEMV
+    const bool traced = tid == 0 && n_traced < 24 && ci.opcode != 0x7000;   // rows 64..127 hold the GEMV stamps
+#else
     const bool traced = tid == 0 && n_traced < 56 && ci.opcode != 0x7000;
+#endif
     if (traced) c.profile[c.sm * VDC_NUM_PROFILE_EVENTS + 16 + 2 * n_traced] = globaltimer_ns();
     switch (ci.opcode) {
       case 0x7000:  // TERMINATEC

@@ -203,6 +203,15 @@ struct Ctx {
   int sm;
 };
 
+#ifdef VDC_TRACE_CHUNKS
+// Life of a ring entry on SM 0: stamps 0 published by the control warp, 1 copy issued by the load port,
+// 2 seen by the consuming warp, 3 slots given back.  Written behind the per-SM profile rows.
+#define CHUNK_STAMP(c, n, k)                                                                               \
+  if ((c).sm == 0 && (n) < 1500u) (c).profile[VDC_MAX_SMS * VDC_NUM_PROFILE_EVENTS + (n) * 4 + (k)] = globaltimer_ns()
+#else
+#define CHUNK_STAMP(c, n, k)
+#endif
+
 __device__ __forceinline__ void* slot_ptr(const Ctx& c, int slot) { return c.slots + (size_t)slot * VDC_SLOT_BYTES; }
 
 __device__ __noinline__ void raise_abort(const Ctx& c, int code, int role, int pc, int opcode, int bar, int aux) {

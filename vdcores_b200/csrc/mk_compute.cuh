@@ -7,6 +7,13 @@
 
 namespace vdc {
 
+#ifndef VDC_GEMV_VARIANT
+#define VDC_GEMV_VARIANT 1   // 1: bf16 x bf16 + f32 mixed-precision FMA (no unpacking); 0: unpack to f32 pairs
+#endif
+#ifndef VDC_GEMV_UNROLL4
+#define VDC_GEMV_UNROLL4 2
+#endif
+
 // Tasks are inlined into the kernel: measured on B200, the same GEMV loop behind a real function call
 // (its queue state then lives in local memory, shared-memory accesses go through generic pointers)
 // streams at 3.5 TB/s instead of 6.4 TB/s.
@@ -27,6 +34,9 @@ struct Compute {
   unsigned mma_count;  // tensor-core commits issued so far (thread 0)
   unsigned xr_count;   // X chunks normalised by earlier tensor-core tasks (phase of the x_ready barriers)
   unsigned wr_count;   // W chunks converted by earlier tensor-core tasks (phase of the w_ready barriers)
+#ifdef VDC_TRACE_GEMV
+  unsigned gemv_ord = 0;
+#endif
 
   // CTA-wide pop: thread 0 waits for the entry (bounded), everybody gets its
   // word after one compute_sync.  Returns kPopAbort once a wait was given up.
@@ -161,7 +171,7 @@ template <int R>
 __device__ __forceinline__ void gemv_chunk(const uint8_t* w, const uint8_t* x, int K, int lane, int it0, int it1,
                                            float (&out)[R]) {
   constexpr int NA = R >= 8 ? 1 : (R == 4 ? 2 : 4);
-  constexpr int UNROLL = R >= 8 ? 1 : (R == 4 ? 2 : 4);
+  constexpr int UNROLL = R >= 8 ? 1 : (R == 4 ? VDC_GEMV_UNROLL4 : 4);
   float2 acc[R][NA];
 #pragma unroll
   for (int r = 0; r < R; ++r)
@@ -189,6 +199,51 @@ __device__ __forceinline__ void gemv_chunk(const uint8_t* w, const uint8_t* x, i
     out[r] = warp_sum(v);
   }
 }
+
+#if VDC_GEMV_VARIANT >= 1
+// Mixed-precision FMA of sm_100: d(f32) = a(bf16) * b(bf16) + c(f32), one rounding; the bf16 pairs are used
+// as they come out of shared memory, nothing is converted.
+__device__ __forceinline__ void fma_bf16x2(float& lo, float& hi, uint32_t w, uint32_t x) {
+  asm("{\n\t.reg .b16 wl, wh, xl, xh;\n\t"
+      "mov.b32 {wl, wh}, %2;\n\t"
+      "mov.b32 {xl, xh}, %3;\n\t"
+      "fma.rn.f32.bf16 %0, wl, xl, %0;\n\t"
+      "fma.rn.f32.bf16 %1, wh, xh, %1;\n\t}"
+      : "+f"(lo), "+f"(hi)
+      : "r"(w), "r"(x));
+}
+template <int R>
+__device__ __forceinline__ void gemv_chunk_mixed(const uint8_t* w, const uint8_t* x, int K, int lane, int it0, int it1,
+                                                 float (&out)[R]) {
+  constexpr int NA = R >= 8 ? 1 : (R == 4 ? 2 : 4);
+  constexpr int UNROLL = R >= 8 ? 1 : (R == 4 ? VDC_GEMV_UNROLL4 : 4);
+  float lo[R][NA], hi[R][NA];
+#pragma unroll
+  for (int r = 0; r < R; ++r)
+#pragma unroll
+    for (int a = 0; a < NA; ++a) lo[r][a] = hi[r][a] = 0.f;
+#pragma unroll UNROLL
+  for (int it = it0; it < it1; ++it) {
+    const int off = (it << 9) + (lane << 4);
+    const uint4 xv = lds128(x + off);
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const uint4 wv = lds128(w + (size_t)r * K * 2 + off);
+      fma_bf16x2(lo[r][0 % NA], hi[r][0 % NA], wv.x, xv.x);
+      fma_bf16x2(lo[r][1 % NA], hi[r][1 % NA], wv.y, xv.y);
+      fma_bf16x2(lo[r][2 % NA], hi[r][2 % NA], wv.z, xv.z);
+      fma_bf16x2(lo[r][3 % NA], hi[r][3 % NA], wv.w, xv.w);
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    float v = lo[r][0] + hi[r][0];
+#pragma unroll
+    for (int a = 1; a < NA; ++a) v += lo[r][a] + hi[r][a];
+    out[r] = warp_sum(v);
+  }
+}
+#endif
 
 // Same for e4m3 weights (one byte each, per-row fp32 scale applied by the caller):
 // 16 weights per lane and step, converted two at a time to fp16 and widened to
@@ -306,6 +361,16 @@ VDC_TASK void task_gemv_rows(Compute& q, int n_chunks, int mode, bool accumulate
                                bool dyn = false, const PeerOut* peers = nullptr) {
   Shared* sh = q.sh;
   const Ctx& c = q.c;
+#ifdef VDC_TRACE_GEMV
+  // eight stamps for each of the GEMV tasks 4..11 of this SM (layers 1 and 2 of a dense model)
+  const unsigned g_ord = q.gemv_ord++;
+#define GEMV_STAMP(i)                                                                         \
+  if (q.tid == 0 && g_ord >= 4 && g_ord < 12)                                                  \
+  c.profile[c.sm * VDC_NUM_PROFILE_EVENTS + 64 + (g_ord - 4) * 8 + (i)] = globaltimer_ns()
+#else
+#define GEMV_STAMP(i)
+#endif
+  GEMV_STAMP(0);
   int normw_mask = 0;
   if (norm) normw_mask = q.pop();
   const int x_mask = q.pop();
@@ -336,7 +401,9 @@ VDC_TASK void task_gemv_rows(Compute& q, int n_chunks, int mode, bool accumulate
   if (((x_meta & 0xFFFFu) >> VDC_FLAG_BITS) == 32u) {
     // XVEC hand-over: the slots are empty.  Wait for the producers' barrier here, then every
     // thread copies its share of the vector from global memory (past L1) into the slots.
+    GEMV_STAMP(1);
     if ((x_meta & VDC_F_BARRIER) && !q.wait_barrier((int)(x_meta >> 22), 0x7200)) return;
+    GEMV_STAMP(2);
     const uint8_t* xg = reinterpret_cast<const uint8_t*>(x_addr);
     for (int i = q.tid * 8; i < K; i += kCT * 8) {
       const uint4 v = ldcg128(xg + i * 2);
@@ -393,10 +460,13 @@ VDC_TASK void task_gemv_rows(Compute& q, int n_chunks, int mode, bool accumulate
   const int steps = wfmt == 2 ? K >> 10 : (wfmt == 1 ? K >> 9 : K >> 8);
   const int it0 = member == 0 ? 0 : (steps + 1) / 2, it1 = member == 0 ? (steps + 1) / 2 : steps;
   float* pair_part = sh->red + pair * (2 * 2 * 16);  // [buffer][member][row]
+  GEMV_STAMP(3);
   q.warp_phase_begin((unsigned)n_chunks, (unsigned)pair);  // its sync also publishes the normalised vector
+  GEMV_STAMP(4);
   if (norm) q.free_slots(normw_mask);
   for (int i = pair, trip = 0; i < n_chunks; i += 4, ++trip) {
     const int w_mask = q.warp_wait((unsigned)i);
+    if (q.lane == 0 && member == 0) CHUNK_STAMP(c, q.head + (unsigned)i, 2);
     const bool arrived = w_mask != kPopAbort;
     float acc[R];
     const int row0 = i * R;
@@ -404,7 +474,11 @@ VDC_TASK void task_gemv_rows(Compute& q, int n_chunks, int mode, bool accumulate
       const uint8_t* w = (const uint8_t*)slot_ptr(c, first_slot(w_mask));
       if (wfmt == 2) gemv_chunk_nvfp4<R>(w, x, K, q.lane, it0, it1, acc);
       else if (wfmt == 1) gemv_chunk_fp8<R>(w, x, K, q.lane, it0, it1, acc);
+#if VDC_GEMV_VARIANT >= 1
+      else gemv_chunk_mixed<R>(w, x, K, q.lane, it0, it1, acc);
+#else
       else gemv_chunk<R>(w, x, K, q.lane, it0, it1, acc);
+#endif
     } else {
 #pragma unroll
       for (int r = 0; r < R; ++r) acc[r] = 0.f;
@@ -436,6 +510,7 @@ VDC_TASK void task_gemv_rows(Compute& q, int n_chunks, int mode, bool accumulate
     if (q.lane == 0) {
       atomicOr(&sh->slot_avail, (uint32_t)w_mask & kSlotMaskAll);
       sh->warp_next[q.warp] = i + 4 < n_chunks ? q.head + i + 4 : 0xFFFFFFFFu;
+      CHUNK_STAMP(c, q.head + (unsigned)i, 3);
     }
     if (mode == VDC_GEMV_MODE_SILU_PAIRS) {
       float g = 0.f, u = 0.f;
@@ -509,8 +584,13 @@ VDC_TASK void task_gemv_rows(Compute& q, int n_chunks, int mode, bool accumulate
   // Output rows were written by lanes of every warp.  The CTA barrier inside
   // warp_phase_end orders them before thread 0, whose gpu-scope fence in
   // release() is cumulative, so no per-thread fence is needed here.
+  GEMV_STAMP(5);
+  // Every writing warp drains its own global writes while the other warps still compute, so that the
+  // releasing fence of thread 0 behind the CTA barrier finds nothing outstanding.
+  if (member == 0 && (out_meta & VDC_F_BARRIER)) __threadfence();
   if (peers != nullptr) __threadfence_system();  // the peer stores of this thread, before the arrival below
   q.warp_phase_end((unsigned)n_chunks);
+  GEMV_STAMP(6);
   if (q.aborted) return;
   if (peers != nullptr && q.tid < peers->n)
     red_release_sys_add(reinterpret_cast<int*>(__ldg(peers->table + q.tid) + peers->cnt_off), 1);
@@ -533,6 +613,7 @@ VDC_TASK void task_gemv_rows(Compute& q, int n_chunks, int mode, bool accumulate
   q.release(out_meta);
   q.release(rec_meta);
   q.free_slots(x_mask);
+  GEMV_STAMP(7);
 }
 
 // ------------------------------------------------------------------------- //

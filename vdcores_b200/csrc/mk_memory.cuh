@@ -141,7 +141,9 @@ __device__ void control_warp(const Ctx& c, const VdcMInst* __restrict__ insts, i
           const uint32_t avail = *reinterpret_cast<volatile uint32_t*>(&sh->slot_avail);  // same word for all lanes
           const uint32_t cand = __ballot_sync(0xffffffffu, lane_ok && (avail & want) == want);
           if (cand) {
-            slot = __ffs(cand) - 1;
+            // activation vectors live for a whole task: they go to the top of the pool, so that the
+            // weight chunks below them keep whole groups of slots
+            slot = opid == 32 ? 31 - __clz(cand) : __ffs(cand) - 1;
             break;
           }
           n_alloc_retry++;
@@ -182,6 +184,7 @@ __device__ void control_warp(const Ctx& c, const VdcMInst* __restrict__ insts, i
         __threadfence_block();
         sh->ring_tail = tail + 1;
         if (opid == 28) sh->demand_pos = demand + size;
+        CHUNK_STAMP(c, tail, 0);
       }
       if (opid == 28) demand += size;
       tail++;
@@ -571,6 +574,7 @@ __device__ void load_port(const Ctx& c, int port) {
       case 9:   // 1-D bulk load from a raw address
         mbar_arrive_expect_tx(bar, inst.size);
         bulk_load_1d(dst, reinterpret_cast<const void*>(inst.address), inst.size, bar);
+        CHUNK_STAMP(c, cursor - 1, 1);
         break;
       case 10:
         mbar_arrive_expect_tx(bar, inst.size);
