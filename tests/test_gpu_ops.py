@@ -278,6 +278,39 @@ def test_wait_budget_returns_status_instead_of_hanging(cuda_device):
     assert float((torch.ones(8, device=dev) * 2).sum()) == 16.0
 
 
+@pytest.mark.parametrize("own,depth", [(0, 0), (3, 6)])
+def test_gemv_chunks_drawn_from_a_shared_counter(cuda_device, own, depth):
+    """Six SMs run the same projection over the whole matrix: each streams the chunks it owns, then they draw the
+    rest from one counter (OP_DYN_CHUNKS).  Every row must be computed exactly once, whoever took its chunk."""
+    from vdcores_b200 import isa
+    from vdcores_b200.program import Dst, Program, Src
+    dev = cuda_device
+    M, K, R, S = 1024, 2048, 8, 6
+    w, x = seeded((M, K), 51, 0.02), seeded((K,), 52)
+    h0 = seeded((M,), 53)
+    wd, xd = w.to(dev), x.to(dev)
+    h = h0.clone().to(dev)
+    P = Program(S)
+    ctr, done = P.new_barrier(), P.new_barrier()
+    for sm in range(S):
+        P.gemv(sm, w_addr=wd.data_ptr(), n_rows=M, K=K, R=R, x=Src(xd.data_ptr(), K * 2),
+               out=Dst(h.data_ptr(), M * 2, "add_bf16", release=done), shared_counter=ctr, own_chunks=(sm * own, own),
+               shared_first=S * own, shared_depth=depth)
+    n = max(max(len(a) for a in P.m), max(len(a) for a in P.c)) + 2
+    P.insts_per_sm = ((n + 15) // 16) * 16
+    c, m, bars = P.finalize()
+    bt = torch.from_numpy(bars).to(dev)
+    prof = torch.zeros(S * isa.NUM_PROFILE_EVENTS, dtype=torch.int64, device=dev)
+    from vdcores_b200 import runtime
+    runtime.launch_dae(S, 0, torch.from_numpy(c).to(dev), torch.from_numpy(m).to(dev), None, bt, prof, 0,
+                       timeout_ns=TIMEOUT_NS, insts_per_sm=P.insts_per_sm)
+    assert int(bt[done]) == 0
+    drawn = int(bt[ctr])
+    assert M // R - S * own <= drawn <= M // R - S * own + 2 * S     # every chunk once, at most two overshoots per SM
+    ref = h0 + O.linear(x[None], w)[0]
+    assert O.rel_l2(h.cpu(), ref) < 3e-3
+
+
 def test_gemv_gives_up_together_when_its_activation_never_arrives(cuda_device):
     """A projection whose activation barrier nobody releases, next to one that streams normally:
     the waiting task reports the barrier, the streaming task's warp pairs leave their loop together

@@ -72,12 +72,21 @@
   X(OP_CC0_STRIDE32, VDC_MOP(29, 0))                                                   \
   X(OP_PT_LOAD32, VDC_MOP(30, 0))                                                      \
   X(OP_PT_APPLY, VDC_MOP(31, 0))                                                       \
-  X(OP_ALLOC_XVEC, VDC_MOP(32, VDC_F_ALLOCATE))
+  X(OP_ALLOC_XVEC, VDC_MOP(32, VDC_F_ALLOCATE))                                        \
+  X(OP_DYN_CHUNKS, VDC_MOP(33, 0))
 
 // OP_ALLOC_XVEC: allocates slots for an activation vector and hands {address, size, barrier} to the
 // compute task, which waits for the barrier itself (BARRIER flag: the load port does NOT wait) and reads
 // the vector from global memory with ordinary loads.  It takes the copy engine, one ring hop and one
 // CTA barrier out of the path between "the producers' barrier opened" and "the stage computes".
+//
+// OP_DYN_CHUNKS: the next instruction (a plain 1-D load of one weight chunk) is issued for chunk indices
+// drawn one at a time from a counter all SMs share (barrier word `bar`, starts at 0, atomically incremented)
+// until the index reaches size | arg << 16; chunk i is read at the template's address + i * its size.  Four
+// end markers follow the last chunk in the ring (one per consuming warp pair; the address field holds the
+// number of chunks this SM drew, low half, and the marker's ordinal 0..3, high half).  SMs that stream faster take more chunks, so a stage ends everywhere within
+// one chunk time instead of waiting for the SM with the slowest memory path.
+#define VDC_STREAM_END 0x20000000   // ring word of an end marker
 //
 // Compute opcodes.  The first block keeps reference names (control ops and the
 // ops whose tile contracts this runtime still honours); the second block is
@@ -211,6 +220,8 @@
 #define VDC_GEMV_NORM_BIT 0x1000
 #define VDC_GEMV_PEERS_BIT 0x4000  // STORE_F32 to every rank's exchange block; two more words (see below)
 #define VDC_GEMV_DYN_BIT 0x2000    // the chunk count is min(n_chunks, int32 word): one more pop (a raw address: the word)
+#define VDC_GEMV_DYNROWS_BIT 0x8000  // chunks come from OP_DYN_CHUNKS: row = chunk index * R, the index from the chunk's
+                                     // address; one more word (last): 48-bit address of the matrix
 
 // ATTN_DECODE args[2] bits
 #define VDC_ATTN_QKNORM_BIT 0x1

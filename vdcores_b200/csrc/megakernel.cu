@@ -159,12 +159,19 @@ __device__ __forceinline__ void compute_core(const Ctx& c, const VdcCInst* __res
           VDC_LOAD_PEERS(peer_args);
           peers = &peer_args;
         }
+        uint64_t dyn_base = 0;
+        if (ci.args[1] & VDC_GEMV_DYNROWS_BIT) {
+          VdcCInst e2;
+          *reinterpret_cast<uint2*>(&e2) = ld_word(q.pc);
+          q.pc += 1;
+          dyn_base = addr48(e2);
+        }
         switch (R) {
-          case 1: task_gemv_rows<1>(q, ci.args[0], mode, accumulate, norm, K, row_base, scales, wfmt, moe, dyn, peers); break;
-          case 2: task_gemv_rows<2>(q, ci.args[0], mode, accumulate, norm, K, row_base, scales, wfmt, moe, dyn, peers); break;
-          case 4: task_gemv_rows<4>(q, ci.args[0], mode, accumulate, norm, K, row_base, scales, wfmt, moe, dyn, peers); break;
-          case 8: task_gemv_rows<8>(q, ci.args[0], mode, accumulate, norm, K, row_base, scales, wfmt, moe, dyn, peers); break;
-          case 16: task_gemv_rows<16>(q, ci.args[0], mode, accumulate, norm, K, row_base, scales, wfmt, moe, dyn, peers); break;
+          case 1: task_gemv_rows<1>(q, ci.args[0], mode, accumulate, norm, K, row_base, scales, wfmt, moe, dyn, peers, dyn_base); break;
+          case 2: task_gemv_rows<2>(q, ci.args[0], mode, accumulate, norm, K, row_base, scales, wfmt, moe, dyn, peers, dyn_base); break;
+          case 4: task_gemv_rows<4>(q, ci.args[0], mode, accumulate, norm, K, row_base, scales, wfmt, moe, dyn, peers, dyn_base); break;
+          case 8: task_gemv_rows<8>(q, ci.args[0], mode, accumulate, norm, K, row_base, scales, wfmt, moe, dyn, peers, dyn_base); break;
+          case 16: task_gemv_rows<16>(q, ci.args[0], mode, accumulate, norm, K, row_base, scales, wfmt, moe, dyn, peers, dyn_base); break;
           default: raise_abort(c, VDC_ERR_BAD_OPCODE, 0, (int)q.pc, ci.opcode, -1, R); q.aborted = true; break;
         }
         break;

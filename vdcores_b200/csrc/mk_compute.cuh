@@ -358,7 +358,7 @@ struct PeerOut {
 template <int R>
 VDC_TASK void task_gemv_rows(Compute& q, int n_chunks, int mode, bool accumulate, bool norm, int K, int row_base,
                                const float* scales = nullptr, int wfmt = 0, const MoeDown* moe = nullptr,
-                               bool dyn = false, const PeerOut* peers = nullptr) {
+                               bool dyn = false, const PeerOut* peers = nullptr, uint64_t dyn_base = 0) {
   Shared* sh = q.sh;
   const Ctx& c = q.c;
 #ifdef VDC_TRACE_GEMV
@@ -405,13 +405,26 @@ VDC_TASK void task_gemv_rows(Compute& q, int n_chunks, int mode, bool accumulate
     if ((x_meta & VDC_F_BARRIER) && !q.wait_barrier((int)(x_meta >> 22), 0x7200)) return;
     GEMV_STAMP(2);
     const uint8_t* xg = reinterpret_cast<const uint8_t*>(x_addr);
-    for (int i = q.tid * 8; i < K; i += kCT * 8) {
-      const uint4 v = ldcg128(xg + i * 2);
-      *reinterpret_cast<uint4*>(x + i * 2) = v;
-      if (norm) {
-        const float f[8] = {bf_lo(v.x), bf_hi(v.x), bf_lo(v.y), bf_hi(v.y), bf_lo(v.z), bf_hi(v.z), bf_lo(v.w), bf_hi(v.w)};
+    // up to eight loads per thread are in flight before the first one is used
+    for (int i0 = q.tid * 8; i0 < K; i0 += kCT * 8 * 8) {
+      uint4 v[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) ss = fmaf(f[j], f[j], ss);
+      for (int j = 0; j < 8; ++j) {
+        const int i = i0 + j * kCT * 8;
+        v[j] = i < K ? ldcg128(xg + i * 2) : make_uint4(0u, 0u, 0u, 0u);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int i = i0 + j * kCT * 8;
+        if (i < K) {
+          *reinterpret_cast<uint4*>(x + i * 2) = v[j];
+          if (norm) {
+            const float f[8] = {bf_lo(v[j].x), bf_hi(v[j].x), bf_lo(v[j].y), bf_hi(v[j].y),
+                                bf_lo(v[j].z), bf_hi(v[j].z), bf_lo(v[j].w), bf_hi(v[j].w)};
+#pragma unroll
+            for (int e = 0; e < 8; ++e) ss = fmaf(f[e], f[e], ss);
+          }
+        }
       }
     }
   } else if (norm) {
@@ -461,15 +474,27 @@ VDC_TASK void task_gemv_rows(Compute& q, int n_chunks, int mode, bool accumulate
   const int it0 = member == 0 ? 0 : (steps + 1) / 2, it1 = member == 0 ? (steps + 1) / 2 : steps;
   float* pair_part = sh->red + pair * (2 * 2 * 16);  // [buffer][member][row]
   GEMV_STAMP(3);
-  q.warp_phase_begin((unsigned)n_chunks, (unsigned)pair);  // its sync also publishes the normalised vector
+  const bool dyn_rows = dyn_base != 0;
+  // (chunks drawn from the shared counter: their number is only known at the end marker)
+  q.warp_phase_begin(dyn_rows ? 0x10000000u : (unsigned)n_chunks, (unsigned)pair);  // its sync also publishes the vector
   GEMV_STAMP(4);
   if (norm) q.free_slots(normw_mask);
+  if (dyn_rows) n_chunks = 0x0FFFFFFF;
   for (int i = pair, trip = 0; i < n_chunks; i += 4, ++trip) {
     const int w_mask = q.warp_wait((unsigned)i);
     if (q.lane == 0 && member == 0) CHUNK_STAMP(c, q.head + (unsigned)i, 2);
+    if (w_mask == VDC_STREAM_END) {  // both members of the pair read the same entry: they leave together
+      // the k-th of the four consecutive markers sits k entries behind the last chunk of the phase
+      n_chunks = i - (int)(sh->ring[(q.head + (unsigned)i) % kQ].address >> 32);
+      break;
+    }
     const bool arrived = w_mask != kPopAbort;
     float acc[R];
-    const int row0 = i * R;
+    int row0 = i * R;
+    if (dyn_rows && arrived) {
+      const uint32_t chunk_bytes = (uint32_t)R * (uint32_t)(wfmt == 2 ? (K >> 1) + (K >> 4) : (wfmt == 1 ? K : 2 * K));
+      row0 = (int)((sh->ring[(q.head + (unsigned)i) % kQ].address - dyn_base) / chunk_bytes) * R;
+    }
     if (arrived) {
       const uint8_t* w = (const uint8_t*)slot_ptr(c, first_slot(w_mask));
       if (wfmt == 2) gemv_chunk_nvfp4<R>(w, x, K, q.lane, it0, it1, acc);
@@ -589,7 +614,15 @@ VDC_TASK void task_gemv_rows(Compute& q, int n_chunks, int mode, bool accumulate
   // releasing fence of thread 0 behind the CTA barrier finds nothing outstanding.
   if (member == 0 && (out_meta & VDC_F_BARRIER)) __threadfence();
   if (peers != nullptr) __threadfence_system();  // the peer stores of this thread, before the arrival below
-  q.warp_phase_end((unsigned)n_chunks);
+  if (dyn_rows) {
+    // every pair has met its end marker and knows the chunk count; the ring moves on past the four markers
+    if (q.lane == 0) sh->warp_next[q.warp] = 0xFFFFFFFFu;
+    compute_sync();
+    if (q.tid == 0) sh->cta_head = q.head + (unsigned)n_chunks + 4u;
+    q.warp_phase_end((unsigned)n_chunks + 4u);
+  } else {
+    q.warp_phase_end((unsigned)n_chunks);
+  }
   GEMV_STAMP(6);
   if (q.aborted) return;
   if (peers != nullptr && q.tid < peers->n)

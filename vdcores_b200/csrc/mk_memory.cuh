@@ -451,6 +451,117 @@ __device__ void control_warp(const Ctx& c, const VdcMInst* __restrict__ insts, i
           ind_pending = true;
           break;
         }
+        case 33: {  // DYN_CHUNKS: stream the template load for chunk indices drawn from a shared counter
+          const int total = (int)(size | (arg << 16));
+          int* counter = c.bars + (num_slots >> 6);
+          if (pc + 1 - ic_base >= 64u) {
+            ic_base = (pc + 1) & ~31u;
+            icache_fill(sh, insts, ic_base, n_insts, lane);
+          }
+          const uint4 t = *reinterpret_cast<const uint4*>(&sh->icache[pc + 1 - ic_base]);
+          const uint32_t t_op = t.x & 0xFFFFu, t_bytes = t.x >> 16;
+          const int req = (int)(t.y & 63u);
+          const uint64_t t_addr = ((uint64_t)t.w << 32) | t.z;
+          const uint32_t want = ((1u << req) - 1u) << lane;
+          const bool lane_ok = req > 0 && req < kSlots && lane + req <= kSlots;
+          // the address field limits how many ring entries may be unconsumed when a chunk is drawn (0: no
+          // limit): near the end of a stage an SM must not sit on chunks that an idle SM could take
+          const unsigned depth = (uint32_t)address != 0u ? (uint32_t)address : 0x7FFFFFFFu;
+          int idx = 0, taken = 0;
+          bool ok = true;
+          {
+            uint32_t it = 0;
+            uint64_t t0 = 0;
+            while (tail - (head_cache = ring_head(sh, lane)) > depth)
+              if (control_backoff(c, lane, it, t0, pc, opcode, -5)) {
+                ok = false;
+                break;
+              }
+          }
+          if (ok && lane == 0) idx = atomicAdd(counter, 1);
+          idx = ok ? __shfl_sync(0xffffffffu, idx, 0) : total;
+          while (ok && idx < total) {
+            int nxt = 0;
+            {
+              uint32_t it = 0;
+              uint64_t t0 = 0;
+              while (tail + 1u - (head_cache = ring_head(sh, lane)) > depth)
+                if (control_backoff(c, lane, it, t0, pc, opcode, -5)) {
+                  ok = false;
+                  break;
+                }
+              if (!ok) break;
+            }
+            if (lane == 0) nxt = atomicAdd(counter, 1);  // the next draw travels while this chunk is placed
+            int slot = 0;
+            uint32_t it = 0;
+            uint64_t t0 = 0;
+            while (true) {
+              const uint32_t avail = *reinterpret_cast<volatile uint32_t*>(&sh->slot_avail);
+              const uint32_t cand = __ballot_sync(0xffffffffu, lane_ok && (avail & want) == want);
+              if (cand) {
+                slot = __ffs(cand) - 1;
+                break;
+              }
+              n_alloc_retry++;
+              if (VDC_ALLOC_SLEEP) __nanosleep(VDC_ALLOC_SLEEP);
+              if (control_backoff(c, lane, it, t0, pc + 1, t_op, req)) {
+                ok = false;
+                break;
+              }
+            }
+            if (!ok) break;
+            const uint32_t mask = ((1u << req) - 1u) << slot;
+            if (lane == 0) atomicAnd(&sh->slot_avail, ~mask);
+            while (tail - head_cache >= (unsigned)kQ) {
+              head_cache = ring_head(sh, lane);
+              if (tail - head_cache < (unsigned)kQ) break;
+              n_ring_wait++;
+              if (control_backoff(c, lane, it, t0, pc + 1, t_op, -2)) {
+                ok = false;
+                break;
+              }
+            }
+            if (!ok) break;
+            if (lane == 0) {
+              const unsigned e = tail % kQ;
+              const uint64_t a = t_addr + (uint64_t)(uint32_t)idx * t_bytes;
+              *reinterpret_cast<uint4*>(&sh->ring[e]) = make_uint4(t.x, t.y, (uint32_t)a, (uint32_t)(a >> 32));
+              sh->ring_word[e] = (int)mask;
+              __threadfence_block();
+              sh->ring_tail = tail + 1;
+              CHUNK_STAMP(c, tail, 0);
+            }
+            tail++;
+            taken++;
+            n_inst++;
+            idx = __shfl_sync(0xffffffffu, nxt, 0);
+          }
+          for (int k = 0; ok && k < 4; ++k) {  // end markers, one per consuming warp pair
+            uint32_t it = 0;
+            uint64_t t0 = 0;
+            while (tail - head_cache >= (unsigned)kQ) {
+              head_cache = ring_head(sh, lane);
+              if (tail - head_cache < (unsigned)kQ) break;
+              if (control_backoff(c, lane, it, t0, pc, opcode, -4)) {
+                ok = false;
+                break;
+              }
+            }
+            if (!ok) break;
+            if (lane == 0) {
+              const unsigned e = tail % kQ;
+              *reinterpret_cast<uint4*>(&sh->ring[e]) = make_uint4(33u << VDC_FLAG_BITS, 0u, (uint32_t)taken, (uint32_t)k);
+              sh->ring_word[e] = VDC_STREAM_END;
+              __threadfence_block();
+              sh->ring_tail = tail + 1;
+            }
+            tail++;
+          }
+          if (!ok) running = false;
+          next_pc = pc + 2;
+          break;
+        }
         case 30: {  // PT_LOAD32: lane i keeps 32-bit word i of the table at `address` (size words, at most 32)
           tbl = lane < (int)size ? (uint32_t)ld_relaxed_gpu(reinterpret_cast<const int*>(address) + lane) : 0u;
           break;

@@ -36,6 +36,8 @@ GEMV_NORM_BIT = _defs["GEMV_NORM_BIT"]
 GEMV_ACC_BIT = _defs["GEMV_ACC_BIT"]
 GEMV_DYN_BIT = _defs["GEMV_DYN_BIT"]
 GEMV_PEERS_BIT = _defs["GEMV_PEERS_BIT"]
+GEMV_DYNROWS_BIT = _defs["GEMV_DYNROWS_BIT"]
+STREAM_END = _defs["STREAM_END"]
 ATTN_QKNORM_BIT = _defs["ATTN_QKNORM_BIT"]
 ATTN_PACKED_BIT = _defs["ATTN_PACKED_BIT"]
 GEMM_MODE_STORE_ROWS = _defs["GEMM_MODE_STORE_ROWS"]

@@ -303,13 +303,19 @@ class Program:
              norm_w: Optional[Src] = None, eps: float = 0.0, pair_out: Optional[Dst] = None, row_base: int = 0,
              stream: bool = False, fp8_scales: Optional[int] = None, nvfp4_scales: Optional[int] = None,
              w_indirect: Optional[tuple] = None, wait_issue: Optional[int] = None, moe: Optional[dict] = None,
-             dyn_count_addr: Optional[int] = None, peers: Optional[tuple] = None):
+             dyn_count_addr: Optional[int] = None, peers: Optional[tuple] = None, shared_counter: Optional[int] = None,
+             own_chunks: Optional[tuple] = None, shared_first: int = 0, shared_depth: int = 0):
         """y[0:n_rows] = W[0:n_rows, :K] @ x for the contiguous row block at w_addr
         (bf16; e4m3 with fp8_scales = address of the block's fp32 per-row scales;
         or NVFP4 rows — K/2 code bytes + K/16 block scales — with nvfp4_scales =
         address of the fp32 per-row tensor scales), streamed as chunks of R rows.  The task writes y straight to
         out.addr (kind 'store') or adds it there (kind 'add_bf16'); in SILU_PAIRS
-        mode rows (2j, 2j+1) are (gate_j, up_j) and n_rows/2 values are written."""
+        mode rows (2j, 2j+1) are (gate_j, up_j) and n_rows/2 values are written.
+        shared_counter: a barrier id used as a counter that starts at 0.  w_addr / n_rows / out / scales then
+        describe the WHOLE matrix on every SM that runs the task: the SM first streams the chunks it owns
+        (own_chunks = (first, count)), then draws chunks shared_first, shared_first + 1, ... from the counter
+        until the matrix is exhausted, never holding more than shared_depth unconsumed ring entries when it
+        draws (0: no limit), so the SMs that finish early take the tail of the stage."""
         assert fp8_scales is None or nvfp4_scales is None
         if nvfp4_scales is not None:
             row_bytes, kmult, op, scales = K // 2 + K // 16, 1024, isa.OP_GEMV_ROWS_NVFP4, nvfp4_scales
@@ -350,14 +356,30 @@ class Program:
             self.mem(sm, isa.OP_CC0_STRIDE32, size=stride & 0xFFFF, arg=stride >> 16, address=waddr)
         elif dyn_count_addr is not None:
             self.dyn_count(sm, dyn_count_addr, 0, n_chunks)
-        self.repeat(sm, n_chunks, [chunk_bytes], dynamic=dyn_count_addr is not None)
-        self.mem(sm, isa.OP_ALLOC_TMA_LOAD_1D_STREAM if stream else isa.OP_ALLOC_TMA_LOAD_1D, size=chunk_bytes,
-                 nslot=slots_for(chunk_bytes), address=w_addr, flags=isa.F_JUMP)
-        self.bytes_loaded[sm] += chunk_bytes * n_chunks
+        if shared_counter is not None:
+            assert dyn_count_addr is None and w_indirect is None and moe is None and peers is None and row_base == 0
+            assert shared_counter in self.bar_counts and self.bar_counts[shared_counter] == 0
+            own_first, own_n = own_chunks if own_chunks is not None else (0, 0)
+            n_shared = n_chunks - shared_first
+            assert 0 <= own_first and own_first + own_n <= shared_first <= n_chunks and 0 <= shared_depth < 1 << 16
+            if own_n:
+                self.repeat(sm, own_n, [chunk_bytes])
+                self.mem(sm, isa.OP_ALLOC_TMA_LOAD_1D, size=chunk_bytes, nslot=slots_for(chunk_bytes),
+                         address=w_addr + own_first * chunk_bytes, flags=isa.F_JUMP)
+            self.mem(sm, isa.OP_DYN_CHUNKS, size=n_shared & 0xFFFF, arg=n_shared >> 16, bar=shared_counter,
+                     address=shared_depth)
+            self.mem(sm, isa.OP_ALLOC_TMA_LOAD_1D, size=chunk_bytes, nslot=slots_for(chunk_bytes),
+                     address=w_addr + shared_first * chunk_bytes)
+            self.bytes_loaded[sm] += chunk_bytes * (own_n + n_shared // max(1, self.num_sms))
+        else:
+            self.repeat(sm, n_chunks, [chunk_bytes], dynamic=dyn_count_addr is not None)
+            self.mem(sm, isa.OP_ALLOC_TMA_LOAD_1D_STREAM if stream else isa.OP_ALLOC_TMA_LOAD_1D, size=chunk_bytes,
+                     nslot=slots_for(chunk_bytes), address=w_addr, flags=isa.F_JUMP)
+            self.bytes_loaded[sm] += chunk_bytes * n_chunks
         rb8 = row_base // R     # index of the first chunk within the whole matrix
         a1 = R | (mode << 8) | (isa.GEMV_NORM_BIT if norm_w is not None else 0) | \
             (isa.GEMV_ACC_BIT if out.kind == "add_bf16" else 0) | (isa.GEMV_DYN_BIT if dyn_count_addr is not None else 0) | \
-            (isa.GEMV_PEERS_BIT if peers is not None else 0)
+            (isa.GEMV_PEERS_BIT if peers is not None else 0) | (isa.GEMV_DYNROWS_BIT if shared_counter is not None else 0)
         a2 = (K // 256) | ((rb8 >> 16) << 8)
         e = f32_bits(eps)
         if moe is not None:
@@ -378,6 +400,9 @@ class Program:
             # first row inside an exchange block, the rows go to every rank's block
             assert mode == isa.GEMV_MODE_STORE_F32
             self._peer_words(sm, peers)
+        if shared_counter is not None:
+            assert 0 < w_addr < 1 << 48
+            self.comp(sm, isa.OP_EXT, w_addr & 0xFFFF, (w_addr >> 16) & 0xFFFF, (w_addr >> 32) & 0xFFFF)
 
     def _peer_words(self, sm, peers):
         table, n, cnt_off = peers
