@@ -299,7 +299,11 @@ int64_t vdc_config(const char* name) {
   return -1;
 }
 
-const char* vdc_family_specs(void) { return ""; }
+// Families of parameterised compute ops, in the reference's definition syntax (include/dae/opcode.cuh.inc:36-37).
+const char* vdc_family_specs(void) {
+  return "GEMV_WGMMA\tFIELDS=M|N|K|BLOAD|RESIDUAL, M_MULTIPLE=64, N_FIXED=8, K_MULTIPLE=16, BLOAD_MIN=1, RESIDUAL_MAX=1\n"
+         "GEMV_MMA\tFIELDS=M|N|K, M_FIXED=64, N_FIXED=8, K_MULTIPLE=16";
+}
 
 // ------------------------------------------------------------------------- //
 // launch without any allocation

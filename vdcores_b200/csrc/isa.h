@@ -88,9 +88,10 @@
 // one chunk time instead of waiting for the SM with the slowest memory path.
 #define VDC_STREAM_END 0x20000000   // ring word of an end marker
 //
-// Compute opcodes.  The first block keeps reference names (control ops and the
-// ops whose tile contracts this runtime still honours); the second block is
-// the B200-native decode set.
+// Compute opcodes.  The first block keeps reference names (control ops); the 0x72xx / 0x73xx blocks are
+// the B200-native decode set; the 0x74xx block carries the reference's operator names and tile contracts
+// (include/dae/opcode.cuh.inc:56-82, tools/generate_selected_compute_ops.py:235-258), so that its
+// instruction classes resolve and its schedules run: see mk_refops.cuh.
 // X(name, value, words): `words` = 8-byte words the instruction occupies in the compute stream
 // before any optional trailing words (flags of the first word announce those).
 #define VDC_COMPUTE_OPS(X)                                                             \
@@ -112,6 +113,24 @@
   X(OP_BATCH_ADVANCE, 0x7320, 5)                                                       \
   X(OP_XREDUCE, 0x7330, 6)                                                             \
   X(OP_XWAIT, 0x7331, 3)                                                               \
+  X(OP_GEMV_WGMMA__M_64__N_8__K_256__BLOAD_4__RESIDUAL_0, 0x7400, 1)                   \
+  X(OP_GEMV_WGMMA__M_64__N_8__K_256__BLOAD_4__RESIDUAL_1, 0x7401, 1)                   \
+  X(OP_GEMV_WGMMA__M_64__N_8__K_256__BLOAD_2__RESIDUAL_0, 0x7402, 1)                   \
+  X(OP_GEMV_WGMMA__M_64__N_8__K_256__BLOAD_2__RESIDUAL_1, 0x7403, 1)                   \
+  X(OP_GEMV_WGMMA__M_64__N_8__K_256__BLOAD_1__RESIDUAL_0, 0x7404, 1)                   \
+  X(OP_GEMV_WGMMA__M_64__N_8__K_256__BLOAD_1__RESIDUAL_1, 0x7405, 1)                   \
+  X(OP_GEMV_MMA__M_64__N_8__K_256, 0x7408, 1)                                          \
+  X(OP_RMS_NORM_F16_K_4096_SMEM, 0x7410, 1)                                            \
+  X(OP_RMS_NORM_F16_K_2048_SMEM, 0x7411, 1)                                            \
+  X(OP_RMS_NORM_F16_K_5120_SMEM, 0x7412, 1)                                            \
+  X(OP_RMS_NORM_F16_K_128_SMEM, 0x7413, 1)                                             \
+  X(OP_ROPE_INTERLEAVE_512, 0x7418, 1)                                                 \
+  X(OP_SILU_MUL_SHARED_BF16_K_64_SW128, 0x7420, 1)                                     \
+  X(OP_SILU_MUL_SHARED_BF16_K_4096_INTER, 0x7421, 1)                                   \
+  X(OP_ARGMAX_PARTIAL_bf16_1024_65536_128, 0x7428, 1)                                  \
+  X(OP_ARGMAX_REDUCE_bf16_1024_128, 0x7429, 1)                                         \
+  X(OP_ARGMAX_PARTIAL_bf16_1152_50688_132, 0x742A, 1)                                  \
+  X(OP_ARGMAX_REDUCE_bf16_1152_132, 0x742B, 1)                                         \
   X(OP_EXT, 0x7FFF, 1)
 
 // OP_L2_PREFETCH (two words): args = 48-bit address in three 16-bit pieces (low

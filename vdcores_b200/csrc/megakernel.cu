@@ -3,6 +3,7 @@
 #include "mk_memory.cuh"
 #include "mk_compute.cuh"
 #include "mk_tensor.cuh"
+#include "mk_refops.cuh"
 
 namespace vdc {
 
@@ -322,6 +323,22 @@ __device__ __forceinline__ void compute_core(const Ctx& c, const VdcCInst* __res
                    reinterpret_cast<const int*>(addr48(e2)));
         break;
       }
+      // ---- the reference's operators (tile contracts of its schedules)
+      case 0x7400: case 0x7401: task_ref_gemv(q, ci.args[0], 4, ci.opcode & 1); break;
+      case 0x7402: case 0x7403: task_ref_gemv(q, ci.args[0], 2, ci.opcode & 1); break;
+      case 0x7404: case 0x7405: task_ref_gemv(q, ci.args[0], 1, ci.opcode & 1); break;
+      case 0x7408: task_ref_gemv(q, ci.args[0], 1, false); break;
+      case 0x7410: task_ref_rms(q, 4096, ci.args[0], ci.args[1]); break;
+      case 0x7411: task_ref_rms(q, 2048, ci.args[0], ci.args[1]); break;
+      case 0x7412: task_ref_rms(q, 5120, ci.args[0], ci.args[1]); break;
+      case 0x7413: task_ref_rms(q, 128, ci.args[0], ci.args[1]); break;
+      case 0x7418: task_ref_rope512(q); break;
+      case 0x7420: task_ref_silu(q, 32 * 8); break;                  // one 64 x 8 tile, whatever the token count
+      case 0x7421: task_ref_silu(q, 6144 / 2 * ci.args[0]); break;
+      case 0x7428: task_ref_argmax_partial(q, 1024, 65536, 128, ci.args[0]); break;
+      case 0x7429: task_ref_argmax_reduce(q, 1024, 128, ci.args[0]); break;
+      case 0x742A: task_ref_argmax_partial(q, 1152, 50688, 132, ci.args[0]); break;
+      case 0x742B: task_ref_argmax_reduce(q, 1152, 132, ci.args[0]); break;
       case 0x7240: task_moe_route(q, ci.args[0], ci.args[1], ci.args[2] & 0xFF, ci.args[2] >> 8); break;
       default:
         raise_abort(c, VDC_ERR_BAD_OPCODE, 0, (int)q.pc, ci.opcode, -1, 0);

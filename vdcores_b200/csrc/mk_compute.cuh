@@ -200,7 +200,6 @@ __device__ __forceinline__ void gemv_chunk(const uint8_t* w, const uint8_t* x, i
   }
 }
 
-#if VDC_GEMV_VARIANT >= 1
 // Mixed-precision FMA of sm_100: d(f32) = a(bf16) * b(bf16) + c(f32), one rounding; the bf16 pairs are used
 // as they come out of shared memory, nothing is converted.
 __device__ __forceinline__ void fma_bf16x2(float& lo, float& hi, uint32_t w, uint32_t x) {
@@ -212,6 +211,7 @@ __device__ __forceinline__ void fma_bf16x2(float& lo, float& hi, uint32_t w, uin
       : "+f"(lo), "+f"(hi)
       : "r"(w), "r"(x));
 }
+#if VDC_GEMV_VARIANT >= 1
 template <int R>
 __device__ __forceinline__ void gemv_chunk_mixed(const uint8_t* w, const uint8_t* x, int K, int lane, int it0, int it1,
                                                  float (&out)[R]) {
