@@ -215,11 +215,15 @@ def run_gpu(args):
     else:
         # tensor parallel: every rank builds the same full model (same seed), prefills it with the
         # PyTorch path, keeps its shard of the weights and of the KV cache, and drops the rest
-        from vdcores_b200.tp import TPDecodeEngine
+        from vdcores_b200.tp import TPDecodeEngine, TPFusedEngine
         full = DecodeEngine(cfg, max_seq=max_seq, device=dev, max_steps=W + K + 8)
         full.init_random_weights(seed=0)
         first = full.prefill(prompt)
-        eng = TPDecodeEngine(cfg, max_seq=max_seq, rank=rank, world=world, device=dev, max_steps=2 * (W + K) + 16)
+        # dense models: one launch per step and rank, the partial sums cross NVLink as peer stores inside the
+        # kernel; mixture-of-experts models (and --tp-impl nccl): two launches per layer around NCCL collectives
+        fused = args.tp_impl == "fused" and not cfg.n_experts
+        eng = (TPFusedEngine if fused else TPDecodeEngine)(cfg, max_seq=max_seq, rank=rank, world=world, device=dev,
+                                                           max_steps=2 * (W + K) + 16)
         dbg('prefill done')
         eng.load_from_full(full, PROMPT_LEN)
         dbg('shard loaded')
@@ -230,7 +234,8 @@ def run_gpu(args):
         del full
         torch.cuda.empty_cache()
         tokens_per_step, scaling = 1, "strong"
-        parallelism = f"tp{world}" if not cfg.n_experts else f"attention tp{world}, experts ep{world}"
+        parallelism = ((f"tp{world}, in-kernel exchange over peer memory" if fused else f"tp{world}, NCCL collectives")
+                       if not cfg.n_experts else f"attention tp{world}, experts ep{world}, NCCL collectives")
     stream = torch.cuda.current_stream()
 
     def barrier():
@@ -330,7 +335,8 @@ def run_gpu(args):
         "gpu_launches": K * eng.launches_per_step,
         # greedy ids of the sharded run against the single-GPU engine on the same weights and prompt; a random-init
         # model has near-ties, after the first one the two trajectories differ legitimately (prefix = steps before it)
-        **({"tokens_match_single_gpu": tokens_match, "tokens_match_prefix": match_prefix} if tokens_match is not None else {}),
+        **({"tokens_match_single_gpu": tokens_match, "tokens_match_prefix": match_prefix,
+            "single_gpu_first_tokens": ref_tokens[:4]} if tokens_match is not None else {}),
         "clocks": clk.summary(),
     }
     if not args.no_cpu_baseline:
@@ -353,6 +359,8 @@ def main():
                     help="shape of the random-init model (qwen3-8b: 36 layers, FFN 12288, per-head QK norm, 4096-token prompt)")
     ap.add_argument("--batch", type=int, default=1,
                     help="sequences decoded in lock-step (> 1: tensor-core projections, bf16, one GPU)")
+    ap.add_argument("--tp-impl", default="fused", choices=["fused", "nccl"],
+                    help="N > 1, dense models: exchange inside the kernel (peer stores) or NCCL collectives between launches")
     ap.add_argument("--layers", type=int, default=32,
                     help="profiling only: a model with fewer layers of the same shape (the JSON line says so)")
     args = ap.parse_args()

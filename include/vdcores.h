@@ -90,6 +90,14 @@ int vdc_set_cache_policy(const void* ptr, size_t bytes, uint64_t stream, float h
  * No counterpart in the reference (it has no multi-GPU path). */
 int vdc_enable_peer_access(int peer_device);
 
+/* Exchange blocks of the in-kernel tensor-parallel exchange: vdc_peer_alloc allocates `bytes` of zeroed device
+ * memory on the current device as an allocation of its own (so that its IPC handle names exactly that block),
+ * vdc_ipc_export writes its 64-byte CUDA IPC handle for the other ranks' vdc_ipc_open, vdc_peer_free releases
+ * it (after every importer has closed its mapping).  No counterpart in the reference (it has no multi-GPU path). */
+int vdc_peer_alloc(size_t bytes, uint64_t* out_ptr);
+int vdc_peer_free(uint64_t ptr);
+int vdc_ipc_export(uint64_t ptr, void* handle_out, size_t handle_bytes);
+
 /* Maps a device allocation exported by another process (the 64-byte CUDA IPC memory handle of
  * its base allocation) for kernels of the CURRENT device and returns its address in *out_ptr;
  * peer access to the exporting device is enabled as needed.  vdc_ipc_close unmaps it.  Used for

@@ -188,7 +188,8 @@ def test_attention_split_merge_paged(cuda_device, G, n_kv, pos, qk_norm, pages_p
     for p in range(pos):
         kpool[table[p // 64], :, p % 64] = kc[p]
         vpool[table[p // 64], :, p % 64] = vc[p]
-    kpool, vpool = kpool.to(dev), vpool.to(dev)
+    from vdcores_b200.decode import kv_page_swizzle       # page rows live in HBM in the bank-friendly piece order
+    kpool, vpool = kv_page_swizzle(kpool).to(dev), kv_page_swizzle(vpool).to(dev)
     # projection output stored per KV head group: [G query heads | key | value]
     qkv = torch.cat([torch.cat((q.view(n_kv, G * D)[h], k_new.view(n_kv, D)[h], v_new.view(n_kv, D)[h]))
                      for h in range(n_kv)]).to(dev)
@@ -231,6 +232,7 @@ def test_attention_split_merge_paged(cuda_device, G, n_kv, pos, qk_norm, pages_p
     assert O.rel_l2(out.cpu(), ref) < 6e-3
     # the new K (normed + rotated) and V rows landed in the right page, nothing else changed
     page, row = int(table[pos // 64]), pos % 64
+    kpool, vpool = kv_page_swizzle(kpool), kv_page_swizzle(vpool)
     assert O.rel_l2(kpool[page, :, row].cpu(), kh) < 6e-3
     assert torch.equal(vpool[page, :, row].cpu(), v_new.view(n_kv, D))
     if pos > 0:

@@ -18,7 +18,7 @@ from typing import List
 import torch
 
 from . import isa, runtime
-from .decode import BF16, DecodeConfig, DecodeEngine
+from .decode import BF16, DecodeConfig, DecodeEngine, kv_page_swizzle
 from .program import Dst, Program, Src, slots_for
 
 
@@ -325,14 +325,15 @@ class BatchDecodeEngine(DecodeEngine):
                 n_pages = (T + isa.KV_PAGE - 1) // isa.KV_PAGE
                 pad = torch.zeros(n_pages * isa.KV_PAGE, cfg.n_kv_heads, isa.HEAD_DIM, dtype=BF16, device=self.dev)
                 pad[:T] = src.to(self.dev)
-                pool[pt[:n_pages]] = pad.view(n_pages, isa.KV_PAGE, cfg.n_kv_heads, isa.HEAD_DIM).permute(0, 2, 1, 3)
+                pool[pt[:n_pages]] = kv_page_swizzle(
+                    pad.view(n_pages, isa.KV_PAGE, cfg.n_kv_heads, isa.HEAD_DIM).permute(0, 2, 1, 3))
 
     def read_kv(self, layer: int, T: int, b: int = 0):
         n_pages = (T + isa.KV_PAGE - 1) // isa.KV_PAGE
         pt = self.page_tables[b].long().to(self.dev)[:n_pages]
         out = []
         for pool in (self.kpool[layer], self.vpool[layer]):
-            t = pool[pt].permute(0, 2, 1, 3).reshape(n_pages * isa.KV_PAGE, self.cfg.n_kv_heads, isa.HEAD_DIM)
+            t = kv_page_swizzle(pool[pt]).permute(0, 2, 1, 3).reshape(n_pages * isa.KV_PAGE, self.cfg.n_kv_heads, isa.HEAD_DIM)
             out.append(t[:T])
         return out
 

@@ -253,6 +253,35 @@ int vdc_enable_peer_access(int peer_device) {
   return VDC_OK;
 }
 
+int vdc_peer_alloc(size_t bytes, uint64_t* out_ptr) {
+  if (!out_ptr || bytes == 0) return fail_arg("bad peer allocation request");
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, bytes);   // a block of its own: its IPC handle names exactly this allocation
+  if (e != cudaSuccess) return fail_cuda(e, "cudaMalloc(exchange block)");
+  e = cudaMemset(p, 0, bytes);
+  if (e != cudaSuccess) {
+    cudaFree(p);
+    return fail_cuda(e, "cudaMemset(exchange block)");
+  }
+  *out_ptr = reinterpret_cast<uint64_t>(p);
+  return VDC_OK;
+}
+
+int vdc_peer_free(uint64_t ptr) {
+  cudaError_t e = cudaFree(reinterpret_cast<void*>(ptr));
+  if (e != cudaSuccess) return fail_cuda(e, "cudaFree(exchange block)");
+  return VDC_OK;
+}
+
+int vdc_ipc_export(uint64_t ptr, void* handle_out, size_t handle_bytes) {
+  if (!ptr || !handle_out || handle_bytes != sizeof(cudaIpcMemHandle_t)) return fail_arg("bad IPC export request");
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, reinterpret_cast<void*>(ptr));
+  if (e != cudaSuccess) return fail_cuda(e, "cudaIpcGetMemHandle");
+  memcpy(handle_out, &h, sizeof(h));
+  return VDC_OK;
+}
+
 int vdc_ipc_open(const void* handle, size_t handle_bytes, uint64_t* out_ptr) {
   if (!handle || !out_ptr || handle_bytes != sizeof(cudaIpcMemHandle_t)) return fail_arg("bad IPC handle");
   cudaIpcMemHandle_t h;

@@ -110,6 +110,14 @@ __device__ __forceinline__ float ld_relaxed_gpu_f32(const float* p) {
   asm volatile("ld.relaxed.gpu.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
   return v;
 }
+__device__ __forceinline__ int atom_acq_rel_gpu_add(int* p, int v) {
+  int old;
+  asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory");
+  return old;
+}
+__device__ __forceinline__ void red_relaxed_gpu_add(int* p, int v) {
+  asm volatile("red.relaxed.gpu.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 __device__ __forceinline__ void red_release_gpu_add(int* p, int v) {
   asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
@@ -177,12 +185,10 @@ struct __align__(16) Shared {
   volatile int pair_ok[4][2][2];            // GEMV warp pairs: [pair][trip parity][member] chunk arrived
   int att_done[8];                          // attention: warps finished with page pair i % 8
   alignas(16) float red[4096 + 64];                     // task scratch (reductions)
-  alignas(16) float scores[VDC_KV_PAGE * 8];
-  alignas(16) float probs[VDC_KV_PAGE * 8];
-  alignas(16) float wmax[kCW * 8];
-  alignas(16) float qrot[8 * VDC_HEAD_DIM];
+  alignas(16) __nv_bfloat16 qbf[8 * VDC_HEAD_DIM];  // attention: rotated query heads (bf16), tensor-core A operand
   alignas(16) float misc[64];
-  uint4 newrows[32];                        // attention: rotated new key row, new value row (bf16)
+  uint4 newrows[32];                        // attention: rotated new key row, new value row (bf16, page-row swizzle)
+  uint4 zero_row[16];                       // attention: stands in for value rows past the last valid position
   // tensor cores (batched decode): tensor memory is allocated by the first task that needs it
   uint32_t tmem_base;                       // written by tcgen05.alloc
   volatile int tmem_ready;
@@ -259,18 +265,40 @@ __device__ __forceinline__ bool wait_until(const Ctx& c, Pred ready, int role, i
 
 __device__ __forceinline__ bool wait_global_barrier(const Ctx& c, int bar, int role, int pc, int opcode) {
   const int* p = c.bars + bar;
-  bool ok = wait_until(c, [&] { return ld_relaxed_gpu(p) == 0; }, role, pc, opcode, bar, 0);
-  asm volatile("fence.acq_rel.gpu;" ::: "memory");  // pairs with the releasing red of the producers
+  // every poll is an acquire load: the one that reads zero pairs with the producers' releasing reds, and no
+  // separate fence (one more trip to L2) stands between the open barrier and the first dependent access
+  bool ok = wait_until(c, [&] { return ld_acquire_gpu(p) == 0; }, role, pc, opcode, bar, 0);
   fence_proxy_async();  // later bulk copies (async proxy) must observe what the releasing stores wrote
   return ok;
 }
 // The same wait for a consumer that reads the produced data with ordinary loads (no bulk copy follows).
 __device__ __forceinline__ bool wait_global_barrier_generic(const Ctx& c, int bar, int role, int pc, int opcode) {
   const int* p = c.bars + bar;
-  bool ok = wait_until(c, [&] { return ld_relaxed_gpu(p) == 0; }, role, pc, opcode, bar, 0);
-  asm volatile("fence.acq_rel.gpu;" ::: "memory");
+  bool ok = wait_until(c, [&] { return ld_acquire_gpu(p) == 0; }, role, pc, opcode, bar, 0);
   return ok;
 }
+// Tensor-core helpers of the decode attention (legacy warp-level MMA: the problem is 4..8 query rows
+// by 64 positions per page, far below the 128-row tiles of the tcgen05 path the batched projections use).
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t saddr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(saddr) : "memory");
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], uint32_t saddr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(saddr) : "memory");
+}
+// D(16x8, fp32) += A(16x16, bf16, rows 8..15 zero) * B(16x8, bf16).  Only rows 0..7 of A carry data:
+// a_lo / a_hi are this thread's pairs (row lane/4, k = 2(lane%4) + {0,1}) and (same row, k + 8).
+__device__ __forceinline__ void mma_rows8(float& d0, float& d1, float& z0, float& z1, uint32_t a_lo, uint32_t a_hi,
+                                          uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%5}, {%7,%8}, {%0,%1,%2,%3};"
+               : "+f"(d0), "+f"(d1), "+f"(z0), "+f"(z1) : "r"(a_lo), "r"(0u), "r"(a_hi), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
 __device__ __forceinline__ uint4 ldcg128(const void* p) {  // 16 bytes past L1: another SM wrote them
   uint4 v;
   asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));

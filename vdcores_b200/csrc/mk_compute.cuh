@@ -127,6 +127,17 @@ struct Compute {
     // those it observed through the CTA barrier, so no separate fence is needed
     if (tid == 0 && (m & VDC_F_BARRIER) && (m & VDC_F_WRITEBACK)) red_release_gpu_add(c.bars + (m >> 22), -1);
   }
+  // The same count-down for a task whose every writing thread ran __threadfence() after its last global
+  // write and then met thread 0 at a CTA barrier: the writes are performed at gpu scope before the barrier
+  // lets thread 0 through, so the count-down itself carries no fence of its own (a fence here costs one more
+  // trip to L2 on the path every consumer SM is waiting on).
+  __device__ __forceinline__ void release_prefenced(uint32_t m) {
+#ifdef VDC_STRICT_RELEASE
+    release(m);
+#else
+    if (tid == 0 && (m & VDC_F_BARRIER) && (m & VDC_F_WRITEBACK)) red_relaxed_gpu_add(c.bars + (m >> 22), -1);
+#endif
+  }
   // Caller guarantees (with a compute_sync) that no thread still reads the slots.
   __device__ __forceinline__ void free_slots(int mask) {
     if (tid == 0 && mask > 0) atomicOr(&sh->slot_avail, (uint32_t)mask & kSlotMaskAll);
@@ -606,12 +617,10 @@ VDC_TASK void task_gemv_rows(Compute& q, int n_chunks, int mode, bool accumulate
       reinterpret_cast<int*>(sh->misc)[48 + q.warp] = best.idx;
     }
   }
-  // Output rows were written by lanes of every warp.  The CTA barrier inside
-  // warp_phase_end orders them before thread 0, whose gpu-scope fence in
-  // release() is cumulative, so no per-thread fence is needed here.
   GEMV_STAMP(5);
-  // Every writing warp drains its own global writes while the other warps still compute, so that the
-  // releasing fence of thread 0 behind the CTA barrier finds nothing outstanding.
+  // Output rows were written by the lower warp of every pair.  Each of them drains its own global writes
+  // here, while the other warps still compute; the CTA barrier inside warp_phase_end then lets thread 0
+  // count the barrier down without a fence of its own (release_prefenced).
   if (member == 0 && (out_meta & VDC_F_BARRIER)) __threadfence();
   if (peers != nullptr) __threadfence_system();  // the peer stores of this thread, before the arrival below
   if (dyn_rows) {
@@ -643,7 +652,7 @@ VDC_TASK void task_gemv_rows(Compute& q, int n_chunks, int mode, bool accumulate
     recg[2] = 0.f;
     recg[3] = 0.f;
   }
-  q.release(out_meta);
+  q.release_prefenced(out_meta);   // every writing warp fenced before warp_phase_end
   q.release(rec_meta);
   q.free_slots(x_mask);
   GEMV_STAMP(7);
@@ -702,10 +711,8 @@ struct AttnArgs {
 template <int G>
 VDC_TASK void task_attn_decode(Compute& q, const AttnArgs& a) {
   constexpr int D = VDC_HEAD_DIM;
-  constexpr int NG = G / 4;                  // groups of four query heads
-  constexpr int WPG = kCW / NG;              // warps per group
-  constexpr int PPW = VDC_KV_PAGE / WPG;     // positions of a page per warp: 8 or 16
-  constexpr int ROUNDS = PPW / 4;            // four positions per round (eight lanes each)
+  constexpr int PPW = VDC_KV_PAGE / kCW;     // positions of a page per warp: one 8-column MMA tile
+  static_assert(PPW == 8 && D == 128 && G <= 8, "the page loop maps one MMA tile of 8 positions to each warp");
   constexpr int REC = G * D + 16 * ((2 * G + 15) / 16);
   Shared* sh = q.sh;
   const Ctx& c = q.c;
@@ -713,6 +720,7 @@ VDC_TASK void task_attn_decode(Compute& q, const AttnArgs& a) {
 
   ATTN_STAMP(0);
   if (q.tid < 8) sh->att_done[q.tid] = 0;
+  if (q.tid >= 32 && q.tid < 48) sh->zero_row[q.tid - 32] = make_uint4(0u, 0u, 0u, 0u);
   if (a.wait_bar != 0xFFFF && !q.wait_barrier(a.wait_bar, 0x7210)) return;
   ATTN_STAMP(1);
 
@@ -722,6 +730,7 @@ VDC_TASK void task_attn_decode(Compute& q, const AttnArgs& a) {
   count = count < 0 ? 0 : (count > a.max_pages ? a.max_pages : count);
   const bool owner = count > 0 && a.base_page + count == n_pages;
   const int tail_valid = (pos % VDC_KV_PAGE) + 1;  // valid rows of the last page, new row included
+  const int sw_new = pos & 7;                      // piece swizzle of the new row (its row index mod 8)
 
   const float* rope = a.rope + (size_t)pos * D;
   const __nv_bfloat16* knew = a.qkv + G * D;
@@ -755,132 +764,103 @@ VDC_TASK void task_attn_decode(Compute& q, const AttnArgs& a) {
     const float r1 = bf16_round(bf16_round(a1 * cs.y) - bf16_round(b1 * sn.y));
     const float r64 = bf16_round(bf16_round(b0 * cs.x) + bf16_round(a0 * sn.x));
     const float r65 = bf16_round(bf16_round(b1 * cs.y) + bf16_round(a1 * sn.y));
-    if (is_k) {
-      krow[i0] = __float2bfloat16_rn(r0);
-      krow[i0 + 1] = __float2bfloat16_rn(r1);
-      krow[i0 + 64] = __float2bfloat16_rn(r64);
-      krow[i0 + 65] = __float2bfloat16_rn(r65);
-    } else {
-      float* dst = sh->qrot + head * D;  // pre-scaled: scores come out in the exp2 domain
-      dst[i0] = r0 * scale_log2;
-      dst[i0 + 1] = r1 * scale_log2;
-      dst[i0 + 64] = r64 * scale_log2;
-      dst[i0 + 65] = r65 * scale_log2;
-    }
+    // the key row takes the piece order of its row inside the page; query rows stay linear
+    uint32_t* dst = reinterpret_cast<uint32_t*>(is_k ? krow : sh->qbf + head * D);
+    const int sw = is_k ? sw_new : 0;
+    const int e_lo = (((i0 >> 3) ^ sw) << 3) | (i0 & 7), e_hi = ((((i0 + 64) >> 3) ^ sw) << 3) | (i0 & 7);
+    dst[e_lo >> 1] = pack_bf16x2(r0, r1);
+    dst[e_hi >> 1] = pack_bf16x2(r64, r65);
   }
   if (q.tid >= kCT - D / 8) {
     const int t = q.tid - (kCT - D / 8);
-    reinterpret_cast<uint4*>(vrow)[t] = ldcg128(reinterpret_cast<const uint4*>(vnew) + t);
+    reinterpret_cast<uint4*>(vrow)[t ^ sw_new] = ldcg128(reinterpret_cast<const uint4*>(vnew) + t);
   }
   const unsigned n_ent = 2u * (unsigned)count;  // ring entries: K page, V page, K page, ...
-  q.warp_phase_begin(n_ent, 0u);              // its CTA barrier also publishes qrot / krow / vrow
+  q.warp_phase_begin(n_ent, 0u);              // its CTA barrier also publishes qbf / krow / vrow / zero_row
   ATTN_STAMP(2);
 
-  // QK phase: eight lanes per position, each with two 8-dim pieces (sub, sub + 8) of the row;
-  // PV phase: lane l owns output dims 4l..4l+3 of the warp's four heads.
-  const int hg = q.warp / WPG, slice = (q.warp % WPG) * PPW;
-  const int sub = q.lane & 7, pl = q.lane >> 3;
-  float qreg[4][16];
+  // Tensor-core page loop.  A warp owns positions 8w..8w+7 of every page: one 16x8x16 MMA tile column.
+  // Scores: S[g][p] = sum_d Q[g][d] K[p][d], Q rows 0..G-1 of the A operand (rows G..15 zero), eight
+  // k-steps; thread (gid = lane / 4, t = lane % 4) ends up with row gid, positions 2t and 2t + 1.
+  // Output: O[g][d] += P[g][p] V[p][d] with the warp's eight positions as the lower half of a k-step
+  // (upper half zero), sixteen 8-dim tiles; thread holds row gid, dims 8 nt + 2t, + 1.
+  // Page rows are 256 bytes with their 16-byte pieces stored at (piece XOR (row mod 8)), in HBM and
+  // therefore in the slot: the eight row addresses of one ldmatrix fall into eight different banks.
+  const int gid = q.lane >> 2, t4 = q.lane & 3;
+  const int lrow = q.lane & 7, lmi = q.lane >> 3;    // ldmatrix: this lane supplies row lrow of matrix lmi
+  const int slice = q.warp * PPW;
+  uint32_t qa[8][2];
+  {
+    const uint32_t* qb = reinterpret_cast<const uint32_t*>(sh->qbf) + gid * (D / 2);
 #pragma unroll
-  for (int g = 0; g < 4; ++g)
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const float* src = sh->qrot + (hg * 4 + g) * D + (sub + h * 8) * 8;
-      const float4 lo = *reinterpret_cast<const float4*>(src);
-      const float4 hi = *reinterpret_cast<const float4*>(src + 4);
-      qreg[g][h * 8 + 0] = lo.x; qreg[g][h * 8 + 1] = lo.y; qreg[g][h * 8 + 2] = lo.z; qreg[g][h * 8 + 3] = lo.w;
-      qreg[g][h * 8 + 4] = hi.x; qreg[g][h * 8 + 5] = hi.y; qreg[g][h * 8 + 6] = hi.z; qreg[g][h * 8 + 7] = hi.w;
+    for (int ks = 0; ks < 8; ++ks) {
+      qa[ks][0] = gid < G ? qb[8 * ks + t4] : 0u;
+      qa[ks][1] = gid < G ? qb[8 * ks + 4 + t4] : 0u;
     }
-  float m_run[4], l_run[4], acc[4][4];
-#pragma unroll
-  for (int g = 0; g < 4; ++g) {
-    m_run[g] = -INFINITY;
-    l_run[g] = 0.f;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) acc[g][j] = 0.f;
   }
+  const uint32_t krow_s = (uint32_t)__cvta_generic_to_shared(krow);
+  const uint32_t vrow_s = (uint32_t)__cvta_generic_to_shared(vrow);
+  const uint32_t zero_s = (uint32_t)__cvta_generic_to_shared(sh->zero_row);
+  float m_run = -INFINITY, l_run = 0.f, acc[16][2], z0 = 0.f, z1 = 0.f;
+#pragma unroll
+  for (int nt = 0; nt < 16; ++nt) acc[nt][0] = acc[nt][1] = 0.f;
   for (int blk = 0; blk < count; ++blk) {
     const int k_mask = q.warp_wait(2u * (unsigned)blk);
     if (k_mask == kPopAbort) break;
     ATTN_STAMP(3 + 3 * (blk & 1));
-    const uint8_t* kb = (const uint8_t*)slot_ptr(c, first_slot(k_mask));
     const bool last = owner && blk == count - 1;
     const int valid = last ? tail_valid : VDC_KV_PAGE;
     const int newpos = last ? tail_valid - 1 : -1;  // this row of the page is not in HBM yet
-    // ---- scores of this warp's positions
-    float s[ROUNDS][4];
+    const int p_l = slice + lrow;                   // the page row this lane addresses
+    // ---- scores of the warp's eight positions
+    const uint32_t kb_s = (uint32_t)__cvta_generic_to_shared(slot_ptr(c, first_slot(k_mask)));
+    const uint32_t k_base = p_l == newpos ? krow_s : kb_s + (uint32_t)p_l * (D * 2);
+    float s0 = 0.f, s1 = 0.f, u0 = 0.f, u1 = 0.f;   // two accumulation chains: even and odd k-steps
 #pragma unroll
-    for (int rd = 0; rd < ROUNDS; ++rd) {
-      const int p = slice + rd * 4 + pl;
-      const uint8_t* kr = (p == newpos) ? reinterpret_cast<const uint8_t*>(krow) : kb + p * (D * 2);
-#pragma unroll
-      for (int g = 0; g < 4; ++g) s[rd][g] = 0.f;
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const uint4 kv = lds128(kr + (sub + h * 8) * 16);
-        const float kf[8] = {bf_lo(kv.x), bf_hi(kv.x), bf_lo(kv.y), bf_hi(kv.y),
-                             bf_lo(kv.z), bf_hi(kv.z), bf_lo(kv.w), bf_hi(kv.w)};
-#pragma unroll
-        for (int g = 0; g < 4; ++g)
-#pragma unroll
-          for (int j = 0; j < 8; ++j) s[rd][g] = fmaf(qreg[g][h * 8 + j], kf[j], s[rd][g]);
-      }
-#pragma unroll
-      for (int g = 0; g < 4; ++g) {
-        s[rd][g] += __shfl_xor_sync(0xffffffffu, s[rd][g], 1);
-        s[rd][g] += __shfl_xor_sync(0xffffffffu, s[rd][g], 2);
-        s[rd][g] += __shfl_xor_sync(0xffffffffu, s[rd][g], 4);
-        if (p >= valid) s[rd][g] = -INFINITY;
-      }
+    for (int j = 0; j < 4; ++j) {
+      uint32_t kr[4];
+      ldsm_x4(kr, k_base + (uint32_t)(((4 * j + lmi) ^ lrow) << 4));
+      mma_rows8(s0, s1, z0, z1, qa[2 * j][0], qa[2 * j][1], kr[0], kr[1]);
+      mma_rows8(u0, u1, z0, z1, qa[2 * j + 1][0], qa[2 * j + 1][1], kr[2], kr[3]);
     }
-    // ---- online softmax over the warp's positions (values are uniform over the eight lanes of a position)
-    float alpha[4];
+    s0 += u0;
+    s1 += u1;
+    // ---- online softmax (exp2 domain); a row's eight positions sit in the four lanes of a quad
+    const int p0 = slice + 2 * t4;
+    s0 = p0 < valid ? s0 * scale_log2 : -INFINITY;
+    s1 = p0 + 1 < valid ? s1 * scale_log2 : -INFINITY;
+    float mx = fmaxf(s0, s1);
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float m_new = fmaxf(m_run, mx);
+    const bool none = m_new == -INFINITY;
+    const float alpha = none ? 1.f : exp2f(m_run - m_new);
+    const float e0 = none ? 0.f : exp2f(s0 - m_new), e1 = none ? 0.f : exp2f(s1 - m_new);
+    float sum = e0 + e1;
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    m_run = m_new;
+    l_run = l_run * alpha + sum;
+    // probabilities enter the PV product rounded to bf16, as a bf16 attention module hands them over
+    const uint32_t pa = pack_bf16x2(e0, e1);
 #pragma unroll
-    for (int g = 0; g < 4; ++g) {
-      float mx = s[0][g];
-#pragma unroll
-      for (int rd = 1; rd < ROUNDS; ++rd) mx = fmaxf(mx, s[rd][g]);
-      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
-      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
-      const float m_new = fmaxf(m_run[g], mx);
-      alpha[g] = (m_new == -INFINITY) ? 1.f : exp2f(m_run[g] - m_new);
-      m_run[g] = m_new;
-      float sum = 0.f;
-#pragma unroll
-      for (int rd = 0; rd < ROUNDS; ++rd) {
-        // HF rounds probabilities to bf16 after the softmax; here they stay fp32
-        s[rd][g] = (m_new == -INFINITY) ? 0.f : exp2f(s[rd][g] - m_new);
-        sum += s[rd][g];
-      }
-      sum += __shfl_xor_sync(0xffffffffu, sum, 8);
-      sum += __shfl_xor_sync(0xffffffffu, sum, 16);
-      l_run[g] = l_run[g] * alpha[g] + sum;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) acc[g][j] *= alpha[g];
+    for (int nt = 0; nt < 16; ++nt) {
+      acc[nt][0] *= alpha;
+      acc[nt][1] *= alpha;
     }
     // ---- O += P V
     const int v_mask = q.warp_wait(2u * (unsigned)blk + 1u);
     if (v_mask == kPopAbort) break;
     ATTN_STAMP(4 + 3 * (blk & 1));
-    const uint8_t* vb = (const uint8_t*)slot_ptr(c, first_slot(v_mask));
+    const uint32_t vb_s = (uint32_t)__cvta_generic_to_shared(slot_ptr(c, first_slot(v_mask)));
+    const uint32_t v_base = p_l == newpos ? vrow_s : (p_l >= valid ? zero_s : vb_s + (uint32_t)p_l * (D * 2));
 #pragma unroll
-    for (int rd = 0; rd < ROUNDS; ++rd)
+    for (int j = 0; j < 4; ++j) {
+      uint32_t vr[4];
+      ldsm_x4_trans(vr, v_base + (uint32_t)(((4 * j + lmi) ^ lrow) << 4));
 #pragma unroll
-      for (int pp = 0; pp < 4; ++pp) {
-        const int p = slice + rd * 4 + pp;
-        float pr[4];
-#pragma unroll
-        for (int g = 0; g < 4; ++g) pr[g] = __shfl_sync(0xffffffffu, s[rd][g], pp * 8);
-        if (p < valid) {  // uniform over the warp
-          const uint8_t* vr = (p == newpos) ? reinterpret_cast<const uint8_t*>(vrow) : vb + p * (D * 2);
-          const uint2 vv = *reinterpret_cast<const uint2*>(vr + q.lane * 8);
-          const float vf[4] = {bf_lo(vv.x), bf_hi(vv.x), bf_lo(vv.y), bf_hi(vv.y)};
-#pragma unroll
-          for (int g = 0; g < 4; ++g)
-#pragma unroll
-            for (int j = 0; j < 4; ++j) acc[g][j] = fmaf(pr[g], vf[j], acc[g][j]);
-        }
-      }
+      for (int mi = 0; mi < 4; ++mi) mma_rows8(acc[4 * j + mi][0], acc[4 * j + mi][1], z0, z1, pa, 0u, vr[mi], 0u);
+    }
     // ---- the warp is done with this page pair; the last of the eight gives the slots back
     __syncwarp();
     if (q.lane == 0) {
@@ -893,91 +873,153 @@ VDC_TASK void task_attn_decode(Compute& q, const AttnArgs& a) {
     ATTN_STAMP(5 + 3 * (blk & 1));
   }
   if (q.lane == 0) sh->warp_next[q.warp] = 0xFFFFFFFFu;
-  // ---- the warps' states meet in shared memory: red[warp][4 heads][128], then m and l
+  // ---- the warps' states meet in shared memory, four query rows at a time: red[warp][4][128], then m and l
   float* red = sh->red;
-  *reinterpret_cast<float4*>(red + (q.warp * 4 + 0) * D + q.lane * 4) = make_float4(acc[0][0], acc[0][1], acc[0][2], acc[0][3]);
-  *reinterpret_cast<float4*>(red + (q.warp * 4 + 1) * D + q.lane * 4) = make_float4(acc[1][0], acc[1][1], acc[1][2], acc[1][3]);
-  *reinterpret_cast<float4*>(red + (q.warp * 4 + 2) * D + q.lane * 4) = make_float4(acc[2][0], acc[2][1], acc[2][2], acc[2][3]);
-  *reinterpret_cast<float4*>(red + (q.warp * 4 + 3) * D + q.lane * 4) = make_float4(acc[3][0], acc[3][1], acc[3][2], acc[3][3]);
-  if (q.lane < 4) {
-    float mv = m_run[0], lv = l_run[0];
-#pragma unroll
-    for (int g = 1; g < 4; ++g)
-      if (q.lane == g) {
-        mv = m_run[g];
-        lv = l_run[g];
-      }
-    red[kCW * 4 * D + q.warp * 8 + q.lane] = mv;
-    red[kCW * 4 * D + q.warp * 8 + 4 + q.lane] = lv;
-  }
-  q.warp_phase_end(n_ent);  // CTA barrier: every warp is done with the pages and has published its state
-  if (q.aborted) return;
-  ATTN_STAMP(11);
+  float* ml = red + kCW * 4 * D;   // [warp][m of 4 rows | l of 4 rows]
   float* rec = a.records + (size_t)a.split * REC;
-  for (int o = q.tid; o < G * D; o += kCT) {
-    const int g = o / D, d = o % D, w0 = (g >> 2) * WPG, gg = g & 3;
-    const float* ml = red + kCW * 4 * D;
-    float m = -INFINITY;
 #pragma unroll
-    for (int k = 0; k < WPG; ++k) m = fmaxf(m, ml[(w0 + k) * 8 + gg]);
-    float num = 0.f, l = 0.f;
+  for (int pass = 0; pass < (G + 3) / 4; ++pass) {
+    if (pass > 0) compute_sync();  // the previous pass has been folded
+    if ((gid >> 2) == pass) {
+      float* dst = red + (q.warp * 4 + (gid & 3)) * D + 2 * t4;
 #pragma unroll
-    for (int k = 0; k < WPG; ++k) {
-      const float mw = ml[(w0 + k) * 8 + gg];
-      const float wgt = (mw == -INFINITY) ? 0.f : exp2f(mw - m);
-      num = fmaf(wgt, red[((w0 + k) * 4 + gg) * D + d], num);
-      l = fmaf(wgt, ml[(w0 + k) * 8 + 4 + gg], l);
+      for (int nt = 0; nt < 16; ++nt) *reinterpret_cast<float2*>(dst + 8 * nt) = make_float2(acc[nt][0], acc[nt][1]);
+      if (t4 == 0) {
+        ml[q.warp * 8 + (gid & 3)] = m_run;
+        ml[q.warp * 8 + 4 + (gid & 3)] = l_run;
+      }
     }
-    rec[o] = num;
-    if (d == 0) {
-      rec[G * D + g] = m;
-      rec[G * D + G + g] = l;
+    if (pass == 0) {
+      q.warp_phase_end(n_ent);  // CTA barrier: every warp is done with the pages and has published its state
+      if (q.aborted) return;
+      ATTN_STAMP(11);
+    } else {
+      compute_sync();
+    }
+    for (int o = q.tid; o < 4 * D; o += kCT) {
+      const int gg = o / D, d = o % D, g = pass * 4 + gg;
+      if (g >= G) break;
+      float m = -INFINITY;
+#pragma unroll
+      for (int k = 0; k < kCW; ++k) m = fmaxf(m, ml[k * 8 + gg]);
+      float num = 0.f, l = 0.f;
+#pragma unroll
+      for (int k = 0; k < kCW; ++k) {
+        const float mw = ml[k * 8 + gg];
+        const float wgt = (mw == -INFINITY) ? 0.f : exp2f(mw - m);
+        num = fmaf(wgt, red[(k * 4 + gg) * D + d], num);
+        l = fmaf(wgt, ml[k * 8 + 4 + gg], l);
+      }
+      rec[g * D + d] = num;
+      if (d == 0) {
+        rec[G * D + g] = m;
+        rec[G * D + G + g] = l;
+      }
     }
   }
   if (owner && q.tid >= 64 && q.tid < 64 + 2 * (D / 8)) {
-    // the new cache rows go to HBM; the next step's page loads (a later launch) see them
+    // the new cache rows go to HBM (already in the page-row piece order); the next step's page loads
+    // (a later launch) see them
     const int t = q.tid - 64;
     const size_t off = (size_t)ld_relaxed_gpu(a.state + VDC_ST_NEWROW) * (D * 2);
     uint8_t* dst = (t < D / 8 ? a.k_rows : a.v_rows) + off;
     reinterpret_cast<uint4*>(dst)[t % (D / 8)] = reinterpret_cast<const uint4*>(sh->newrows)[t];
   }
-  // arrival: the record is complete once every writer passed the barrier; thread 0's
-  // gpu-scope fence before the counter bump makes it visible to whoever arrives last
+  // arrival: every writer drains its own record writes (in parallel), the barrier collects them, and
+  // thread 0's acquire-release bump of the head's counter publishes them to whoever arrives last
+  __threadfence();
   compute_sync();
   if (q.tid == 0) {
-    __threadfence();
-    const int old = atomicAdd(a.counter, 1);
-    __threadfence();
+    const int old = atom_acq_rel_gpu_add(a.counter, 1);
     sh->misc[34] = (old == a.n_splits - 1) ? 1.f : 0.f;
   }
   compute_sync();
   ATTN_STAMP(12);
   if (sh->misc[34] == 0.f) return;
 
-  // ---- last arrival for this head: merge the split records (read past L1: other SMs wrote them)
-  for (int o = q.tid; o < G * D; o += kCT) {
-    const int g = o / D;
-    float m = -INFINITY;
-    for (int sidx = 0; sidx < a.n_splits; ++sidx) m = fmaxf(m, __ldcg(a.records + (size_t)sidx * REC + G * D + g));
-    float num = 0.f, den = 0.f;
-    for (int sidx = 0; sidx < a.n_splits; ++sidx) {
+  // ---- last arrival for this head: merge the split records (read past L1: other SMs wrote them).
+  // Two outputs per thread.  The numerators of the first sixteen splits are requested before anything
+  // else; meanwhile one warp per query row turns the splits' maxima and sums into weights in shared
+  // memory, so the whole merge costs about one L2 round trip.
+  const int ns = a.n_splits;
+  float* wts = red;                  // [n_splits][G] weights 2^(m_s - m), then den[G]
+  const int o = q.tid * 2;           // G * 128 outputs over 256 threads: G / 4 rounds
+  float2 vs[16];
+#pragma unroll
+  for (int k = 0; k < 16; ++k)
+    vs[k] = k < ns ? __ldcg(reinterpret_cast<const float2*>(a.records + (size_t)k * REC + o)) : make_float2(0.f, 0.f);
+  if (q.warp < G) {
+    const int g = q.warp;
+    // lane-strided over the splits; the first two rounds stay in registers
+    float mr[2] = {-INFINITY, -INFINITY}, lr[2] = {0.f, 0.f};
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int sidx = q.lane + 32 * k;
+      if (sidx < ns) {
+        mr[k] = __ldcg(a.records + (size_t)sidx * REC + G * D + g);
+        lr[k] = __ldcg(a.records + (size_t)sidx * REC + G * D + G + g);
+      }
+    }
+    float m = fmaxf(mr[0], mr[1]);
+    for (int sidx = q.lane + 64; sidx < ns; sidx += 32) m = fmaxf(m, __ldcg(a.records + (size_t)sidx * REC + G * D + g));
+#pragma unroll
+    for (int sh_ = 16; sh_ > 0; sh_ >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, sh_));
+    float den = 0.f;
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int sidx = q.lane + 32 * k;
+      if (sidx < ns) {
+        const float w = (mr[k] == -INFINITY) ? 0.f : exp2f(mr[k] - m);
+        wts[sidx * G + g] = w;
+        den = fmaf(w, lr[k], den);
+      }
+    }
+    for (int sidx = q.lane + 64; sidx < ns; sidx += 32) {
       const float* r = a.records + (size_t)sidx * REC;
       const float ms = __ldcg(r + G * D + g);
       const float w = (ms == -INFINITY) ? 0.f : exp2f(ms - m);
-      num = fmaf(w, __ldcg(r + o), num);
+      wts[sidx * G + g] = w;
       den = fmaf(w, __ldcg(r + G * D + G + g), den);
     }
-    const __nv_bfloat16 res = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
-    if (a.bpad)
-      *reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<uint8_t*>(a.out) + (size_t)(o >> 3) * a.bpad * 16 +
-                                        (a.b >> 3) * 128 + (a.b & 7) * 16 + (o & 7) * 2) = res;
-    else
-      a.out[o] = res;
+    den = warp_sum(den);
+    if (q.lane == 0) wts[ns * G + g] = den;
   }
   compute_sync();
+#pragma unroll
+  for (int rnd = 0; rnd < (G * D) / (2 * kCT); ++rnd) {
+    const int oo = o + rnd * 2 * kCT, g = oo / D;
+    float n0 = 0.f, n1 = 0.f;
+    if (rnd == 0) {
+#pragma unroll
+      for (int k = 0; k < 16; ++k) {
+        const float w = k < ns ? wts[k * G + g] : 0.f;
+        n0 = fmaf(w, vs[k].x, n0);
+        n1 = fmaf(w, vs[k].y, n1);
+      }
+    }
+#pragma unroll 8
+    for (int sidx = rnd == 0 ? 16 : 0; sidx < ns; ++sidx) {
+      const float2 v = __ldcg(reinterpret_cast<const float2*>(a.records + (size_t)sidx * REC + oo));
+      const float w = wts[sidx * G + g];
+      n0 = fmaf(w, v.x, n0);
+      n1 = fmaf(w, v.y, n1);
+    }
+    const float den = wts[ns * G + g];
+    const __nv_bfloat16 r0 = __float2bfloat16_rn(den > 0.f ? n0 / den : 0.f);
+    const __nv_bfloat16 r1 = __float2bfloat16_rn(den > 0.f ? n1 / den : 0.f);
+    if (a.bpad) {
+      uint8_t* dst = reinterpret_cast<uint8_t*>(a.out) + (size_t)(oo >> 3) * a.bpad * 16 + (a.b >> 3) * 128 + (a.b & 7) * 16 +
+                     (oo & 7) * 2;
+      *reinterpret_cast<__nv_bfloat162*>(dst) = __halves2bfloat162(r0, r1);
+    } else {
+      *reinterpret_cast<__nv_bfloat162*>(a.out + oo) = __halves2bfloat162(r0, r1);
+    }
+  }
+  __threadfence();   // every writer drains its outputs in parallel
+  compute_sync();
+  ATTN_STAMP(13);
   if (q.tid == 0) {
     *a.counter = 0;  // ready for the next layer / step; ordered before its use by the barrier chain
-    __threadfence();
     red_release_gpu_add(c.bars + a.bar, -1);
   }
 }

@@ -70,11 +70,6 @@ __device__ __forceinline__ size_t kc_piece(int bpad, int b, int k) {
   return ((size_t)(k >> 3) * (size_t)(bpad >> 3) + (size_t)(b >> 3)) * 128 + (size_t)(b & 7) * 16;
 }
 
-__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
-  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-  return *reinterpret_cast<const uint32_t*>(&v);
-}
-
 // Bounded wait on one of the tensor-core completion barriers (thread 0 only).
 __device__ __forceinline__ bool mma_wait(Compute& q, unsigned commit_index) {
   uint64_t* bar = &q.sh->mma_bar[commit_index & 3u];

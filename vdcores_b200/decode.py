@@ -84,6 +84,18 @@ class DenseWeights:
     router: Optional[List[torch.Tensor]] = None
 
 
+def kv_page_swizzle(pages: torch.Tensor) -> torch.Tensor:
+    """Piece order of KV page rows in HBM.  `pages` is [..., 64 rows, 128] bf16; every 256-byte row is stored
+    with its sixteen 16-byte pieces at index (piece XOR (row mod 8)).  A page reaches shared memory as one
+    linear copy, and with this order the eight row addresses of an `ldmatrix` (same piece, eight consecutive
+    rows) fall into eight different banks.  The map is its own inverse: it converts both ways."""
+    assert pages.shape[-2] == isa.KV_PAGE and pages.shape[-1] == isa.HEAD_DIM
+    rows = torch.arange(isa.KV_PAGE, device=pages.device)
+    idx = torch.arange(isa.HEAD_DIM // 8, device=pages.device)[None, :] ^ (rows[:, None] & 7)      # [64, 16]
+    v = pages.reshape(*pages.shape[:-1], isa.HEAD_DIM // 8, 8)
+    return v[..., rows[:, None], idx, :].reshape(pages.shape)
+
+
 def rows_per_chunk(K: int, even: bool = False, row_bytes: Optional[int] = None) -> int:
     """Largest power-of-two row count whose rows (bf16 unless row_bytes is given) fit one 32 KB bulk copy."""
     row_bytes = 2 * K if row_bytes is None else row_bytes
@@ -659,7 +671,8 @@ class DecodeEngine:
                 n_pages = (T + isa.KV_PAGE - 1) // isa.KV_PAGE
                 pad = torch.zeros(n_pages * isa.KV_PAGE, cfg.n_kv_heads, isa.HEAD_DIM, dtype=BF16, device=self.dev)
                 pad[:T] = src.to(self.dev)
-                pool[pt[:n_pages]] = pad.view(n_pages, isa.KV_PAGE, cfg.n_kv_heads, isa.HEAD_DIM).permute(0, 2, 1, 3)
+                pool[pt[:n_pages]] = kv_page_swizzle(
+                    pad.view(n_pages, isa.KV_PAGE, cfg.n_kv_heads, isa.HEAD_DIM).permute(0, 2, 1, 3))
 
     def read_kv(self, layer: int, T: int):
         """Contiguous [T, n_kv_heads, 128] views of layer `layer`'s cache (tests)."""
@@ -667,7 +680,7 @@ class DecodeEngine:
         pt = self.page_table.long().to(self.dev)[:n_pages]
         out = []
         for pool in (self.kpool[layer], self.vpool[layer]):
-            t = pool[pt].permute(0, 2, 1, 3).reshape(n_pages * isa.KV_PAGE, self.cfg.n_kv_heads, isa.HEAD_DIM)
+            t = kv_page_swizzle(pool[pt]).permute(0, 2, 1, 3).reshape(n_pages * isa.KV_PAGE, self.cfg.n_kv_heads, isa.HEAD_DIM)
             out.append(t[:T])
         return out
 

@@ -49,6 +49,12 @@ _lib.vdc_ipc_open.argtypes = [ctypes.c_char_p, ctypes.c_size_t, ctypes.POINTER(c
 _lib.vdc_ipc_open.restype = _i32
 _lib.vdc_ipc_close.argtypes = [_u64]
 _lib.vdc_ipc_close.restype = _i32
+_lib.vdc_peer_alloc.argtypes = [ctypes.c_size_t, ctypes.POINTER(ctypes.c_uint64)]
+_lib.vdc_peer_alloc.restype = _i32
+_lib.vdc_peer_free.argtypes = [_u64]
+_lib.vdc_peer_free.restype = _i32
+_lib.vdc_ipc_export.argtypes = [_u64, ctypes.c_char_p, ctypes.c_size_t]
+_lib.vdc_ipc_export.restype = _i32
 _lib.vdc_opcode_name.restype = ctypes.c_char_p
 _lib.vdc_opcode_name.argtypes = [_i32]
 _lib.vdc_opcode_value.argtypes = [_i32]
@@ -61,7 +67,7 @@ _lib.vdc_last_error.restype = ctypes.c_char_p
 EXPORTED_SYMBOLS = [
     "vdc_version", "vdc_init", "vdc_set_smem_size", "vdc_launch", "vdc_launch_async", "vdc_launch_static",
     "vdc_read_status",
-    "vdc_build_tma_desc", "vdc_set_cache_policy", "vdc_enable_peer_access", "vdc_ipc_open", "vdc_ipc_close", "vdc_opcode_count", "vdc_opcode_name", "vdc_opcode_value",
+    "vdc_build_tma_desc", "vdc_set_cache_policy", "vdc_enable_peer_access", "vdc_ipc_open", "vdc_ipc_close", "vdc_peer_alloc", "vdc_peer_free", "vdc_ipc_export", "vdc_opcode_count", "vdc_opcode_name", "vdc_opcode_value",
     "vdc_opcode_is_compute", "vdc_config", "vdc_family_specs", "vdc_last_error",
 ]
 
@@ -202,6 +208,28 @@ def ipc_open(handle: bytes) -> int:
     out = ctypes.c_uint64(0)
     _check(_lib.vdc_ipc_open(handle, len(handle), ctypes.byref(out)))
     return int(out.value)
+
+
+class PeerBlock:
+    """Device memory allocated by the library as a block of its own (cudaMalloc), zeroed; `handle` is its
+    64-byte CUDA IPC handle for other processes' ipc_open.  `tensor(dtype)` views it as a torch tensor."""
+
+    def __init__(self, nbytes: int):
+        out = ctypes.c_uint64(0)
+        _check(_lib.vdc_peer_alloc(int(nbytes), ctypes.byref(out)))
+        self.ptr, self.nbytes = int(out.value), int(nbytes)
+        buf = ctypes.create_string_buffer(64)
+        _check(_lib.vdc_ipc_export(self.ptr, buf, 64))
+        self.handle = bytes(buf.raw)
+        self.__cuda_array_interface__ = {"shape": (self.nbytes,), "typestr": "|u1", "data": (self.ptr, False), "version": 2}
+
+    def tensor(self, dtype=torch.uint8):
+        return torch.as_tensor(self, device=f"cuda:{torch.cuda.current_device()}").view(dtype)
+
+    def free(self):
+        if self.ptr:
+            _check(_lib.vdc_peer_free(self.ptr))
+            self.ptr = 0
 
 
 def ipc_close(ptr: int):

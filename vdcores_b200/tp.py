@@ -24,7 +24,7 @@ import torch
 import torch.distributed as dist
 
 from . import isa, runtime
-from .decode import BF16, DecodeConfig, DecodeEngine, DenseWeights, rows_per_chunk
+from .decode import BF16, DecodeConfig, DecodeEngine, DenseWeights, kv_page_swizzle, rows_per_chunk
 from .program import Dst, Program, Src
 
 
@@ -384,7 +384,7 @@ class TPDecodeEngine:
                 n_pages = (T + isa.KV_PAGE - 1) // isa.KV_PAGE
                 pad = torch.zeros(n_pages * isa.KV_PAGE, self.nkv, isa.HEAD_DIM, dtype=BF16, device=self.dev)
                 pad[:T] = src[:, h0:h0 + self.nkv].to(self.dev)
-                pool[:n_pages] = pad.view(n_pages, isa.KV_PAGE, self.nkv, isa.HEAD_DIM).permute(0, 2, 1, 3)
+                pool[:n_pages] = kv_page_swizzle(pad.view(n_pages, isa.KV_PAGE, self.nkv, isa.HEAD_DIM).permute(0, 2, 1, 3))
 
     # ------------------------------------------------------------------ decode
     def _launch(self, i: int):
@@ -525,34 +525,24 @@ class TPFusedEngine(TPDecodeEngine):
         self.off_best = 2 * Pn * H * 4
         self.off_cnt = self.off_best + Pn * 16
         n_bytes = self.off_cnt + (2 * L + 1) * 4
-        self.xchg = torch.zeros((n_bytes + 255) // 256 * 64, dtype=torch.float32, device=self.dev)
-        self._peer_storages = []
+        # the block is an allocation of its own made by the library, so that its CUDA IPC handle names exactly it
+        with torch.cuda.device(self.dev):
+            self._block = runtime.PeerBlock((n_bytes + 255) // 256 * 256)
+            self.xchg = self._block.tensor(torch.float32)
+        self._peer_mappings = []
         bases = [0] * Pn
-        if Pn == 1:
-            bases[0] = self.xchg.data_ptr()
-        else:
-            handle = self.xchg.untyped_storage()._share_cuda_()
+        bases[self.rank] = self._block.ptr
+        if Pn > 1:
             handles = [None] * Pn
-            dist.all_gather_object(handles, handle, group=self.group)
+            dist.all_gather_object(handles, (self.dev.index, self._block.handle), group=self.group)
             for r in range(Pn):
                 if r == self.rank:
-                    bases[r] = self.xchg.data_ptr()
                     continue
-                assert torch.cuda.can_device_access_peer(self.dev.index, handles[r][0]), "peer access is required"
-                # handles[r] = (device, 64-byte IPC handle of the base allocation, size, offset, ...): mapped
-                # with THIS device current, so that this device's kernels can store there
-                raw = bytes(handles[r][1])
-                # the caching allocator wraps the 64-byte driver handle: [format version][b"c": a plain
-                # cudaMalloc block][handle] (66 bytes), or [b"c"][handle] (65) in older releases
-                if len(raw) in (65, 66):
-                    assert raw[len(raw) - 65:len(raw) - 64] == b"c", "the exchange block must come from a plain (not expandable) segment"
-                    raw = raw[-64:]
-                if len(raw) != 64:
-                    raise RuntimeError(f"unexpected CUDA IPC handle of {len(raw)} bytes from the allocator")
-                with torch.cuda.device(self.dev):
-                    base = runtime.ipc_open(raw)
-                self._peer_storages.append(base)
-                bases[r] = base + int(handles[r][3])
+                peer_dev, handle = handles[r]
+                assert torch.cuda.can_device_access_peer(self.dev.index, peer_dev), "peer access is required"
+                with torch.cuda.device(self.dev):      # mapped with THIS device current: its kernels store there
+                    bases[r] = runtime.ipc_open(handle)
+                self._peer_mappings.append(bases[r])
             torch.cuda.synchronize(self.dev)
             dist.barrier(group=self.group)
         self.peer_table = torch.tensor(bases, dtype=torch.int64, device=self.dev)
@@ -665,6 +655,7 @@ class TPFusedEngine(TPDecodeEngine):
         n = max(max(len(x) for x in P.m), max(len(x) for x in P.c)) + 2
         P.insts_per_sm = ((n + 63) // 64) * 64
         c, m, bars = P.finalize()
+        self.program = P
         self.programs = [(torch.from_numpy(c).to(self.dev), torch.from_numpy(m).to(self.dev),
                           torch.from_numpy(bars).to(self.dev), P.insts_per_sm)]
 
@@ -686,7 +677,13 @@ class TPFusedEngine(TPDecodeEngine):
                              torch.cuda.current_stream(self.dev).cuda_stream, self.timeout_ns)
 
     def close(self):
+        """Unmaps the other ranks' blocks, waits for every rank to have done so, then frees this rank's."""
         torch.cuda.synchronize(self.dev)
-        for base in self._peer_storages:
-            runtime.ipc_close(base)
-        self._peer_storages = []
+        with torch.cuda.device(self.dev):
+            for base in self._peer_mappings:
+                runtime.ipc_close(base)
+        self._peer_mappings = []
+        if self.world > 1:
+            dist.barrier(group=self.group)
+        self.xchg = None
+        self._block.free()
