@@ -110,9 +110,9 @@ __device__ __forceinline__ float ld_relaxed_gpu_f32(const float* p) {
   asm volatile("ld.relaxed.gpu.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
   return v;
 }
-__device__ __forceinline__ int atom_acq_rel_gpu_add(int* p, int v) {
+__device__ __forceinline__ int atom_acquire_gpu_add(int* p, int v) {
   int old;
-  asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory");
+  asm volatile("atom.acquire.gpu.global.add.s32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory");
   return old;
 }
 __device__ __forceinline__ void red_relaxed_gpu_add(int* p, int v) {

@@ -925,12 +925,13 @@ VDC_TASK void task_attn_decode(Compute& q, const AttnArgs& a) {
     uint8_t* dst = (t < D / 8 ? a.k_rows : a.v_rows) + off;
     reinterpret_cast<uint4*>(dst)[t % (D / 8)] = reinterpret_cast<const uint4*>(sh->newrows)[t];
   }
-  // arrival: every writer drains its own record writes (in parallel), the barrier collects them, and
-  // thread 0's acquire-release bump of the head's counter publishes them to whoever arrives last
+  // arrival: every writer drains its own record writes (in parallel) before the barrier lets thread 0
+  // bump the head's counter, so the bump needs no releasing fence of its own; its acquire side orders the
+  // merge's reads behind the other splits' bumps
   __threadfence();
   compute_sync();
   if (q.tid == 0) {
-    const int old = atom_acq_rel_gpu_add(a.counter, 1);
+    const int old = atom_acquire_gpu_add(a.counter, 1);
     sh->misc[34] = (old == a.n_splits - 1) ? 1.f : 0.f;
   }
   compute_sync();
@@ -1019,8 +1020,8 @@ VDC_TASK void task_attn_decode(Compute& q, const AttnArgs& a) {
   compute_sync();
   ATTN_STAMP(13);
   if (q.tid == 0) {
-    *a.counter = 0;  // ready for the next layer / step; ordered before its use by the barrier chain
-    red_release_gpu_add(c.bars + a.bar, -1);
+    *a.counter = 0;  // this layer's counter is next used by the next step, a later launch
+    red_relaxed_gpu_add(c.bars + a.bar, -1);  // every writer fenced before the barrier above
   }
 }
 

@@ -16,6 +16,7 @@ serves every step.
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass
 from typing import List, Optional
 
@@ -197,7 +198,7 @@ class DecodeEngine:
         self.rec_floats = G * isa.HEAD_DIM + 16 * ((2 * G + 15) // 16)
         max_rec_per_load = 32768 // (self.rec_floats * 4)
         self.n_splits = max(1, min(self.num_sms // cfg.n_kv_heads, self.max_pages))
-        self.pages_per_split = (self.max_pages + self.n_splits - 1) // self.n_splits
+        self.pages_per_split = max((self.max_pages + self.n_splits - 1) // self.n_splits, int(os.environ.get("VDC_PPS", "1")))
         self.n_splits = (self.max_pages + self.pages_per_split - 1) // self.pages_per_split
         self.max_rec_per_load = max_rec_per_load
         self.attn_part = z(cfg.n_kv_heads, self.n_splits, self.rec_floats, dt=torch.float32)
