@@ -111,8 +111,8 @@
   X(OP_GEMM_TC_BF16, 0x7300, 11)                                                       \
   X(OP_EMBED_PACK, 0x7310, 6)                                                          \
   X(OP_BATCH_ADVANCE, 0x7320, 5)                                                       \
-  X(OP_XREDUCE, 0x7330, 6)                                                             \
-  X(OP_XWAIT, 0x7331, 3)                                                               \
+  X(OP_XREDUCE, 0x7330, 5)                                                             \
+  X(OP_XWAIT, 0x7331, 5)                                                               \
   X(OP_GEMV_WGMMA__M_64__N_8__K_256__BLOAD_4__RESIDUAL_0, 0x7400, 1)                   \
   X(OP_GEMV_WGMMA__M_64__N_8__K_256__BLOAD_4__RESIDUAL_1, 0x7401, 1)                   \
   X(OP_GEMV_WGMMA__M_64__N_8__K_256__BLOAD_2__RESIDUAL_0, 0x7402, 1)                   \
@@ -157,14 +157,17 @@
 // best[rank][4], int32 arrival counters that only ever grow.  A GEMV_ROWS task with VDC_GEMV_PEERS_BIT
 // (mode STORE_F32; its output "address" is the byte offset of its first row inside a block) stores its
 // rows into its slot of every rank's block and then adds 1 to every rank's counter with a system-scope
-// release; its two extra words are the 48-bit address of the table of block base addresses and
-// [ranks, counter byte offset low, high].  ARGMAX_FINAL with args[1] = 2 does the same with its record
-// (same two extra words).
-// XREDUCE (six words): [n elements, ranks, barrier] [48-bit address of xbuf[parity][0][first element]]
-// [hidden/16, arrivals per step low, high] [48-bit address of the first hidden element]
-// [48-bit state block] [48-bit local counter address]: waits (bounded) until the counter has reached
-// arrivals-per-step * (state.STEP + 1), then hidden[i] = bf16(hidden[i] + sum over ranks).
-// XWAIT (three words): [barrier, arrivals per step, 0] [48-bit counter address] [48-bit state block].
+// release; its two extra words are the 48-bit address of a table {block base address of every rank,
+// state block address} and [ranks, exchange number, exchanges per step].  The partial rows travel as tagged
+// 8-byte entries {fp32 bits, tag}, tag = state.STEP * exchanges per step + exchange number + 1: a reader that
+// finds its tag has the payload, no fence or counter is involved.  ARGMAX_FINAL with args[1] = 2 sends its
+// record the same way (two entries: value, row index; same two extra words).
+// XREDUCE (five words): [n elements, ranks, barrier] [48-bit address of this rank's entries xbuf[parity][0][first
+// element]] [entries per rank / 2, exchange number, exchanges per step] [48-bit address of the first hidden
+// element] [48-bit state block]: every thread polls (bounded) its element's entry of every rank, then
+// hidden[i] = bf16(hidden[i] + sum over ranks in rank order).
+// XWAIT (five words): [barrier, ranks, exchange number] [48-bit address of the ranks' candidate entries]
+// [48-bit state block] [48-bit address of the compact records it writes] [exchanges per step, 0, 0].
 //
 // MOE_ROUTE: args = [n_experts, top_k, rank | world << 8].  Pops the fp32 router logits and a raw address;
 // writes int32 ids[16], fp32 weights[16] (softmax over all experts, top-k, renormalised, rounded to bf16),

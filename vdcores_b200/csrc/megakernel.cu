@@ -17,7 +17,7 @@ namespace vdc {
     (dst).table = reinterpret_cast<const unsigned long long*>(                                          \
         (uint64_t)p0.args[0] | ((uint64_t)p0.args[1] << 16) | ((uint64_t)p0.args[2] << 32));            \
     (dst).n = p1.args[0];                                                                               \
-    (dst).cnt_off = (uint32_t)p1.args[1] | ((uint32_t)p1.args[2] << 16);                                \
+    (dst).ex = (uint32_t)p1.args[1] | ((uint32_t)p1.args[2] << 16);                                     \
   }
 
 // ------------------------------------------------------------------------- //
@@ -297,30 +297,32 @@ __device__ __forceinline__ void compute_core(const Ctx& c, const VdcCInst* __res
         }
         break;
       }
-      case 0x7330: {  // XREDUCE (six words)
+      case 0x7330: {  // XREDUCE (five words)
         auto addr48 = [](const VdcCInst& w) {
           return (uint64_t)w.args[0] | ((uint64_t)w.args[1] << 16) | ((uint64_t)w.args[2] << 32);
         };
-        VdcCInst e[5];
+        VdcCInst e[4];
         e[0] = ex;
 #pragma unroll
-        for (int k = 1; k < 5; ++k) *reinterpret_cast<uint2*>(&e[k]) = ld_word(q.pc + (uint32_t)(k - 1));
-        q.pc += 4;
-        task_xreduce(q, ci.args[0], ci.args[1], ci.args[2], reinterpret_cast<const float*>(addr48(e[0])),
-                     (size_t)e[1].args[0] * 4, (int)e[1].args[1] | ((int)e[1].args[2] << 16),
-                     reinterpret_cast<__nv_bfloat16*>(addr48(e[2])), reinterpret_cast<const int*>(addr48(e[3])),
-                     reinterpret_cast<const int*>(addr48(e[4])));
+        for (int k = 1; k < 4; ++k) *reinterpret_cast<uint2*>(&e[k]) = ld_word(q.pc + (uint32_t)(k - 1));
+        q.pc += 3;
+        task_xreduce(q, ci.args[0], ci.args[1], ci.args[2], reinterpret_cast<const unsigned long long*>(addr48(e[0])),
+                     (size_t)e[1].args[0] * 2, (uint32_t)e[1].args[1] | ((uint32_t)e[1].args[2] << 16),
+                     reinterpret_cast<__nv_bfloat16*>(addr48(e[2])), reinterpret_cast<const int*>(addr48(e[3])));
         break;
       }
-      case 0x7331: {  // XWAIT (three words)
+      case 0x7331: {  // XWAIT (five words)
         auto addr48 = [](const VdcCInst& w) {
           return (uint64_t)w.args[0] | ((uint64_t)w.args[1] << 16) | ((uint64_t)w.args[2] << 32);
         };
-        VdcCInst e2;
-        *reinterpret_cast<uint2*>(&e2) = ld_word(q.pc);
-        q.pc += 1;
-        task_xwait(q, ci.args[0], ci.args[1], reinterpret_cast<const int*>(addr48(ex)),
-                   reinterpret_cast<const int*>(addr48(e2)));
+        VdcCInst e[4];
+        e[0] = ex;
+#pragma unroll
+        for (int k = 1; k < 4; ++k) *reinterpret_cast<uint2*>(&e[k]) = ld_word(q.pc + (uint32_t)(k - 1));
+        q.pc += 3;
+        task_xwait(q, ci.args[0], ci.args[1], (uint32_t)ci.args[2] | ((uint32_t)e[3].args[0] << 16),
+                   reinterpret_cast<const unsigned long long*>(addr48(e[0])), reinterpret_cast<const int*>(addr48(e[1])),
+                   reinterpret_cast<uint32_t*>(addr48(e[2])));
         break;
       }
       // ---- the reference's operators (tile contracts of its schedules)

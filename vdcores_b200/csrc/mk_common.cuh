@@ -110,6 +110,19 @@ __device__ __forceinline__ float ld_relaxed_gpu_f32(const float* p) {
   asm volatile("ld.relaxed.gpu.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
   return v;
 }
+// One 8-byte entry of the in-kernel tensor-parallel exchange: {payload, sequence tag}.  An aligned 64-bit
+// scalar store is a single copy, so a reader that finds the tag it expects has the payload that goes with it:
+// no fence and no arrival counter stand between a partial result and its consumers on the other GPUs.
+__device__ __forceinline__ void st_tagged_sys(unsigned long long addr, uint32_t payload, uint32_t tag) {
+  const unsigned long long v = ((unsigned long long)tag << 32) | payload;
+  asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(addr), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_tagged_sys(const void* p) {
+  unsigned long long v;
+  asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+
 __device__ __forceinline__ int atom_acquire_gpu_add(int* p, int v) {
   int old;
   asm volatile("atom.acquire.gpu.global.add.s32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory");

@@ -256,44 +256,83 @@ __device__ __forceinline__ void gemv_chunk_mixed(const uint8_t* w, const uint8_t
 }
 #endif
 
-// Same for e4m3 weights (one byte each, per-row fp32 scale applied by the caller):
-// 16 weights per lane and step, converted two at a time to fp16 and widened to
-// fp32 in registers; products accumulate in fp32.
-__device__ __forceinline__ float2 e4m3x2_to_float2(uint32_t pair16) {
+// Same for e4m3 weights (one byte each, per-row fp32 scale applied by the caller).  The activation
+// vector has been converted to fp16 in place (exact for normalised activations); 16 weights per lane and
+// step become fp16 pairs with one conversion per pair and go straight into the mixed-precision FMA
+// d(f32) = a(f16) * b(f16) + c(f32): half a conversion and one FMA per weight, nothing is widened.
+__device__ __forceinline__ float2 e4m3x2_to_float2(uint32_t pair16) {   // widened pair (batched path's conversion)
   const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)pair16, __NV_E4M3);
   return __half22float2(*reinterpret_cast<const __half2*>(&h));
 }
+__device__ __forceinline__ uint32_t e4m3x2_to_f16x2(uint32_t pair16) {
+  uint32_t d;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(d) : "h"((unsigned short)pair16));
+  return d;
+}
+__device__ __forceinline__ void fma_f16x2(float& lo, float& hi, uint32_t w, uint32_t x) {
+  asm("{\n\t.reg .b16 wl, wh, xl, xh;\n\t"
+      "mov.b32 {wl, wh}, %2;\n\t"
+      "mov.b32 {xl, xh}, %3;\n\t"
+      "fma.rn.f32.f16 %0, wl, xl, %0;\n\t"
+      "fma.rn.f32.f16 %1, wh, xh, %1;\n\t}"
+      : "+f"(lo), "+f"(hi)
+      : "r"(w), "r"(x));
+}
 
 template <int R>
-__device__ __forceinline__ void gemv_chunk_fp8(const uint8_t* w, const uint8_t* x, int K, int lane, int it0, int it1,
-                                               float (&out)[R]) {
+__device__ __forceinline__ void gemv_chunk_fp8_rows(const uint8_t* w, const uint8_t* x16, int K, int lane, int it0, int it1,
+                                                    float (&out)[R]) {
   constexpr int NA = R >= 8 ? 1 : (R == 4 ? 2 : 4);
-  float2 acc[R][NA];
+  float lo[R][NA], hi[R][NA];
 #pragma unroll
   for (int r = 0; r < R; ++r)
 #pragma unroll
-    for (int a = 0; a < NA; ++a) acc[r][a] = make_float2(0.f, 0.f);
+    for (int a = 0; a < NA; ++a) lo[r][a] = hi[r][a] = 0.f;
+#pragma unroll 1
   for (int it = it0; it < it1; ++it) {  // 512 weights per warp step
     const int e0 = (it << 9) + (lane << 4);  // first element of this lane
-    const uint4 xa = lds128(x + e0 * 2), xb = lds128(x + e0 * 2 + 16);
-    const float2 xf[8] = {bf2(xa.x), bf2(xa.y), bf2(xa.z), bf2(xa.w), bf2(xb.x), bf2(xb.y), bf2(xb.z), bf2(xb.w)};
+    const uint4 xa = lds128(x16 + e0 * 2), xb = lds128(x16 + e0 * 2 + 16);
+    const uint32_t xx[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
 #pragma unroll
     for (int r = 0; r < R; ++r) {
       const uint4 wv = lds128(w + (size_t)r * K + e0);
       const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        acc[r][(2 * j) % NA] = __ffma2_rn(e4m3x2_to_float2(ww[j] & 0xFFFFu), xf[2 * j], acc[r][(2 * j) % NA]);
-        acc[r][(2 * j + 1) % NA] = __ffma2_rn(e4m3x2_to_float2(ww[j] >> 16), xf[2 * j + 1], acc[r][(2 * j + 1) % NA]);
+        fma_f16x2(lo[r][(2 * j) % NA], hi[r][(2 * j) % NA], e4m3x2_to_f16x2(ww[j] & 0xFFFFu), xx[2 * j]);
+        fma_f16x2(lo[r][(2 * j + 1) % NA], hi[r][(2 * j + 1) % NA], e4m3x2_to_f16x2(ww[j] >> 16), xx[2 * j + 1]);
       }
     }
   }
 #pragma unroll
   for (int r = 0; r < R; ++r) {
-    float v = acc[r][0].x + acc[r][0].y;
+    float v = lo[r][0] + hi[r][0];
 #pragma unroll
-    for (int a = 1; a < NA; ++a) v += acc[r][a].x + acc[r][a].y;
+    for (int a = 1; a < NA; ++a) v += lo[r][a] + hi[r][a];
     out[r] = warp_sum(v);
+  }
+}
+
+// Option: a chunk of more than VDC_QROWS rows is walked in groups of VDC_QROWS rows, one pass over K per
+// group (a smaller unrolled body).  Measured on B200 with groups of 2, 4 and no grouping: no difference for
+// e4m3 and NVFP4 rows (the stream is bound by the chunks' lifetime in the slots, not by the loop), so off.
+#ifndef VDC_QROWS
+#define VDC_QROWS 16
+#endif
+template <int R>
+__device__ __forceinline__ void gemv_chunk_fp8(const uint8_t* w, const uint8_t* x16, int K, int lane, int it0, int it1,
+                                               float (&out)[R]) {
+  if constexpr (R <= VDC_QROWS) {
+    gemv_chunk_fp8_rows<R>(w, x16, K, lane, it0, it1, out);
+  } else {
+#pragma unroll 1
+    for (int g = 0; g < R / VDC_QROWS; ++g) {
+      float part[VDC_QROWS];
+      gemv_chunk_fp8_rows<VDC_QROWS>(w + (size_t)g * VDC_QROWS * K, x16, K, lane, it0, it1, part);
+#pragma unroll
+      for (int r = 0; r < R; ++r)
+        if (r / VDC_QROWS == g) out[r] = part[r % VDC_QROWS];
+    }
   }
 }
 
@@ -313,8 +352,8 @@ __device__ __forceinline__ float e4m3_to_float(uint32_t byte) {
 }
 
 template <int R>
-__device__ __forceinline__ void gemv_chunk_nvfp4(const uint8_t* w, const uint8_t* x16, int K, int lane, int it0,
-                                                 int it1, float (&out)[R]) {
+__device__ __forceinline__ void gemv_chunk_nvfp4_rows(const uint8_t* w, const uint8_t* x16, int K, int lane, int it0,
+                                                      int it1, float (&out)[R]) {
   const int row_bytes = (K >> 1) + (K >> 4);
   float acc[R];
 #pragma unroll
@@ -329,8 +368,9 @@ __device__ __forceinline__ void gemv_chunk_nvfp4(const uint8_t* w, const uint8_t
     for (int r = 0; r < R; ++r) {
       const uint8_t* row = w + (size_t)r * row_bytes;
       const uint4 cv = lds128(row + (e0 >> 1));
-      const uint32_t sc2 = *reinterpret_cast<const uint16_t*>(row + (K >> 1) + (e0 >> 4));
+      const uint32_t sc2 = e4m3x2_to_f16x2(*reinterpret_cast<const uint16_t*>(row + (K >> 1) + (e0 >> 4)));  // two block scales
       const uint32_t cw[4] = {cv.x, cv.y, cv.z, cv.w};
+      uint32_t bs[2];   // the two block sums, fp16 pairs
 #pragma unroll
       for (int b = 0; b < 2; ++b) {  // two blocks of 16 weights = 8 bytes each
         __half2 s0 = __float2half2_rn(0.f), s1 = s0;
@@ -340,13 +380,39 @@ __device__ __forceinline__ void gemv_chunk_nvfp4(const uint8_t* w, const uint8_t
           s0 = __hfma2(e2m1x2_to_half2((word >> (8 * (j & 3))) & 0xFFu), xh[b * 8 + j], s0);
           s1 = __hfma2(e2m1x2_to_half2((word >> (8 * ((j + 1) & 3))) & 0xFFu), xh[b * 8 + j + 1], s1);
         }
-        const float2 f = __half22float2(__hadd2(s0, s1));
-        acc[r] = fmaf(f.x + f.y, e4m3_to_float((sc2 >> (8 * b)) & 0xFFu), acc[r]);
+        const __half2 t = __hadd2(s0, s1);
+        bs[b] = *reinterpret_cast<const uint32_t*>(&t);
+      }
+      // acc += (lo + hi of block b) * scale_b: the scale pair is {scale_0, scale_1}; two mixed FMAs per block
+      {
+        const uint32_t s00 = __byte_perm(sc2, 0, 0x1010), s11 = __byte_perm(sc2, 0, 0x3232);
+        float a0 = 0.f, a1 = 0.f;
+        fma_f16x2(a0, a1, bs[0], s00);
+        fma_f16x2(a0, a1, bs[1], s11);
+        acc[r] += a0 + a1;
       }
     }
   }
 #pragma unroll
   for (int r = 0; r < R; ++r) out[r] = warp_sum(acc[r]);
+}
+
+template <int R>
+__device__ __forceinline__ void gemv_chunk_nvfp4(const uint8_t* w, const uint8_t* x16, int K, int lane, int it0,
+                                                 int it1, float (&out)[R]) {
+  if constexpr (R <= VDC_QROWS) {
+    gemv_chunk_nvfp4_rows<R>(w, x16, K, lane, it0, it1, out);
+  } else {
+    const int row_bytes = (K >> 1) + (K >> 4);
+#pragma unroll 1
+    for (int g = 0; g < R / VDC_QROWS; ++g) {
+      float part[VDC_QROWS];
+      gemv_chunk_nvfp4_rows<VDC_QROWS>(w + (size_t)g * VDC_QROWS * row_bytes, x16, K, lane, it0, it1, part);
+#pragma unroll
+      for (int r = 0; r < R; ++r)
+        if (r / VDC_QROWS == g) out[r] = part[r % VDC_QROWS];
+    }
+  }
 }
 
 // wfmt: 0 bf16, 1 e4m3 (scales = fp32 per-row scales of the task's rows), 2 NVFP4 (scales likewise).
@@ -359,12 +425,17 @@ struct MoeDown {           // mode MOE_DOWN: per-row accumulation over the selec
 
 // Tensor parallel without a collective library: the exchange blocks of all ranks are mapped into
 // this process; a task writes its fp32 partial rows into its own slot of every rank's block with
-// plain peer stores and then bumps every rank's arrival counter (system-scope release).
+// tagged 8-byte peer stores ({fp32 bits, exchange tag}); the consumers poll the entries themselves.
 struct PeerOut {
-  const unsigned long long* table;  // base address of each rank's exchange block
+  const unsigned long long* table;  // base address of each rank's exchange block; entry [n] is the state block
   int n;                            // ranks
-  uint32_t cnt_off;                 // byte offset of the arrival counter inside a block
+  uint32_t ex;                      // exchange number | exchanges per step << 16
 };
+// The tag of exchange number (ex & 0xFFFF) in the current step: unique over a run, never zero (a zeroed
+// exchange block matches nothing).
+__device__ __forceinline__ uint32_t exchange_tag(const int* state, uint32_t ex) {
+  return (uint32_t)ld_relaxed_gpu(state + VDC_ST_STEP) * (ex >> 16) + (ex & 0xFFFFu) + 1u;
+}
 
 template <int R>
 VDC_TASK void task_gemv_rows(Compute& q, int n_chunks, int mode, bool accumulate, bool norm, int K, int row_base,
@@ -465,8 +536,9 @@ VDC_TASK void task_gemv_rows(Compute& q, int n_chunks, int mode, bool accumulate
     }
     // the sync inside warp_phase_begin publishes the normalised vector
   }
-  if (wfmt == 2) {
-    // NVFP4 block dots run in half precision: the activation vector becomes fp16 in place
+  if (wfmt != 0) {
+    // e4m3 weights meet the activations in the mixed fp16 FMA, NVFP4 block dots run in half precision: the
+    // activation vector becomes fp16 in place
     compute_sync();  // the vector was written (copied or normalised) by other threads
     for (int i = q.tid * 2; i < K; i += kCT * 2) {
       const uint32_t xv = *reinterpret_cast<const uint32_t*>(x + i * 2);
@@ -476,6 +548,8 @@ VDC_TASK void task_gemv_rows(Compute& q, int n_chunks, int mode, bool accumulate
   }
 
   ArgBest best = {-INFINITY, 0x7fffffff};
+  const uint32_t peer_tag =
+      peers != nullptr ? exchange_tag(reinterpret_cast<const int*>(__ldg(peers->table + peers->n)), peers->ex) : 0u;
   // Chunk i belongs to the pair of warps (i % 4, i % 4 + 4): each member takes one half of K
   // for all R rows, the halves meet in shared memory at a two-warp named barrier, and the
   // lower warp finishes the chunk.  A chunk therefore stays resident for half the time one
@@ -568,9 +642,9 @@ VDC_TASK void task_gemv_rows(Compute& q, int n_chunks, int mode, bool accumulate
       for (int r = 0; r < R; ++r)
         if (q.lane == r) v = acc[r];
       if (q.lane < R && mode == VDC_GEMV_MODE_STORE_F32 && peers != nullptr) {
-        // `outg` is the byte offset of the task's first row inside an exchange block
-        const unsigned long long off = reinterpret_cast<unsigned long long>(outg) + (unsigned long long)(row0 + q.lane) * 4ull;
-        for (int pr = 0; pr < peers->n; ++pr) *reinterpret_cast<float*>(__ldg(peers->table + pr) + off) = v;
+        // `outg` is the byte offset of the task's first row entry inside an exchange block
+        const unsigned long long off = reinterpret_cast<unsigned long long>(outg) + (unsigned long long)(row0 + q.lane) * 8ull;
+        for (int pr = 0; pr < peers->n; ++pr) st_tagged_sys(__ldg(peers->table + pr) + off, __float_as_uint(v), peer_tag);
       } else if (q.lane < R && mode == VDC_GEMV_MODE_STORE_F32) {
         reinterpret_cast<float*>(outg)[row0 + q.lane] = v;
       } else if (q.lane < R && mode == VDC_GEMV_MODE_MOE_DOWN && moe->acc == nullptr) {
@@ -622,7 +696,6 @@ VDC_TASK void task_gemv_rows(Compute& q, int n_chunks, int mode, bool accumulate
   // here, while the other warps still compute; the CTA barrier inside warp_phase_end then lets thread 0
   // count the barrier down without a fence of its own (release_prefenced).
   if (member == 0 && (out_meta & VDC_F_BARRIER)) __threadfence();
-  if (peers != nullptr) __threadfence_system();  // the peer stores of this thread, before the arrival below
   if (dyn_rows) {
     // every pair has met its end marker and knows the chunk count; the ring moves on past the four markers
     if (q.lane == 0) sh->warp_next[q.warp] = 0xFFFFFFFFu;
@@ -634,8 +707,6 @@ VDC_TASK void task_gemv_rows(Compute& q, int n_chunks, int mode, bool accumulate
   }
   GEMV_STAMP(6);
   if (q.aborted) return;
-  if (peers != nullptr && q.tid < peers->n)
-    red_release_sys_add(reinterpret_cast<int*>(__ldg(peers->table + q.tid) + peers->cnt_off), 1);
   if (mode == VDC_GEMV_MODE_ARGMAX && q.tid == 0) {
     float bv = sh->misc[40];
     int bi = reinterpret_cast<int*>(sh->misc)[48];
@@ -1140,19 +1211,16 @@ __device__ void task_argmax_final(Compute& q, int n, int local_only, const PeerO
       }
     }
     if (q.lane == 0 && local_only && peers != nullptr) {
-      // vocabulary shard under in-kernel tensor parallelism: this rank's best candidate goes into
-      // its record of every rank's exchange block (`log` holds the record's byte offset)
+      // vocabulary shard under in-kernel tensor parallelism: this rank's best candidate goes into its two
+      // tagged entries ({value, tag}, {row index, tag}) of every rank's exchange block (`log` holds their
+      // byte offset)
       const unsigned long long off = reinterpret_cast<unsigned long long>(log);
+      const uint32_t tag = exchange_tag(reinterpret_cast<const int*>(__ldg(peers->table + peers->n)), peers->ex);
       for (int pr = 0; pr < peers->n; ++pr) {
-        float* rec_p = reinterpret_cast<float*>(__ldg(peers->table + pr) + off);
-        rec_p[0] = bv;
-        reinterpret_cast<int*>(rec_p)[1] = bi;
-        rec_p[2] = 0.f;
-        rec_p[3] = 0.f;
+        const unsigned long long base = __ldg(peers->table + pr) + off;
+        st_tagged_sys(base, __float_as_uint(bv), tag);
+        st_tagged_sys(base + 8, (uint32_t)bi, tag);
       }
-      __threadfence_system();
-      for (int pr = 0; pr < peers->n; ++pr)
-        red_release_sys_add(reinterpret_cast<int*>(__ldg(peers->table + pr) + peers->cnt_off), 1);
     } else if (q.lane == 0 && local_only) {
       // tensor-parallel vocabulary shard: leave this rank's best candidate as one
       // record; the ranks' records are reduced by a second, global call
@@ -1186,44 +1254,58 @@ __device__ void task_argmax_final(Compute& q, int n, int local_only, const PeerO
 // ------------------------------------------------------------------------- //
 // tasks: in-kernel tensor-parallel exchange (peer stores instead of a collective library)
 // ------------------------------------------------------------------------- //
-// Bounded wait until the arrival counter `cnt` (bumped by tasks of every rank, never reset
-// within a run) has reached per_step * (steps completed + 1).  Thread 0 only.
-__device__ __forceinline__ bool xchg_wait(Compute& q, const int* cnt, const int* state, int per_step, int opcode) {
-  const int target = per_step * (ld_relaxed_gpu(state + VDC_ST_STEP) + 1);
-  const bool ok = wait_until(q.c, [&] { return ld_acquire_sys(cnt) >= target; }, 0, (int)q.pc, opcode, -1, 100);
-  if (!ok) q.sh->aborted = 1;
-  return ok;
+// Bounded wait (any thread) until the tagged entry at `p` carries `tag`; returns its payload.  A wait that
+// gives up raises the abort and marks the CTA.
+__device__ __forceinline__ uint32_t tagged_wait(Compute& q, const void* p, uint32_t tag, int opcode) {
+  unsigned long long v = ld_tagged_sys(p);
+  if ((uint32_t)(v >> 32) != tag) {
+    const bool ok = wait_until(q.c, [&] { return (uint32_t)((v = ld_tagged_sys(p)) >> 32) == tag; }, 0, (int)q.pc, opcode, -1, 20);
+    if (!ok) q.sh->aborted = 1;
+  }
+  return (uint32_t)v;
 }
 
-// XREDUCE: hidden[i] = bf16(hidden[i] + sum over ranks of xbuf[rank][i]) for a slice of n elements,
-// once every rank's partial rows have arrived; counts `bar` down.  Pops nothing.
-__device__ void task_xreduce(Compute& q, int n, int n_ranks, int bar, const float* xbuf, size_t rank_stride,
-                             int per_step, __nv_bfloat16* hidden, const int* state, const int* cnt) {
-  if (q.tid == 0) xchg_wait(q, cnt, state, per_step, 0x7330);
+// XREDUCE: hidden[i] = bf16(hidden[i] + sum over ranks of the partial sums) for a slice of n elements.  Every
+// thread polls its own element's entry of every rank ({fp32 bits, tag} written by the ranks' projections),
+// so the slice is folded as soon as the last partial row lands; counts `bar` down.  Pops nothing.
+__device__ void task_xreduce(Compute& q, int n, int n_ranks, int bar, const unsigned long long* xbuf, size_t rank_stride,
+                             uint32_t ex, __nv_bfloat16* hidden, const int* state) {
+  const uint32_t tag = exchange_tag(state, ex);
+  for (int i = q.tid; i < n; i += kCT) {
+    float sum = 0.f;
+    for (int r = 0; r < n_ranks; ++r)   // rank order: every rank folds the same sum
+      sum += __uint_as_float(tagged_wait(q, xbuf + (size_t)r * rank_stride + i, tag, 0x7330));
+    hidden[i] = __float2bfloat16_rn(__bfloat162float(hidden[i]) + sum);
+  }
+  __threadfence();   // every writer drains its own outputs; thread 0 then counts down without a fence
   compute_sync();
   if (q.sh->aborted) {
     q.aborted = true;
     return;
   }
-  for (int i = q.tid; i < n; i += kCT) {
-    float sum = 0.f;
-    for (int r = 0; r < n_ranks; ++r) sum += __ldcg(xbuf + (size_t)r * rank_stride + i);  // written by peers: read past L1
-    hidden[i] = __float2bfloat16_rn(__bfloat162float(hidden[i]) + sum);
-  }
-  compute_sync();
-  if (q.tid == 0 && bar != 0xFFFF) red_release_gpu_add(q.c.bars + bar, -1);
+  if (q.tid == 0 && bar != 0xFFFF) red_relaxed_gpu_add(q.c.bars + bar, -1);
 }
 
-// XWAIT: counts `bar` down once the arrival counter has reached this step's target.  Pops nothing.
-__device__ void task_xwait(Compute& q, int bar, int per_step, const int* cnt, const int* state) {
-  if (q.tid == 0) {
-    if (xchg_wait(q, cnt, state, per_step, 0x7331)) {
-      asm volatile("fence.proxy.async;" ::: "memory");  // a bulk copy reads what the peers wrote
-      red_release_gpu_add(q.c.bars + bar, -1);
-    }
+// XWAIT: collects the ranks' best candidates (two tagged entries per rank: value, row index) into compact
+// records {f32 value, i32 index, 0, 0} at `rec_out` and counts `bar` down.  Pops nothing.
+__device__ void task_xwait(Compute& q, int bar, int n_ranks, uint32_t ex, const unsigned long long* entries,
+                           const int* state, uint32_t* rec_out) {
+  const uint32_t tag = exchange_tag(state, ex);
+  if (q.tid < 2 * n_ranks) {
+    const uint32_t v = tagged_wait(q, entries + q.tid, tag, 0x7331);
+    rec_out[(q.tid >> 1) * 4 + (q.tid & 1)] = v;
+    rec_out[(q.tid >> 1) * 4 + 2 + (q.tid & 1)] = 0u;
+    __threadfence();
   }
   compute_sync();
-  if (q.sh->aborted) q.aborted = true;
+  if (q.sh->aborted) {
+    q.aborted = true;
+    return;
+  }
+  if (q.tid == 0) {
+    asm volatile("fence.proxy.async;" ::: "memory");  // a bulk copy reads the records
+    red_release_gpu_add(q.c.bars + bar, -1);
+  }
 }
 
 }  // namespace vdc

@@ -405,34 +405,41 @@ class Program:
             self.comp(sm, isa.OP_EXT, w_addr & 0xFFFF, (w_addr >> 16) & 0xFFFF, (w_addr >> 32) & 0xFFFF)
 
     def _peer_words(self, sm, peers):
-        table, n, cnt_off = peers
-        assert 0 <= table < 1 << 48 and table % 8 == 0 and 1 <= n <= 255 and 0 <= cnt_off < 1 << 32 and cnt_off % 4 == 0
+        """peers = (address of the table {every rank's exchange block base, state block}, ranks, exchange number,
+        exchanges per step)."""
+        table, n, ex, n_ex = peers
+        assert 0 <= table < 1 << 48 and table % 8 == 0 and 1 <= n <= 255 and 0 <= ex < n_ex <= 0xFFFF
         self.comp(sm, isa.OP_EXT, table & 0xFFFF, (table >> 16) & 0xFFFF, (table >> 32) & 0xFFFF)
-        self.comp(sm, isa.OP_EXT, n, cnt_off & 0xFFFF, cnt_off >> 16)
+        self.comp(sm, isa.OP_EXT, n, ex, n_ex)
 
-    def xreduce(self, sm, *, n, n_ranks, xbuf_addr, hidden_elems, per_step, hidden_addr, state_addr, cnt_addr,
+    def xreduce(self, sm, *, n, n_ranks, xbuf_addr, hidden_elems, ex, n_ex, hidden_addr, state_addr,
                 release: Optional[int] = None):
-        """hidden[i] = bf16(hidden[i] + sum over ranks of xbuf[rank][i]) for n elements, once the
-        arrival counter at cnt_addr has reached per_step * (state.STEP + 1)."""
-        assert 0 < n <= 0xFFFF and hidden_elems % 16 == 0 and 0 < per_step < 1 << 32
+        """hidden[i] = bf16(hidden[i] + sum over ranks of the partial sums) for n elements: xbuf_addr is this
+        rank's first tagged entry {fp32 bits, tag} of rank 0 for the slice, the ranks' entry arrays lie
+        hidden_elems entries apart; every entry is polled until it carries the tag of exchange `ex` of the
+        current step (state.STEP * n_ex + ex + 1)."""
+        assert 0 < n <= 0xFFFF and hidden_elems % 2 == 0 and hidden_elems // 2 <= 0xFFFF and 0 <= ex < n_ex <= 0xFFFF
         if release is not None:
             self.bar_counts[release] += 1
         a48 = lambda a: (a & 0xFFFF, (a >> 16) & 0xFFFF, (a >> 32) & 0xFFFF)
         self.comp(sm, isa.OP_XREDUCE, n, n_ranks, 0xFFFF if release is None else release)
         self.comp(sm, isa.OP_EXT, *a48(xbuf_addr))
-        self.comp(sm, isa.OP_EXT, hidden_elems * 4 // 16, per_step & 0xFFFF, per_step >> 16)
-        for a in (hidden_addr, state_addr, cnt_addr):
+        self.comp(sm, isa.OP_EXT, hidden_elems // 2, ex, n_ex)
+        for a in (hidden_addr, state_addr):
             assert 0 <= a < 1 << 48
             self.comp(sm, isa.OP_EXT, *a48(a))
 
-    def xwait(self, sm, *, per_step, cnt_addr, state_addr, release: int):
-        """Counts `release` down once the arrival counter has reached per_step * (state.STEP + 1)."""
-        assert 0 < per_step <= 0xFFFF
+    def xwait(self, sm, *, n_ranks, ex, n_ex, entries_addr, state_addr, records_addr, release: int):
+        """Waits for the ranks' candidate entries ({value, tag}, {row index, tag} per rank) of exchange `ex`,
+        writes them as compact records {f32, i32, 0, 0} to records_addr and counts `release` down."""
+        assert 0 < n_ranks <= 128 and 0 <= ex < n_ex <= 0xFFFF
         self.bar_counts[release] += 1
         a48 = lambda a: (a & 0xFFFF, (a >> 16) & 0xFFFF, (a >> 32) & 0xFFFF)
-        self.comp(sm, isa.OP_XWAIT, release, per_step, 0)
-        self.comp(sm, isa.OP_EXT, *a48(cnt_addr))
-        self.comp(sm, isa.OP_EXT, *a48(state_addr))
+        self.comp(sm, isa.OP_XWAIT, release, n_ranks, ex)
+        for a in (entries_addr, state_addr, records_addr):
+            assert 0 <= a < 1 << 48
+            self.comp(sm, isa.OP_EXT, *a48(a))
+        self.comp(sm, isa.OP_EXT, n_ex, 0, 0)
 
     def add_releases(self, bar: int, n: int):
         """Declares n count-downs of `bar` that tasks perform themselves (not

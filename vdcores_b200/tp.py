@@ -126,7 +126,9 @@ class TPDecodeEngine:
             self.route = z(64, dt=torch.int32)      # int32 ids[16] | fp32 weights[16] | int32 local[16] | int32 count[16]
         self.rec_floats = G * D + 16 * ((2 * G + 15) // 16)
         self.n_splits = max(1, min(self.num_sms // self.nkv, self.max_pages))
-        self.pages_per_split = (self.max_pages + self.n_splits - 1) // self.n_splits
+        # a page costs about a microsecond on the tensor cores, one more split record costs the merge a load
+        # per output: with few KV heads per rank two pages per unit beat one
+        self.pages_per_split = max(2, (self.max_pages + self.n_splits - 1) // self.n_splits)
         self.n_splits = (self.max_pages + self.pages_per_split - 1) // self.pages_per_split
         self.attn_part = z(self.nkv, self.n_splits, self.rec_floats, dt=torch.float32)
         self.attn_cnt = z(L, self.nkv, dt=torch.int32)
@@ -503,16 +505,14 @@ class TPDecodeEngine:
 class TPFusedEngine(TPDecodeEngine):
     """Tensor-parallel decode of a dense model with the exchange inside the kernel: one launch
     per step and rank, no collective library call in the step.  Every rank owns an exchange
-    block that all ranks map through CUDA IPC; the row-split projections (O, down) store
-    their fp32 partial rows into every rank's block with plain peer stores over NVLink and
-    bump every rank's arrival counter; an XREDUCE task per slice of the hidden state waits
-    for the counter and folds the ranks' partial sums into the replicated hidden state.
-    The vocabulary shard's best candidate travels the same way.  Bounded waits throughout:
-    a rank that never arrives makes the others time out and report, not hang.
-
-    Status: exercised on a GPU with one rank (the whole exchange path, peers = self); the
-    mapping of other ranks' blocks (world > 1) has not passed a test yet, so the collective
-    path of TPDecodeEngine remains the one the benchmark uses."""
+    block (allocated by the library, mapped by all ranks through CUDA IPC); the row-split
+    projections (O, down) store their fp32 partial rows into every rank's block as tagged
+    8-byte entries {value, exchange tag} with plain peer stores over NVLink; an XREDUCE task
+    per slice of the hidden state polls the entries of its slice and folds the ranks' partial
+    sums into the replicated hidden state as soon as the last one lands — no fence, counter
+    or collective stands between a partial row and its consumers.  The vocabulary shard's
+    best candidate travels the same way.  Bounded waits throughout: a rank that never
+    arrives makes the others time out and report, not hang."""
 
     SLICE = 128     # hidden elements per XREDUCE task
 
@@ -521,10 +521,10 @@ class TPFusedEngine(TPDecodeEngine):
         super().__init__(*args, **kw)
         assert not self.cfg.n_experts, "the fused exchange covers dense models"
         H, Pn, L = self.cfg.hidden, self.world, self.cfg.n_layers
-        # exchange block: xbuf[2][ranks][H] fp32 | best[ranks][4] fp32 | counters int32[2L + 1]
-        self.off_best = 2 * Pn * H * 4
-        self.off_cnt = self.off_best + Pn * 16
-        n_bytes = self.off_cnt + (2 * L + 1) * 4
+        # exchange block of tagged 8-byte entries {payload, tag}: xbuf[2][ranks][H] | best[ranks][value, row index]
+        self.n_ex = 2 * L + 1                       # exchanges per step: two per layer and the vocabulary winner
+        self.off_best = 2 * Pn * H * 8
+        n_bytes = self.off_best + Pn * 16
         # the block is an allocation of its own made by the library, so that its CUDA IPC handle names exactly it
         with torch.cuda.device(self.dev):
             self._block = runtime.PeerBlock((n_bytes + 255) // 256 * 256)
@@ -545,7 +545,9 @@ class TPFusedEngine(TPDecodeEngine):
                 self._peer_mappings.append(bases[r])
             torch.cuda.synchronize(self.dev)
             dist.barrier(group=self.group)
-        self.peer_table = torch.tensor(bases, dtype=torch.int64, device=self.dev)
+        # what the sending tasks read: every rank's block, then this rank's state block (for the step number)
+        self.peer_table = torch.tensor(bases + [self.state.data_ptr()], dtype=torch.int64, device=self.dev)
+        self.best_rec = torch.zeros(Pn, 4, dtype=torch.int32, device=self.dev)
         self.launches_per_step = 1
 
     # ------------------------------------------------------------------ program
@@ -561,21 +563,20 @@ class TPFusedEngine(TPDecodeEngine):
         load = [0] * S
         P = Program(S, insts_per_sm=isa.MAX_INSTS)
 
-        def exchange(half: int, n_tasks: int, release: int):
-            """XREDUCE tasks for exchange number `half` (two per layer): n_tasks row-split tasks per rank signal it."""
+        def exchange(half: int, release: int):
+            """XREDUCE tasks for exchange number `half` (two per layer), one per slice of the hidden state."""
             par = half & 1
             order = sorted(range(S), key=lambda s: (load[s], s))
             for i, e0 in enumerate(range(0, H, self.SLICE)):
                 n = min(self.SLICE, H - e0)
-                P.xreduce(order[i % S], n=n, n_ranks=Pn, xbuf_addr=xb + (par * Pn * H + e0) * 4, hidden_elems=H,
-                          per_step=Pn * n_tasks, hidden_addr=hid + e0 * 2, state_addr=st,
-                          cnt_addr=xb + self.off_cnt + 4 * half, release=release)
+                P.xreduce(order[i % S], n=n, n_ranks=Pn, xbuf_addr=xb + (par * Pn * H + e0) * 8, hidden_elems=H,
+                          ex=half, n_ex=self.n_ex, hidden_addr=hid + e0 * 2, state_addr=st, release=release)
 
         def peers(half: int):
-            return (table, Pn, self.off_cnt + 4 * half)
+            return (table, Pn, half, self.n_ex)
 
         def my_slot(half: int, r0: int) -> int:
-            return (((half & 1) * Pn + self.rank) * H + r0) * 4      # byte offset inside an exchange block
+            return (((half & 1) * Pn + self.rank) * H + r0) * 8      # byte offset of an entry inside an exchange block
 
         # ---- embedding row of the current token into the hidden state
         b_hid = P.new_barrier()
@@ -614,9 +615,9 @@ class TPFusedEngine(TPDecodeEngine):
             for sm, u0, cnt in tasks:
                 r0, n = u0 * R, cnt * R
                 P.gemv(sm, w_addr=self.wo[l].data_ptr() + r0 * K * 2, n_rows=n, K=K, R=R, x=Src(ao, K * 2, wait=b_merge),
-                       out=Dst(my_slot(2 * l, r0), n * 4, "store"), mode=isa.GEMV_MODE_STORE_F32, peers=peers(2 * l))
+                       out=Dst(my_slot(2 * l, r0), n * 8, "store"), mode=isa.GEMV_MODE_STORE_F32, peers=peers(2 * l))
             b_h1 = P.new_barrier()
-            exchange(2 * l, len(tasks), b_h1)
+            exchange(2 * l, b_h1)
             # ---- gate/up over the local FFN rows, down over the local columns
             b_gu = P.new_barrier()
             R = rows_per_chunk(H, even=True)
@@ -631,10 +632,10 @@ class TPFusedEngine(TPDecodeEngine):
             for sm, u0, cnt in tasks:
                 r0, n = u0 * R, cnt * R
                 P.gemv(sm, w_addr=self.wd[l].data_ptr() + r0 * K * 2, n_rows=n, K=K, R=R, x=Src(act, K * 2, wait=b_gu),
-                       out=Dst(my_slot(2 * l + 1, r0), n * 4, "store"), mode=isa.GEMV_MODE_STORE_F32,
+                       out=Dst(my_slot(2 * l + 1, r0), n * 8, "store"), mode=isa.GEMV_MODE_STORE_F32,
                        peers=peers(2 * l + 1))
             b_hid = P.new_barrier()
-            exchange(2 * l + 1, len(tasks), b_hid)
+            exchange(2 * l + 1, b_hid)
         # ---- vocabulary shard, this rank's best candidate to every rank, global winner
         b_logits = P.new_barrier()
         R = rows_per_chunk(H)
@@ -649,8 +650,9 @@ class TPFusedEngine(TPDecodeEngine):
         P.argmax_final(0, records=Src(self.argmax_rec.data_ptr(), len(lm) * 16, wait=b_logits), n=len(lm),
                        state_addr=st, log_addr=self.off_best + 16 * self.rank, local_only=True, peers=peers(last))
         b_best = P.new_barrier()
-        P.xwait(0, per_step=Pn, cnt_addr=xb + self.off_cnt + 4 * last, state_addr=st, release=b_best)
-        P.argmax_final(0, records=Src(xb + self.off_best, Pn * 16, wait=b_best), n=Pn, state_addr=st,
+        P.xwait(0, n_ranks=Pn, ex=last, n_ex=self.n_ex, entries_addr=xb + self.off_best, state_addr=st,
+                records_addr=self.best_rec.data_ptr(), release=b_best)
+        P.argmax_final(0, records=Src(self.best_rec.data_ptr(), Pn * 16, wait=b_best), n=Pn, state_addr=st,
                        log_addr=self.token_log.data_ptr())
         n = max(max(len(x) for x in P.m), max(len(x) for x in P.c)) + 2
         P.insts_per_sm = ((n + 63) // 64) * 64
