@@ -263,14 +263,20 @@ def run_gpu(args):
     tf = None
     if world > 1:
         reset()
-        feed, agree, beyond = first, 0, []
+        # The two engines round differently (the sharded one adds fp32 partial sums to the residual, the single-GPU one
+        # a bf16 projection output), which moves bf16 logits by a few ulps (0.4 % each): ids may differ only where the
+        # single-GPU engine's two best logits are closer than 5 % of the best one
+        feed, agree, beyond, worst = first, 0, [], 0.0
         for i in range(N_CHECK):
             got = eng.step_host(feed)
             agree += int(got == single_gpu_tokens[i])
-            if got != single_gpu_tokens[i] and single_gpu_gaps[i] > 0.02:     # relative gap; a bf16 ulp is 0.4 %
-                beyond.append(i)
+            if got != single_gpu_tokens[i]:
+                worst = max(worst, single_gpu_gaps[i])
+                if single_gpu_gaps[i] > 0.05:
+                    beyond.append(i)
             feed = single_gpu_tokens[i]
-        tf = {"steps": N_CHECK, "agree": agree, "disagree_beyond_near_ties": len(beyond)}
+        tf = {"steps": N_CHECK, "agree": agree, "disagree_beyond_near_ties": len(beyond),
+              "max_rel_gap_at_a_disagreement": worst}
     # ---- device-resident arm: K launches back to back, CUDA events on the launching stream
     reset()
     for _ in range(W):
@@ -339,9 +345,9 @@ def run_gpu(args):
                    **({"layers": args.layers, "note": "reduced-depth profiling case, not a benchmark result"}
                       if args.layers != 32 else {})},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     # dram__bytes_read+write per launch: ncu measured 1.007 x the algorithmic bytes on a
+                     # dram__bytes_read+write per launch: ncu measured 1.006 x the algorithmic bytes on a
                      # 4-layer case of the same program (profiles/), scaled here by the bytes of this launch
-                     "traffic": bytes_per_launch * 1.007 / 1e9, "traffic_unit": "GB", "peak_kind": f"of {peak_kind}", "frac_of_8TBs": achieved / 8000.0,
+                     "traffic": bytes_per_launch * 1.006 / 1e9, "traffic_unit": "GB", "peak_kind": f"of {peak_kind}", "frac_of_8TBs": achieved / 8000.0,
                      "bytes_per_launch": bytes_per_launch},
         "e2e": ({"value": tokens_per_step * K / (e2e_ms * 1e-3), "unit": "tokens/s",
                  "h2d_bytes_per_step": 4 * tokens_per_step, "d2h_bytes_per_step": 4 * tokens_per_step}

@@ -150,6 +150,10 @@ def test_compute_word_counts_follow_the_table_in_the_header():
                   records_addr=1 << 19, counter_addr=1 << 20, out_addr=1 << 21, split=0, n_splits=1, release=b)
     P.l2_prefetch(0, 1 << 30, 4096)
     P.argmax_final(0, records=Src(1 << 20, 64), n=4, state_addr=1 << 16, log_addr=1 << 17)
+    # the in-kernel tensor-parallel exchange: tagged-entry reducers and the candidate collector
+    P.xreduce(0, n=128, n_ranks=2, xbuf_addr=1 << 26, hidden_elems=4096, ex=3, n_ex=65, hidden_addr=1 << 21,
+              state_addr=1 << 16, release=b)
+    P.xwait(0, n_ranks=2, ex=64, n_ex=65, entries_addr=1 << 27, state_addr=1 << 16, records_addr=1 << 22, release=b)
     i, stream = 0, P.c[0]
     seen = []
     while i < len(stream):
@@ -160,4 +164,12 @@ def test_compute_word_counts_follow_the_table_in_the_header():
         seen.append(op)
         i += n
     assert seen == [isa.OP_GEMV_ROWS_BF16, isa.OP_GEMV_ROWS_FP8, isa.OP_ATTN_DECODE_PAGED_G4, isa.OP_L2_PREFETCH,
-                    isa.OP_ARGMAX_FINAL]
+                    isa.OP_ARGMAX_FINAL, isa.OP_XREDUCE, isa.OP_XWAIT]
+    # XREDUCE carries [entries per rank / 2, exchange number, exchanges per step] in its third word
+    k = [j for j, w in enumerate(stream) if w[0] == isa.OP_XREDUCE][0]
+    assert tuple(stream[k + 2][1:4]) == (2048, 3, 65)
+    # a projection that sends its rows to the ranks' exchange blocks: two trailing words [table], [ranks, ex, n_ex]
+    P2 = Program(1)
+    P2.gemv(0, w_addr=1 << 30, n_rows=64, K=512, R=16, x=Src(1 << 20, 1024), out=Dst(4096, 64 * 8, "store"),
+            mode=isa.GEMV_MODE_STORE_F32, peers=(1 << 23, 2, 3, 65))
+    assert tuple(P2.c[0][-1][1:4]) == (2, 3, 65) and P2.c[0][-2][0] == isa.OP_EXT
