@@ -223,8 +223,16 @@ def run_gpu(args):
         # dense models: one launch per step and rank, the partial sums cross NVLink as peer stores inside the
         # kernel; mixture-of-experts models (and --tp-impl nccl): two launches per layer around NCCL collectives
         fused = args.tp_impl == "fused" and not cfg.n_experts
-        eng = (TPFusedEngine if fused else TPDecodeEngine)(cfg, max_seq=max_seq, rank=rank, world=world, device=dev,
-                                                           max_steps=2 * (W + K) + 16 + N_CHECK)
+        kw = dict(max_seq=max_seq, rank=rank, world=world, device=dev, max_steps=2 * (W + K) + 16 + N_CHECK)
+        eng = None
+        if fused:
+            try:
+                eng = TPFusedEngine(cfg, **kw)
+            except RuntimeError as e:          # raised on every rank together: no peer mapping on this machine
+                dbg(f"in-kernel exchange unavailable, using the NCCL engine: {e}")
+                fused = False
+        if eng is None:
+            eng = TPDecodeEngine(cfg, **kw)
         dbg('prefill done')
         eng.load_from_full(full, PROMPT_LEN)
         dbg('shard loaded')

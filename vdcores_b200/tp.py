@@ -535,16 +535,27 @@ class TPFusedEngine(TPDecodeEngine):
         if Pn > 1:
             handles = [None] * Pn
             dist.all_gather_object(handles, (self.dev.index, self._block.handle), group=self.group)
-            for r in range(Pn):
-                if r == self.rank:
-                    continue
-                peer_dev, handle = handles[r]
-                assert torch.cuda.can_device_access_peer(self.dev.index, peer_dev), "peer access is required"
-                with torch.cuda.device(self.dev):      # mapped with THIS device current: its kernels store there
-                    bases[r] = runtime.ipc_open(handle)
-                self._peer_mappings.append(bases[r])
+            # a rank that cannot map a peer still takes part in the agreement below, so that all ranks give up
+            # together instead of one leaving the others at a barrier
+            error = None
+            try:
+                for r in range(Pn):
+                    if r == self.rank:
+                        continue
+                    peer_dev, handle = handles[r]
+                    if not torch.cuda.can_device_access_peer(self.dev.index, peer_dev):
+                        raise RuntimeError(f"device {self.dev.index} has no peer access to device {peer_dev}")
+                    with torch.cuda.device(self.dev):      # mapped with THIS device current: its kernels store there
+                        bases[r] = runtime.ipc_open(handle)
+                    self._peer_mappings.append(bases[r])
+            except Exception as e:     # noqa: BLE001 (reported below, on every rank)
+                error = e
             torch.cuda.synchronize(self.dev)
-            dist.barrier(group=self.group)
+            agreed = torch.tensor([0 if error else 1], dtype=torch.int32, device=self.dev)
+            dist.all_reduce(agreed, op=dist.ReduceOp.MIN, group=self.group)
+            if int(agreed.item()) == 0:
+                self.close()
+                raise RuntimeError(f"exchange blocks could not be mapped on every rank (this rank: {error!r})")
         # what the sending tasks read: every rank's block, then this rank's state block (for the step number)
         self.peer_table = torch.tensor(bases + [self.state.data_ptr()], dtype=torch.int64, device=self.dev)
         self.best_rec = torch.zeros(Pn, 4, dtype=torch.int32, device=self.dev)
@@ -688,4 +699,6 @@ class TPFusedEngine(TPDecodeEngine):
         if self.world > 1:
             dist.barrier(group=self.group)
         self.xchg = None
-        self._block.free()
+        if self._block is not None:
+            self._block.free()
+            self._block = None
