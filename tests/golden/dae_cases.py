@@ -31,8 +31,11 @@ class FakeTensor:
     def dim(self):
         return len(self.shape)
 
-    def stride(self):
-        return self._strides
+    def stride(self, i=None):
+        return self._strides if i is None else self._strides[i]
+
+    def view(self, *shape):
+        return FakeTensor(shape, self._es, self._addr)
 
     def numel(self):
         n = 1
@@ -117,6 +120,55 @@ def build_cases(D):
                                         D.RepeatM.onSync(0, 23, 4, [ld(), 8192], [ld(), 8192], [st(), 1024]) +
                                         D.RepeatM.onSync(1, 9, 3, [ld(), 8192], [ld(), 8192], asyncPort=False) +
                                         D.RepeatM.onSync(0, None, 3, [ld(), 8192]))
+    return cases
+
+
+def build_attention_cases(D, M):
+    """Decode attention: the operator encodings, the strided tensor-map recipes of dae.model (M) and a
+    SchedAttentionDecoding launch with the fused QK-norm + RoPE path (streams, barrier table, tensor maps)."""
+    from functools import partial
+    T = FakeTensor
+    cases = {}
+    cases["attention_compute"] = encode([
+        D.ATTENTION_M64N64K16_F16_F32_64_64_hdim(3, 17), D.ATTENTION_M64N64K16_F16_F32_64_64_hdim_MMA(2, 64, False, False),
+        D.ATTENTION_M64N64K16_F16_F32_64_64_hdim_split(2, 1, 4, 40, 128),
+        D.ATTENTION_M64N64K16_F16_F32_64_64_hdim_split_MMA(5, 15, 8, 1, 4096), D.ATTN_SPLIT_POST_REDUCE(2),
+    ])
+    n_req, S, n_heads, Dh, blk = 2, 192, 8, 128, 64
+    q, o = T((n_req, n_heads, 1, Dh)), T((n_req, n_heads, Dh), addr=0x7f08_0000_0000)
+    k, v = T((n_req, S, n_heads, Dh), addr=0x7f10_0000_0000), T((n_req, S, n_heads, Dh), addr=0x7f18_0000_0000)
+    side = T((S, 3 * Dh), addr=0x7f20_0000_0000)
+    dae = D.Launcher(n_req * n_heads, device="cpu")
+    tQ = D.TmaTensor(dae, q)._build("load", Dh, 64, M.tma_gqa_load_q, M.cord_gqa_load_q)
+    tK = D.TmaTensor(dae, k)._build("load", Dh, blk, partial(M.build_tma_wgmma_k, iN=-3), partial(M.cord_func_K_major, iN=-3))
+    tV = D.TmaTensor(dae, v)._build("load", Dh, blk, partial(M.build_tma_wgmma_mn, iK=-3), partial(M.cord_func_MN_major, iK=-3))
+    tSide = D.TmaTensor(dae, side).tensor1d("load", 3 * Dh)
+    kst = [D.TmaTensor(dae, T((S, n_heads * Dh), addr=0x7f10_0000_0000 + r * S * n_heads * Dh * 2)).tensor1d("store", Dh)
+           for r in range(n_req)]
+    g = dae.add_group("attn", 1)
+    g.addBarrier("bar_q", 1)
+    g.addBarrier("bar_k", 1)
+    g.addBarrier("bar_o")                      # bound late, from the schedule's own count
+    dae.build_groups()
+    sched = D.SchedAttentionDecoding(n_req, 150, blk, n_heads, o, (tQ, tK, tV), side_input=tSide, k_store=kst, token_pos=149) \
+        .bar("q", g["bar_q"]).bar("k", g["bar_k"]).bar("o", g["bar_o"]).place(n_req * n_heads)
+    dae.bind_late_barrier_counts(sched)
+    dae.s(sched)
+    plain = D.SchedAttentionDecoding(n_req, 64, blk, n_heads, o, (tQ, tK, tV)).place(n_req * n_heads)
+    dae.s(plain)
+    dae.build_instructions()
+    used_c, used_m = min(dae.cptrs), min(dae.mptrs)      # every SM has written at least this many (the rest of a ring is unspecified)
+    cases["attention_cinsts"] = dae.cinsts[:, :used_c].numpy().copy().reshape(-1)
+    cases["attention_minsts"] = dae.minsts[:, :used_m].numpy().copy().reshape(-1)
+    cases["attention_bars"] = np.array([dae.bar_values[i] for i in range(dae.num_bars)], dtype=np.int64).view(np.uint8)
+    cases["attention_tmas"] = torch.stack(dae.tmas).numpy().copy().reshape(-1)
+    k2 = T((4, 256, 128), addr=0x7f30_0000_0000)
+    recs = [M.build_tma_wgmma_k(k2, 128, 64)[1], M.build_tma_wgmma_mn(k2, 128, 64)[1], M.build_tma_wgmma_mn(k2, 64, 32)[1]]
+    cases["model_recipes"] = torch.stack(recs).numpy().copy().reshape(-1)
+    cords = [M.cord_func_K_major(k, 4, iN=-3)(1, 64, 3, 0), M.cord_func_MN_major(k, 5, iK=-3)(1, 128, 5, 64),
+             M.cord_func_K_major(k2, 4)(2, 64, 64), M.cord_func_MN_major(k2, 5)(3, 16, 64),
+             M.cord_func_MN_major_cord2(k2, 5)(16, 64), M.cord_gqa_load_q(q, 5)(1, 6), M.get_other_dims(4, -3)]
+    cases["model_cords"] = np.array([c + [0] * (4 - len(c)) for c in cords], dtype=np.int64).reshape(-1).view(np.uint8)
     return cases
 
 

@@ -37,14 +37,14 @@ def load_reference_dae():
         for k, v in vars(m).items():
             if not k.startswith("_"):
                 setattr(ns, k, v)
-    return ns
+    return ns, importlib.import_module("dae.model")
 
 
 if __name__ == "__main__":
     sys.path.insert(0, HERE)
     import dae_cases
-    D = load_reference_dae()
-    cases = {**dae_cases.build_cases(D), **dae_cases.build_launcher_cases(D)}
+    D, M = load_reference_dae()
+    cases = {**dae_cases.build_cases(D), **dae_cases.build_launcher_cases(D), **dae_cases.build_attention_cases(D, M)}
     out = os.path.join(HERE, "dae_api.npz")
     np.savez_compressed(out, **cases)
     print("wrote", out, {k: v.size for k, v in cases.items()})

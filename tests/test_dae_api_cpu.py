@@ -54,6 +54,17 @@ def test_launcher_streams_match_the_reference(D, golden):
         assert np.array_equal(got[name], golden[name]), f"{name} differs from the reference's"
 
 
+def test_attention_operators_schedule_and_recipes_match_the_reference(D, golden):
+    """The decode-attention instruction encodings, a SchedAttentionDecoding launch (fused QK-norm + RoPE path and
+    the plain one) and the strided tensor-map recipes / coordinate functions of dae.model."""
+    import dae_cases
+    import dae.model as M
+    got = dae_cases.build_attention_cases(D, M)
+    for name in ("attention_compute", "model_recipes", "model_cords", "attention_tmas", "attention_bars",
+                 "attention_cinsts", "attention_minsts"):
+        assert np.array_equal(got[name], golden[name]), f"{name} differs from the reference's"
+
+
 def test_family_names_and_errors(D):
     from dae.op_families import family_ref, family_spec_by_name
     assert family_ref("GEMV_WGMMA", M=64, N=8, K=256, BLOAD=4, RESIDUAL=False).canonical_name == \

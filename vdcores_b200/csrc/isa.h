@@ -131,6 +131,11 @@
   X(OP_ARGMAX_REDUCE_bf16_1024_128, 0x7429, 1)                                         \
   X(OP_ARGMAX_PARTIAL_bf16_1152_50688_132, 0x742A, 1)                                  \
   X(OP_ARGMAX_REDUCE_bf16_1152_132, 0x742B, 1)                                         \
+  X(OP_ATTENTION_M64N64K16_F16_F32_64_64_hdim, 0x7430, 1)                              \
+  X(OP_ATTENTION_M64N64K16_F16_F32_64_64_hdim_MMA, 0x7431, 1)                          \
+  X(OP_ATTENTION_M64N64K16_F16_F32_64_64_hdim_split, 0x7432, 1)                        \
+  X(OP_ATTENTION_M64N64K16_F16_F32_64_64_hdim_split_MMA, 0x7433, 1)                    \
+  X(OP_ATTN_SPLIT_POST_REDUCE, 0x7434, 1)                                              \
   X(OP_EXT, 0x7FFF, 1)
 
 // OP_L2_PREFETCH (two words): args = 48-bit address in three 16-bit pieces (low

@@ -341,6 +341,11 @@ __device__ __forceinline__ void compute_core(const Ctx& c, const VdcCInst* __res
       case 0x7429: task_ref_argmax_reduce(q, 1024, 128, ci.args[0]); break;
       case 0x742A: task_ref_argmax_partial(q, 1152, 50688, 132, ci.args[0]); break;
       case 0x742B: task_ref_argmax_reduce(q, 1152, 132, ci.args[0]); break;
+      case 0x7430: case 0x7431: task_ref_attn_decode(q, ci.args[0], ci.args[1], ci.args[2], false, 0, 1); break;
+      case 0x7432: case 0x7433:   // [blocks | split << 12, active rows | last length << 8, first position]
+        task_ref_attn_decode(q, ci.args[0] & 0xFFF, ci.args[1] >> 8, 0, true, ci.args[0] >> 12, ci.args[1] & 0xFF);
+        break;
+      case 0x7434: task_ref_attn_post_reduce(q, ci.args[0]); break;
       case 0x7240: task_moe_route(q, ci.args[0], ci.args[1], ci.args[2] & 0xFF, ci.args[2] >> 8); break;
       default:
         raise_abort(c, VDC_ERR_BAD_OPCODE, 0, (int)q.pc, ci.opcode, -1, 0);

@@ -439,3 +439,59 @@ class SchedArgmax(Schedule):
         if role == "final":
             return self._bar_release_if_present(role, min(self.num_token, self.num_sms))
         return 0
+
+
+class SchedAttentionDecoding(Schedule):
+    """Decode attention (one query token per request), one SM per (request, head): the SM's stream is the
+    attention instruction, [the side input row (q-norm | k-norm | rope) of the token's position and the
+    k-store row, for the fused QK-norm + RoPE path], the Q tile behind the "q" barrier, a REPEAT over the
+    first seq_len / block - 1 (K block, V block) pairs, the last pair with its K behind the "k" barrier (only
+    the last block holds a row produced in this step), and the output row store releasing "o".
+    Mirrors python/dae/schedule.py:250-325 of the reference."""
+
+    def __init__(self, reqs: int, seq_len: int, KV_BLOCK_SIZE: int, NUM_KV_HEADS: int, matO: torch.Tensor, tmas,
+                 side_input=None, k_store=None, token_pos=None):
+        super().__init__()
+        self.reqs, self.seq_len, self.block_size, self.num_heads = reqs, seq_len, KV_BLOCK_SIZE, NUM_KV_HEADS
+        self.matO, self.tmas = matO, tmas
+        self.side_input, self.k_store, self.token_pos = side_input, k_store, token_pos
+        self.required_sms = reqs * NUM_KV_HEADS
+        self.AttentionInst = select_attention_decode_instruction(matO.shape[-1])
+        self.use_qwen_fused_qk = side_input is not None
+        if self.use_qwen_fused_qk and (k_store is None or token_pos is None):
+            raise ValueError("SchedAttentionDecoding requires side_input, k_store, and token_pos together for the "
+                             "fused Qwen path")
+
+    def _on_place(self):
+        assert self.num_sms == self.required_sms, (
+            f"SchedAttentionDecoding requires {self.required_sms} SMs, got {self.num_sms}")
+
+    def schedule(self, sm: int):
+        if sm < 0:
+            return []
+        req, head = divmod(sm, self.num_heads)
+        head_dim = self.matO.shape[-1]
+        tQ, tK, tV = self.tmas
+        n_blocks = (self.seq_len + self.block_size - 1) // self.block_size
+        last_len = self.seq_len % self.block_size or self.block_size
+        fused = self.use_qwen_fused_qk
+        insts = [self.AttentionInst(n_blocks, last_len, need_norm=fused, need_rope=fused)]
+        if fused:
+            insts += [self.side_input.cord(self.token_pos * 3 * head_dim).group(),
+                      self.k_store[req].cord((self.token_pos * self.num_heads + head) * head_dim).group()]
+        last0 = self.block_size * (n_blocks - 1)
+        insts += [
+            tQ.cord(req, head).bar(self._bar("q")).group(),
+            RepeatM.on(n_blocks - 1,
+                       [tK.cord(req, 0, head, 0).group(), tK.cord2tma(0, self.block_size, 0, 0)],
+                       [tV.cord(req, 0, head, 0).group(), tV.cord2tma(0, self.block_size, 0, 0)]),
+            tK.cord(req, last0, head, 0).bar(self._bar("k")).group(),
+            tV.cord(req, last0, head, 0).group(),
+            TmaStore1D(self.matO[req, head, ...], numSlots=2).bar(self._bar("o")).group(),
+        ]
+        return insts
+
+    def bar_release_count(self, role: str):
+        if role != "o":
+            return 0
+        return self._bar_release_if_present(role, self.num_sms)
