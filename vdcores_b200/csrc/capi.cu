@@ -10,9 +10,11 @@
 
 extern "C" size_t vdc_megakernel_dynamic_smem();
 extern "C" cudaError_t vdc_megakernel_prepare();
+// ref_ops != 0 selects the full kernel (native operators + the reference's tile-contract operators); 0 the kernel
+// with the native operators only, which the decode engines launch every step.
 extern "C" cudaError_t vdc_megakernel_launch(int num_sms, const void* cinsts, const void* minsts, const void* tmas,
                                              int* bars, uint64_t* profile, vdc_status* status, int insts_per_sm,
-                                             uint64_t timeout_ns, cudaStream_t stream);
+                                             uint64_t timeout_ns, cudaStream_t stream, int ref_ops);
 
 namespace {
 
@@ -96,9 +98,9 @@ int vdc_set_smem_size(int bytes) {
   return VDC_OK;
 }
 
-int vdc_launch_async(int num_sms, int insts_per_sm, const void* compute_insts, const void* memory_insts,
-                     const void* tma_descs, int* bars, const int* bars_init, uint64_t* profile, uint64_t stream,
-                     uint64_t timeout_ns) {
+static int launch_async_impl(int num_sms, int insts_per_sm, const void* compute_insts, const void* memory_insts,
+                             const void* tma_descs, int* bars, const int* bars_init, uint64_t* profile, uint64_t stream,
+                             uint64_t timeout_ns, int ref_ops) {
   int dev;
   if (int r = current_device(&dev)) return r;
   if (int r = check_launch_args(dev, num_sms, insts_per_sm, compute_insts, memory_insts, bars, profile)) return r;
@@ -109,9 +111,17 @@ int vdc_launch_async(int num_sms, int insts_per_sm, const void* compute_insts, c
   }
   if (timeout_ns == 0) timeout_ns = 2000000000ull;
   cudaError_t e = vdc_megakernel_launch(num_sms, compute_insts, memory_insts, tma_descs, bars, profile,
-                                        g_status[dev], insts_per_sm, timeout_ns, s);
+                                        g_status[dev], insts_per_sm, timeout_ns, s, ref_ops);
   if (e != cudaSuccess) return fail_cuda(e, "megakernel launch");
   return VDC_OK;
+}
+
+// The decode engines' per-step launch: the kernel with the native operators only.
+int vdc_launch_async(int num_sms, int insts_per_sm, const void* compute_insts, const void* memory_insts,
+                     const void* tma_descs, int* bars, const int* bars_init, uint64_t* profile, uint64_t stream,
+                     uint64_t timeout_ns) {
+  return launch_async_impl(num_sms, insts_per_sm, compute_insts, memory_insts, tma_descs, bars, bars_init, profile, stream,
+                           timeout_ns, 0);
 }
 
 int vdc_read_status(uint64_t stream, vdc_status* status, int clear) {
@@ -144,8 +154,9 @@ int vdc_launch(int num_sms, int insts_per_sm, const void* compute_insts, const v
                vdc_status* status) {
   cudaError_t e = cudaDeviceSynchronize();
   if (e != cudaSuccess) return fail_cuda(e, "cudaDeviceSynchronize (before launch)");
-  if (int r = vdc_launch_async(num_sms, insts_per_sm, compute_insts, memory_insts, tma_descs, bars, nullptr, profile,
-                               stream, timeout_ns))
+  // the entry point behind the reference's launch_dae: the full kernel, which also runs its tile-contract operators
+  if (int r = launch_async_impl(num_sms, insts_per_sm, compute_insts, memory_insts, tma_descs, bars, nullptr, profile,
+                                stream, timeout_ns, 1))
     return r;
   e = cudaDeviceSynchronize();
   if (e != cudaSuccess) return fail_cuda(e, "cudaDeviceSynchronize (after launch)");
@@ -392,7 +403,7 @@ int vdc_launch_static(int num_sms, int insts_per_sm, const void* compute_insts, 
   if (e != cudaSuccess) return fail_cuda(e, "cudaMemcpyAsync(bars)");
   if (timeout_ns == 0) timeout_ns = 2000000000ull;
   e = vdc_megakernel_launch(num_sms, compute_insts, memory_insts, tma_descs, d_bars, d_profile, d_status, insts_per_sm,
-                            timeout_ns, s);
+                            timeout_ns, s, 1);   // an embedder's streams may hold any operator: the full kernel
   if (e != cudaSuccess) return fail_cuda(e, "megakernel launch");
   vdc_status h{};
   e = cudaMemcpyAsync(&h, d_status, sizeof(h), cudaMemcpyDeviceToHost, s);

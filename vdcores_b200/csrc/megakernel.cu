@@ -37,6 +37,37 @@ __device__ __forceinline__ int compute_op_words(uint16_t op) {
   }
 }
 
+// The reference's operators (tile contracts of its schedules).  They are compiled into the full kernel only
+// (vdc_launch, the entry point behind the reference's launch_dae); the kernel the native decode engines launch
+// leaves them out: measured on B200, their presence in the dispatcher costs the batch-1 step 1.8 %.
+__device__ __forceinline__ bool dispatch_ref_op(Compute& q, const VdcCInst& ci) {
+  switch (ci.opcode) {
+      case 0x7400: case 0x7401: task_ref_gemv(q, ci.args[0], 4, ci.opcode & 1); break;
+      case 0x7402: case 0x7403: task_ref_gemv(q, ci.args[0], 2, ci.opcode & 1); break;
+      case 0x7404: case 0x7405: task_ref_gemv(q, ci.args[0], 1, ci.opcode & 1); break;
+      case 0x7408: task_ref_gemv(q, ci.args[0], 1, false); break;
+      case 0x7410: task_ref_rms(q, 4096, ci.args[0], ci.args[1]); break;
+      case 0x7411: task_ref_rms(q, 2048, ci.args[0], ci.args[1]); break;
+      case 0x7412: task_ref_rms(q, 5120, ci.args[0], ci.args[1]); break;
+      case 0x7413: task_ref_rms(q, 128, ci.args[0], ci.args[1]); break;
+      case 0x7418: task_ref_rope512(q); break;
+      case 0x7420: task_ref_silu(q, 32 * 8); break;                  // one 64 x 8 tile, whatever the token count
+      case 0x7421: task_ref_silu(q, 6144 / 2 * ci.args[0]); break;
+      case 0x7428: task_ref_argmax_partial(q, 1024, 65536, 128, ci.args[0]); break;
+      case 0x7429: task_ref_argmax_reduce(q, 1024, 128, ci.args[0]); break;
+      case 0x742A: task_ref_argmax_partial(q, 1152, 50688, 132, ci.args[0]); break;
+      case 0x742B: task_ref_argmax_reduce(q, 1152, 132, ci.args[0]); break;
+      case 0x7430: case 0x7431: task_ref_attn_decode(q, ci.args[0], ci.args[1], ci.args[2], false, 0, 1); break;
+      case 0x7432: case 0x7433:   // [blocks | split << 12, active rows | last length << 8, first position]
+        task_ref_attn_decode(q, ci.args[0] & 0xFFF, ci.args[1] >> 8, 0, true, ci.args[0] >> 12, ci.args[1] & 0xFF);
+        break;
+      case 0x7434: task_ref_attn_post_reduce(q, ci.args[0]); break;
+      default: return false;
+  }
+  return true;
+}
+
+template <bool kRefOps>
 __device__ __forceinline__ void compute_core(const Ctx& c, const VdcCInst* __restrict__ insts, int n_insts, int tid) {
   Compute q{c, c.sh, tid, tid >> 5, tid & 31, 0u, 0u, 0u, false, 0ull};
   uint32_t count = 0;
@@ -325,29 +356,11 @@ __device__ __forceinline__ void compute_core(const Ctx& c, const VdcCInst* __res
                    reinterpret_cast<uint32_t*>(addr48(e[2])));
         break;
       }
-      // ---- the reference's operators (tile contracts of its schedules)
-      case 0x7400: case 0x7401: task_ref_gemv(q, ci.args[0], 4, ci.opcode & 1); break;
-      case 0x7402: case 0x7403: task_ref_gemv(q, ci.args[0], 2, ci.opcode & 1); break;
-      case 0x7404: case 0x7405: task_ref_gemv(q, ci.args[0], 1, ci.opcode & 1); break;
-      case 0x7408: task_ref_gemv(q, ci.args[0], 1, false); break;
-      case 0x7410: task_ref_rms(q, 4096, ci.args[0], ci.args[1]); break;
-      case 0x7411: task_ref_rms(q, 2048, ci.args[0], ci.args[1]); break;
-      case 0x7412: task_ref_rms(q, 5120, ci.args[0], ci.args[1]); break;
-      case 0x7413: task_ref_rms(q, 128, ci.args[0], ci.args[1]); break;
-      case 0x7418: task_ref_rope512(q); break;
-      case 0x7420: task_ref_silu(q, 32 * 8); break;                  // one 64 x 8 tile, whatever the token count
-      case 0x7421: task_ref_silu(q, 6144 / 2 * ci.args[0]); break;
-      case 0x7428: task_ref_argmax_partial(q, 1024, 65536, 128, ci.args[0]); break;
-      case 0x7429: task_ref_argmax_reduce(q, 1024, 128, ci.args[0]); break;
-      case 0x742A: task_ref_argmax_partial(q, 1152, 50688, 132, ci.args[0]); break;
-      case 0x742B: task_ref_argmax_reduce(q, 1152, 132, ci.args[0]); break;
-      case 0x7430: case 0x7431: task_ref_attn_decode(q, ci.args[0], ci.args[1], ci.args[2], false, 0, 1); break;
-      case 0x7432: case 0x7433:   // [blocks | split << 12, active rows | last length << 8, first position]
-        task_ref_attn_decode(q, ci.args[0] & 0xFFF, ci.args[1] >> 8, 0, true, ci.args[0] >> 12, ci.args[1] & 0xFF);
-        break;
-      case 0x7434: task_ref_attn_post_reduce(q, ci.args[0]); break;
       case 0x7240: task_moe_route(q, ci.args[0], ci.args[1], ci.args[2] & 0xFF, ci.args[2] >> 8); break;
       default:
+        if constexpr (kRefOps) {
+          if (dispatch_ref_op(q, ci)) break;
+        }
         raise_abort(c, VDC_ERR_BAD_OPCODE, 0, (int)q.pc, ci.opcode, -1, 0);
         q.aborted = true;
         break;
@@ -360,6 +373,7 @@ __device__ __forceinline__ void compute_core(const Ctx& c, const VdcCInst* __res
 // ------------------------------------------------------------------------- //
 // the kernel
 // ------------------------------------------------------------------------- //
+template <bool kRefOps>
 __global__ void __launch_bounds__(VDC_THREADS, 1)
 vdc_megakernel(const VdcCInst* __restrict__ cinsts, const VdcMInst* __restrict__ minsts,
                const CUtensorMap* __restrict__ tmas, int* bars, uint64_t* profile, vdc_status* status,
@@ -395,7 +409,7 @@ vdc_megakernel(const VdcCInst* __restrict__ cinsts, const VdcMInst* __restrict__
   __syncthreads();
 
   if (tid < kCT) {
-    compute_core(c, cinsts + (size_t)c.sm * insts_per_sm, insts_per_sm, tid);
+    compute_core<kRefOps>(c, cinsts + (size_t)c.sm * insts_per_sm, insts_per_sm, tid);
   } else {
     const int w = (tid - kCT) >> 5, lane = tid & 31;
     if (w == 0) control_warp(c, minsts + (size_t)c.sm * insts_per_sm, insts_per_sm, lane);
@@ -436,16 +450,25 @@ vdc_megakernel(const VdcCInst* __restrict__ cinsts, const VdcMInst* __restrict__
 extern "C" size_t vdc_megakernel_dynamic_smem() { return (size_t)VDC_NUM_SLOTS * VDC_SLOT_BYTES + 1024 + 2048; }
 
 extern "C" cudaError_t vdc_megakernel_prepare() {
-  return cudaFuncSetAttribute(vdc::vdc_megakernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  cudaError_t e = cudaFuncSetAttribute(vdc::vdc_megakernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)vdc_megakernel_dynamic_smem());
+  if (e != cudaSuccess) return e;
+  return cudaFuncSetAttribute(vdc::vdc_megakernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                               (int)vdc_megakernel_dynamic_smem());
 }
 
 extern "C" cudaError_t vdc_megakernel_launch(int num_sms, const void* cinsts, const void* minsts, const void* tmas,
                                              int* bars, uint64_t* profile, vdc_status* status, int insts_per_sm,
-                                             uint64_t timeout_ns, cudaStream_t stream) {
-  vdc::vdc_megakernel<<<num_sms, VDC_THREADS, vdc_megakernel_dynamic_smem(), stream>>>(
-      reinterpret_cast<const VdcCInst*>(cinsts), reinterpret_cast<const VdcMInst*>(minsts),
-      reinterpret_cast<const CUtensorMap*>(tmas), bars, profile, status, insts_per_sm, timeout_ns);
+                                             uint64_t timeout_ns, cudaStream_t stream, int ref_ops) {
+  // ref_ops: the full kernel, which also knows the reference's tile-contract operators
+  if (ref_ops)
+    vdc::vdc_megakernel<true><<<num_sms, VDC_THREADS, vdc_megakernel_dynamic_smem(), stream>>>(
+        reinterpret_cast<const VdcCInst*>(cinsts), reinterpret_cast<const VdcMInst*>(minsts),
+        reinterpret_cast<const CUtensorMap*>(tmas), bars, profile, status, insts_per_sm, timeout_ns);
+  else
+    vdc::vdc_megakernel<false><<<num_sms, VDC_THREADS, vdc_megakernel_dynamic_smem(), stream>>>(
+        reinterpret_cast<const VdcCInst*>(cinsts), reinterpret_cast<const VdcMInst*>(minsts),
+        reinterpret_cast<const CUtensorMap*>(tmas), bars, profile, status, insts_per_sm, timeout_ns);
   return cudaGetLastError();
 }
 
