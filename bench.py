@@ -201,7 +201,6 @@ def run_gpu(args):
     if world == 1 and args.batch > 1:
         # batched decode: the projections run on the tensor cores, one state block per sequence
         from vdcores_b200.batch import BatchDecodeEngine
-        assert args.wkind in ("bf16", "fp8"), "batched decode: bf16 or fp8 projections"
         eng = BatchDecodeEngine(cfg, args.batch, max_seq=max_seq, device=dev, max_steps=W + K + 8, wkind=args.wkind)
         eng.init_random_weights(seed=0)
         prompt = torch.randint(0, cfg.vocab, (args.batch, PROMPT_LEN), generator=g)

@@ -140,7 +140,8 @@ const char* vdc_family_specs(void);
  *   other arguments as for vdc_launch; outputs are whatever the program's stores write.
  * Limits: num_sms <= 160 (more is rejected with VDC_ERR_ARG).  The first call
  * on a device does the one-time set-up (shared-memory attribute, address of the
- * array): make that call before any stream capture.  All calls on a device share
+ * array).  The call synchronises its stream (it returns the status), so it cannot be
+ * part of a stream capture.  All calls on a device share
  * the one array: it keeps the last call's contents (status and barriers are
  * re-initialised at the start of every call), and two calls that overlap on the
  * GPU would race on it, so keep them on one stream or serialise them.

@@ -20,9 +20,10 @@ def _bpad(B):
     return next(p for p in (16, 32, 64, 128) if B <= p)
 
 
-def _gemm_program(dev, x, w, n_sms, mode, out, norm_w=None, eps=1e-5, ld=0, keys=None, stats=None, scales=None):
-    """w: bf16 weights, or (with scales) uint8 e4m3 codes and their fp32 per-row scales."""
-    from vdcores_b200.batch import (BLOCK_ROWS, emit_projection, pack_blocks, pack_blocks_fp8, pack_kc,
+def _gemm_program(dev, x, w, n_sms, mode, out, norm_w=None, eps=1e-5, ld=0, keys=None, stats=None, scales=None,
+                  wfmt=None, n_rows=None):
+    """w: bf16 weights, or (with scales) uint8 e4m3 codes / NVFP4 rows (wfmt "nvfp4") and their fp32 per-row scales."""
+    from vdcores_b200.batch import (BLOCK_ROWS, emit_projection, pack_blocks, pack_blocks_fp8, pack_blocks_nvfp4, pack_kc,
                                     projection_blocks)
     from vdcores_b200.program import Program
     B, K = x.shape
@@ -30,7 +31,8 @@ def _gemm_program(dev, x, w, n_sms, mode, out, norm_w=None, eps=1e-5, ld=0, keys
     xp = torch.zeros(Bp, K, dtype=BF16)
     xp[:B] = x
     xd = pack_kc(xp.to(dev))
-    wd = pack_blocks_fp8(w.to(dev)) if scales is not None else pack_blocks(w.to(dev))
+    wfmt = wfmt or ("fp8" if scales is not None else "bf16")
+    wd = {"fp8": pack_blocks_fp8, "bf16": pack_blocks, "nvfp4": lambda t: pack_blocks_nvfp4(t, K)}[wfmt](w.to(dev))
     sd = scales.to(dev) if scales is not None else None
     nwd = norm_w.to(dev) if norm_w is not None else None
     if norm_w is not None:      # the producers of a normed input leave its per-row sums of squares
@@ -47,7 +49,7 @@ def _gemm_program(dev, x, w, n_sms, mode, out, norm_w=None, eps=1e-5, ld=0, keys
                             norm_addr=nwd.data_ptr() if nwd is not None else None, eps=eps, ld=ld,
                             keys_addr=keys.data_ptr() if keys is not None else 0,
                             stats_addr=stats.data_ptr() if stats is not None else 0,
-                            wfmt="fp8" if sd is not None else "bf16", scales_addr=sd.data_ptr() if sd is not None else 0)
+                            wfmt=wfmt, scales_addr=sd.data_ptr() if sd is not None else 0)
     run_program(P, dev)
     assert float(scr.abs().max()) == 0.0 and int(cnt.abs().max()) == 0, "scratch and counters are left clear"
     return units
@@ -86,6 +88,26 @@ def test_gemm_tc_fp8_weights(cuda_device, B, K, M, n_sms, norm):
     xin = O.rms_norm(x, nw, 1e-5) if norm else x
     ref = (xin.float() @ wq.t()).to(BF16)
     assert O.rel_l2(y.cpu(), ref) < 4e-3
+
+
+@pytest.mark.parametrize("B,K,M,n_sms,norm", [(7, 512, 256, 1, False), (16, 4096, 640, 5, True), (40, 1024, 96, 2, False)])
+def test_gemm_tc_nvfp4_weights(cuda_device, B, K, M, n_sms, norm):
+    """NVFP4 weights (e2m1 values, one e4m3 scale per 16 inputs, fp32 tensor scale): value times block scale is
+    converted to bf16 in shared memory (exact), the tensor scale applied in the epilogue; compared with the
+    oracle's linear layer over the same codes."""
+    from vdcores_b200 import isa
+    dev = cuda_device
+    x, w = seeded((B, K), 51), seeded((M, K), 52, 0.05)
+    from vdcores_b200.decode import quantize_nvfp4_rows
+    lin = O.QLinear.make(w, "nvfp4")
+    rows, ts = quantize_nvfp4_rows(w)          # the engine's codec: the same codes as the oracle's
+    assert torch.equal(rows[:, :K // 2], lin.q)
+    scales = ts.expand(M).contiguous()
+    nw = (1 + 0.1 * torch.randn(K, generator=torch.Generator().manual_seed(53))).to(BF16) if norm else None
+    y = torch.zeros(B, M, dtype=BF16, device=dev)
+    _gemm_program(dev, x, rows, n_sms, isa.GEMM_MODE_STORE_ROWS, y, norm_w=nw, ld=M, scales=scales, wfmt="nvfp4")
+    xin = O.rms_norm(x, nw, 1e-5) if norm else x
+    assert O.rel_l2(y.cpu(), lin(xin)) < 4e-3
 
 
 def test_gemm_tc_residual_add_and_silu(cuda_device):
@@ -210,28 +232,29 @@ def test_batch_prefill_and_host_steps(cuda_device):
             toks[b] = ref_next
 
 
-def test_batch_decode_fp8_matches_oracle(cuda_device):
-    """Batched decode with e4m3 layer projections against one oracle per sequence that dequantises
-    the same codes: per-layer hidden states within rel-L2 3e-2."""
+@pytest.mark.parametrize("wkind,tol", [("fp8", 3e-2), ("nvfp4", 6e-2)])
+def test_batch_decode_quantised_matches_oracle(cuda_device, wkind, tol):
+    """Batched decode with e4m3 / NVFP4 layer projections against one oracle per sequence that dequantises
+    the same codes: per-layer hidden states within rel-L2 3e-2 / 6e-2."""
     import copy
     import dataclasses
     from vdcores_b200.batch import BatchDecodeEngine
     cfg_b = small_cfg("llama")
     w_b = perturb_norms(O.ModelWeights.random(cfg_b, seed=6))
-    cfg = dataclasses.replace(cfg_b, wkind="fp8")
+    cfg = dataclasses.replace(cfg_b, wkind=wkind)
     w = copy.copy(w_b)
     w.cfg = cfg
     w.layers = []
     for lw in w_b.layers:
         ql = copy.copy(lw)
         for name in ("wq", "wk", "wv", "wo", "gate", "up", "down"):
-            setattr(ql, name, O.QLinear.make(getattr(lw, name).w, "fp8"))
+            setattr(ql, name, O.QLinear.make(getattr(lw, name).w, wkind))
         w.layers.append(ql)
     batch = 5
     g = torch.Generator().manual_seed(33)
     lens = [int(v) for v in torch.randint(2, 60, (batch,), generator=g)]
     prompts = [torch.randint(0, cfg.vocab, (n,), generator=g) for n in lens]
-    eng = BatchDecodeEngine(engine_config(cfg), batch, max_seq=128, device=cuda_device, taps=True, wkind="fp8",
+    eng = BatchDecodeEngine(engine_config(cfg), batch, max_seq=128, device=cuda_device, taps=True, wkind=wkind,
                             timeout_ns=500_000_000)
     eng.load_weights(dense_weights(w_b))       # the engine quantises the same bf16 weights with the same rule
     orcs, toks = [], []
@@ -252,7 +275,7 @@ def test_batch_decode_fp8_matches_oracle(cuda_device):
             _, nxt_ref, gap = orcs[b].step(toks[b], caps)
             for l in range(cfg.n_layers):
                 r = O.rel_l2(taps[l][b], caps[l]["hidden_state_out"])
-                assert r < 3e-2, f"step {step} sequence {b} layer {l}: rel-L2 {r:.3e}"
+                assert r < tol, f"step {step} sequence {b} layer {l}: rel-L2 {r:.3e}"
             if gap > GAP:
                 assert got[b] == nxt_ref
             if got[b] != nxt_ref:

@@ -65,6 +65,19 @@ def pack_blocks_fp8(codes: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def pack_blocks_nvfp4(rows: torch.Tensor, K: int) -> torch.Tensor:
+    """[M, K/2 + K/16] NVFP4 rows (e2m1 pairs, then the e4m3 block scales) -> flat: per block of 256 rows
+    and per 16 inputs, the rows' 8 code bytes followed by the rows' scale bytes ([K/16][N x 8 | N]), so that
+    any K-range of a block is one contiguous piece of 9 N bytes per 16 inputs."""
+    M = rows.shape[0]
+    codes, bs = rows[:, :K // 2].reshape(M, K // 16, 8), rows[:, K // 2:]
+    out = torch.empty(M * K * 9 // 16, dtype=rows.dtype, device=rows.device)
+    for r0, n in projection_blocks(M):
+        blk = torch.cat((codes[r0:r0 + n].permute(1, 0, 2).reshape(K // 16, n * 8), bs[r0:r0 + n].t()), dim=1)
+        out[r0 * K * 9 // 16:(r0 + n) * K * 9 // 16] = blk.reshape(-1)
+    return out
+
+
 def chunk_geometry(N: int, Bpad: int, K: int):
     """(Kc, G): inputs per W chunk (N * Kc * 2 bytes <= 32 KB, Kc divides K) and W chunks per X chunk
     (the X chunk fills at most one 8 KB slot when it can)."""
@@ -104,8 +117,8 @@ def emit_projection(P: Program, *, sms, load, w_addr, M, K, x_addr, B, Bpad, mod
     x k-chunk-major at x_addr).  scratch_addr: fp32 [blocks][B][256]; counter_addr: int32 [blocks]."""
     blocks = projection_blocks(M)
     Kc, G = chunk_geometry(blocks[0][1], Bpad, K)
-    wbpe = 2 if wfmt == "bf16" else 1
-    units = plan_units(blocks, K // Kc, sms, load, Kc * wbpe)
+    wb16 = {"bf16": 32, "fp8": 16, "nvfp4": 9}[wfmt]       # bytes per 16 weights of one row
+    units = plan_units(blocks, K // Kc, sms, load, Kc * wb16 // 16)
     slices = [0] * len(blocks)
     for _, bi, _, _ in units:
         slices[bi] += 1
@@ -114,7 +127,7 @@ def emit_projection(P: Program, *, sms, load, w_addr, M, K, x_addr, B, Bpad, mod
     for sm, bi, c0, cnt in units:
         r0, N = blocks[bi]
         k0 = c0 * Kc
-        P.gemm_tc(sm, w_addr=w_addr + (r0 * K + k0 * N) * wbpe, N=N, K=K, k_len=cnt * Kc, Kc=Kc, G=G,
+        P.gemm_tc(sm, w_addr=w_addr + (r0 * K + k0 * N) * wb16 // 16, N=N, K=K, k_len=cnt * Kc, Kc=Kc, G=G,
                   wfmt=wfmt, scales_addr=scales_addr + 4 * r0 if scales_addr else 0,
                   x_addr=x_addr + k0 * Bpad * 2, B=B, Bpad=Bpad, out_addr=out_addr, mode=mode, x_wait=x_wait,
                   norm_w=Src(norm_addr + k0 * 2, cnt * Kc * 2) if norm_addr is not None else None, eps=eps, n0=r0,
@@ -126,11 +139,13 @@ def emit_projection(P: Program, *, sms, load, w_addr, M, K, x_addr, B, Bpad, mod
 
 class BatchDecodeEngine(DecodeEngine):
     """`batch` sequences decoded together, one kernel launch per step.  Dense models; the layer
-    projections are bf16 or e4m3 with per-row scales (wkind "fp8"), everything else bf16."""
+    projections are bf16, e4m3 with per-row scales (wkind "fp8") or NVFP4 (wkind "nvfp4": e2m1 values, e4m3 block
+    scales, fp32 tensor scale), everything else bf16."""
+    GEMV_PROJECTIONS = False
 
     def __init__(self, cfg: DecodeConfig, batch: int, max_seq: int, device="cuda:0", num_sms=None, taps=False,
                  page_perm_seed=None, max_steps: int = 256, timeout_ns: int = 2_000_000_000, wkind: str = "bf16"):
-        assert 1 <= batch <= 128 and not cfg.n_experts and wkind in ("bf16", "fp8")
+        assert 1 <= batch <= 128 and not cfg.n_experts and wkind in ("bf16", "fp8", "nvfp4")
         self.batch = batch
         self.bpad = next(p for p in (16, 32, 64, 128) if batch <= p)
         super().__init__(cfg, max_seq, device=device, num_sms=num_sms, taps=False, page_perm_seed=None,
@@ -204,8 +219,9 @@ class BatchDecodeEngine(DecodeEngine):
 
         def gemm_stage(w, name, K, x_addr, x_wait, mode, out_addr, release, norm=None, ld=0, keys=0, stats=0):
             M = w.shape[0]
-            fp8 = name is not None and self.wkind == "fp8"      # the vocabulary projection stays bf16
-            pk = pack_blocks_fp8(w) if fp8 else pack_blocks(w)
+            wf = self.wkind if name is not None else "bf16"     # the vocabulary projection stays bf16
+            fp8 = wf != "bf16"
+            pk = pack_blocks_fp8(w) if wf == "fp8" else pack_blocks_nvfp4(w, K) if wf == "nvfp4" else pack_blocks(w)
             if name is not None:
                 packed[name].append(pk)
             kind = name or "lm"
@@ -218,7 +234,7 @@ class BatchDecodeEngine(DecodeEngine):
             emit_projection(P, sms=sms, load=load, w_addr=pk.data_ptr(), M=M, K=K, x_addr=x_addr, B=B, Bpad=Bp,
                             mode=mode, out_addr=out_addr, scratch_addr=scr.data_ptr(), counter_addr=cnt.data_ptr(),
                             x_wait=x_wait, release=release, norm_addr=norm.data_ptr() if norm is not None else None,
-                            eps=cfg.eps, ld=ld, keys_addr=keys, stats_addr=stats, wfmt="fp8" if fp8 else "bf16",
+                            eps=cfg.eps, ld=ld, keys_addr=keys, stats_addr=stats, wfmt=wf,
                             scales_addr=self.scales[name][len(packed[name]) - 1].data_ptr() if fp8 else 0)
             return pk
 

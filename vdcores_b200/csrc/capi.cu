@@ -396,7 +396,8 @@ int vdc_launch_static(int num_sms, int insts_per_sm, const void* compute_insts, 
   uint64_t* d_profile = reinterpret_cast<uint64_t*>(base + VDC_STATIC_PROFILE_OFF);
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   // the array keeps the previous call's contents: the status must start at zero,
-  // the barriers at the caller's counts; profile rows are fully rewritten by the kernel
+  // the barriers at the caller's counts; the profile rows stay internal (the kernel writes only its start / end
+  // stamps and the traced task pairs into them, nothing reads the rest)
   cudaError_t e = cudaMemsetAsync(d_status, 0, sizeof(vdc_status), s);
   if (e != cudaSuccess) return fail_cuda(e, "cudaMemsetAsync(status)");
   e = cudaMemcpyAsync(d_bars, bars_init, sizeof(int) * VDC_MAX_BARS, cudaMemcpyDeviceToDevice, s);

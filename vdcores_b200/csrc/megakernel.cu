@@ -276,7 +276,7 @@ __device__ __forceinline__ void compute_core(const Ctx& c, const VdcCInst* __res
         g.scratch = reinterpret_cast<float*>(addr48(e[5]));
         g.counter = reinterpret_cast<int*>(addr48(e[6]));
         g.n_slices = e[7].args[0];
-        g.wfmt = (ci.args[1] >> 13) & 1;
+        g.wfmt = (ci.args[1] >> 13) & 3;   // 0 bf16, 1 e4m3, 2 NVFP4
         g.scales = reinterpret_cast<const float*>(addr48(e[8]));
         const bool ok = g.N >= 16 && g.N <= 256 && g.B >= 1 && g.B <= g.Bpad &&
                         (g.Bpad == 16 || g.Bpad == 32 || g.Bpad == 64 || g.Bpad == 128) && g.KS >= 1 && g.G >= 1 &&

@@ -102,7 +102,7 @@ struct GemmTc {
   float* scratch;  // [B][N] fp32 partial sums of this block (n_slices > 1)
   int* counter;    // arrivals of this block's units
   int n_slices;
-  int wfmt;             // 0: bf16 weights, 1: e4m3 weights (converted to bf16 in shared memory)
+  int wfmt;             // 0: bf16 weights; 1: e4m3, 2: NVFP4 (both converted to bf16 in shared memory)
   const float* scales;  // e4m3: fp32 per-row scales of the block, applied in the epilogue
 };
 
@@ -203,7 +203,7 @@ VDC_TASK void task_gemm_tc(Compute& q, const GemmTc& g) {
   int normw_mask = 0;
   if (g.norm) normw_mask = q.pop();
   int stage_mask[kStages] = {0, 0};
-  if (g.wfmt == 1) {
+  if (g.wfmt != 0) {
 #pragma unroll
     for (int st = 0; st < kStages; ++st) stage_mask[st] = q.pop();  // allocate-only entries: bf16 staging buffers
   }
@@ -224,7 +224,7 @@ VDC_TASK void task_gemm_tc(Compute& q, const GemmTc& g) {
   // run ahead of it, normalising the X chunks in place and signalling each chunk's barrier.
   TCS(0);
   q.warp_phase_begin(n_ent, q.warp == 0 ? 0u : n_ent);
-  if (q.warp > 0 && (g.norm || g.wfmt == 1)) {
+  if (q.warp > 0 && (g.norm || g.wfmt != 0)) {
     // The seven warps work as a team of 224 threads, ahead of the issuer: they normalise each X
     // chunk in place and, for e4m3 weights, convert each W chunk into a bf16 staging buffer.
     // One warp does the (bounded) waiting and tells the team, so that all leave together on an abort.
@@ -268,7 +268,7 @@ VDC_TASK void task_gemm_tc(Compute& q, const GemmTc& g) {
         asm volatile("bar.sync 6, %0;" ::"n"(kTeam) : "memory");
         if (t == 0) mbar_arrive(&sh->x_ready[(q.xr_count + (unsigned)grp) & 15u]);
       }
-      if (g.wfmt == 1) {
+      if (g.wfmt != 0) {
         // W chunk j: [Kc/16][N/8][8 rows][16 k] e4m3 bytes -> staging buffer j % kStages as
         // [Kc/8][N/8][8 rows][8 k] bf16 (exact), once the tensor cores are done with the
         // buffer's previous occupant (chunk j - kStages)
@@ -286,20 +286,40 @@ VDC_TASK void task_gemm_tc(Compute& q, const GemmTc& g) {
         if (wm == kPopAbort) break;
         const uint8_t* src = (const uint8_t*)slot_ptr(c, first_slot(wm));
         uint8_t* dst = (uint8_t*)slot_ptr(c, first_slot(stage_mask[j % kStages]));
-        const int pieces = g.KS * g.N;  // 16-byte pieces of the e4m3 chunk: (16-k group, row)
-        for (int p = t; p < pieces; p += kTeam) {
-          const uint4 v = lds128(src + p * 16);
-          const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
-          uint32_t o[8];
+        const int pieces = g.KS * g.N;  // (16-k group, row) pairs of the chunk: 16 weights each
+        if (g.wfmt == 1) {
+          for (int p = t; p < pieces; p += kTeam) {   // e4m3: one 16-byte piece per pair
+            const uint4 v = lds128(src + p * 16);
+            const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
+            uint32_t o[8];
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const float2 lo = e4m3x2_to_float2(wv[i] & 0xFFFFu), hi = e4m3x2_to_float2(wv[i] >> 16);
-            o[2 * i] = pack_bf16x2(lo.x, lo.y);
-            o[2 * i + 1] = pack_bf16x2(hi.x, hi.y);
+            for (int i = 0; i < 4; ++i) {
+              const float2 lo = e4m3x2_to_float2(wv[i] & 0xFFFFu), hi = e4m3x2_to_float2(wv[i] >> 16);
+              o[2 * i] = pack_bf16x2(lo.x, lo.y);
+              o[2 * i + 1] = pack_bf16x2(hi.x, hi.y);
+            }
+            const int i16 = p / g.N, row = p - i16 * g.N;
+            *reinterpret_cast<uint4*>(dst + ((size_t)(2 * i16) * g.N + row) * 16) = make_uint4(o[0], o[1], o[2], o[3]);
+            *reinterpret_cast<uint4*>(dst + ((size_t)(2 * i16 + 1) * g.N + row) * 16) = make_uint4(o[4], o[5], o[6], o[7]);
           }
-          const int i16 = p / g.N, row = p - i16 * g.N;
-          *reinterpret_cast<uint4*>(dst + ((size_t)(2 * i16) * g.N + row) * 16) = make_uint4(o[0], o[1], o[2], o[3]);
-          *reinterpret_cast<uint4*>(dst + ((size_t)(2 * i16 + 1) * g.N + row) * 16) = make_uint4(o[4], o[5], o[6], o[7]);
+        } else {
+          // NVFP4: per 16-k group [N x 8 bytes of e2m1 pairs | N e4m3 block scales]; code times block scale is
+          // exact in bf16 (two significant bits times four), the per-row tensor scale waits for the epilogue
+          for (int p = t; p < pieces; p += kTeam) {
+            const int i16 = p / g.N, row = p - i16 * g.N;
+            const uint8_t* grp = src + (size_t)i16 * 9 * g.N;
+            const uint2 cv = *reinterpret_cast<const uint2*>(grp + row * 8);
+            const float sc = e4m3_to_float(grp[8 * g.N + row]);
+            const uint32_t cw[2] = {cv.x, cv.y};
+            uint32_t o[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const float2 f = __half22float2(e2m1x2_to_half2((cw[i >> 2] >> (8 * (i & 3))) & 0xFFu));
+              o[i] = pack_bf16x2(f.x * sc, f.y * sc);
+            }
+            *reinterpret_cast<uint4*>(dst + ((size_t)(2 * i16) * g.N + row) * 16) = make_uint4(o[0], o[1], o[2], o[3]);
+            *reinterpret_cast<uint4*>(dst + ((size_t)(2 * i16 + 1) * g.N + row) * 16) = make_uint4(o[4], o[5], o[6], o[7]);
+          }
         }
         fence_proxy_async_smem();
         asm volatile("bar.sync 6, %0;" ::"n"(kTeam) : "memory");  // also: everybody has read told[] and the chunk
@@ -329,7 +349,7 @@ VDC_TASK void task_gemm_tc(Compute& q, const GemmTc& g) {
       }
       const int wm = q.warp_wait(w_entry(j));
       if (wm == kPopAbort) break;
-      if (g.wfmt == 1) {
+      if (g.wfmt != 0) {
         // the converted chunk, not the loaded one, is the operand
         int ok = 1;
         if (q.lane == 0) {
@@ -367,7 +387,7 @@ VDC_TASK void task_gemm_tc(Compute& q, const GemmTc& g) {
       if (q.lane == 0) {
         tc_fence_after();
         uint64_t adesc = umma_desc(smem_u32(slot_ptr(c, first_slot(xm))) + (uint32_t)(jj * g.KS) * 2u * lbo_a, lbo_a, 128u);
-        const int b_slot = g.wfmt == 1 ? first_slot(stage_mask[j % kStages]) : first_slot(wm);
+        const int b_slot = g.wfmt != 0 ? first_slot(stage_mask[j % kStages]) : first_slot(wm);
         uint64_t bdesc = umma_desc(smem_u32(slot_ptr(c, b_slot)), lbo_b, 128u);
         const uint64_t step_a = (uint64_t)((2u * lbo_a) >> 4), step_b = (uint64_t)((2u * lbo_b) >> 4);
         umma_bf16(tmem, adesc, bdesc, idesc, (uint32_t)(j != 0));
@@ -384,7 +404,7 @@ VDC_TASK void task_gemm_tc(Compute& q, const GemmTc& g) {
 #endif
         // the previous chunk's reads are certainly done once its commit arrived
         if (j > 0) {
-          int done = (g.wfmt == 1 ? 0 : w_prev) | x_done;  // e4m3 chunks were freed by the converting team
+          int done = (g.wfmt != 0 ? 0 : w_prev) | x_done;  // e4m3 chunks were freed by the converting team
           if (!mma_wait(q, q.mma_count - 1)) done = 0;
           if (done) atomicOr(&sh->slot_avail, (uint32_t)done & kSlotMaskAll);
           sh->warp_next[0] = q.head + x_entry(grp);  // ring entries before this group may be recycled
@@ -399,7 +419,7 @@ VDC_TASK void task_gemm_tc(Compute& q, const GemmTc& g) {
     }
     if (q.lane == 0) {
       x_prev = xm == kPopAbort ? 0 : (xm & (int)kSlotMaskAll);
-      if (g.wfmt == 1) w_prev = 0;
+      if (g.wfmt != 0) w_prev = 0;
       if (q.mma_count > 0 && mma_wait(q, q.mma_count - 1) && (w_prev | x_prev))
         atomicOr(&sh->slot_avail, (uint32_t)(w_prev | x_prev) & kSlotMaskAll);
       sh->warp_next[0] = 0xFFFFFFFFu;
@@ -414,10 +434,10 @@ VDC_TASK void task_gemm_tc(Compute& q, const GemmTc& g) {
   q.warp_phase_end(n_ent);  // CTA barrier: accumulator complete (lane 0 saw the last commit)
   tc_fence_after();
   if (g.norm) q.xr_count += (unsigned)n_x;
-  if (g.wfmt == 1) q.wr_count += (unsigned)g.n_w;
+  if (g.wfmt != 0) q.wr_count += (unsigned)g.n_w;
   q.mma_count = mma_base + (unsigned)g.n_w;  // every thread keeps the count (thread 0 counted along)
   if (q.aborted) return;
-  if (g.wfmt == 1) q.free_slots(stage_mask[0] | stage_mask[1]);
+  if (g.wfmt != 0) q.free_slots(stage_mask[0] | stage_mask[1]);
   TCS(1);
 
   // Lane b of the accumulator belongs to sequence b; warps w and w+4 share the lane quarter

@@ -149,6 +149,8 @@ def quantize_nvfp4_rows(w: torch.Tensor):
 
 
 class DecodeEngine:
+    GEMV_PROJECTIONS = True     # the layer projections run as GEMV tasks (batch 1)
+
     def __init__(self, cfg: DecodeConfig, max_seq: int, device="cuda", num_sms: Optional[int] = None,
                  taps: bool = False, page_perm_seed: Optional[int] = None, max_steps: int = 4096,
                  timeout_ns: int = 0, l2_prefetch_bytes: int = 0, wkind: str = "bf16", shared_counters: bool = False):
@@ -159,7 +161,9 @@ class DecodeEngine:
         assert wkind in ("bf16", "fp8", "nvfp4")
         self.cfg = cfg
         self.wkind = wkind                  # storage of the layer projections; embed / norms / lm_head stay bf16
-        kmult = {"bf16": 256, "fp8": 512, "nvfp4": 1024}[wkind]
+        # the GEMV task walks K in warp steps of 256 / 512 / 1024 weights; the batched tensor-core path (a subclass)
+        # needs multiples of 16 only
+        kmult = {"bf16": 256, "fp8": 512, "nvfp4": 1024}[wkind] if self.GEMV_PROJECTIONS else 256
         assert cfg.hidden % kmult == 0 and cfg.ffn % kmult == 0 and cfg.q_width % kmult == 0
         self.dev = torch.device(device)
         props = torch.cuda.get_device_properties(self.dev)

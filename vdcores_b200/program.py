@@ -506,23 +506,24 @@ class Program:
         With n_slices > 1 the block's K is shared by that many units: partial sums meet in
         scratch_addr, counter_addr counts arrivals.  The caller declares `release` once per
         block with add_releases.  wfmt "fp8": the weights are e4m3 bytes (chunk layout
-        [Kc/16][N/8][8][16]) with fp32 per-row scales at scales_addr; two bf16 staging
-        buffers are allocated for the task."""
-        assert wfmt in ("bf16", "fp8") and (wfmt == "bf16" or (scales_addr and scales_addr % 16 == 0))
-        wbpe = 2 if wfmt == "bf16" else 1
+        [Kc/16][N/8][8][16]) with fp32 per-row scales at scales_addr; wfmt "nvfp4": per 16 inputs
+        [N rows x 8 bytes of e2m1 pairs | N e4m3 block scales], fp32 per-row (tensor) scales at
+        scales_addr; two bf16 staging buffers are allocated for the task in both cases."""
+        assert wfmt in ("bf16", "fp8", "nvfp4") and (wfmt == "bf16" or (scales_addr and scales_addr % 16 == 0))
+        wb16 = {"bf16": 32, "fp8": 16, "nvfp4": 9}[wfmt]       # bytes per 16 weights of one row
         assert N % 16 == 0 and 16 <= N <= 256 and Bpad in (16, 32, 64, 128) and 1 <= B <= Bpad
         assert Kc % 16 == 0 and k_len % Kc == 0 and k_len > 0 and n0 % 16 == 0 and ld % 16 == 0 and K % 16 == 0
         assert norm_w is None or stats_addr
         assert n_slices == 1 or (scratch_addr and counter_addr)
         n_w = k_len // Kc
-        wbytes = N * Kc * wbpe
+        wbytes = N * Kc * wb16 // 16
         assert N * Kc * 2 <= 32768 and n_w <= 0xFFFF and 1 <= G <= 15 and Kc // 16 <= 255
         assert Bpad * G * Kc * 2 <= 32768
         wslots = slots_for(wbytes)
         if norm_w is not None:
             assert norm_w.nbytes == k_len * 2
             self.load(sm, norm_w, default_port=1)
-        if wfmt == "fp8":
+        if wfmt != "bf16":
             for _ in range(2):      # staging buffers: slots only, nothing is loaded or stored
                 self.mem(sm, isa.OP_ALLOC_WB_TMA_STORE_1D, size=0, nslot=slots_for(N * Kc * 2), address=0)
 
@@ -553,7 +554,7 @@ class Program:
             assert 0 <= a < 1 << 48
         assert out_addr % 16 == 0 and keys_addr % 8 == 0 and stats_addr % 4 == 0 and scratch_addr % 16 == 0
         self.comp(sm, isa.OP_GEMM_TC_BF16, n_w, (N // 16) | (mode << 8) | ((1 << 12) if norm_w is not None else 0) |
-                  ((1 << 13) if wfmt == "fp8" else 0), (Kc // 16) | (G << 8))
+                  ({"bf16": 0, "fp8": 1, "nvfp4": 2}[wfmt] << 13), (Kc // 16) | (G << 8))
         self.comp(sm, isa.OP_EXT, e >> 16, e & 0xFFFF, B)
         self.comp(sm, isa.OP_EXT, *a48(out_addr))
         self.comp(sm, isa.OP_EXT, *a48(keys_addr))
