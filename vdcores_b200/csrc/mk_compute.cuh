@@ -440,7 +440,8 @@ __device__ __forceinline__ uint32_t exchange_tag(const int* state, uint32_t ex) 
 template <int R>
 VDC_TASK void task_gemv_rows(Compute& q, int n_chunks, int mode, bool accumulate, bool norm, int K, int row_base,
                                const float* scales = nullptr, int wfmt = 0, const MoeDown* moe = nullptr,
-                               bool dyn = false, const PeerOut* peers = nullptr, uint64_t dyn_base = 0) {
+                               bool dyn = false, const PeerOut* peers = nullptr, uint64_t dyn_base = 0,
+                               const float* partial = nullptr) {
   Shared* sh = q.sh;
   const Ctx& c = q.c;
 #ifdef VDC_TRACE_GEMV
@@ -615,6 +616,10 @@ VDC_TASK void task_gemv_rows(Compute& q, int n_chunks, int mode, bool accumulate
     if (wfmt != 0) {
 #pragma unroll
       for (int r = 0; r < R; ++r) acc[r] *= __ldg(scales + row0 + r);
+    }
+    if (partial != nullptr) {   // the rows' sums over the other K-range, left by an earlier task of this SM
+#pragma unroll
+      for (int r = 0; r < R; ++r) acc[r] += __ldcg(partial + row0 + r);
     }
     __syncwarp();
     if (q.lane == 0) {

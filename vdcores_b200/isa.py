@@ -37,6 +37,7 @@ GEMV_ACC_BIT = _defs["GEMV_ACC_BIT"]
 GEMV_DYN_BIT = _defs["GEMV_DYN_BIT"]
 GEMV_PEERS_BIT = _defs["GEMV_PEERS_BIT"]
 GEMV_DYNROWS_BIT = _defs["GEMV_DYNROWS_BIT"]
+GEMV_PARTIAL_BIT = _defs["GEMV_PARTIAL_BIT"]
 STREAM_END = _defs["STREAM_END"]
 ATTN_QKNORM_BIT = _defs["ATTN_QKNORM_BIT"]
 ATTN_PACKED_BIT = _defs["ATTN_PACKED_BIT"]

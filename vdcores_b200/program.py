@@ -304,7 +304,8 @@ class Program:
              stream: bool = False, fp8_scales: Optional[int] = None, nvfp4_scales: Optional[int] = None,
              w_indirect: Optional[tuple] = None, wait_issue: Optional[int] = None, moe: Optional[dict] = None,
              dyn_count_addr: Optional[int] = None, peers: Optional[tuple] = None, shared_counter: Optional[int] = None,
-             own_chunks: Optional[tuple] = None, shared_first: int = 0, shared_depth: int = 0):
+             own_chunks: Optional[tuple] = None, shared_first: int = 0, shared_depth: int = 0,
+             partial_in: Optional[int] = None):
         """y[0:n_rows] = W[0:n_rows, :K] @ x for the contiguous row block at w_addr
         (bf16; e4m3 with fp8_scales = address of the block's fp32 per-row scales;
         or NVFP4 rows — K/2 code bytes + K/16 block scales — with nvfp4_scales =
@@ -315,7 +316,9 @@ class Program:
         describe the WHOLE matrix on every SM that runs the task: the SM first streams the chunks it owns
         (own_chunks = (first, count)), then draws chunks shared_first, shared_first + 1, ... from the counter
         until the matrix is exhausted, never holding more than shared_depth unconsumed ring entries when it
-        draws (0: no limit), so the SMs that finish early take the tail of the stage."""
+        draws (0: no limit), so the SMs that finish early take the tail of the stage.
+        partial_in: address of fp32 sums of the same rows over another K-range (written by an earlier STORE_F32
+        task of this SM); they are added to the task's sums before the result is rounded."""
         assert fp8_scales is None or nvfp4_scales is None
         if nvfp4_scales is not None:
             row_bytes, kmult, op, scales = K // 2 + K // 16, 1024, isa.OP_GEMV_ROWS_NVFP4, nvfp4_scales
@@ -379,7 +382,8 @@ class Program:
         rb8 = row_base // R     # index of the first chunk within the whole matrix
         a1 = R | (mode << 8) | (isa.GEMV_NORM_BIT if norm_w is not None else 0) | \
             (isa.GEMV_ACC_BIT if out.kind == "add_bf16" else 0) | (isa.GEMV_DYN_BIT if dyn_count_addr is not None else 0) | \
-            (isa.GEMV_PEERS_BIT if peers is not None else 0) | (isa.GEMV_DYNROWS_BIT if shared_counter is not None else 0)
+            (isa.GEMV_PEERS_BIT if peers is not None else 0) | (isa.GEMV_DYNROWS_BIT if shared_counter is not None else 0) | \
+            (isa.GEMV_PARTIAL_BIT if partial_in is not None else 0)
         a2 = (K // 256) | ((rb8 >> 16) << 8)
         e = f32_bits(eps)
         if moe is not None:
@@ -395,6 +399,9 @@ class Program:
         if scales is not None:
             assert scales % 4 == 0 and 0 <= scales < 1 << 48
             self.comp(sm, isa.OP_EXT, scales & 0xFFFF, (scales >> 16) & 0xFFFF, (scales >> 32) & 0xFFFF)
+        if partial_in is not None:
+            assert moe is None and partial_in % 4 == 0 and 0 < partial_in < 1 << 48
+            self.comp(sm, isa.OP_EXT, partial_in & 0xFFFF, (partial_in >> 16) & 0xFFFF, (partial_in >> 32) & 0xFFFF)
         if peers is not None:
             # (table address, ranks, counter byte offset): out.addr is then the byte offset of the task's
             # first row inside an exchange block, the rows go to every rank's block
