@@ -156,25 +156,31 @@ def test_two_rank_expert_parallel_sum_reproduces_the_moe_block():
 
 
 def test_exchange_protocol_two_buffers_suffice():
-    """Model of the in-kernel tensor-parallel exchange (TPFusedEngine): every rank writes the partial
-    rows of exchange h into slot [h % 2][rank] of every rank's block, then bumps every rank's
-    counter h; a rank folds exchange h once its counter h is complete and only then produces
-    exchange h + 1.  Under random interleavings of the ranks (and of each rank's individual remote
-    writes) no rank may ever read a slot that already holds data of exchange h + 2."""
+    """Model of the in-kernel tensor-parallel exchange (TPFusedEngine): every rank writes the partial rows of
+    exchange h as tagged entries {payload, tag = step * n_ex + h + 1} into slot [h % 2][rank] of every rank's
+    block (one remote store per entry, in any order, no fence and no counter); a rank folds exchange h once every
+    writer's entry in its own block carries that tag, and only then produces exchange h + 1.  Under random
+    interleavings of the ranks and of each rank's individual remote writes, over several steps that reuse the
+    exchange numbers: a fold never sees a payload of another exchange under the tag it waits for, no slot is
+    overwritten before its owner has folded it, and nobody deadlocks."""
     import random
     for seed in range(200):
         rng = random.Random(seed)
-        n_ranks, n_ex = rng.choice([2, 3, 4, 8]), 7
-        xbuf = [[[None] * n_ranks for _ in range(2)] for _ in range(n_ranks)]     # [owner][parity][writer] -> tag
-        cnt = [[0] * n_ex for _ in range(n_ranks)]
-        # per rank: list of pending micro-steps of the exchange it is in
-        state = [{"h": 0, "todo": None} for _ in range(n_ranks)]
+        n_ranks, n_ex, n_steps = rng.choice([2, 3, 4, 8]), 5, 3
+        total = n_ex * n_steps
+        # [owner][parity][writer] -> (tag, payload); payload names the (global exchange, writer) it belongs to
+        xbuf = [[[(0, None)] * n_ranks for _ in range(2)] for _ in range(n_ranks)]
+        folded = [[-1] * 2 for _ in range(n_ranks)]          # last global exchange each owner folded, per parity
+        state = [{"g": 0, "todo": None} for _ in range(n_ranks)]
+
+        def tag_of(g):
+            step, h = divmod(g, n_ex)
+            return step * n_ex + h + 1
 
         def start(r):
-            h = state[r]["h"]
             steps = [("write", p) for p in range(n_ranks)]
             rng.shuffle(steps)
-            state[r]["todo"] = steps + [("signal", p) for p in range(n_ranks)] + [("fold", None)]
+            state[r]["todo"] = steps + [("fold", None)]
 
         for r in range(n_ranks):
             start(r)
@@ -182,22 +188,23 @@ def test_exchange_protocol_two_buffers_suffice():
         guard = 0
         while live:
             guard += 1
-            assert guard < 100000, "deadlock in the model"
+            assert guard < 200000, "deadlock in the model"
             r = rng.choice(sorted(live))
-            h = state[r]["h"]
+            g = state[r]["g"]
             kind, p = state[r]["todo"][0]
             if kind == "write":
-                xbuf[p][h & 1][r] = h
-            elif kind == "signal":
-                cnt[p][h] += 1
-            else:
-                if cnt[r][h] < n_ranks:
-                    continue                         # bounded wait in the kernel; here: try another rank
-                assert all(tag == h for tag in xbuf[r][h & 1]), (seed, r, h, xbuf[r][h & 1])
-                state[r]["h"] = h + 1
-                if h + 1 == n_ex:
-                    live.discard(r)
-                    continue
-                start(r)
+                # the slot's previous content (exchange g - 2 of this writer) must have been folded by its owner
+                old_tag, old = xbuf[p][g & 1][r]
+                assert old is None or folded[p][g & 1] >= old[0], (seed, r, p, g, old)
+                xbuf[p][g & 1][r] = (tag_of(g), (g, r))
+                state[r]["todo"].pop(0)
                 continue
-            state[r]["todo"].pop(0)
+            if any(t != tag_of(g) for t, _ in xbuf[r][g & 1]):
+                continue                                 # bounded poll in the kernel; here: let another rank run
+            assert all(pl == (g, w) for w, (_, pl) in enumerate(xbuf[r][g & 1])), (seed, r, g)
+            folded[r][g & 1] = g
+            state[r]["g"] = g + 1
+            if g + 1 == total:
+                live.discard(r)
+            else:
+                start(r)
