@@ -1,9 +1,9 @@
 """Generates tests/golden/dae_api.npz: the byte encodings the REFERENCE's python/dae produces for the cases
-in dae_cases.py.  Run in a checkout that has the reference (VDCORES_REFERENCE_ROOT, default
-/root/reference); the reference's compiled ``dae.runtime`` extension is replaced by this repository's
+in dae_cases.py.  Run where a checkout of the reference is available (its root in the environment variable
+VDCORES_REFERENCE_ROOT); the reference's compiled ``dae.runtime`` extension is replaced by this repository's
 ctypes runtime (opcode table, config, family specs), nothing is launched and no GPU is needed.
 
-    python tests/golden/make_dae_golden.py
+    VDCORES_REFERENCE_ROOT=<reference checkout> python tests/golden/make_dae_golden.py
 """
 import importlib
 import os
@@ -14,7 +14,9 @@ import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
-REF = os.environ.get("VDCORES_REFERENCE_ROOT", "/root/reference")
+REF = os.environ.get("VDCORES_REFERENCE_ROOT")
+if not REF:
+    raise SystemExit("set VDCORES_REFERENCE_ROOT to the root of a checkout of the reference")
 
 
 def load_reference_dae():
