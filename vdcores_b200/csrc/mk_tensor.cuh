@@ -106,7 +106,7 @@ struct GemmTc {
   const float* scales;  // e4m3: fp32 per-row scales of the block, applied in the epilogue
 };
 
-constexpr int kStages = 2;  // bf16 staging buffers of the e4m3 path
+constexpr int kStages = VDC_TC_STAGES;  // bf16 staging buffers of the converted-weight paths
 
 struct EpiAcc {
   float ssq;   // ADD_PACKED: squares of the new values
@@ -202,7 +202,7 @@ VDC_TASK void task_gemm_tc(Compute& q, const GemmTc& g) {
   }
   int normw_mask = 0;
   if (g.norm) normw_mask = q.pop();
-  int stage_mask[kStages] = {0, 0};
+  int stage_mask[kStages] = {};
   if (g.wfmt != 0) {
 #pragma unroll
     for (int st = 0; st < kStages; ++st) stage_mask[st] = q.pop();  // allocate-only entries: bf16 staging buffers
@@ -437,7 +437,12 @@ VDC_TASK void task_gemm_tc(Compute& q, const GemmTc& g) {
   if (g.wfmt != 0) q.wr_count += (unsigned)g.n_w;
   q.mma_count = mma_base + (unsigned)g.n_w;  // every thread keeps the count (thread 0 counted along)
   if (q.aborted) return;
-  if (g.wfmt != 0) q.free_slots(stage_mask[0] | stage_mask[1]);
+  if (g.wfmt != 0) {
+    int all = 0;
+#pragma unroll
+    for (int st = 0; st < kStages; ++st) all |= stage_mask[st];
+    q.free_slots(all);
+  }
   TCS(1);
 
   // Lane b of the accumulator belongs to sequence b; warps w and w+4 share the lane quarter

@@ -515,7 +515,7 @@ class Program:
         block with add_releases.  wfmt "fp8": the weights are e4m3 bytes (chunk layout
         [Kc/16][N/8][8][16]) with fp32 per-row scales at scales_addr; wfmt "nvfp4": per 16 inputs
         [N rows x 8 bytes of e2m1 pairs | N e4m3 block scales], fp32 per-row (tensor) scales at
-        scales_addr; two bf16 staging buffers are allocated for the task in both cases."""
+        scales_addr; isa.TC_STAGES bf16 staging buffers are allocated for the task in both cases."""
         assert wfmt in ("bf16", "fp8", "nvfp4") and (wfmt == "bf16" or (scales_addr and scales_addr % 16 == 0))
         wb16 = {"bf16": 32, "fp8": 16, "nvfp4": 9}[wfmt]       # bytes per 16 weights of one row
         assert N % 16 == 0 and 16 <= N <= 256 and Bpad in (16, 32, 64, 128) and 1 <= B <= Bpad
@@ -531,7 +531,7 @@ class Program:
             assert norm_w.nbytes == k_len * 2
             self.load(sm, norm_w, default_port=1)
         if wfmt != "bf16":
-            for _ in range(2):      # staging buffers: slots only, nothing is loaded or stored
+            for _ in range(isa.TC_STAGES):      # staging buffers: slots only, nothing is loaded or stored
                 self.mem(sm, isa.OP_ALLOC_WB_TMA_STORE_1D, size=0, nslot=slots_for(N * Kc * 2), address=0)
 
         def group(first_w, count, wait=None, jump=False):
