@@ -244,6 +244,7 @@
 #define VDC_GEMV_MODE_STORE_F32 3   // fp32 partial results (tensor-parallel row-split projections)
 #define VDC_GEMV_MODE_MOE_DOWN 4    // weighted fp32 accumulation over the selected experts
 #define VDC_TC_STAGES 2  // bf16 staging buffers of a batched projection with converted (e4m3 / NVFP4) weights (3: measured no faster)
+#define VDC_GEMV_STRIDE_BIT 0x0040   // one more word [s, 0, 0]: chunk i holds rows (i * s) * R ... of the task's matrix (chunks dealt round-robin to s SMs)
 #define VDC_GEMV_PARTIAL_BIT 0x0080  // one more word: address of fp32 partial sums of the task's rows, added before rounding
 #define VDC_GEMV_ACC_BIT 0x0800
 #define VDC_GEMV_NORM_BIT 0x1000

@@ -185,6 +185,13 @@ __device__ __forceinline__ void compute_core(const Ctx& c, const VdcCInst* __res
           scales = reinterpret_cast<const float*>((uint64_t)e2.args[0] | ((uint64_t)e2.args[1] << 16) |
                                                   ((uint64_t)e2.args[2] << 32));
         }
+        int chunk_stride = 1;
+        if (ci.args[1] & VDC_GEMV_STRIDE_BIT) {
+          VdcCInst e2;
+          *reinterpret_cast<uint2*>(&e2) = ld_word(q.pc);
+          q.pc += 1;
+          chunk_stride = e2.args[0];
+        }
         const float* partial = nullptr;   // fp32 sums over another K-range of the same rows (a projection in two passes)
         if (ci.args[1] & VDC_GEMV_PARTIAL_BIT) {
           VdcCInst e2;
@@ -206,11 +213,11 @@ __device__ __forceinline__ void compute_core(const Ctx& c, const VdcCInst* __res
           dyn_base = addr48(e2);
         }
         switch (R) {
-          case 1: task_gemv_rows<1>(q, ci.args[0], mode, accumulate, norm, K, row_base, scales, wfmt, moe, dyn, peers, dyn_base, partial); break;
-          case 2: task_gemv_rows<2>(q, ci.args[0], mode, accumulate, norm, K, row_base, scales, wfmt, moe, dyn, peers, dyn_base, partial); break;
-          case 4: task_gemv_rows<4>(q, ci.args[0], mode, accumulate, norm, K, row_base, scales, wfmt, moe, dyn, peers, dyn_base, partial); break;
-          case 8: task_gemv_rows<8>(q, ci.args[0], mode, accumulate, norm, K, row_base, scales, wfmt, moe, dyn, peers, dyn_base, partial); break;
-          case 16: task_gemv_rows<16>(q, ci.args[0], mode, accumulate, norm, K, row_base, scales, wfmt, moe, dyn, peers, dyn_base, partial); break;
+          case 1: task_gemv_rows<1>(q, ci.args[0], mode, accumulate, norm, K, row_base, scales, wfmt, moe, dyn, peers, dyn_base, partial, chunk_stride); break;
+          case 2: task_gemv_rows<2>(q, ci.args[0], mode, accumulate, norm, K, row_base, scales, wfmt, moe, dyn, peers, dyn_base, partial, chunk_stride); break;
+          case 4: task_gemv_rows<4>(q, ci.args[0], mode, accumulate, norm, K, row_base, scales, wfmt, moe, dyn, peers, dyn_base, partial, chunk_stride); break;
+          case 8: task_gemv_rows<8>(q, ci.args[0], mode, accumulate, norm, K, row_base, scales, wfmt, moe, dyn, peers, dyn_base, partial, chunk_stride); break;
+          case 16: task_gemv_rows<16>(q, ci.args[0], mode, accumulate, norm, K, row_base, scales, wfmt, moe, dyn, peers, dyn_base, partial, chunk_stride); break;
           default: raise_abort(c, VDC_ERR_BAD_OPCODE, 0, (int)q.pc, ci.opcode, -1, R); q.aborted = true; break;
         }
         break;

@@ -441,7 +441,7 @@ template <int R>
 VDC_TASK void task_gemv_rows(Compute& q, int n_chunks, int mode, bool accumulate, bool norm, int K, int row_base,
                                const float* scales = nullptr, int wfmt = 0, const MoeDown* moe = nullptr,
                                bool dyn = false, const PeerOut* peers = nullptr, uint64_t dyn_base = 0,
-                               const float* partial = nullptr) {
+                               const float* partial = nullptr, int chunk_stride = 1) {
   Shared* sh = q.sh;
   const Ctx& c = q.c;
 #ifdef VDC_TRACE_GEMV
@@ -576,7 +576,7 @@ VDC_TASK void task_gemv_rows(Compute& q, int n_chunks, int mode, bool accumulate
     }
     const bool arrived = w_mask != kPopAbort;
     float acc[R];
-    int row0 = i * R;
+    int row0 = i * R * chunk_stride;
     if (dyn_rows && arrived) {
       const uint32_t chunk_bytes = (uint32_t)R * (uint32_t)(wfmt == 2 ? (K >> 1) + (K >> 4) : (wfmt == 1 ? K : 2 * K));
       row0 = (int)((sh->ring[(q.head + (unsigned)i) % kQ].address - dyn_base) / chunk_bytes) * R;

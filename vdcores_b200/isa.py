@@ -38,6 +38,7 @@ GEMV_DYN_BIT = _defs["GEMV_DYN_BIT"]
 GEMV_PEERS_BIT = _defs["GEMV_PEERS_BIT"]
 GEMV_DYNROWS_BIT = _defs["GEMV_DYNROWS_BIT"]
 GEMV_PARTIAL_BIT = _defs["GEMV_PARTIAL_BIT"]
+GEMV_STRIDE_BIT = _defs["GEMV_STRIDE_BIT"]
 TC_STAGES = _defs["TC_STAGES"]
 STREAM_END = _defs["STREAM_END"]
 ATTN_QKNORM_BIT = _defs["ATTN_QKNORM_BIT"]

@@ -305,7 +305,7 @@ class Program:
              w_indirect: Optional[tuple] = None, wait_issue: Optional[int] = None, moe: Optional[dict] = None,
              dyn_count_addr: Optional[int] = None, peers: Optional[tuple] = None, shared_counter: Optional[int] = None,
              own_chunks: Optional[tuple] = None, shared_first: int = 0, shared_depth: int = 0,
-             partial_in: Optional[int] = None):
+             partial_in: Optional[int] = None, chunk_stride: int = 1):
         """y[0:n_rows] = W[0:n_rows, :K] @ x for the contiguous row block at w_addr
         (bf16; e4m3 with fp8_scales = address of the block's fp32 per-row scales;
         or NVFP4 rows — K/2 code bytes + K/16 block scales — with nvfp4_scales =
@@ -318,7 +318,9 @@ class Program:
         until the matrix is exhausted, never holding more than shared_depth unconsumed ring entries when it
         draws (0: no limit), so the SMs that finish early take the tail of the stage.
         partial_in: address of fp32 sums of the same rows over another K-range (written by an earlier STORE_F32
-        task of this SM); they are added to the task's sums before the result is rounded."""
+        task of this SM); they are added to the task's sums before the result is rounded.
+        chunk_stride s > 1: the task's chunk i is chunk i * s of the matrix that starts at w_addr (rows, outputs
+        and scales likewise): the chunks of a stage dealt round-robin to s SMs; n_rows counts the task's own rows."""
         assert fp8_scales is None or nvfp4_scales is None
         if nvfp4_scales is not None:
             row_bytes, kmult, op, scales = K // 2 + K // 16, 1024, isa.OP_GEMV_ROWS_NVFP4, nvfp4_scales
@@ -375,7 +377,7 @@ class Program:
                      address=w_addr + shared_first * chunk_bytes)
             self.bytes_loaded[sm] += chunk_bytes * (own_n + n_shared // max(1, self.num_sms))
         else:
-            self.repeat(sm, n_chunks, [chunk_bytes], dynamic=dyn_count_addr is not None)
+            self.repeat(sm, n_chunks, [chunk_bytes * chunk_stride], dynamic=dyn_count_addr is not None)
             self.mem(sm, isa.OP_ALLOC_TMA_LOAD_1D_STREAM if stream else isa.OP_ALLOC_TMA_LOAD_1D, size=chunk_bytes,
                      nslot=slots_for(chunk_bytes), address=w_addr, flags=isa.F_JUMP)
             self.bytes_loaded[sm] += chunk_bytes * n_chunks
@@ -383,7 +385,8 @@ class Program:
         a1 = R | (mode << 8) | (isa.GEMV_NORM_BIT if norm_w is not None else 0) | \
             (isa.GEMV_ACC_BIT if out.kind == "add_bf16" else 0) | (isa.GEMV_DYN_BIT if dyn_count_addr is not None else 0) | \
             (isa.GEMV_PEERS_BIT if peers is not None else 0) | (isa.GEMV_DYNROWS_BIT if shared_counter is not None else 0) | \
-            (isa.GEMV_PARTIAL_BIT if partial_in is not None else 0)
+            (isa.GEMV_PARTIAL_BIT if partial_in is not None else 0) | (isa.GEMV_STRIDE_BIT if chunk_stride > 1 else 0)
+        assert chunk_stride == 1 or (shared_counter is None and moe is None and peers is None and 1 < chunk_stride <= 0xFFFF)
         a2 = (K // 256) | ((rb8 >> 16) << 8)
         e = f32_bits(eps)
         if moe is not None:
@@ -399,6 +402,8 @@ class Program:
         if scales is not None:
             assert scales % 4 == 0 and 0 <= scales < 1 << 48
             self.comp(sm, isa.OP_EXT, scales & 0xFFFF, (scales >> 16) & 0xFFFF, (scales >> 32) & 0xFFFF)
+        if chunk_stride > 1:
+            self.comp(sm, isa.OP_EXT, chunk_stride, 0, 0)
         if partial_in is not None:
             assert moe is None and partial_in % 4 == 0 and 0 < partial_in < 1 << 48
             self.comp(sm, isa.OP_EXT, partial_in & 0xFFFF, (partial_in >> 16) & 0xFFFF, (partial_in >> 32) & 0xFFFF)
