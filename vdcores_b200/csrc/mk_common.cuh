@@ -191,10 +191,10 @@ struct __align__(16) Shared {
   volatile unsigned pf_window;              // bytes the frontier may run ahead
   volatile int pf_go, pf_exit;
   uint32_t pt_words[32];                    // control warp: the table words PT_LOAD32 fetched (page loop)
-  volatile int pop_val[2];
-  volatile uint32_t pop_meta[2];
-  volatile uint32_t pop_size[2];
-  volatile uint64_t pop_addr[2];
+  volatile int pop_val[8];                  // what thread 0 read for the CTA-wide pops (entry index mod 8)
+  volatile uint32_t pop_meta[8];
+  volatile uint32_t pop_size[8];
+  volatile uint64_t pop_addr[8];
   volatile int pair_ok[4][2][2];            // GEMV warp pairs: [pair][trip parity][member] chunk arrived
   int att_done[8];                          // attention: warps finished with page pair i % 8
   alignas(16) float red[4096 + 64];                     // task scratch (reductions)

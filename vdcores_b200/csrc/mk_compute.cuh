@@ -34,6 +34,7 @@ struct Compute {
   unsigned mma_count;  // tensor-core commits issued so far (thread 0)
   unsigned xr_count;   // X chunks normalised by earlier tensor-core tasks (phase of the x_ready barriers)
   unsigned wr_count;   // W chunks converted by earlier tensor-core tasks (phase of the w_ready barriers)
+  int batch = 0;       // size of the last pop_many
 #ifdef VDC_TRACE_GEMV
   unsigned gemv_ord = 0;
 #endif
@@ -51,24 +52,57 @@ struct Compute {
         ok = wait_until(c, [&] { return mbar_try_wait(bar, parity); }, 0, (int)pc, 0, -1, 0);
         stall += (uint64_t)(clock64() - t0);
       }
-      sh->pop_val[head & 1u] = ok ? sh->ring_word[e] : kPopAbort;
-      sh->pop_addr[head & 1u] = sh->ring[e].address;
-      sh->pop_meta[head & 1u] = (uint32_t)sh->ring[e].opcode | ((uint32_t)sh->ring[e].num_slots << 16);
-      sh->pop_size[head & 1u] = sh->ring[e].size;
+      sh->pop_val[head & 7u] = ok ? sh->ring_word[e] : kPopAbort;
+      sh->pop_addr[head & 7u] = sh->ring[e].address;
+      sh->pop_meta[head & 7u] = (uint32_t)sh->ring[e].opcode | ((uint32_t)sh->ring[e].num_slots << 16);
+      sh->pop_size[head & 7u] = sh->ring[e].size;
       if (!ok) sh->aborted = 1;
       __threadfence_block();
       sh->cta_head = head + 1;
     }
     compute_sync();
-    const int v = sh->pop_val[head & 1u];
+    const int v = sh->pop_val[head & 7u];
     head++;
     if (v == kPopAbort) aborted = true;
     return v;
   }
+  // The next n (<= 4) entries in one go: thread 0 waits for each, one CTA barrier publishes them all.  Entry j of
+  // the batch is then read with val_at / addr_at / meta_at(j).  A task that takes several operands pays one
+  // barrier instead of one per operand.
+  __device__ __forceinline__ void pop_many(int n) {
+    if (tid == 0) {
+      for (int j = 0; j < n; ++j) {
+        const unsigned idx = head + (unsigned)j, e = idx % kQ;
+        const uint32_t parity = (idx / kQ) & 1u;
+        uint64_t* bar = &sh->full[e];
+        bool ok = mbar_try_wait(bar, parity);
+        if (!ok) {
+          const long long t0 = clock64();
+          ok = wait_until(c, [&] { return mbar_try_wait(bar, parity); }, 0, (int)pc, 0, -1, 0);
+          stall += (uint64_t)(clock64() - t0);
+        }
+        sh->pop_val[idx & 7u] = ok ? sh->ring_word[e] : kPopAbort;
+        sh->pop_addr[idx & 7u] = sh->ring[e].address;
+        sh->pop_meta[idx & 7u] = (uint32_t)sh->ring[e].opcode | ((uint32_t)sh->ring[e].num_slots << 16);
+        sh->pop_size[idx & 7u] = sh->ring[e].size;
+        if (!ok) sh->aborted = 1;
+      }
+      __threadfence_block();
+      sh->cta_head = head + (unsigned)n;
+    }
+    compute_sync();
+    for (int j = 0; j < n; ++j)
+      if (sh->pop_val[(head + (unsigned)j) & 7u] == kPopAbort) aborted = true;
+    head += (unsigned)n;
+    batch = n;
+  }
+  __device__ __forceinline__ int val_at(int j) const { return sh->pop_val[(head - (unsigned)batch + (unsigned)j) & 7u]; }
+  __device__ __forceinline__ uint64_t addr_at(int j) const { return sh->pop_addr[(head - (unsigned)batch + (unsigned)j) & 7u]; }
+  __device__ __forceinline__ uint32_t meta_at(int j) const { return sh->pop_meta[(head - (unsigned)batch + (unsigned)j) & 7u]; }
   // Address / (opcode | num_slots << 16) of the instruction behind the last pop.
-  __device__ __forceinline__ uint64_t addr() const { return sh->pop_addr[(head - 1u) & 1u]; }
-  __device__ __forceinline__ uint32_t meta() const { return sh->pop_meta[(head - 1u) & 1u]; }
-  __device__ __forceinline__ uint32_t size() const { return sh->pop_size[(head - 1u) & 1u]; }
+  __device__ __forceinline__ uint64_t addr() const { return sh->pop_addr[(head - 1u) & 7u]; }
+  __device__ __forceinline__ uint32_t meta() const { return sh->pop_meta[(head - 1u) & 7u]; }
+  __device__ __forceinline__ uint32_t size() const { return sh->pop_size[(head - 1u) & 7u]; }
   // CTA-wide wait on a global barrier by the compute core itself (thread 0 polls; the data it
   // orders is then read with ordinary loads).  Returns false once a wait was given up.
   __device__ __forceinline__ bool wait_barrier(int bar, int opcode) {
@@ -454,20 +488,23 @@ VDC_TASK void task_gemv_rows(Compute& q, int n_chunks, int mode, bool accumulate
 #define GEMV_STAMP(i)
 #endif
   GEMV_STAMP(0);
+  // operands: [norm weights], activation vector, output (raw address), [argmax record (raw address)]
+  q.pop_many((norm ? 1 : 0) + 2 + (mode == VDC_GEMV_MODE_ARGMAX ? 1 : 0));
+  int k_op = 0;
   int normw_mask = 0;
-  if (norm) normw_mask = q.pop();
-  const int x_mask = q.pop();
-  const uint32_t x_meta = q.meta();
-  const uint64_t x_addr = q.addr();
-  q.pop();  // output vector: raw address
-  __nv_bfloat16* outg = reinterpret_cast<__nv_bfloat16*>(q.addr());
-  const uint32_t out_meta = q.meta();
+  if (norm) normw_mask = q.val_at(k_op++);
+  const int x_mask = q.val_at(k_op);
+  const uint32_t x_meta = q.meta_at(k_op);
+  const uint64_t x_addr = q.addr_at(k_op);
+  ++k_op;
+  __nv_bfloat16* outg = reinterpret_cast<__nv_bfloat16*>(q.addr_at(k_op));
+  const uint32_t out_meta = q.meta_at(k_op);
+  ++k_op;
   float* recg = nullptr;
   uint32_t rec_meta = 0;
   if (mode == VDC_GEMV_MODE_ARGMAX) {
-    q.pop();  // candidate record: raw address
-    recg = reinterpret_cast<float*>(q.addr());
-    rec_meta = q.meta();
+    recg = reinterpret_cast<float*>(q.addr_at(k_op));
+    rec_meta = q.meta_at(k_op);
   }
   if (dyn) {
     // the count word was written by another SM; this hand-over was published only after the
