@@ -150,6 +150,22 @@ int vdc_launch_static(int num_sms, int insts_per_sm, const void* compute_insts, 
                       const void* tma_descs, const int* bars_init, uint64_t stream, uint64_t timeout_ns,
                       vdc_status* status);
 
+/* Host-side check of a program before it is uploaded: walks every SM's compute
+ * and memory stream in HOST memory (the arrays vdc_launch takes, before the copy
+ * to the device) and rejects what the kernel could only report after a launch:
+ * an unknown opcode, a multi-word instruction whose continuation words are
+ * missing or run past the stream, a GEMV with an unsupported rows-per-chunk
+ * count, a slot request or special slot id out of range, a loop that does not jump
+ * backwards, a stream without its terminator.  Touches no GPU state.  On a
+ * finding returns VDC_ERR_BAD_OPCODE or VDC_ERR_ARG, writes the SM and the
+ * instruction index to *bad_sm / *bad_pc (either may be null) and leaves a
+ * sentence in vdc_last_error().
+ * Replaces: the only checks the reference makes before a launch, the stream
+ * lengths asserted against max_insts (python/dae/launcher.py:67-68); it has no
+ * check of the instruction words themselves. */
+int vdc_validate_streams(int num_sms, int insts_per_sm, const void* compute_insts_host, const void* memory_insts_host,
+                         int* bad_sm, int* bad_pc);
+
 /* Text of the last CUDA error seen by this library on the calling thread. */
 const char* vdc_last_error(void);
 

@@ -59,3 +59,67 @@ def test_argument_errors_without_a_gpu():
     rc = lib.vdc_build_tma_desc(buf, ctypes.c_void_p(4096), 2, 7, shape, None, box, es, 0, 0)
     assert rc == isa.ERR_ARG
     assert lib.vdc_config(b"no_such_key") == -1
+
+
+def _small_program():
+    from vdcores_b200 import isa
+    from vdcores_b200.program import Dst, Program, Src
+    P = Program(2)
+    b = P.new_barrier()
+    P.copy(1, Src(1 << 22, 1024), Dst(1 << 20, 1024, release=b), 1024)
+    P.gemv(0, w_addr=1 << 30, n_rows=64, K=512, R=16, x=Src(1 << 20, 1024, wait=b),
+           out=Dst(1 << 21, 128, "store"), fp8_scales=1 << 24, chunk_stride=2)
+    P.insts_per_sm = 64
+    return P, isa
+
+
+def test_validate_streams_accepts_emitted_programs_and_names_what_is_wrong():
+    """vdc_validate_streams walks host copies of both streams: what Program emits passes; an unknown opcode,
+    a truncated multi-word instruction, a bad rows-per-chunk count, a forward loop and a missing terminator
+    are each reported with the SM and the instruction index."""
+    import numpy as np
+    from vdcores_b200 import runtime
+    from vdcores_b200.program import CINST, MINST
+    P, isa = _small_program()
+    c, m, _ = P.finalize()                      # runs the check itself
+    runtime.validate_streams(2, 64, c, m)
+    n_c0 = len(P.c[0])
+
+    def broken(edit):
+        cc, mm = c.copy().view(CINST).reshape(2, 64), m.copy().view(MINST).reshape(2, 64)
+        edit(cc, mm)
+        return cc.view(np.uint8).reshape(-1, 8), mm.view(np.uint8).reshape(-1, 16)
+
+    def set_op(arr, sm, pc, op):
+        if pc < 0:                                   # from the terminator to the end of the stream
+            arr[sm, -pc:][arr.dtype.names[0]] = op
+        else:
+            arr[sm, pc][arr.dtype.names[0]] = op
+
+    cases = [
+        (lambda cc, mm: set_op(cc, 0, 0, 0x7999), r"compute stream of SM 0, instruction 0 .*unknown opcode"),
+        (lambda cc, mm: set_op(cc, 0, 2, isa.OP_DUMMY), r"compute stream of SM 0, instruction 2 .*continuation word expected"),
+        (lambda cc, mm: set_op(cc, 0, -(n_c0 - 1), isa.OP_DUMMY), r"compute stream of SM 0.*no TERMINATEC"),
+        (lambda cc, mm: set_op(mm, 1, 0, 60 << 6), r"memory stream of SM 1, instruction 0 .*unknown opcode"),
+        (lambda cc, mm: set_op(mm, 1, -(len(P.m[1]) - 1), isa.OP_ISSUE_BARRIER), r"memory stream of SM 1.*no TERMINATE"),
+    ]
+    for edit, pattern in cases:
+        cc, mm = broken(edit)
+        with pytest.raises(ValueError, match=pattern):
+            runtime.validate_streams(2, 64, cc, mm)
+    # rows per chunk: the low five bits of the flags word
+    cc, mm = broken(lambda cc, mm: None)
+    v = cc.view(CINST).reshape(2, 64)
+    name1 = v.dtype.names[2]
+    v[0, 0][name1] = (int(v[0, 0][name1]) & ~31) | 3
+    with pytest.raises(ValueError, match="rows per chunk"):
+        runtime.validate_streams(2, 64, v.view(np.uint8).reshape(-1, 8), mm)
+    with pytest.raises(ValueError, match="num_sms \\* insts_per_sm"):
+        runtime.validate_streams(3, 64, c, m)
+
+
+def test_finalize_rejects_a_malformed_program_on_the_host():
+    P, isa = _small_program()
+    P.comp(0, 0x7999, 0, 0, 0)
+    with pytest.raises(ValueError, match="unknown opcode"):
+        P.finalize()

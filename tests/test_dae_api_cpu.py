@@ -83,3 +83,16 @@ def test_family_names_and_errors(D):
                  "OP_ROPE_INTERLEAVE_512", "OP_SILU_MUL_SHARED_BF16_K_64_SW128", "OP_ARGMAX_PARTIAL_bf16_1024_65536_128",
                  "OP_COPY", "OP_DUMMY", "OP_LOOPC", "OP_TERMINATEC"):
         assert hasattr(opcode, name) and name in supported_compute_ops
+
+
+def test_library_validator_accepts_the_reference_built_streams():
+    """The streams the reference's own Launcher wrote for the golden program (loops, groups, late barriers,
+    argmax) pass the C-ABI's host-side walk of the instruction words."""
+    from vdcores_b200 import runtime
+    z = np.load(os.path.join(os.path.dirname(__file__), "golden", "dae_api.npz"))
+    S = len(z["launcher_ptrs"].view(np.int64)) // 2
+    c, m = z["launcher_cinsts"].reshape(S, -1, 8), z["launcher_minsts"].reshape(S, -1, 16)
+    N = 64
+    cc, mm = np.zeros((S, N, 8), np.uint8), np.zeros((S, N, 16), np.uint8)
+    cc[:, :c.shape[1]], mm[:, :m.shape[1]] = c, m
+    runtime.validate_streams(S, N, cc.reshape(-1, 8), mm.reshape(-1, 16))

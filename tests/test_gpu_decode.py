@@ -14,9 +14,12 @@ REL_L2_BF16 = 1e-2
 GAP = 1e-2
 
 
-@pytest.mark.parametrize("kind,prompt_len,n_steps", [("llama", 70, 6), ("qwen3", 130, 4), ("llama", 1, 3),
-                                                     ("moe", 70, 4)])
-def test_decode_matches_oracle(cuda_device, kind, prompt_len, n_steps):
+@pytest.mark.parametrize("kind,prompt_len,n_steps,num_sms", [("llama", 70, 6, None), ("qwen3", 130, 4, None),
+                                                             ("llama", 1, 3, None), ("moe", 70, 4, None),
+                                                             ("llama", 70, 3, 61), ("qwen3", 130, 2, 132)])
+def test_decode_matches_oracle(cuda_device, kind, prompt_len, n_steps, num_sms):
+    """num_sms: the program planned for fewer SMs than the device has (61: an odd count that divides nothing;
+    132: the reference's SM count) — the planner deals every stage to whatever count it is given."""
     from vdcores_b200.decode import DecodeEngine
     cfg = small_cfg(kind)
     w = perturb_norms(O.ModelWeights.random(cfg, seed=3))
@@ -29,7 +32,7 @@ def test_decode_matches_oracle(cuda_device, kind, prompt_len, n_steps):
         _, first, _ = orc.prefill(prompt[:-1].tolist())
     # the device decodes the last prompt token first, exactly like the oracle's next step
     eng = DecodeEngine(engine_config(cfg), max_seq=256, device=cuda_device, taps=True, page_perm_seed=5,
-                       timeout_ns=500_000_000)
+                       timeout_ns=500_000_000, num_sms=num_sms)
     eng.load_weights(dense_weights(w))
     eng.load_kv([k[:prompt_len - 1] for k in orc.k], [v[:prompt_len - 1] for v in orc.v])
     tok = int(prompt[-1])

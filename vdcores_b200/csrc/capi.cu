@@ -36,12 +36,13 @@ struct OpEntry {
   const char* name;
   int value;
   int is_compute;
+  int words;   // 8-byte words of a compute instruction before its optional trailing words
 };
 const OpEntry kOps[] = {
-#define X(name, value) {#name, (int)(value), 0},
+#define X(name, value) {#name, (int)(value), 0, 0},
     VDC_MEMORY_OPS(X)
 #undef X
-#define X(name, value, words) {#name, (int)(value), 1},
+#define X(name, value, words) {#name, (int)(value), 1, words},
         VDC_COMPUTE_OPS(X)
 #undef X
 };
@@ -316,6 +317,90 @@ int vdc_opcode_count(void) { return kNumOps; }
 const char* vdc_opcode_name(int i) { return (i >= 0 && i < kNumOps) ? kOps[i].name : nullptr; }
 int vdc_opcode_value(int i) { return (i >= 0 && i < kNumOps) ? kOps[i].value : -1; }
 int vdc_opcode_is_compute(int i) { return (i >= 0 && i < kNumOps) ? kOps[i].is_compute : 0; }
+
+namespace {
+const OpEntry* find_op(int value, int is_compute) {
+  for (int i = 0; i < kNumOps; ++i)
+    if (kOps[i].is_compute == is_compute && kOps[i].value == value) return &kOps[i];
+  return nullptr;
+}
+int fail_stream(int code, const char* stream, int sm, int pc, int opcode, const char* what, int* bad_sm, int* bad_pc) {
+  static thread_local char msg[160];
+  snprintf(msg, sizeof msg, "%s stream of SM %d, instruction %d (opcode 0x%04x): %s", stream, sm, pc, opcode, what);
+  g_err = msg;
+  if (bad_sm) *bad_sm = sm;
+  if (bad_pc) *bad_pc = pc;
+  return code;
+}
+}  // namespace
+
+int vdc_validate_streams(int num_sms, int insts_per_sm, const void* compute_insts_host, const void* memory_insts_host,
+                         int* bad_sm, int* bad_pc) {
+  if (bad_sm) *bad_sm = -1;
+  if (bad_pc) *bad_pc = -1;
+  if (num_sms <= 0 || num_sms > VDC_MAX_SMS) return fail_arg("num_sms out of range");
+  if (insts_per_sm <= 0 || insts_per_sm > VDC_MAX_INSTS) return fail_arg("insts_per_sm out of range");
+  if (!compute_insts_host || !memory_insts_host) return fail_arg("null instruction stream");
+  const VdcCInst* C = static_cast<const VdcCInst*>(compute_insts_host);
+  const VdcMInst* M = static_cast<const VdcMInst*>(memory_insts_host);
+  for (int sm = 0; sm < num_sms; ++sm) {
+    // compute stream: walk instruction by instruction (the counts of the table plus the trailing words the
+    // flags of the first word announce), until TERMINATEC
+    const VdcCInst* c = C + (size_t)sm * insts_per_sm;
+    bool ended = false;
+    for (int pc = 0; pc < insts_per_sm;) {
+      const int op = c[pc].opcode;
+      const OpEntry* e = find_op(op, 1);
+      if (!e || op == 0x7FFF)
+        return fail_stream(VDC_ERR_BAD_OPCODE, "compute", sm, pc, op, e ? "continuation word where an instruction starts" : "unknown opcode", bad_sm, bad_pc);
+      int words = e->words;
+      if (op >= 0x7200 && op <= 0x7203) {
+        const int f = c[pc].args[1], R = f & 31;
+        if (R != 1 && R != 2 && R != 4 && R != 8 && R != 16)
+          return fail_stream(VDC_ERR_ARG, "compute", sm, pc, op, "rows per chunk must be 1, 2, 4, 8 or 16", bad_sm, bad_pc);
+        words += ((f & VDC_GEMV_STRIDE_BIT) ? 1 : 0) + ((f & VDC_GEMV_PARTIAL_BIT) ? 1 : 0) +
+                 ((f & VDC_GEMV_PEERS_BIT) ? 2 : 0) + ((f & VDC_GEMV_DYNROWS_BIT) ? 1 : 0);
+      }
+      if (op == 0x7220 && c[pc].args[1] == 2) words += 2;
+      if (pc + words > insts_per_sm)
+        return fail_stream(VDC_ERR_ARG, "compute", sm, pc, op, "instruction runs past the end of the stream", bad_sm, bad_pc);
+      for (int k = 1; k < words; ++k)
+        if (c[pc + k].opcode != 0x7FFF)
+          return fail_stream(VDC_ERR_BAD_OPCODE, "compute", sm, pc + k, c[pc + k].opcode, "continuation word expected", bad_sm, bad_pc);
+      if (op == 0x7001 && c[pc].args[1] >= pc)
+        return fail_stream(VDC_ERR_ARG, "compute", sm, pc, op, "loop target is not an earlier instruction", bad_sm, bad_pc);
+      if (op == 0x7000) {
+        ended = true;
+        break;
+      }
+      pc += words;
+    }
+    if (!ended) return fail_stream(VDC_ERR_ARG, "compute", sm, insts_per_sm, 0, "no TERMINATEC", bad_sm, bad_pc);
+    // memory stream: every word is an instruction; known id, the table's ALLOCATE bit, a slot
+    // request the pool can serve, backward jumps, and a TERMINATE
+    const VdcMInst* m = M + (size_t)sm * insts_per_sm;
+    ended = false;
+    for (int pc = 0; pc < insts_per_sm; ++pc) {
+      const int op = m[pc].opcode, id = op >> VDC_FLAG_BITS;
+      const OpEntry* e = nullptr;
+      for (int i = 0; i < kNumOps && !e; ++i)
+        if (!kOps[i].is_compute && (kOps[i].value >> VDC_FLAG_BITS) == id) e = &kOps[i];
+      if (!e) return fail_stream(VDC_ERR_BAD_OPCODE, "memory", sm, pc, op, "unknown opcode", bad_sm, bad_pc);
+      if ((e->value & VDC_F_ALLOCATE) != (op & VDC_F_ALLOCATE))
+        return fail_stream(VDC_ERR_BAD_OPCODE, "memory", sm, pc, op, "ALLOCATE flag does not fit the opcode", bad_sm, bad_pc);
+      if ((op & VDC_F_ALLOCATE) && (m[pc].num_slots & 63) >= VDC_NUM_SLOTS + VDC_NUM_SPECIAL_SLOTS)
+        return fail_stream(VDC_ERR_ARG, "memory", sm, pc, op, "slot request or special slot id out of range", bad_sm, bad_pc);
+      if (id == 3 && m[pc].coords[0] >= pc)
+        return fail_stream(VDC_ERR_ARG, "memory", sm, pc, op, "loop target is not an earlier instruction", bad_sm, bad_pc);
+      if (id == 1) {
+        ended = true;
+        break;
+      }
+    }
+    if (!ended) return fail_stream(VDC_ERR_ARG, "memory", sm, insts_per_sm, 0, "no TERMINATE", bad_sm, bad_pc);
+  }
+  return VDC_OK;
+}
 
 int64_t vdc_config(const char* name) {
   if (!name) return -1;

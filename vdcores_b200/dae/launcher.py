@@ -310,6 +310,7 @@ class Launcher:
         unbound = [b for b, v in self.bar_values.items() if v is None]
         if unbound:
             raise ValueError(f"Cannot launch with unbound barrier counts: {unbound}")
+        runtime.validate_streams(self.num_sms, self.max_insts, self.cinsts.numpy(), self.minsts.numpy())
         cinsts = self.cinsts.to(self.device).view(self.num_sms * self.max_insts, 8)
         minsts = self.minsts.to(self.device).view(self.num_sms * self.max_insts, 16)
         stream = torch.cuda.current_stream().cuda_stream

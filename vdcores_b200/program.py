@@ -633,9 +633,13 @@ class Program:
         self.comp(sm, isa.OP_ARGMAX_FINAL, n, 1 if local_only else 0)
 
     # ------------------------------------------------------------------ output
-    def finalize(self):
+    def finalize(self, check: bool = True):
         """Appends the terminators and returns (compute u8[S*N,8], memory
-        u8[S*N,16], bars int32[MAX_BARS]) as numpy arrays."""
+        u8[S*N,16], bars int32[MAX_BARS]) as numpy arrays.  With `check` the
+        streams go through the library's own walk of the instruction words
+        (runtime.validate_streams) first, so that a malformed program raises
+        here, on the host, instead of ending a launch with a device-side status.
+        (validate() adds the checks that need the whole program: barriers and sizes.)"""
         if not self._finalized:
             for sm in range(self.num_sms):
                 self.mem(sm, isa.OP_TERMINATE)
@@ -655,7 +659,11 @@ class Program:
         bars = np.zeros(isa.MAX_BARS, dtype=np.int32)
         for b, cnt in self.bar_counts.items():
             bars[b] = cnt
-        return (cm.view(np.uint8).reshape(self.num_sms * n, 8), mm.view(np.uint8).reshape(self.num_sms * n, 16), bars)
+        c8, m8 = cm.view(np.uint8).reshape(self.num_sms * n, 8), mm.view(np.uint8).reshape(self.num_sms * n, 16)
+        if check:
+            from . import runtime
+            runtime.validate_streams(self.num_sms, n, c8, m8)
+        return c8, m8, bars
 
     def validate(self):
         """Static checks of the streams before they go to the device; raises ValueError.

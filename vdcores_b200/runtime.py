@@ -63,12 +63,14 @@ _lib.vdc_config.restype = ctypes.c_int64
 _lib.vdc_config.argtypes = [ctypes.c_char_p]
 _lib.vdc_family_specs.restype = ctypes.c_char_p
 _lib.vdc_last_error.restype = ctypes.c_char_p
+_lib.vdc_validate_streams.argtypes = [_i32, _i32, _vp, _vp, ctypes.POINTER(_i32), ctypes.POINTER(_i32)]
+_lib.vdc_validate_streams.restype = _i32
 
 EXPORTED_SYMBOLS = [
     "vdc_version", "vdc_init", "vdc_set_smem_size", "vdc_launch", "vdc_launch_async", "vdc_launch_static",
     "vdc_read_status",
     "vdc_build_tma_desc", "vdc_set_cache_policy", "vdc_enable_peer_access", "vdc_ipc_open", "vdc_ipc_close", "vdc_peer_alloc", "vdc_peer_free", "vdc_ipc_export", "vdc_opcode_count", "vdc_opcode_name", "vdc_opcode_value",
-    "vdc_opcode_is_compute", "vdc_config", "vdc_family_specs", "vdc_last_error",
+    "vdc_opcode_is_compute", "vdc_config", "vdc_family_specs", "vdc_last_error", "vdc_validate_streams",
 ]
 
 
@@ -147,6 +149,22 @@ def launch_dae(num_sms, smem_size, compute_insts, memory_insts, tma_descs, bars,
                          _ptr(bars), _ptr(profile), int(stream), int(timeout_ns), ctypes.byref(st))
     _check(rc, st)
     return 0
+
+
+def validate_streams(num_sms, insts_per_sm, compute_insts, memory_insts):
+    """Host-side check of a program's instruction words before the upload (numpy arrays or CPU tensors of
+    num_sms * insts_per_sm 8-byte / 16-byte instructions).  Raises ValueError naming the SM, the instruction
+    and what is wrong with it; needs no GPU."""
+    import numpy as np
+    c = np.ascontiguousarray(np.asarray(compute_insts)).view(np.uint8).reshape(-1)
+    m = np.ascontiguousarray(np.asarray(memory_insts)).view(np.uint8).reshape(-1)
+    if c.size != num_sms * insts_per_sm * 8 or m.size != num_sms * insts_per_sm * 16:
+        raise ValueError("streams must hold num_sms * insts_per_sm instructions")
+    sm, pc = _i32(-1), _i32(-1)
+    rc = _lib.vdc_validate_streams(num_sms, insts_per_sm, c.ctypes.data_as(_vp), m.ctypes.data_as(_vp),
+                                   ctypes.byref(sm), ctypes.byref(pc))
+    if rc != 0:
+        raise ValueError(last_error())
 
 
 def launch_async(num_sms, insts_per_sm, compute_insts, memory_insts, tma_descs, bars, bars_init, profile,
