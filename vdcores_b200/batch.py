@@ -142,6 +142,7 @@ class BatchDecodeEngine(DecodeEngine):
     projections are bf16, e4m3 with per-row scales (wkind "fp8") or NVFP4 (wkind "nvfp4": e2m1 values, e4m3 block
     scales, fp32 tensor scale), everything else bf16."""
     GEMV_PROJECTIONS = False
+    SHARED_CACHE = False     # True: the batch rows are consecutive positions of ONE sequence (prefill.PrefillEngine)
 
     def __init__(self, cfg: DecodeConfig, batch: int, max_seq: int, device="cuda:0", num_sms=None, taps=False,
                  page_perm_seed=None, max_steps: int = 256, timeout_ns: int = 2_000_000_000, wkind: str = "bf16"):
@@ -170,6 +171,18 @@ class BatchDecodeEngine(DecodeEngine):
         self.state = z(B, self.state_words, dt=torch.int32)
         self.state_host = torch.zeros(B, self.state_words, dtype=torch.int32).pin_memory()
         self.token_log = z(B, max_steps, dt=torch.int32)
+        self._alloc_cache(page_perm_seed)
+        self.taps_enabled = taps
+        if taps:
+            assert Bp * H * 2 <= 32768, "taps copy the hidden matrix with one bulk load"
+            self.taps = z(L, Bp * H)
+        self._cur = 0
+        self.positions = [0] * B
+
+    def _alloc_cache(self, page_perm_seed):
+        """Paged pools and page tables: every sequence owns max_pages pages of one pool."""
+        cfg, B, L = self.cfg, self.batch, self.cfg.n_layers
+        z = lambda *s: torch.zeros(*s, dtype=BF16, device=self.dev)
         self.kpool = z(L, B * self.max_pages, cfg.n_kv_heads, isa.KV_PAGE, isa.HEAD_DIM)
         self.vpool = z(L, B * self.max_pages, cfg.n_kv_heads, isa.KV_PAGE, isa.HEAD_DIM)
         tables = []
@@ -180,12 +193,6 @@ class BatchDecodeEngine(DecodeEngine):
                 t = torch.randperm(self.max_pages, generator=torch.Generator().manual_seed(page_perm_seed + b)).to(torch.int32)
             tables.append(t + b * self.max_pages)
         self.page_tables = torch.stack(tables)        # [B, max_pages] global page ids
-        self.taps_enabled = taps
-        if taps:
-            assert Bp * H * 2 <= 32768, "taps copy the hidden matrix with one bulk load"
-            self.taps = z(L, Bp * H)
-        self._cur = 0
-        self.positions = [0] * B
 
     # ------------------------------------------------------------------ weights
     def weight_bytes(self) -> int:
@@ -261,13 +268,31 @@ class BatchDecodeEngine(DecodeEngine):
             units = [(b, h, s) for s in range(self.n_splits) for b in range(B) for h in range(cfg.n_kv_heads)]
             kp, vp = self.kpool[l].data_ptr(), self.vpool[l].data_ptr()
             grp = (G + 2) * D * 2
+            b_rows = None
+            if self.SHARED_CACHE:
+                # the rows of all the chunk's positions go to the pools first: position p attends to rows the
+                # tasks of positions < p write in this same launch
+                b_rows = P.new_barrier()
+                P.add_releases(b_rows, B * cfg.n_kv_heads)
+                for (b, h), sm in zip([(b, h) for b in range(B) for h in range(cfg.n_kv_heads)],
+                                      self._pick(load, B * cfg.n_kv_heads)):
+                    sb = st + 4 * sw * b
+                    P.attn_decode(
+                        sm, G=G, state_addr=sb,
+                        rope=Src(self.rope.data_ptr(), D * 4, indirect=(sb + 4 * isa.ST_POS, 9, None)),
+                        norm_w=Src(self.qknorm[l].data_ptr(), 2 * D * 2) if cfg.qk_norm else None,
+                        qkv=Src(qkv + (b * self.qkv_rows) * 2 + h * grp, grp, wait=b_qkv),
+                        k_page_addr=kp + h * page_bytes, v_page_addr=vp + h * page_bytes, page_shift=page_shift,
+                        base_page=0, max_pages=0, records_addr=0, counter_addr=0, out_addr=0, split=0, n_splits=1,
+                        release=b_rows, qk_eps=cfg.qk_norm_eps, append=True)
             for (b, h, s), sm in zip(units, self._pick(load, len(units), 2 * page_bytes * self.pages_per_split)):
                 sb = st + 4 * sw * b
                 P.attn_decode(
                     sm, G=G, state_addr=sb,
                     rope=Src(self.rope.data_ptr(), D * 4, indirect=(sb + 4 * isa.ST_POS, 9, None)),
                     norm_w=Src(self.qknorm[l].data_ptr(), 2 * D * 2) if cfg.qk_norm else None,
-                    qkv=Src(qkv + (b * self.qkv_rows) * 2 + h * grp, grp, wait=b_qkv),
+                    qkv=Src(qkv + (b * self.qkv_rows) * 2 + h * grp, grp, wait=b_qkv if b_rows is None else b_rows),
+                    wait_issue=b_rows,
                     k_page_addr=kp + h * page_bytes, v_page_addr=vp + h * page_bytes, page_shift=page_shift,
                     base_page=s * self.pages_per_split, max_pages=self.pages_per_split,
                     records_addr=self.attn_part[b, h].data_ptr(), counter_addr=self.attn_cnt[l, b, h].data_ptr(),

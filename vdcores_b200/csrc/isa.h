@@ -256,6 +256,9 @@
 // ATTN_DECODE args[2] bits
 #define VDC_ATTN_QKNORM_BIT 0x1
 #define VDC_ATTN_PACKED_BIT 0x2   // output goes to a k-chunk-major matrix; last word args[2] = b | Bpad/16 << 8
+#define VDC_ATTN_APPEND_BIT 0x4   // cache append only: the new key row (normed, rotated) and value row go to the pools, the
+                                  // task counts `release` down once and ends; no pages, no records (chunked prefill: the
+                                  // rows of a whole chunk of positions are in the pools before any of them attends)
 
 // words of the per-sequence decode state block in device memory
 #define VDC_ST_POS 0        // number of cached positions = position of the token being decoded

@@ -888,6 +888,21 @@ VDC_TASK void task_attn_decode(Compute& q, const AttnArgs& a) {
     const int t = q.tid - (kCT - D / 8);
     reinterpret_cast<uint4*>(vrow)[t ^ sw_new] = ldcg128(reinterpret_cast<const uint4*>(vnew) + t);
   }
+  if (a.flags & VDC_ATTN_APPEND_BIT) {
+    // cache append only (chunked prefill): the rows go to the pools now; the attention tasks of the chunk's
+    // positions start behind the barrier counted down here and find every row of the chunk in HBM
+    compute_sync();
+    if (q.tid >= 64 && q.tid < 64 + 2 * (D / 8)) {
+      const int t = q.tid - 64;
+      const size_t off = (size_t)ld_relaxed_gpu(a.state + VDC_ST_NEWROW) * (D * 2);
+      uint8_t* dst = (t < D / 8 ? a.k_rows : a.v_rows) + off;
+      reinterpret_cast<uint4*>(dst)[t % (D / 8)] = reinterpret_cast<const uint4*>(sh->newrows)[t];
+    }
+    __threadfence();
+    compute_sync();
+    if (q.tid == 0) red_relaxed_gpu_add(c.bars + a.bar, -1);
+    return;
+  }
   const unsigned n_ent = 2u * (unsigned)count;  // ring entries: K page, V page, K page, ...
   q.warp_phase_begin(n_ent, 0u);              // its CTA barrier also publishes qbf / krow / vrow / zero_row
   ATTN_STAMP(2);

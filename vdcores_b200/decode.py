@@ -817,6 +817,32 @@ class DecodeEngine:
         self.set_state(T, tok)
         return tok
 
+    def prefill_device(self, tokens: torch.Tensor) -> int:
+        """The prompt goes through the decode megakernel itself, one position per launch: the same program as a
+        decode step, with the next prompt id written over the step's own argmax before the next launch (an 8-byte
+        device-to-device copy on the engine's stream: {next id, step counter 0}).  No PyTorch arithmetic and no
+        host round trip inside the loop; the KV rows and the returned first generated id have exactly the decode
+        path's numerics.  Cost: one decode step per prompt position (PrefillEngine in prefill.py does 64
+        positions per launch)."""
+        T = int(tokens.numel())
+        assert 1 <= T < self.max_seq
+        forced = torch.zeros(T, 2, dtype=torch.int32)
+        forced[:T - 1, 0] = tokens[1:].to(torch.int32)
+        forced = forced.to(self.dev)
+        self.set_state(0, int(tokens[0]))
+        word = self.state[isa.ST_TOKEN:isa.ST_STEP + 1]
+        assert isa.ST_STEP == isa.ST_TOKEN + 1
+        with torch.cuda.stream(self.stream):
+            for t in range(T):
+                runtime.launch_async(self.num_sms, self.insts_per_sm, self.cinsts, self.minsts, None, self.bars,
+                                     self.bars_init, self.profile, self.stream.cuda_stream, self.timeout_ns)
+                if t + 1 < T:
+                    word.copy_(forced[t], non_blocking=True)
+        runtime.read_status(self.stream.cuda_stream)
+        tok = int(self.token_log[0])
+        self.set_state(T, tok)
+        return tok
+
     # ------------------------------------------------------------------ decode
     def step_async(self):
         """Enqueues one decode step (one kernel launch); no synchronisation."""

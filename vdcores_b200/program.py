@@ -460,7 +460,8 @@ class Program:
 
     def attn_decode(self, sm, *, G, state_addr, rope: Src, norm_w: Optional[Src], qkv: Src, k_page_addr, v_page_addr,
                     page_shift, base_page, max_pages, records_addr, counter_addr, out_addr, split, n_splits,
-                    release, qk_eps: float = 1e-6, packed: Optional[tuple] = None):
+                    release, qk_eps: float = 1e-6, packed: Optional[tuple] = None, append: bool = False,
+                    wait_issue: Optional[int] = None):
         """One (KV head, split) unit of the decode attention.  k_page_addr /
         v_page_addr: this head's rows inside page 0 of the layer's K / V pool;
         the page table in the state block selects the page.  The unit that
@@ -468,8 +469,13 @@ class Program:
         writes G*128 bf16 to out_addr and counts `release` down once (declare it
         with add_releases(release, 1) per head).  packed=(b, Bpad): out_addr is the
         head's first k group inside a k-chunk-major [Bpad, q_width] matrix and the
-        outputs go to its row b (batched decode)."""
+        outputs go to its row b (batched decode).  append: the unit only writes the new key / value rows to the
+        pools and counts `release` down (max_pages must be 0).  wait_issue: the page loads are not issued before
+        this barrier opens (pages that tasks of the same launch are still writing: chunked prefill)."""
         page_bytes = isa.KV_PAGE * isa.HEAD_DIM * 2
+        assert not append or max_pages == 0
+        if wait_issue is not None and max_pages:
+            self.mem(sm, isa.OP_ISSUE_BARRIER, bar=wait_issue)
         assert qkv.nbytes == (G + 2) * isa.HEAD_DIM * 2 and qkv.addr % 16 == 0 and qkv.indirect is None
         # the rope row is table + position * 512 bytes: the task reads the position from the state block itself
         assert rope.indirect is None or (rope.indirect[0] == state_addr + 4 * isa.ST_POS and rope.indirect[1] == 9)
@@ -489,7 +495,8 @@ class Program:
         self.bytes_loaded[sm] += 2 * page_bytes * max_pages
         e = f32_bits(qk_eps)
         op = isa.OP_ATTN_DECODE_PAGED_G4 if G == 4 else isa.OP_ATTN_DECODE_PAGED_G8
-        flags = (isa.ATTN_QKNORM_BIT if norm_w is not None else 0) | (isa.ATTN_PACKED_BIT if packed else 0)
+        flags = ((isa.ATTN_QKNORM_BIT if norm_w is not None else 0) | (isa.ATTN_PACKED_BIT if packed else 0) |
+                 (isa.ATTN_APPEND_BIT if append else 0))
         self.comp(sm, op, max_pages, base_page, flags)
         self.comp(sm, isa.OP_EXT, e >> 16, e & 0xFFFF, n_splits)
         a48 = lambda a: (a & 0xFFFF, (a >> 16) & 0xFFFF, (a >> 32) & 0xFFFF)
