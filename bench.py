@@ -198,6 +198,7 @@ def run_gpu(args):
     max_seq = ((PROMPT_LEN + max(W + K, 32) + 8 + 63) // 64) * 64      # 32: steps of the sharded engines' agreement check
     g = torch.Generator().manual_seed(0)
     prompt = torch.randint(0, cfg.vocab, (PROMPT_LEN,), generator=g)
+    prefill_info = {"impl": "PyTorch ops (library GEMMs)", "prompt_tokens": PROMPT_LEN}
     if world == 1 and args.batch > 1:
         # batched decode: the projections run on the tensor cores, one state block per sequence
         from vdcores_b200.batch import BatchDecodeEngine
@@ -209,7 +210,22 @@ def run_gpu(args):
     elif world == 1:
         eng = DecodeEngine(cfg, max_seq=max_seq, device=dev, max_steps=W + K + 8, wkind=args.wkind)
         eng.init_random_weights(seed=0)
-        first = eng.prefill(prompt)
+        if args.prefill == "device" and args.wkind == "bf16" and not cfg.n_experts:
+            # the prompt goes through the megakernel too: 128 positions per launch into this engine's own pools
+            from vdcores_b200.prefill import PrefillEngine
+            pre = PrefillEngine(eng, chunk=128).adopt_weights()
+            pre.prefill(prompt)                          # first call: one-time set-up of the kernel
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            first = pre.prefill(prompt)
+            torch.cuda.synchronize()
+            dt = time.perf_counter() - t0
+            prefill_info = {"impl": "megakernel, 128 prompt positions per launch", "prompt_tokens": PROMPT_LEN,
+                            "ms": dt * 1e3, "tokens_per_s": PROMPT_LEN / dt, "launches": (PROMPT_LEN + 127) // 128}
+            del pre
+            torch.cuda.empty_cache()
+        else:
+            first = eng.prefill(prompt)
         tokens_per_step, scaling, parallelism = 1, "strong", "single GPU"
     else:
         # tensor parallel: every rank builds the same full model (same seed), prefills it with the
@@ -360,6 +376,7 @@ def run_gpu(args):
                  "h2d_bytes_per_step": 4 * tokens_per_step, "d2h_bytes_per_step": 4 * tokens_per_step}
                 if not args.no_e2e else None),
         "gpu_launches": K * eng.launches_per_step,
+        "prefill": prefill_info,      # untimed set-up of the decode measurement; reported for the time to first token
         # greedy ids of the sharded engine, fed the single-GPU engine's ids, against that engine's next ids: true when
         # they agree on every step whose two best single-GPU logits are more than a near-tie apart
         **({"tokens_match_single_gpu": tf["disagree_beyond_near_ties"] == 0, "teacher_forced": tf} if tf else {}),
@@ -387,6 +404,8 @@ def main():
                     help="sequences decoded in lock-step (> 1: tensor-core projections, bf16, one GPU)")
     ap.add_argument("--tp-impl", default="fused", choices=["fused", "nccl"],
                     help="N > 1, dense models: exchange inside the kernel (peer stores) or NCCL collectives between launches")
+    ap.add_argument("--prefill", default="device", choices=["device", "torch"],
+                    help="single GPU, batch 1, bf16 dense: prompt through the megakernel (device) or PyTorch ops (torch)")
     ap.add_argument("--layers", type=int, default=32,
                     help="profiling only: a model with fewer layers of the same shape (the JSON line says so)")
     args = ap.parse_args()

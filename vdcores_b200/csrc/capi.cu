@@ -339,7 +339,9 @@ int vdc_validate_streams(int num_sms, int insts_per_sm, const void* compute_inst
   if (bad_sm) *bad_sm = -1;
   if (bad_pc) *bad_pc = -1;
   if (num_sms <= 0 || num_sms > VDC_MAX_SMS) return fail_arg("num_sms out of range");
-  if (insts_per_sm <= 0 || insts_per_sm > VDC_MAX_INSTS) return fail_arg("insts_per_sm out of range");
+  // VDC_MAX_INSTS is the ring the reference fixes; the native engines size theirs to the program, and the only
+  // limit of the wire format is the 16-bit jump target
+  if (insts_per_sm <= 0 || insts_per_sm > 65536) return fail_arg("insts_per_sm out of range");
   if (!compute_insts_host || !memory_insts_host) return fail_arg("null instruction stream");
   const VdcCInst* C = static_cast<const VdcCInst*>(compute_insts_host);
   const VdcMInst* M = static_cast<const VdcMInst*>(memory_insts_host);
