@@ -210,22 +210,7 @@ def run_gpu(args):
     elif world == 1:
         eng = DecodeEngine(cfg, max_seq=max_seq, device=dev, max_steps=W + K + 8, wkind=args.wkind)
         eng.init_random_weights(seed=0)
-        if args.prefill == "device" and args.wkind == "bf16" and not cfg.n_experts:
-            # the prompt goes through the megakernel too: 128 positions per launch into this engine's own pools
-            from vdcores_b200.prefill import PrefillEngine
-            pre = PrefillEngine(eng, chunk=128).adopt_weights()
-            pre.prefill(prompt)                          # first call: one-time set-up of the kernel
-            torch.cuda.synchronize()
-            t0 = time.perf_counter()
-            first = pre.prefill(prompt)
-            torch.cuda.synchronize()
-            dt = time.perf_counter() - t0
-            prefill_info = {"impl": "megakernel, 128 prompt positions per launch", "prompt_tokens": PROMPT_LEN,
-                            "ms": dt * 1e3, "tokens_per_s": PROMPT_LEN / dt, "launches": (PROMPT_LEN + 127) // 128}
-            del pre
-            torch.cuda.empty_cache()
-        else:
-            first = eng.prefill(prompt)
+        first, prefill_info = run_prefill(eng, prompt, args.prefill == "device" and not cfg.n_experts)
         tokens_per_step, scaling, parallelism = 1, "strong", "single GPU"
     else:
         # tensor parallel: every rank builds the same full model (same seed), prefills it with the
@@ -234,7 +219,7 @@ def run_gpu(args):
         N_CHECK = 32
         full = DecodeEngine(cfg, max_seq=max_seq, device=dev, max_steps=max(W + K, N_CHECK) + 8)
         full.init_random_weights(seed=0)
-        first = full.prefill(prompt)
+        first, prefill_info = run_prefill(full, prompt, False)
         # dense models: one launch per step and rank, the partial sums cross NVLink as peer stores inside the
         # kernel; mixture-of-experts models (and --tp-impl nccl): two launches per layer around NCCL collectives
         fused = args.tp_impl == "fused" and not cfg.n_experts
@@ -388,6 +373,27 @@ def run_gpu(args):
     print(json.dumps(line))
 
 
+def run_prefill(eng, prompt, on_device):
+    """Fills eng's KV pools with the prompt and returns (first generated id, what ran and how long it took)."""
+    import torch
+    T = int(prompt.numel())
+    if not on_device:
+        return eng.prefill(prompt), {"impl": "PyTorch ops (library GEMMs)", "prompt_tokens": T}
+    # the prompt goes through the megakernel too: 128 positions per launch into this engine's own pools
+    from vdcores_b200.prefill import PrefillEngine
+    pre = PrefillEngine(eng, chunk=128).adopt_weights()
+    pre.prefill(prompt)                          # first call: one-time set-up of the kernel
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    first = pre.prefill(prompt)
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    del pre
+    torch.cuda.empty_cache()
+    return first, {"impl": "megakernel, 128 prompt positions per launch", "prompt_tokens": T, "ms": dt * 1e3,
+                   "tokens_per_s": T / dt, "launches": (T + 127) // 128}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -405,7 +411,7 @@ def main():
     ap.add_argument("--tp-impl", default="fused", choices=["fused", "nccl"],
                     help="N > 1, dense models: exchange inside the kernel (peer stores) or NCCL collectives between launches")
     ap.add_argument("--prefill", default="device", choices=["device", "torch"],
-                    help="single GPU, batch 1, bf16 dense: prompt through the megakernel (device) or PyTorch ops (torch)")
+                    help="batch 1, dense models: prompt through the megakernel (device) or PyTorch ops (torch)")
     ap.add_argument("--layers", type=int, default=32,
                     help="profiling only: a model with fewer layers of the same shape (the JSON line says so)")
     args = ap.parse_args()

@@ -83,3 +83,36 @@ def test_position_by_position_prefill_matches_oracle(cuda_device, kind, prompt_l
     cfg, prompt, orc, nxt, gap, eng = _setup(kind, prompt_len, cuda_device, seed=25)
     first = eng.prefill_device(prompt)
     _check_cache_and_continue(cfg, prompt_len, orc, nxt, gap, eng, first, n_steps=3)
+
+
+@pytest.mark.parametrize("wkind,tol,base", [("fp8", 3e-2, "llama"), ("nvfp4", 6e-2, "qwen3_1k")])
+def test_chunked_prefill_with_quantised_projections(cuda_device, wkind, tol, base):
+    """The prefill engine adopts the decode engine's stored e4m3 / NVFP4 projections (same codes and scales,
+    repacked for the tensor-core tasks); cache rows against the oracle that dequantises the same codes."""
+    import copy
+    import dataclasses
+    from vdcores_b200.decode import DecodeEngine
+    from vdcores_b200.prefill import PrefillEngine
+    cfg_b = small_cfg(base)
+    w_b = perturb_norms(O.ModelWeights.random(cfg_b, seed=6))
+    cfg = dataclasses.replace(cfg_b, wkind=wkind)
+    w = copy.copy(w_b)
+    w.cfg = cfg
+    w.layers = []
+    for lw in w_b.layers:
+        q = copy.copy(lw)
+        for name in ("wq", "wk", "wv", "wo", "gate", "up", "down"):
+            setattr(q, name, O.QLinear.make(getattr(lw, name).w, wkind))
+        w.layers.append(q)
+    T = 90
+    prompt = torch.randint(0, cfg.vocab, (T,), generator=torch.Generator().manual_seed(31))
+    orc = O.DecodeOracle(w, 128)
+    _, nxt, gap = orc.prefill(prompt.tolist())
+    eng = DecodeEngine(engine_config(cfg), max_seq=128, device=cuda_device, wkind=wkind, timeout_ns=500_000_000)
+    eng.load_weights(dense_weights(w_b))
+    first = PrefillEngine(eng, chunk=32, timeout_ns=500_000_000).adopt_weights().prefill(prompt)
+    for l in range(cfg.n_layers):
+        k_dev, v_dev = eng.read_kv(l, T)
+        assert O.rel_l2(k_dev.cpu(), orc.k[l][:T]) < 2 * tol and O.rel_l2(v_dev.cpu(), orc.v[l][:T]) < 2 * tol
+    if gap > 5 * GAP:
+        assert first == nxt

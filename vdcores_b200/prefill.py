@@ -13,13 +13,11 @@ the prompt is prefilled for: nothing is copied when decode takes over.
 The reference has no prefill of its own on the device either side of its decode schedules: its correctness runs
 take the prompt's cache from a HuggingFace forward (app/python/llama3/sched.py:574-622 in the reference); this
 engine replaces the PyTorch prefill of decode.DecodeEngine.prefill on the product path."""
-from typing import Optional
-
 import torch
 
 from . import isa, runtime
 from .batch import BatchDecodeEngine
-from .decode import DecodeConfig, DecodeEngine
+from .decode import DecodeEngine
 
 
 class PrefillEngine(BatchDecodeEngine):
@@ -30,7 +28,7 @@ class PrefillEngine(BatchDecodeEngine):
         assert not isinstance(target, BatchDecodeEngine) and not target.cfg.n_experts
         self.target = target
         super().__init__(target.cfg, chunk, target.max_seq, device=target.dev, num_sms=target.num_sms,
-                         max_steps=1, timeout_ns=timeout_ns, wkind="bf16")
+                         max_steps=1, timeout_ns=timeout_ns, wkind=target.wkind)
         self.rope = target.rope
 
     def _alloc_cache(self, page_perm_seed):
@@ -40,14 +38,13 @@ class PrefillEngine(BatchDecodeEngine):
         self.page_tables = t.page_table[None, :].expand(self.batch, -1).contiguous()
 
     def adopt_weights(self):
-        """Takes the target's bf16 tensors (embedding, norms, vocabulary projection, dense layer projections) and
-        packs the projections for the tensor-core tasks.  A target with quantised projections keeps its own
-        stored form; the prefill then needs load_weights() with the source weights."""
+        """Takes the target's tensors (embedding, norms, vocabulary projection, the layer projections in their
+        stored form: bf16 rows, e4m3 codes or NVFP4 rows, with their scales) and packs the projections for the
+        tensor-core tasks; both engines store a projection the same way, only the packing differs."""
         t = self.target
-        assert t.wkind == "bf16", "quantised target: call load_weights with the source weights"
         for name in ("embed", "lm_head", "norm_w", "ln1", "ln2", "qknorm", "wqkv", "wo", "wgu", "wd"):
             setattr(self, name, getattr(t, name))
-        self.router, self.scales, self.w = None, {}, True
+        self.router, self.scales, self.w = None, dict(t.scales), True
         self._build_program()
         return self
 
