@@ -334,7 +334,7 @@ VDC_TASK void task_gemm_tc(Compute& q, const GemmTc& g) {
     int w_prev = 0, x_prev = 0;  // lane 0: slots whose tensor-core reads may still be in flight
     int xm = 0;
 #ifdef VDC_TC_PROFILE
-    long long t_data = 0, t_xr = 0, t_mma = 0, t_wait = 0;
+    long long t_data = 0, t_xr = 0, t_mma = 0, t_wait = 0, t_xw = 0, t_ww = 0;
 #endif
     for (int j = 0; j < g.n_w; ++j) {
       const int grp = j / g.G, jj = j % g.G;
@@ -342,13 +342,25 @@ VDC_TASK void task_gemm_tc(Compute& q, const GemmTc& g) {
       const long long td0 = clock64();
 #endif
       int x_done = 0;
+      if (jj == 0) x_done = xm;  // the previous group's X chunk: its last W chunk is the previous chunk
+#ifdef VDC_TC_PROFILE
+      const long long tq0 = clock64();
+#endif
       if (jj == 0) {
-        x_done = xm;  // the previous group's X chunk: its last W chunk is the previous chunk
         xm = q.warp_wait(x_entry(grp));
         if (xm == kPopAbort) break;
+        if (q.lane == 0) CHUNK_STAMP(c, q.head + x_entry(grp), 2);
       }
+#ifdef VDC_TC_PROFILE
+      if (j > 0) t_xw += clock64() - tq0;
+      const long long tq1 = clock64();
+#endif
       const int wm = q.warp_wait(w_entry(j));
+#ifdef VDC_TC_PROFILE
+      if (j > 0) t_ww += clock64() - tq1;
+#endif
       if (wm == kPopAbort) break;
+      if (q.lane == 0) CHUNK_STAMP(c, q.head + w_entry(j), 2);
       if (g.wfmt != 0) {
         // the converted chunk, not the loaded one, is the operand
         int ok = 1;
@@ -407,6 +419,7 @@ VDC_TASK void task_gemm_tc(Compute& q, const GemmTc& g) {
           int done = (g.wfmt != 0 ? 0 : w_prev) | x_done;  // e4m3 chunks were freed by the converting team
           if (!mma_wait(q, q.mma_count - 1)) done = 0;
           if (done) atomicOr(&sh->slot_avail, (uint32_t)done & kSlotMaskAll);
+          CHUNK_STAMP(c, q.head + w_entry(j - 1), 3);
           sh->warp_next[0] = q.head + x_entry(grp);  // ring entries before this group may be recycled
         }
         w_prev = wm & (int)kSlotMaskAll;
@@ -427,6 +440,7 @@ VDC_TASK void task_gemm_tc(Compute& q, const GemmTc& g) {
       uint64_t* pr = c.profile + c.sm * VDC_NUM_PROFILE_EVENTS;
       pr[8] += t_data; pr[9] += t_xr; pr[10] += t_mma; pr[11] += t_wait; pr[12] += g.n_w;
       pr[13] += (uint64_t)g.n_w * g.KS;
+      pr[14] += t_xw; pr[15] += t_ww;   // waits for X / W chunks after a task's first chunk
 #endif
     }
   }

@@ -1,6 +1,6 @@
 """Where the time of a batch-1 decode step goes: per-task and per-stage timelines from the kernel's own stamps.
 
-    python -m vdcores_b200.stage_trace [--layers 4] [--prompt 2048] [--batch 0]
+    python -m vdcores_b200.stage_trace [--layers 4] [--prompt 2048] [--batch 1]
 
 Every launch leaves, per SM, the global-timer start and end of its first 56 tasks in the profile rows; this
 program decodes a few steps of a Llama-3.1-8B-shaped model with `--layers` layers (random weights), reads the
@@ -9,7 +9,9 @@ first and last SM started and ended it (i.e. the stage and its skew).
 
 With a library built by `python -m vdcores_b200.build --trace VDC_TRACE_ATTN` (or VDC_TRACE_GEMV) and selected
 through VDCORES_LIB, the stamps inside the attention task (barrier seen, prologue, page arrivals, arrival at the
-head's counter, merge) or inside the GEMV task are printed as well."""
+head's counter, merge) or inside the GEMV task are printed as well.  With --batch B > 1 the program is the batched
+one (projections on the tensor cores); a library built with --trace VDC_TC_PROFILE adds where the projection task's
+issuing warp and the task as a whole spend their cycles (sums per SM over one launch)."""
 import argparse
 import collections
 import dataclasses
@@ -32,16 +34,28 @@ def main():
     ap.add_argument("--layers", type=int, default=4)
     ap.add_argument("--prompt", type=int, default=2048)
     ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--batch", type=int, default=1)
     args = ap.parse_args()
     dev = torch.device("cuda", 0)
     cfg = dataclasses.replace(LLAMA31_8B, n_layers=args.layers)
-    eng = DecodeEngine(cfg, max_seq=((args.prompt + 64 + 63) // 64) * 64, device=dev, max_steps=64)
-    eng.init_random_weights(0)
-    g = torch.Generator().manual_seed(0)
-    first = eng.prefill(torch.randint(0, cfg.vocab, (args.prompt,), generator=g))
-    eng.set_state(args.prompt, first)
-    for _ in range(args.steps):
+    max_seq = ((args.prompt + 64 + 63) // 64) * 64
+    if args.batch > 1:
+        from .batch import BatchDecodeEngine
+        eng = BatchDecodeEngine(cfg, args.batch, max_seq=max_seq, device=dev, max_steps=64)
+        eng.init_random_weights(0)
+        for b in range(args.batch):           # the cache contents do not matter for the timing: zero rows
+            eng.set_state(args.prompt, 5 + b, b=b)
+    else:
+        eng = DecodeEngine(cfg, max_seq=max_seq, device=dev, max_steps=64)
+        eng.init_random_weights(0)
+        g = torch.Generator().manual_seed(0)
+        first = eng.prefill(torch.randint(0, cfg.vocab, (args.prompt,), generator=g))
+        eng.set_state(args.prompt, first)
+    for _ in range(args.steps - 1):
         eng.step_async()
+    runtime.read_status(eng.stream.cuda_stream)
+    eng.profile.zero_()                       # the cycle sums of the traced builds accumulate: keep one launch
+    eng.step_async()
     runtime.read_status(eng.stream.cuda_stream)
     pv = eng.profile.view(eng.num_sms, -1).cpu().numpy().astype(np.int64)
     t0 = pv[:, 0].min()
@@ -51,6 +65,11 @@ def main():
     rows = []
     trace = os.environ.get("VDCORES_LIB", "")
     n_traced = 24 if "trace_gemv" in trace else 56
+    if "tc_profile" in trace:
+        # the task stamps (rows 16 + 2 j) must stay clear of the projection task's sums in rows 100-106
+        n_tasks = max(sum(1 for w in eng.program.c[sm] if w[0] not in (isa.OP_EXT, isa.OP_TERMINATEC))
+                      for sm in range(eng.num_sms))
+        assert n_tasks <= 42, f"{n_tasks} tasks on one SM: use fewer layers (--layers 2) with the VDC_TC_PROFILE library"
     for sm in range(eng.num_sms):
         ops = [w[0] for w in eng.program.c[sm] if w[0] not in (isa.OP_EXT, isa.OP_TERMINATEC)]
         for j, o in enumerate(ops[:n_traced]):
@@ -84,6 +103,16 @@ def main():
             col = a[:, i][~np.isnan(a[:, i])]
             if len(col):
                 print(f"   {ATTN_LABELS[k]:16s} {np.median(col):6.2f} {col.min():6.2f} {col.max():6.2f}   (n={len(col)})")
+    if "tc_profile" in trace:
+        clk = 1965.0      # SM cycles per microsecond at the clock the B200s of this pool run at
+        print("projection task, microseconds per SM in this launch (issuing warp, then the whole task):")
+        for row, label in ((8, "waiting for chunks (incl. the stage's input barrier)"), (14, "   of that, X chunks after a task's first"),
+                           (15, "   of that, W chunks after a task's first"), (9, "waiting for the normalised X chunk"),
+                           (10, "issuing MMAs"), (11, "waiting for the previous chunk's commit"), (100, "set-up"),
+                           (101, "streaming loop"), (102, "epilogue from tensor memory"), (103, "partial sums to scratch"),
+                           (104, "arrival at the block's counter"), (105, "last arrival's epilogue")):
+            print(f"   {label:56s} {pv[:, row].mean() / clk:8.1f}")
+        print(f"   weight chunks per SM {pv[:, 12].mean():.0f}, blocks finished per SM {pv[:, 106].mean():.1f}")
     if "trace_gemv" in trace:
         stage = ["qkv", "o", "gate/up", "down"]
         for o in range(8):
