@@ -199,6 +199,7 @@ def run_gpu(args):
     g = torch.Generator().manual_seed(0)
     prompt = torch.randint(0, cfg.vocab, (PROMPT_LEN,), generator=g)
     prefill_info = {"impl": "PyTorch ops (library GEMMs)", "prompt_tokens": PROMPT_LEN}
+    tf, tp_fallback = None, None
     if world == 1 and args.batch > 1:
         # batched decode: the projections run on the tensor cores, one state block per sequence
         from vdcores_b200.batch import BatchDecodeEngine
@@ -219,7 +220,7 @@ def run_gpu(args):
         N_CHECK = 32
         full = DecodeEngine(cfg, max_seq=max_seq, device=dev, max_steps=max(W + K, N_CHECK) + 8)
         full.init_random_weights(seed=0)
-        first, prefill_info = run_prefill(full, prompt, False)
+        first, prefill_info = run_prefill(full, prompt, args.prefill == "device" and not cfg.n_experts)
         # dense models: one launch per step and rank, the partial sums cross NVLink as peer stores inside the
         # kernel; mixture-of-experts models (and --tp-impl nccl): two launches per layer around NCCL collectives
         fused = args.tp_impl == "fused" and not cfg.n_experts
@@ -246,6 +247,49 @@ def run_gpu(args):
             single_gpu_tokens += full.generate(1)
             top2 = torch.topk(full.logits.float(), 2).values
             single_gpu_gaps.append(float((top2[0] - top2[1]) / top2[0].abs().clamp_min(1e-6)))
+
+        def teacher_forced(e):
+            # The two engines round differently (the sharded one adds fp32 partial sums to the residual, the single-GPU
+            # one a bf16 projection output), which moves bf16 logits by a few ulps (0.4 % each): ids may differ only
+            # where the single-GPU engine's two best logits are closer than 5 % of the best one
+            e.set_state(PROMPT_LEN, first)
+            feed, agree, beyond, worst = first, 0, [], 0.0
+            for i in range(N_CHECK):
+                got = e.step_host(feed)
+                agree += int(got == single_gpu_tokens[i])
+                if got != single_gpu_tokens[i]:
+                    worst = max(worst, single_gpu_gaps[i])
+                    if single_gpu_gaps[i] > 0.05:
+                        beyond.append(i)
+                feed = single_gpu_tokens[i]
+            return {"steps": N_CHECK, "agree": agree, "disagree_beyond_near_ties": len(beyond),
+                    "max_rel_gap_at_a_disagreement": worst}
+
+        # ---- teacher-forced agreement with the single-GPU engine (untimed).  The in-kernel exchange has to pass it on
+        # every rank; if a launch gives up a wait (a bounded wait returns a status, the context stays usable) or the
+        # ids disagree beyond near-ties on any rank, all ranks switch to the NCCL engine together and say so.
+        tf, tp_fallback = None, None
+        if fused:
+            ok = 1
+            try:
+                tf = teacher_forced(eng)
+                ok = int(tf["disagree_beyond_near_ties"] == 0)
+            except RuntimeError as e:
+                dbg(f"in-kernel exchange failed a step: {e}")
+                ok = 0
+            if os.environ.get("VDCORES_BENCH_FAIL_EXCHANGE_CHECK"):     # exercises the switch-over (host-side injection)
+                ok = 0
+            flag = torch.tensor([ok], dtype=torch.int32, device=dev)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            if int(flag) == 0:
+                tp_fallback = "the in-kernel exchange did not pass the agreement check on this machine; NCCL engine used"
+                dbg(tp_fallback)
+                retired = eng             # kept alive: its peer mappings are torn down at exit, not mid-run
+                fused, tf = False, None
+                eng = TPDecodeEngine(cfg, **kw)
+                eng.load_from_full(full, PROMPT_LEN)
+        if tf is None:
+            tf = teacher_forced(eng)
         del full
         torch.cuda.empty_cache()
         tokens_per_step, scaling = 1, "strong"
@@ -267,24 +311,6 @@ def run_gpu(args):
         else:
             eng.set_state(PROMPT_LEN, first)
 
-    # ---- sharded engines: teacher-forced agreement with the single-GPU engine (untimed)
-    tf = None
-    if world > 1:
-        reset()
-        # The two engines round differently (the sharded one adds fp32 partial sums to the residual, the single-GPU one
-        # a bf16 projection output), which moves bf16 logits by a few ulps (0.4 % each): ids may differ only where the
-        # single-GPU engine's two best logits are closer than 5 % of the best one
-        feed, agree, beyond, worst = first, 0, [], 0.0
-        for i in range(N_CHECK):
-            got = eng.step_host(feed)
-            agree += int(got == single_gpu_tokens[i])
-            if got != single_gpu_tokens[i]:
-                worst = max(worst, single_gpu_gaps[i])
-                if single_gpu_gaps[i] > 0.05:
-                    beyond.append(i)
-            feed = single_gpu_tokens[i]
-        tf = {"steps": N_CHECK, "agree": agree, "disagree_beyond_near_ties": len(beyond),
-              "max_rel_gap_at_a_disagreement": worst}
     # ---- device-resident arm: K launches back to back, CUDA events on the launching stream
     reset()
     for _ in range(W):
@@ -365,6 +391,7 @@ def run_gpu(args):
         # greedy ids of the sharded engine, fed the single-GPU engine's ids, against that engine's next ids: true when
         # they agree on every step whose two best single-GPU logits are more than a near-tie apart
         **({"tokens_match_single_gpu": tf["disagree_beyond_near_ties"] == 0, "teacher_forced": tf} if tf else {}),
+        **({"tp_fallback": tp_fallback} if tp_fallback else {}),
         "clocks": clk.summary(),
     }
     if not args.no_cpu_baseline:
