@@ -221,6 +221,15 @@ def run_gpu(args):
         full = DecodeEngine(cfg, max_seq=max_seq, device=dev, max_steps=max(W + K, N_CHECK) + 8)
         full.init_random_weights(seed=0)
         first, prefill_info = run_prefill(full, prompt, args.prefill == "device" and not cfg.n_experts)
+        if "ms" in prefill_info:
+            # The megakernel prefill adds the K-slices of a projection block with fp32 atomics: the cache is not
+            # bit-identical from one GPU to the next, and a random-init model turns the last bits into other greedy
+            # ids.  Every rank's shard and every rank's single-GPU trajectory must come from one cache: rank 0's.
+            t = torch.tensor([first], dtype=torch.int64, device=dev)
+            for buf in (full.kpool, full.vpool, t):
+                dist.broadcast(buf, 0)
+            first = int(t)
+            full.set_state(PROMPT_LEN, first)
         # dense models: one launch per step and rank, the partial sums cross NVLink as peer stores inside the
         # kernel; mixture-of-experts models (and --tp-impl nccl): two launches per layer around NCCL collectives
         fused = args.tp_impl == "fused" and not cfg.n_experts
