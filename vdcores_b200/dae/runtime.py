@@ -9,4 +9,4 @@ if _ROOT not in sys.path:
 
 from vdcores_b200.runtime import (  # noqa: E402,F401
     VdcError, build_tma_desc, compute_family_specs, config, init, last_error, launch_async, launch_dae, opcode,
-    read_status, set_cache_policy, set_smem_size, supported_compute_ops)
+    read_status, set_cache_policy, set_smem_size, supported_compute_ops, validate_streams)
