@@ -862,6 +862,37 @@ class DecodeEngine:
         runtime.read_status(self.stream.cuda_stream)
         return self.token_log[first:first + n_steps].tolist()
 
+    def generate_sampled(self, n_steps: int, temperature: float = 1.0, top_k: int = 0, top_p: float = 1.0,
+                         seed: int = 0) -> List[int]:
+        """Decode with temperature / top-k / nucleus sampling instead of the kernel's own argmax.  Every step is
+        the same launch as a greedy step; the draw from the step's logits (a softmax over one vocabulary row: PyTorch
+        ops on the engine's stream, not part of the megakernel) replaces the id the kernel left in the state block
+        before the next launch, without a host round trip.  top_k = 1 or temperature -> 0 reproduce generate()."""
+        assert temperature >= 0.0 and 0.0 < top_p <= 1.0 and top_k >= 0
+        g = torch.Generator(device=self.dev).manual_seed(seed)
+        out = torch.empty(n_steps, dtype=torch.int32, device=self.dev)
+        word = self.state[isa.ST_TOKEN:isa.ST_TOKEN + 1]
+        with torch.cuda.stream(self.stream):
+            for i in range(n_steps):
+                self.step_async()
+                lg = self.logits.float()
+                if temperature < 1e-6 or top_k == 1:
+                    tok = torch.argmax(lg).reshape(1)
+                else:
+                    lg = lg / temperature
+                    if top_k:
+                        lg = lg.masked_fill(lg < torch.topk(lg, top_k).values[-1], float("-inf"))
+                    p = torch.softmax(lg, -1)
+                    if top_p < 1.0:
+                        ps, idx = torch.sort(p, descending=True)
+                        keep = torch.cumsum(ps, 0) - ps < top_p        # the smallest prefix whose mass reaches top_p
+                        p = torch.zeros_like(p).scatter_(0, idx[keep], ps[keep])
+                    tok = torch.multinomial(p, 1, generator=g)
+                out[i] = tok[0]
+                word.copy_(tok.to(torch.int32))
+        runtime.read_status(self.stream.cuda_stream)
+        return out.tolist()
+
     def step_host(self, token: int) -> int:
         """One decode step driven from host buffers: the token id goes up, the
         next id comes back (synchronous)."""
