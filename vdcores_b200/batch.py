@@ -143,6 +143,7 @@ class BatchDecodeEngine(DecodeEngine):
     scales, fp32 tensor scale), everything else bf16."""
     GEMV_PROJECTIONS = False
     SHARED_CACHE = False     # True: the batch rows are consecutive positions of ONE sequence (prefill.PrefillEngine)
+    WITH_VOCAB_PROJECTION = True   # False: the program ends after the last layer (prefill chunks before the last)
 
     def __init__(self, cfg: DecodeConfig, batch: int, max_seq: int, device="cuda:0", num_sms=None, taps=False,
                  page_perm_seed=None, max_steps: int = 256, timeout_ns: int = 2_000_000_000, wkind: str = "bf16"):
@@ -195,6 +196,14 @@ class BatchDecodeEngine(DecodeEngine):
         self.page_tables = torch.stack(tables)        # [B, max_pages] global page ids
 
     # ------------------------------------------------------------------ weights
+    def load_weights(self, w):
+        self._pack_cache = None         # packed copies of the previous weights
+        super().load_weights(w)
+
+    def init_random_weights(self, seed: int = 0, std: float = 0.02):
+        self._pack_cache = None
+        super().init_random_weights(seed, std)
+
     def weight_bytes(self) -> int:
         ts = [self.lm_head, self.norm_w, self.ln1, self.ln2, self.wqkv, self.wo, self.wgu, self.wd]
         ts += list(self.scales.values())
@@ -220,7 +229,9 @@ class BatchDecodeEngine(DecodeEngine):
         hid, qkv, ao, act = (t.data_ptr() for t in (self.hidden, self.qkv, self.attn_out, self.act))
         load = [0] * S
         packed = {"wqkv": [], "wo": [], "wgu": [], "wd": []}
-        self.scratch = {}
+        # fp32 scratch / counters per projection kind and the packed weights outlive a rebuild of the program
+        self.scratch = getattr(self, "scratch", None) or {}
+        self._pack_cache = getattr(self, "_pack_cache", None) or {}
 
         stat = lambda i: self.stats[i].data_ptr()
 
@@ -228,7 +239,11 @@ class BatchDecodeEngine(DecodeEngine):
             M = w.shape[0]
             wf = self.wkind if name is not None else "bf16"     # the vocabulary projection stays bf16
             fp8 = wf != "bf16"
-            pk = pack_blocks_fp8(w) if wf == "fp8" else pack_blocks_nvfp4(w, K) if wf == "nvfp4" else pack_blocks(w)
+            key = (name, len(packed[name]) if name is not None else 0)
+            if key not in self._pack_cache:     # a second program of the same engine (prefill) shares the packed copies
+                self._pack_cache[key] = (pack_blocks_fp8(w) if wf == "fp8" else pack_blocks_nvfp4(w, K) if wf == "nvfp4"
+                                         else pack_blocks(w))
+            pk = self._pack_cache[key]
             if name is not None:
                 packed[name].append(pk)
             kind = name or "lm"
@@ -310,11 +325,14 @@ class BatchDecodeEngine(DecodeEngine):
             b_hid = P.new_barrier()
             gemm_stage(self.wd[l], "wd", F, act, b_gu, isa.GEMM_MODE_ADD_PACKED, hid, b_hid, stats=stat(2 * l + 2))
         # ---- final norm, vocabulary projection, per-sequence argmax
-        b_lm = P.new_barrier()
-        self.lm_head_packed = gemm_stage(self.lm_head, None, H, hid, b_hid, isa.GEMM_MODE_ARGMAX, 0, b_lm,
-                                         norm=self.norm_w, keys=self.keys.data_ptr(), stats=stat(2 * L))
-        if self.taps_enabled:
-            tap(L - 1, b_hid, b_lm)
+        if self.WITH_VOCAB_PROJECTION:
+            b_lm = P.new_barrier()
+            self.lm_head_packed = gemm_stage(self.lm_head, None, H, hid, b_hid, isa.GEMM_MODE_ARGMAX, 0, b_lm,
+                                             norm=self.norm_w, keys=self.keys.data_ptr(), stats=stat(2 * L))
+            if self.taps_enabled:
+                tap(L - 1, b_hid, b_lm)
+        else:
+            b_lm = b_hid        # a prefill chunk that is not the prompt's last: nobody reads its logits
         sm = self._pick(load, 1)[0]
         P.batch_advance(sm, batch=B, state_addr=st, state_stride_words=sw, keys_addr=self.keys.data_ptr(),
                         log_addr=self.token_log.data_ptr(), log_stride=self.max_steps, wait=b_lm,

@@ -45,8 +45,19 @@ class PrefillEngine(BatchDecodeEngine):
         for name in ("embed", "lm_head", "norm_w", "ln1", "ln2", "qknorm", "wqkv", "wo", "wgu", "wd"):
             setattr(self, name, getattr(t, name))
         self.router, self.scales, self.w = None, dict(t.scales), True
+        self._pack_cache = None
         self._build_program()
         return self
+
+    def _build_program(self):
+        """Two programs over the same packed weights: chunks before the prompt's last end after the last layer,
+        the last chunk adds the final norm, the vocabulary projection and the argmax (the first generated id)."""
+        self.WITH_VOCAB_PROJECTION = False
+        super()._build_program()
+        self._body = (self.insts_per_sm, self.cinsts, self.minsts, self.bars_init)
+        self.WITH_VOCAB_PROJECTION = True
+        super()._build_program()
+        self._last = (self.insts_per_sm, self.cinsts, self.minsts, self.bars_init)
 
     # ------------------------------------------------------------------ chunks
     def _chunk_states(self, tokens: torch.Tensor) -> torch.Tensor:
@@ -77,10 +88,12 @@ class PrefillEngine(BatchDecodeEngine):
         self.keys.zero_()
         self.stats.zero_()
         with torch.cuda.stream(self.stream):
-            for c in range(states.shape[0]):
+            n = states.shape[0]
+            for c in range(n):
                 self.state.copy_(states[c], non_blocking=True)
-                runtime.launch_async(self.num_sms, self.insts_per_sm, self.cinsts, self.minsts, None, self.bars,
-                                     self.bars_init, self.profile, self.stream.cuda_stream, self.timeout_ns)
+                insts_per_sm, cinsts, minsts, bars_init = self._last if c == n - 1 else self._body
+                runtime.launch_async(self.num_sms, insts_per_sm, cinsts, minsts, None, self.bars, bars_init,
+                                     self.profile, self.stream.cuda_stream, self.timeout_ns)
         runtime.read_status(self.stream.cuda_stream)
         first = int(self.token_log[(T - 1) % B, 0])
         if set_target_state:
