@@ -167,6 +167,8 @@ class BatchDecodeEngine(DecodeEngine):
         self.pages_per_split = (self.max_pages + self.n_splits - 1) // self.n_splits
         self.n_splits = (self.max_pages + self.pages_per_split - 1) // self.pages_per_split
         self.attn_part = z(B, cfg.n_kv_heads, self.n_splits, self.rec_floats, dt=torch.float32)
+        if self.SHARED_CACHE and cfg.group == 4:      # split records of two positions x four heads (eight query rows)
+            self.attn_part_pair = z((B + 1) // 2, cfg.n_kv_heads, self.n_splits, 8 * isa.HEAD_DIM + 16, dt=torch.float32)
         self.attn_cnt = z(L, B, cfg.n_kv_heads, dt=torch.int32)
         self.state_words = isa.ST_PAGETABLE + self.max_pages
         self.state = z(B, self.state_words, dt=torch.int32)
@@ -279,7 +281,7 @@ class BatchDecodeEngine(DecodeEngine):
                 tap(l - 1, b_hid, b_qkv)
             # ---- attention: one unit per (sequence, KV head, split)
             b_merge = P.new_barrier()
-            P.add_releases(b_merge, B * cfg.n_kv_heads)
+            P.add_releases(b_merge, (B // 2 if self.SHARED_CACHE and G == 4 and B % 2 == 0 else B) * cfg.n_kv_heads)
             units = [(b, h, s) for s in range(self.n_splits) for b in range(B) for h in range(cfg.n_kv_heads)]
             kp, vp = self.kpool[l].data_ptr(), self.vpool[l].data_ptr()
             grp = (G + 2) * D * 2
@@ -300,8 +302,25 @@ class BatchDecodeEngine(DecodeEngine):
                         k_page_addr=kp + h * page_bytes, v_page_addr=vp + h * page_bytes, page_shift=page_shift,
                         base_page=0, max_pages=0, records_addr=0, counter_addr=0, out_addr=0, split=0, n_splits=1,
                         release=b_rows, qk_eps=cfg.qk_norm_eps, append=True)
+            pairs = self.SHARED_CACHE and G == 4 and B % 2 == 0
+            if pairs:
+                # two consecutive prompt positions per unit: half the units walk the same pages (prefill only)
+                units = [(b, h, s) for s in range(self.n_splits) for b in range(0, B, 2) for h in range(cfg.n_kv_heads)]
             for (b, h, s), sm in zip(units, self._pick(load, len(units), 2 * page_bytes * self.pages_per_split)):
                 sb = st + 4 * sw * b
+                if pairs:
+                    P.attn_decode(
+                        sm, G=8, state_addr=sb, pair=(sw, self.qkv_rows),
+                        rope=Src(self.rope.data_ptr(), D * 4, indirect=(sb + 4 * isa.ST_POS, 9, None)),
+                        norm_w=Src(self.qknorm[l].data_ptr(), 2 * D * 2) if cfg.qk_norm else None,
+                        qkv=Src(qkv + (b * self.qkv_rows) * 2 + h * grp, grp, wait=b_rows), wait_issue=b_rows,
+                        k_page_addr=kp + h * page_bytes, v_page_addr=vp + h * page_bytes, page_shift=page_shift,
+                        base_page=s * self.pages_per_split, max_pages=self.pages_per_split,
+                        records_addr=self.attn_part_pair[b // 2, h].data_ptr(),
+                        counter_addr=self.attn_cnt[l, b, h].data_ptr(),
+                        out_addr=ao + (h * G * D) * Bp * 2, split=s, n_splits=self.n_splits, release=b_merge,
+                        qk_eps=cfg.qk_norm_eps, packed=(b, Bp))
+                    continue
                 P.attn_decode(
                     sm, G=G, state_addr=sb,
                     rope=Src(self.rope.data_ptr(), D * 4, indirect=(sb + 4 * isa.ST_POS, 9, None)),

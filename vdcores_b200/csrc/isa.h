@@ -256,6 +256,11 @@
 // ATTN_DECODE args[2] bits
 #define VDC_ATTN_QKNORM_BIT 0x1
 #define VDC_ATTN_PACKED_BIT 0x2   // output goes to a k-chunk-major matrix; last word args[2] = b | Bpad/16 << 8
+#define VDC_ATTN_PAIR_BIT 0x8     // G8 opcode only, chunked prefill of a model with 4 query heads per KV head: the unit serves two
+                                  // consecutive positions (query rows 0..3 / 4..7), both with their cache rows in the pools already;
+                                  // last word args[1] = int32 words from the first position's state block to the second's,
+                                  // args[2] = elements / 8 from the first position's projection row to the second's; the packed
+                                  // output's sequence slot b is the first position's, b + 1 the second's
 #define VDC_ATTN_APPEND_BIT 0x4   // cache append only: the new key row (normed, rotated) and value row go to the pools, the
                                   // task counts `release` down once and ends; no pages, no records (chunked prefill: the
                                   // rows of a whole chunk of positions are in the pools before any of them attends)

@@ -251,8 +251,22 @@ __device__ __forceinline__ void compute_core(const Ctx& c, const VdcCInst* __res
         a.nw = reinterpret_cast<const __nv_bfloat16*>(addr48(e[8]));
         a.qkv = reinterpret_cast<const __nv_bfloat16*>(addr48(e[9]));
         a.wait_bar = e[10].args[0];
-        if (ci.opcode == 0x7210) task_attn_decode<4>(q, a);
-        else task_attn_decode<8>(q, a);
+        a.state_stride = e[10].args[1];
+        a.qkv_stride = (int)e[10].args[2] * 8;
+        if (ci.opcode == 0x7210) {
+          task_attn_decode<4>(q, a);
+        } else if (a.flags & VDC_ATTN_PAIR_BIT) {
+          // pair units exist in the full kernel only (vdc_launch): measured on B200, one more instantiation of
+          // the attention task in the kernel the decode engines launch costs the batch-1 step 1.7 %
+          if constexpr (kRefOps) {
+            task_attn_decode<8, true>(q, a);
+          } else {
+            raise_abort(c, VDC_ERR_BAD_OPCODE, 0, (int)q.pc, ci.opcode, -1, a.flags);
+            q.aborted = true;
+          }
+        } else {
+          task_attn_decode<8>(q, a);
+        }
         break;
       }
       case 0x7230: {  // L2_PREFETCH: every thread touches its share of the range, nobody waits

@@ -819,11 +819,18 @@ struct AttnArgs {
   const __nv_bfloat16* nw;     // q norm | k norm weights (2 x 128), or null
   const __nv_bfloat16* qkv;    // the head group's projection output
   int wait_bar;                // barrier that orders qkv (0xFFFF: none)
+  int state_stride, qkv_stride;  // pair units: int32 words to the second position's state block, elements to its row
 };
 
-template <int G>
+// kPair (chunked prefill, models with four query heads per KV head): the unit serves TWO consecutive prompt
+// positions of one KV head.  Rows 0..3 of the MMA tile are the first position's query heads, rows 4..7 the
+// second's (the tile has eight usable rows either way); both walk the same pages, each row masks the page rows
+// past its own position, and all cache rows, the two positions' own included, are in HBM already (the chunk's
+// cache-append stage ran first), so nothing is patched in from shared memory and nothing is written back.
+template <int G, bool kPair = false>
 VDC_TASK void task_attn_decode(Compute& q, const AttnArgs& a) {
   constexpr int D = VDC_HEAD_DIM;
+  constexpr int GQ = kPair ? G / 2 : G;      // query heads per position
   constexpr int PPW = VDC_KV_PAGE / kCW;     // positions of a page per warp: one 8-column MMA tile
   static_assert(PPW == 8 && D == 128 && G <= 8, "the page loop maps one MMA tile of 8 positions to each warp");
   constexpr int REC = G * D + 16 * ((2 * G + 15) / 16);
@@ -843,9 +850,11 @@ VDC_TASK void task_attn_decode(Compute& q, const AttnArgs& a) {
   count = count < 0 ? 0 : (count > a.max_pages ? a.max_pages : count);
   const bool owner = count > 0 && a.base_page + count == n_pages;
   const int tail_valid = (pos % VDC_KV_PAGE) + 1;  // valid rows of the last page, new row included
+  // pair units: the second position (the first one again in a prompt's ragged tail) lies in the same page
+  const int pos_b = kPair ? ld_relaxed_gpu(a.state + a.state_stride + VDC_ST_POS) : pos;
+  const int tail_valid_b = (pos_b % VDC_KV_PAGE) + 1;
   const int sw_new = pos & 7;                      // piece swizzle of the new row (its row index mod 8)
 
-  const float* rope = a.rope + (size_t)pos * D;
   const __nv_bfloat16* knew = a.qkv + G * D;
   const __nv_bfloat16* vnew = knew + D;
   __nv_bfloat16* krow = reinterpret_cast<__nv_bfloat16*>(sh->newrows);  // rotated new key row
@@ -854,9 +863,11 @@ VDC_TASK void task_attn_decode(Compute& q, const AttnArgs& a) {
 
   // --- prologue: optional per-head RMSNorm, then half-rotation RoPE.  One warp
   // per head: heads 0..G-1 are the queries, "head" G is the new key row.
-  for (int head = q.warp; head <= G; head += kCW) {
-    const bool is_k = head == G;
-    const __nv_bfloat16* src = is_k ? knew : a.qkv + head * D;
+  for (int head = q.warp; head <= (kPair ? G - 1 : G); head += kCW) {
+    const bool is_k = !kPair && head == G;
+    const bool second = kPair && head >= GQ;
+    const __nv_bfloat16* src = is_k ? knew : (second ? a.qkv + a.qkv_stride + (head - GQ) * D : a.qkv + head * D);
+    const float* rope = second ? a.rope + (size_t)pos_b * D : a.rope + (size_t)pos * D;
     const int i0 = q.lane * 2;  // pairs (i0, i0+64), (i0+1, i0+65)
     const uint32_t lo = ldcg32(src + i0), hi = ldcg32(src + i0 + 64);
     float a0 = bf_lo(lo), a1 = bf_hi(lo), b0 = bf_lo(hi), b1 = bf_hi(hi);
@@ -884,7 +895,7 @@ VDC_TASK void task_attn_decode(Compute& q, const AttnArgs& a) {
     dst[e_lo >> 1] = pack_bf16x2(r0, r1);
     dst[e_hi >> 1] = pack_bf16x2(r64, r65);
   }
-  if (q.tid >= kCT - D / 8) {
+  if (!kPair && q.tid >= kCT - D / 8) {
     const int t = q.tid - (kCT - D / 8);
     reinterpret_cast<uint4*>(vrow)[t ^ sw_new] = ldcg128(reinterpret_cast<const uint4*>(vnew) + t);
   }
@@ -937,8 +948,10 @@ VDC_TASK void task_attn_decode(Compute& q, const AttnArgs& a) {
     if (k_mask == kPopAbort) break;
     ATTN_STAMP(3 + 3 * (blk & 1));
     const bool last = owner && blk == count - 1;
-    const int valid = last ? tail_valid : VDC_KV_PAGE;
-    const int newpos = last ? tail_valid - 1 : -1;  // this row of the page is not in HBM yet
+    // rows of the page that exist for the later of the unit's positions / for this thread's query row
+    const int valid = last ? (kPair ? tail_valid_b : tail_valid) : VDC_KV_PAGE;
+    const int valid_row = kPair ? (last ? (gid >= GQ ? tail_valid_b : tail_valid) : VDC_KV_PAGE) : valid;
+    const int newpos = (!kPair && last) ? tail_valid - 1 : -1;  // this row of the page is not in HBM yet
     const int p_l = slice + lrow;                   // the page row this lane addresses
     // ---- scores of the warp's eight positions
     const uint32_t kb_s = (uint32_t)__cvta_generic_to_shared(slot_ptr(c, first_slot(k_mask)));
@@ -955,8 +968,8 @@ VDC_TASK void task_attn_decode(Compute& q, const AttnArgs& a) {
     s1 += u1;
     // ---- online softmax (exp2 domain); a row's eight positions sit in the four lanes of a quad
     const int p0 = slice + 2 * t4;
-    s0 = p0 < valid ? s0 * scale_log2 : -INFINITY;
-    s1 = p0 + 1 < valid ? s1 * scale_log2 : -INFINITY;
+    s0 = p0 < valid_row ? s0 * scale_log2 : -INFINITY;
+    s1 = p0 + 1 < valid_row ? s1 * scale_log2 : -INFINITY;
     float mx = fmaxf(s0, s1);
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
@@ -1045,7 +1058,7 @@ VDC_TASK void task_attn_decode(Compute& q, const AttnArgs& a) {
       }
     }
   }
-  if (owner && q.tid >= 64 && q.tid < 64 + 2 * (D / 8)) {
+  if (!kPair && owner && q.tid >= 64 && q.tid < 64 + 2 * (D / 8)) {
     // the new cache rows go to HBM (already in the page-row piece order); the next step's page loads
     // (a later launch) see them
     const int t = q.tid - 64;
@@ -1137,8 +1150,10 @@ VDC_TASK void task_attn_decode(Compute& q, const AttnArgs& a) {
     const __nv_bfloat16 r0 = __float2bfloat16_rn(den > 0.f ? n0 / den : 0.f);
     const __nv_bfloat16 r1 = __float2bfloat16_rn(den > 0.f ? n1 / den : 0.f);
     if (a.bpad) {
-      uint8_t* dst = reinterpret_cast<uint8_t*>(a.out) + (size_t)(oo >> 3) * a.bpad * 16 + (a.b >> 3) * 128 + (a.b & 7) * 16 +
-                     (oo & 7) * 2;
+      // pair units: query rows GQ.. are the next sequence slot's heads
+      const int bb = (kPair && g >= GQ) ? a.b + 1 : a.b, ob = (kPair && g >= GQ) ? oo - GQ * D : oo;
+      uint8_t* dst = reinterpret_cast<uint8_t*>(a.out) + (size_t)(ob >> 3) * a.bpad * 16 + (bb >> 3) * 128 + (bb & 7) * 16 +
+                     (ob & 7) * 2;
       *reinterpret_cast<__nv_bfloat162*>(dst) = __halves2bfloat162(r0, r1);
     } else {
       *reinterpret_cast<__nv_bfloat162*>(a.out + oo) = __halves2bfloat162(r0, r1);

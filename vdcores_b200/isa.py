@@ -44,6 +44,7 @@ STREAM_END = _defs["STREAM_END"]
 ATTN_QKNORM_BIT = _defs["ATTN_QKNORM_BIT"]
 ATTN_PACKED_BIT = _defs["ATTN_PACKED_BIT"]
 ATTN_APPEND_BIT = _defs["ATTN_APPEND_BIT"]
+ATTN_PAIR_BIT = _defs["ATTN_PAIR_BIT"]
 GEMM_MODE_STORE_ROWS = _defs["GEMM_MODE_STORE_ROWS"]
 GEMM_MODE_SILU_PAIRS = _defs["GEMM_MODE_SILU_PAIRS"]
 GEMM_MODE_ARGMAX = _defs["GEMM_MODE_ARGMAX"]

@@ -461,7 +461,7 @@ class Program:
     def attn_decode(self, sm, *, G, state_addr, rope: Src, norm_w: Optional[Src], qkv: Src, k_page_addr, v_page_addr,
                     page_shift, base_page, max_pages, records_addr, counter_addr, out_addr, split, n_splits,
                     release, qk_eps: float = 1e-6, packed: Optional[tuple] = None, append: bool = False,
-                    wait_issue: Optional[int] = None):
+                    wait_issue: Optional[int] = None, pair: Optional[tuple] = None):
         """One (KV head, split) unit of the decode attention.  k_page_addr /
         v_page_addr: this head's rows inside page 0 of the layer's K / V pool;
         the page table in the state block selects the page.  The unit that
@@ -471,12 +471,18 @@ class Program:
         head's first k group inside a k-chunk-major [Bpad, q_width] matrix and the
         outputs go to its row b (batched decode).  append: the unit only writes the new key / value rows to the
         pools and counts `release` down (max_pages must be 0).  wait_issue: the page loads are not issued before
-        this barrier opens (pages that tasks of the same launch are still writing: chunked prefill)."""
+        this barrier opens (pages that tasks of the same launch are still writing: chunked prefill).
+        pair=(state_stride_words, qkv_stride_elems): G must be 8 and the model's group 4; the unit serves the
+        position of state_addr / qkv and the next one (their state block and projection row lie that far on), both
+        with their cache rows in the pools already; needs `packed`, whose b is the first position's slot."""
         page_bytes = isa.KV_PAGE * isa.HEAD_DIM * 2
         assert not append or max_pages == 0
+        g_row = G // 2 if pair else G       # query heads in one projection row's head group
+        assert pair is None or (G == 8 and packed is not None and not append and pair[0] <= 0xFFFF
+                                and pair[1] % 8 == 0 and pair[1] // 8 <= 0xFFFF)
         if wait_issue is not None and max_pages:
             self.mem(sm, isa.OP_ISSUE_BARRIER, bar=wait_issue)
-        assert qkv.nbytes == (G + 2) * isa.HEAD_DIM * 2 and qkv.addr % 16 == 0 and qkv.indirect is None
+        assert qkv.nbytes == (g_row + 2) * isa.HEAD_DIM * 2 and qkv.addr % 16 == 0 and qkv.indirect is None
         # the rope row is table + position * 512 bytes: the task reads the position from the state block itself
         assert rope.indirect is None or (rope.indirect[0] == state_addr + 4 * isa.ST_POS and rope.indirect[1] == 9)
         # The page ids of up to 32 pages are fetched with one load (a word per lane of the control
@@ -496,7 +502,7 @@ class Program:
         e = f32_bits(qk_eps)
         op = isa.OP_ATTN_DECODE_PAGED_G4 if G == 4 else isa.OP_ATTN_DECODE_PAGED_G8
         flags = ((isa.ATTN_QKNORM_BIT if norm_w is not None else 0) | (isa.ATTN_PACKED_BIT if packed else 0) |
-                 (isa.ATTN_APPEND_BIT if append else 0))
+                 (isa.ATTN_APPEND_BIT if append else 0) | (isa.ATTN_PAIR_BIT if pair else 0))
         self.comp(sm, op, max_pages, base_page, flags)
         self.comp(sm, isa.OP_EXT, e >> 16, e & 0xFFFF, n_splits)
         a48 = lambda a: (a & 0xFFFF, (a >> 16) & 0xFFFF, (a >> 32) & 0xFFFF)
@@ -507,7 +513,8 @@ class Program:
         for addr in (rope.addr, norm_w.addr if norm_w is not None else 0, qkv.addr):
             assert 0 <= addr < 1 << 48
             self.comp(sm, isa.OP_EXT, *a48(addr))
-        self.comp(sm, isa.OP_EXT, 0xFFFF if qkv.wait is None else qkv.wait, 0, 0)
+        self.comp(sm, isa.OP_EXT, 0xFFFF if qkv.wait is None else qkv.wait, pair[0] if pair else 0,
+                  pair[1] // 8 if pair else 0)
 
     # ------------------------------------------------------------------ batched decode (tensor cores)
     def gemm_tc(self, sm, *, w_addr, N, K, k_len, Kc, G, x_addr, B, Bpad, out_addr, mode, x_wait: Optional[int] = None,
