@@ -211,7 +211,7 @@ def run_gpu(args):
     elif world == 1:
         eng = DecodeEngine(cfg, max_seq=max_seq, device=dev, max_steps=W + K + 8, wkind=args.wkind)
         eng.init_random_weights(seed=0)
-        first, prefill_info = run_prefill(eng, prompt, args.prefill == "device" and not cfg.n_experts)
+        first, prefill_info = run_prefill(eng, prompt, args.prefill == "device")
         tokens_per_step, scaling, parallelism = 1, "strong", "single GPU"
     else:
         # tensor parallel: every rank builds the same full model (same seed), prefills it with the
@@ -220,7 +220,7 @@ def run_gpu(args):
         N_CHECK = 32
         full = DecodeEngine(cfg, max_seq=max_seq, device=dev, max_steps=max(W + K, N_CHECK) + 8)
         full.init_random_weights(seed=0)
-        first, prefill_info = run_prefill(full, prompt, args.prefill == "device" and not cfg.n_experts)
+        first, prefill_info = run_prefill(full, prompt, args.prefill == "device")
         if "ms" in prefill_info:
             # The megakernel prefill adds the K-slices of a projection block with fp32 atomics: the cache is not
             # bit-identical from one GPU to the next, and a random-init model turns the last bits into other greedy
@@ -415,6 +415,15 @@ def run_prefill(eng, prompt, on_device):
     T = int(prompt.numel())
     if not on_device:
         return eng.prefill(prompt), {"impl": "PyTorch ops (library GEMMs)", "prompt_tokens": T}
+    if eng.cfg.n_experts:
+        # mixture-of-experts models: the decode program itself over the prompt, one position per launch
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        first = eng.prefill_device(prompt)
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        return first, {"impl": "megakernel, one prompt position per launch (the decode program)", "prompt_tokens": T,
+                       "ms": dt * 1e3, "tokens_per_s": T / dt, "launches": T}
     # the prompt goes through the megakernel too: 128 positions per launch into this engine's own pools
     from vdcores_b200.prefill import PrefillEngine
     pre = PrefillEngine(eng, chunk=128).adopt_weights()
@@ -447,7 +456,7 @@ def main():
     ap.add_argument("--tp-impl", default="fused", choices=["fused", "nccl"],
                     help="N > 1, dense models: exchange inside the kernel (peer stores) or NCCL collectives between launches")
     ap.add_argument("--prefill", default="device", choices=["device", "torch"],
-                    help="batch 1, dense models: prompt through the megakernel (device) or PyTorch ops (torch)")
+                    help="batch 1: prompt through the megakernel (device) or PyTorch ops (torch)")
     ap.add_argument("--layers", type=int, default=32,
                     help="profiling only: a model with fewer layers of the same shape (the JSON line says so)")
     args = ap.parse_args()
