@@ -946,6 +946,7 @@ VDC_TASK void task_attn_decode(Compute& q, const AttnArgs& a) {
   for (int blk = 0; blk < count; ++blk) {
     const int k_mask = q.warp_wait(2u * (unsigned)blk);
     if (k_mask == kPopAbort) break;
+    if (q.tid == 0) CHUNK_STAMP(c, q.head + 2u * (unsigned)blk, 2);
     ATTN_STAMP(3 + 3 * (blk & 1));
     const bool last = owner && blk == count - 1;
     // rows of the page that exist for the later of the unit's positions / for this thread's query row
@@ -992,6 +993,7 @@ VDC_TASK void task_attn_decode(Compute& q, const AttnArgs& a) {
     // ---- O += P V
     const int v_mask = q.warp_wait(2u * (unsigned)blk + 1u);
     if (v_mask == kPopAbort) break;
+    if (q.tid == 0) CHUNK_STAMP(c, q.head + 2u * (unsigned)blk + 1u, 2);
     ATTN_STAMP(4 + 3 * (blk & 1));
     const uint32_t vb_s = (uint32_t)__cvta_generic_to_shared(slot_ptr(c, first_slot(v_mask)));
     const uint32_t v_base = p_l == newpos ? vrow_s : (p_l >= valid ? zero_s : vb_s + (uint32_t)p_l * (D * 2));
@@ -1008,6 +1010,7 @@ VDC_TASK void task_attn_decode(Compute& q, const AttnArgs& a) {
       if (atomicAdd(&sh->att_done[blk & 7], 1) == kCW - 1) {
         sh->att_done[blk & 7] = 0;
         atomicOr(&sh->slot_avail, (uint32_t)(k_mask | v_mask) & kSlotMaskAll);
+        CHUNK_STAMP(c, q.head + 2u * (unsigned)blk + 1u, 3);
       }
       sh->warp_next[q.warp] = q.head + 2u * (unsigned)blk + 2u;
     }

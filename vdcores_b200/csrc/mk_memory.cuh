@@ -319,6 +319,7 @@ __device__ void control_warp(const Ctx& c, const VdcMInst* __restrict__ insts, i
                   *reinterpret_cast<uint4*>(&sh->ring[e]) = make_uint4(b.x, b.y, (uint32_t)addr, (uint32_t)(addr >> 32));
                   sh->ring_word[e] = (int)mask;
                   __threadfence_block();
+                  CHUNK_STAMP(c, tail, 0);
                   sh->ring_tail = ++tail;
                 }
               }

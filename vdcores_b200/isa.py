@@ -15,6 +15,7 @@ SLOT_BYTES = _defs["SLOT_BYTES"]
 NUM_SLOTS = _defs["NUM_SLOTS"]
 NUM_SPECIAL_SLOTS = _defs["NUM_SPECIAL_SLOTS"]
 MAX_INSTS = _defs["MAX_INSTS"]
+MAX_SMS = _defs["MAX_SMS"]
 NUM_PROFILE_EVENTS = _defs["NUM_PROFILE_EVENTS"]
 MAX_TMAS = _defs["MAX_TMAS"]
 MAX_BARS = _defs["MAX_BARS"]

@@ -11,7 +11,9 @@ With a library built by `python -m vdcores_b200.build --trace VDC_TRACE_ATTN` (o
 through VDCORES_LIB, the stamps inside the attention task (barrier seen, prologue, page arrivals, arrival at the
 head's counter, merge) or inside the GEMV task are printed as well.  With --batch B > 1 the program is the batched
 one (projections on the tensor cores); a library built with --trace VDC_TC_PROFILE adds where the projection task's
-issuing warp and the task as a whole spend their cycles (sums per SM over one launch)."""
+issuing warp and the task as a whole spend their cycles (sums per SM over one launch); one built with --trace
+VDC_TRACE_CHUNKS prints the life of SM 0's ring entries --entries LO:HI (published by the control warp, copy issued
+by the load port, seen by the consuming warp, slots given back)."""
 import argparse
 import collections
 import dataclasses
@@ -35,6 +37,7 @@ def main():
     ap.add_argument("--prompt", type=int, default=2048)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--entries", default="60:120", help="ring entries of SM 0 to list (VDC_TRACE_CHUNKS library)")
     args = ap.parse_args()
     dev = torch.device("cuda", 0)
     cfg = dataclasses.replace(LLAMA31_8B, n_layers=args.layers)
@@ -51,19 +54,22 @@ def main():
         g = torch.Generator().manual_seed(0)
         first = eng.prefill(torch.randint(0, cfg.vocab, (args.prompt,), generator=g))
         eng.set_state(args.prompt, first)
+    trace = os.environ.get("VDCORES_LIB", "")
+    if "trace_chunks" in trace:               # that build stamps 1500 ring entries of SM 0 behind the per-SM rows
+        eng.profile = torch.zeros(isa.MAX_SMS * isa.NUM_PROFILE_EVENTS + 1500 * 4, dtype=torch.int64, device=dev)
     for _ in range(args.steps - 1):
         eng.step_async()
     runtime.read_status(eng.stream.cuda_stream)
     eng.profile.zero_()                       # the cycle sums of the traced builds accumulate: keep one launch
     eng.step_async()
     runtime.read_status(eng.stream.cuda_stream)
-    pv = eng.profile.view(eng.num_sms, -1).cpu().numpy().astype(np.int64)
+    raw = eng.profile.cpu().numpy().astype(np.int64)
+    pv = raw[:eng.num_sms * isa.NUM_PROFILE_EVENTS].reshape(eng.num_sms, -1)
     t0 = pv[:, 0].min()
     names = {v: k for k, v in isa.OPCODES.items()}
     print(f"{args.layers} layers, context {args.prompt}: kernel {(pv[:, 1].max() - t0) / 1e3:.1f} us, "
           f"CTA start skew {(pv[:, 0].max() - t0) / 1e3:.2f} us")
     rows = []
-    trace = os.environ.get("VDCORES_LIB", "")
     n_traced = 24 if "trace_gemv" in trace else 56
     if "tc_profile" in trace:
         # the task stamps (rows 16 + 2 j) must stay clear of the projection task's sums in rows 100-106
@@ -103,6 +109,20 @@ def main():
             col = a[:, i][~np.isnan(a[:, i])]
             if len(col):
                 print(f"   {ATTN_LABELS[k]:16s} {np.median(col):6.2f} {col.min():6.2f} {col.max():6.2f}   (n={len(col)})")
+    if "trace_chunks" in trace:
+        lo, hi = (int(v) for v in args.entries.split(":"))
+        ch = raw[isa.MAX_SMS * isa.NUM_PROFILE_EVENTS:][:6000].reshape(1500, 4)
+        print("ring entries of SM 0: published (us since kernel start, +gap to the previous entry) | copy issued | "
+              "seen by the consumer | slots given back (us after published; - = not stamped for this kind of entry)")
+        prev = 0
+        for n in range(1500):
+            a = ch[n]
+            if a[0] == 0:
+                continue
+            if lo <= n < hi:
+                d = [f"{(x - a[0]) / 1e3:6.2f}" if x else "     -" for x in a[1:]]
+                print(f"   {n:5d}  {(a[0] - t0) / 1e3:8.2f} (+{(a[0] - prev) / 1e3 if prev else 0:5.2f}) | {d[0]} | {d[1]} | {d[2]}")
+            prev = a[0]
     if "tc_profile" in trace:
         clk = 1965.0      # SM cycles per microsecond at the clock the B200s of this pool run at
         print("projection task, microseconds per SM in this launch (issuing warp, then the whole task):")
