@@ -32,7 +32,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
 def build_trace(define: str) -> str:
     """A second library with one of the tracing switches compiled in (VDC_TRACE_ATTN: stamps inside the attention
     task, VDC_TRACE_GEMV: inside the GEMV task, VDC_TRACE_CHUNKS: life of SM 0's ring entries, VDC_TC_PROFILE: cycle
-    sums inside the tensor-core projection task, profile rows 8-13 and 100-106); select it with
+    sums inside the tensor-core projection task, profile rows 8-15 and 100-106); select it with
     VDCORES_LIB=<path>.  The stamps go into the launch's profile rows (vdcores_b200.stage_trace prints them)."""
     assert define in ("VDC_TRACE_ATTN", "VDC_TRACE_GEMV", "VDC_TRACE_CHUNKS", "VDC_TC_PROFILE")
     out = os.path.join(HERE, f"libvdcores_b200_{define.lower()}.so")
