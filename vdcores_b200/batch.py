@@ -142,6 +142,7 @@ class BatchDecodeEngine(DecodeEngine):
     projections are bf16, e4m3 with per-row scales (wkind "fp8") or NVFP4 (wkind "nvfp4": e2m1 values, e4m3 block
     scales, fp32 tensor scale), everything else bf16."""
     GEMV_PROJECTIONS = False
+    FULL_KERNEL = True       # the attention variants for long page walks live in the full kernel only
     SHARED_CACHE = False     # True: the batch rows are consecutive positions of ONE sequence (prefill.PrefillEngine)
     WITH_VOCAB_PROJECTION = True   # False: the program ends after the last layer (prefill chunks before the last)
 

@@ -125,6 +125,15 @@ int vdc_launch_async(int num_sms, int insts_per_sm, const void* compute_insts, c
                            timeout_ns, 0);
 }
 
+// The same without the synchronisation of vdc_launch, for the full kernel: the batched engines and the prefill
+// run tasks (attention variants for long page walks) that the batch-1 kernel does not carry.
+int vdc_launch_async_full(int num_sms, int insts_per_sm, const void* compute_insts, const void* memory_insts,
+                          const void* tma_descs, int* bars, const int* bars_init, uint64_t* profile, uint64_t stream,
+                          uint64_t timeout_ns) {
+  return launch_async_impl(num_sms, insts_per_sm, compute_insts, memory_insts, tma_descs, bars, bars_init, profile, stream,
+                           timeout_ns, 1);
+}
+
 int vdc_read_status(uint64_t stream, vdc_status* status, int clear) {
   int dev;
   if (int r = current_device(&dev)) return r;

@@ -256,7 +256,7 @@ __device__ __forceinline__ void compute_core(const Ctx& c, const VdcCInst* __res
         if (ci.opcode == 0x7210) {
           task_attn_decode<4>(q, a);
         } else if (a.flags & VDC_ATTN_PAIR_BIT) {
-          // pair units exist in the full kernel only (vdc_launch): measured on B200, one more instantiation of
+          // pair units exist in the full kernel only (vdc_launch, vdc_launch_async_full): measured on B200, one more instantiation of
           // the attention task in the kernel the decode engines launch costs the batch-1 step 1.7 %
           if constexpr (kRefOps) {
             task_attn_decode<8, true>(q, a);

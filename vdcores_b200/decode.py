@@ -150,6 +150,7 @@ def quantize_nvfp4_rows(w: torch.Tensor):
 
 class DecodeEngine:
     GEMV_PROJECTIONS = True     # the layer projections run as GEMV tasks (batch 1)
+    FULL_KERNEL = False         # batch 1 launches the kernel with the native batch-1 operators only
 
     def __init__(self, cfg: DecodeConfig, max_seq: int, device="cuda", num_sms: Optional[int] = None,
                  taps: bool = False, page_perm_seed: Optional[int] = None, max_steps: int = 4096,
@@ -850,7 +851,8 @@ class DecodeEngine:
         if self.pos >= self.max_seq or self.steps_done >= self.max_steps:
             raise RuntimeError("out of KV pages or token-log space")
         runtime.launch_async(self.num_sms, self.insts_per_sm, self.cinsts, self.minsts, None, self.bars,
-                             self.bars_init, self.profile, self.stream.cuda_stream, self.timeout_ns)
+                             self.bars_init, self.profile, self.stream.cuda_stream, self.timeout_ns,
+                             full=self.FULL_KERNEL)
         self.pos += 1
         self.steps_done += 1
 

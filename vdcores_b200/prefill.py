@@ -30,7 +30,6 @@ class PrefillEngine(BatchDecodeEngine):
         super().__init__(target.cfg, chunk, target.max_seq, device=target.dev, num_sms=target.num_sms,
                          max_steps=1, timeout_ns=timeout_ns, wkind=target.wkind)
         self.rope = target.rope
-        self.full_kernel = target.cfg.group == 4 and chunk % 2 == 0     # the program holds pair units (batch.py)
 
     def _alloc_cache(self, page_perm_seed):
         t = self.target
@@ -93,15 +92,8 @@ class PrefillEngine(BatchDecodeEngine):
             for c in range(n):
                 self.state.copy_(states[c], non_blocking=True)
                 insts_per_sm, cinsts, minsts, bars_init = self._last if c == n - 1 else self._body
-                if self.full_kernel:
-                    # the full kernel (the one behind the reference's launch_dae) has the two-positions-per-unit
-                    # attention task; its entry point is synchronous and takes the live barrier array
-                    self.bars.copy_(bars_init, non_blocking=True)
-                    runtime.launch_dae(self.num_sms, 0, cinsts, minsts, None, self.bars, self.profile,
-                                       self.stream.cuda_stream, timeout_ns=self.timeout_ns, insts_per_sm=insts_per_sm)
-                else:
-                    runtime.launch_async(self.num_sms, insts_per_sm, cinsts, minsts, None, self.bars, bars_init,
-                                         self.profile, self.stream.cuda_stream, self.timeout_ns)
+                runtime.launch_async(self.num_sms, insts_per_sm, cinsts, minsts, None, self.bars, bars_init,
+                                     self.profile, self.stream.cuda_stream, self.timeout_ns, full=True)
         runtime.read_status(self.stream.cuda_stream)
         first = int(self.token_log[(T - 1) % B, 0])
         if set_target_state:

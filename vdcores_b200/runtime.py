@@ -38,6 +38,7 @@ _lib.vdc_init.restype = _i32
 _lib.vdc_set_smem_size.argtypes = [_i32]
 _lib.vdc_launch.argtypes = [_i32, _i32, _vp, _vp, _vp, _vp, _vp, _u64, _u64, ctypes.POINTER(Status)]
 _lib.vdc_launch_async.argtypes = [_i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _u64, _u64]
+_lib.vdc_launch_async_full.argtypes = [_i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _u64, _u64]
 _lib.vdc_launch_static.argtypes = [_i32, _i32, _vp, _vp, _vp, _vp, _u64, _u64, ctypes.POINTER(Status)]
 _lib.vdc_read_status.argtypes = [_u64, ctypes.POINTER(Status), _i32]
 _lib.vdc_build_tma_desc.argtypes = [_vp, _vp, _i32, _i32, ctypes.POINTER(_u64), ctypes.POINTER(_u64),
@@ -67,7 +68,8 @@ _lib.vdc_validate_streams.argtypes = [_i32, _i32, _vp, _vp, ctypes.POINTER(_i32)
 _lib.vdc_validate_streams.restype = _i32
 
 EXPORTED_SYMBOLS = [
-    "vdc_version", "vdc_init", "vdc_set_smem_size", "vdc_launch", "vdc_launch_async", "vdc_launch_static",
+    "vdc_version", "vdc_init", "vdc_set_smem_size", "vdc_launch", "vdc_launch_async", "vdc_launch_async_full",
+    "vdc_launch_static",
     "vdc_read_status",
     "vdc_build_tma_desc", "vdc_set_cache_policy", "vdc_enable_peer_access", "vdc_ipc_open", "vdc_ipc_close", "vdc_peer_alloc", "vdc_peer_free", "vdc_ipc_export", "vdc_opcode_count", "vdc_opcode_name", "vdc_opcode_value",
     "vdc_opcode_is_compute", "vdc_config", "vdc_family_specs", "vdc_last_error", "vdc_validate_streams",
@@ -168,9 +170,11 @@ def validate_streams(num_sms, insts_per_sm, compute_insts, memory_insts):
 
 
 def launch_async(num_sms, insts_per_sm, compute_insts, memory_insts, tma_descs, bars, bars_init, profile,
-                 stream=0, timeout_ns=0):
+                 stream=0, timeout_ns=0, full=False):
+    """Enqueues one launch; full=True selects the kernel with every operator (batched engines, prefill)."""
     init()
-    _check(_lib.vdc_launch_async(num_sms, insts_per_sm, _ptr(compute_insts), _ptr(memory_insts), _ptr(tma_descs),
+    fn = _lib.vdc_launch_async_full if full else _lib.vdc_launch_async
+    _check(fn(num_sms, insts_per_sm, _ptr(compute_insts), _ptr(memory_insts), _ptr(tma_descs),
                                  _ptr(bars), _ptr(bars_init), _ptr(profile), int(stream), int(timeout_ns)))
 
 
