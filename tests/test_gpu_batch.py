@@ -158,8 +158,11 @@ def test_gemm_tc_argmax_keys(cuda_device):
         assert float(ref[b, got[b]]) >= float(ref[b].max()) - 1e-2 * float(ref[b].abs().max())
 
 
-@pytest.mark.parametrize("kind,batch", [("llama", 3), ("qwen3", 20)])
-def test_batch_decode_matches_oracle(cuda_device, kind, batch):
+@pytest.mark.parametrize("kind,batch,num_sms", [("llama", 3, None), ("qwen3", 20, None), ("llama", 20, 32)])
+def test_batch_decode_matches_oracle(cuda_device, kind, batch, num_sms):
+    """20 sequences x 2 KV heads on 32 SMs: more attention units than SMs, so a unit walks all four pages of its
+    sequence alone, two pages per trip (contexts of 4, 3 and 2 pages: last page second in a trip, odd tail page,
+    single trip)."""
     from vdcores_b200.batch import BatchDecodeEngine
     cfg = small_cfg(kind)
     w = perturb_norms(O.ModelWeights.random(cfg, seed=3))
@@ -167,9 +170,12 @@ def test_batch_decode_matches_oracle(cuda_device, kind, batch):
     lens = [int(v) for v in torch.randint(2, 150, (batch,), generator=g)]
     if batch > 4:       # the oracle prefill is the slow part: keep most prompts short
         lens = [l if b < 3 else 2 + l % 20 for b, l in enumerate(lens)]
+    if num_sms is not None:
+        lens[:3] = [200, 131, 100]
     prompts = [torch.randint(0, cfg.vocab, (n,), generator=g) for n in lens]
     eng = BatchDecodeEngine(engine_config(cfg), batch, max_seq=256, device=cuda_device, taps=True, page_perm_seed=5,
-                            timeout_ns=500_000_000)
+                            timeout_ns=500_000_000, num_sms=num_sms)
+    assert num_sms is None or (eng.n_splits == 1 and eng.pages_per_split == 4)
     eng.load_weights(dense_weights(w))
     orcs, toks = [], []
     for b in range(batch):

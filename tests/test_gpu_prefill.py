@@ -48,10 +48,12 @@ def _check_cache_and_continue(cfg, T, orc, nxt, gap, eng, first, n_steps=4):
 
 
 @pytest.mark.parametrize("kind,prompt_len,chunk,perm", [("llama", 150, 16, None), ("llama", 129, 64, 7),
-                                                        ("qwen3", 100, 32, 3), ("llama", 5, 16, None)])
+                                                        ("qwen3", 100, 32, 3), ("llama", 5, 16, None),
+                                                        ("llama", 200, 128, 9), ("qwen3", 150, 128, None)])
 def test_chunked_prefill_matches_oracle(cuda_device, kind, prompt_len, chunk, perm):
     """Chunks that end inside a page, a ragged last chunk, a prompt shorter than one chunk, shuffled page ids,
-    per-head q/k norms."""
+    per-head q/k norms; with 128 positions per launch there are more attention units than SMs and a unit walks
+    its pages alone, two per trip (with and without two positions per unit)."""
     from vdcores_b200.prefill import PrefillEngine
     cfg, prompt, orc, nxt, gap, eng = _setup(kind, prompt_len, cuda_device, seed=21, page_perm_seed=perm)
     pre = PrefillEngine(eng, chunk=chunk, timeout_ns=500_000_000).adopt_weights()

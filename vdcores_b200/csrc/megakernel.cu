@@ -253,13 +253,23 @@ __device__ __forceinline__ void compute_core(const Ctx& c, const VdcCInst* __res
         a.wait_bar = e[10].args[0];
         a.state_stride = e[10].args[1];
         a.qkv_stride = (int)e[10].args[2] * 8;
-        if (ci.opcode == 0x7210) {
+        // units that walk four pages or more take two pages per trip; like the pair units that variant is
+        // compiled into the full kernel only (the batch-1 engines' units walk two pages)
+        bool long_walk = false;
+        if constexpr (kRefOps) long_walk = a.max_pages >= 4 && !(a.flags & VDC_ATTN_APPEND_BIT);
+        if (long_walk && !(a.flags & VDC_ATTN_PAIR_BIT)) {
+          if constexpr (kRefOps) {
+            if (ci.opcode == 0x7210) task_attn_decode<4, false, true>(q, a);
+            else task_attn_decode<8, false, true>(q, a);
+          }
+        } else if (ci.opcode == 0x7210) {
           task_attn_decode<4>(q, a);
         } else if (a.flags & VDC_ATTN_PAIR_BIT) {
           // pair units exist in the full kernel only (vdc_launch, vdc_launch_async_full): measured on B200, one more instantiation of
           // the attention task in the kernel the decode engines launch costs the batch-1 step 1.7 %
           if constexpr (kRefOps) {
-            task_attn_decode<8, true>(q, a);
+            if (long_walk) task_attn_decode<8, true, true>(q, a);
+            else task_attn_decode<8, true>(q, a);
           } else {
             raise_abort(c, VDC_ERR_BAD_OPCODE, 0, (int)q.pc, ci.opcode, -1, a.flags);
             q.aborted = true;

@@ -827,7 +827,7 @@ struct AttnArgs {
 // second's (the tile has eight usable rows either way); both walk the same pages, each row masks the page rows
 // past its own position, and all cache rows, the two positions' own included, are in HBM already (the chunk's
 // cache-append stage ran first), so nothing is patched in from shared memory and nothing is written back.
-template <int G, bool kPair = false>
+template <int G, bool kPair = false, bool kTwo = false>
 VDC_TASK void task_attn_decode(Compute& q, const AttnArgs& a) {
   constexpr int D = VDC_HEAD_DIM;
   constexpr int GQ = kPair ? G / 2 : G;      // query heads per position
@@ -943,7 +943,89 @@ VDC_TASK void task_attn_decode(Compute& q, const AttnArgs& a) {
   float m_run = -INFINITY, l_run = 0.f, acc[16][2], z0 = 0.f, z1 = 0.f;
 #pragma unroll
   for (int nt = 0; nt < 16; ++nt) acc[nt][0] = acc[nt][1] = 0.f;
-  for (int blk = 0; blk < count; ++blk) {
+  int blk = 0;
+  if constexpr (kTwo) {
+    // Two pages per trip (units that walk many pages: batched decode, prefill).  The warp's eight positions of the
+    // second page fill the upper half of the P·V k-step that a single page leaves zero, and one softmax update
+    // serves both pages: 32 instead of 48 MMAs and half the quad shuffles per two pages.  Ring entries of a trip:
+    // K, V of the first page, K, V of the second.  An odd last page takes the single-page body below.
+    bool stop = false;
+    for (; blk + 1 < count && !stop; blk += 2) {
+      const unsigned e0i = 2u * (unsigned)blk;
+      const int ka_mask = q.warp_wait(e0i);
+      if (ka_mask == kPopAbort) { stop = true; break; }
+      const int kb_mask = q.warp_wait(e0i + 2u);
+      if (kb_mask == kPopAbort) { stop = true; break; }
+      const bool last_b = owner && blk + 1 == count - 1;      // only the second page can be the walk's last
+      const int valid_b = last_b ? (kPair ? tail_valid_b : tail_valid) : VDC_KV_PAGE;
+      const int valid_b_row = kPair ? (last_b ? (gid >= GQ ? tail_valid_b : tail_valid) : VDC_KV_PAGE) : valid_b;
+      const int newpos_b = (!kPair && last_b) ? tail_valid - 1 : -1;
+      const int p_l = slice + lrow;
+      const uint32_t ka_s = (uint32_t)__cvta_generic_to_shared(slot_ptr(c, first_slot(ka_mask)));
+      const uint32_t kb_s = (uint32_t)__cvta_generic_to_shared(slot_ptr(c, first_slot(kb_mask)));
+      const uint32_t ka_base = ka_s + (uint32_t)p_l * (D * 2);
+      const uint32_t kb_base = p_l == newpos_b ? krow_s : kb_s + (uint32_t)p_l * (D * 2);
+      float s0 = 0.f, s1 = 0.f, u0 = 0.f, u1 = 0.f, t0 = 0.f, t1 = 0.f, w0 = 0.f, w1 = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint32_t kr[4], ks[4];
+        ldsm_x4(kr, ka_base + (uint32_t)(((4 * j + lmi) ^ lrow) << 4));
+        ldsm_x4(ks, kb_base + (uint32_t)(((4 * j + lmi) ^ lrow) << 4));
+        mma_rows8(s0, s1, z0, z1, qa[2 * j][0], qa[2 * j][1], kr[0], kr[1]);
+        mma_rows8(t0, t1, z0, z1, qa[2 * j][0], qa[2 * j][1], ks[0], ks[1]);
+        mma_rows8(u0, u1, z0, z1, qa[2 * j + 1][0], qa[2 * j + 1][1], kr[2], kr[3]);
+        mma_rows8(w0, w1, z0, z1, qa[2 * j + 1][0], qa[2 * j + 1][1], ks[2], ks[3]);
+      }
+      const int p0 = slice + 2 * t4;
+      s0 = (s0 + u0) * scale_log2;                            // the first page is never the last: all rows exist
+      s1 = (s1 + u1) * scale_log2;
+      t0 = p0 < valid_b_row ? (t0 + w0) * scale_log2 : -INFINITY;
+      t1 = p0 + 1 < valid_b_row ? (t1 + w1) * scale_log2 : -INFINITY;
+      float mx = fmaxf(fmaxf(s0, s1), fmaxf(t0, t1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      const float m_new = fmaxf(m_run, mx);                   // finite: the first page has 64 real scores
+      const float alpha = exp2f(m_run - m_new);
+      const float e0 = exp2f(s0 - m_new), e1 = exp2f(s1 - m_new), e2 = exp2f(t0 - m_new), e3 = exp2f(t1 - m_new);
+      float sum = (e0 + e1) + (e2 + e3);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+      m_run = m_new;
+      l_run = l_run * alpha + sum;
+      const uint32_t pa = pack_bf16x2(e0, e1), pb = pack_bf16x2(e2, e3);
+#pragma unroll
+      for (int nt = 0; nt < 16; ++nt) {
+        acc[nt][0] *= alpha;
+        acc[nt][1] *= alpha;
+      }
+      const int va_mask = q.warp_wait(e0i + 1u);
+      if (va_mask == kPopAbort) { stop = true; break; }
+      const int vb_mask = q.warp_wait(e0i + 3u);
+      if (vb_mask == kPopAbort) { stop = true; break; }
+      const uint32_t va_s = (uint32_t)__cvta_generic_to_shared(slot_ptr(c, first_slot(va_mask)));
+      const uint32_t vb_s = (uint32_t)__cvta_generic_to_shared(slot_ptr(c, first_slot(vb_mask)));
+      const uint32_t va_base = va_s + (uint32_t)p_l * (D * 2);
+      const uint32_t vb_base = p_l == newpos_b ? vrow_s : (p_l >= valid_b ? zero_s : vb_s + (uint32_t)p_l * (D * 2));
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint32_t vr[4], vs2[4];
+        ldsm_x4_trans(vr, va_base + (uint32_t)(((4 * j + lmi) ^ lrow) << 4));
+        ldsm_x4_trans(vs2, vb_base + (uint32_t)(((4 * j + lmi) ^ lrow) << 4));
+#pragma unroll
+        for (int mi = 0; mi < 4; ++mi) mma_rows8(acc[4 * j + mi][0], acc[4 * j + mi][1], z0, z1, pa, pb, vr[mi], vs2[mi]);
+      }
+      __syncwarp();
+      if (q.lane == 0) {
+        if (atomicAdd(&sh->att_done[(blk >> 1) & 7], 1) == kCW - 1) {
+          sh->att_done[(blk >> 1) & 7] = 0;
+          atomicOr(&sh->slot_avail, (uint32_t)(ka_mask | va_mask | kb_mask | vb_mask) & kSlotMaskAll);
+        }
+        sh->warp_next[q.warp] = q.head + e0i + 4u;
+      }
+    }
+    if (stop) blk = count;      // a wait gave up: skip the tail, the phase end below sees the abort
+  }
+  for (; blk < count; ++blk) {
     const int k_mask = q.warp_wait(2u * (unsigned)blk);
     if (k_mask == kPopAbort) break;
     if (q.tid == 0) CHUNK_STAMP(c, q.head + 2u * (unsigned)blk, 2);
