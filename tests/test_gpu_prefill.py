@@ -118,3 +118,33 @@ def test_chunked_prefill_with_quantised_projections(cuda_device, wkind, tol, bas
         assert O.rel_l2(k_dev.cpu(), orc.k[l][:T]) < 2 * tol and O.rel_l2(v_dev.cpu(), orc.v[l][:T]) < 2 * tol
     if gap > 5 * GAP:
         assert first == nxt
+
+
+def test_long_walks_agree_with_the_decode_program(cuda_device):
+    """A 1000-token prompt, 128 positions per launch: units walk up to 16 pages two at a time, through every page
+    count whose odd tail page once shared an arrival counter with the trip before it (15 pages: positions 896..959).
+    Checked against the same prompt run position by position through the decode program (itself checked against the
+    oracle above): cache rows of every layer, first generated id."""
+    from vdcores_b200.decode import DecodeEngine
+    from vdcores_b200.prefill import PrefillEngine
+    cfg = small_cfg("llama")
+    w = perturb_norms(O.ModelWeights.random(cfg, seed=27))
+    T = 1000
+    prompt = torch.randint(0, cfg.vocab, (T,), generator=torch.Generator().manual_seed(28))
+    eng = DecodeEngine(engine_config(cfg), max_seq=1088, device=cuda_device, timeout_ns=500_000_000)
+    eng.load_weights(dense_weights(w))
+    first_ref = eng.prefill_device(prompt)
+    ref = [[t.clone() for t in eng.read_kv(l, T)] for l in range(cfg.n_layers)]
+    top2 = torch.topk(eng.logits.float(), 2).values
+    eng.kpool.zero_()
+    eng.vpool.zero_()
+    pre = PrefillEngine(eng, chunk=128, timeout_ns=500_000_000).adopt_weights()
+    assert pre.n_splits == 1 and pre.pages_per_split == 17
+    first = pre.prefill(prompt)
+    for l in range(cfg.n_layers):
+        k_dev, v_dev = eng.read_kv(l, T)
+        assert O.rel_l2(k_dev, ref[l][0]) < 2 * REL_L2_BF16 and O.rel_l2(v_dev, ref[l][1]) < 2 * REL_L2_BF16, f"layer {l}"
+        kd, ko = k_dev.float().flatten(1), ref[l][0].float().flatten(1)
+        assert float(((kd - ko).norm(dim=1) / ko.norm(dim=1)).max()) < 4 * REL_L2_BF16, f"a K row of layer {l}"
+    if float((top2[0] - top2[1]) / top2[0].abs()) > 5 * GAP:
+        assert first == first_ref

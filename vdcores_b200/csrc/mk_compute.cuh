@@ -1016,8 +1016,11 @@ VDC_TASK void task_attn_decode(Compute& q, const AttnArgs& a) {
       }
       __syncwarp();
       if (q.lane == 0) {
-        if (atomicAdd(&sh->att_done[(blk >> 1) & 7], 1) == kCW - 1) {
-          sh->att_done[(blk >> 1) & 7] = 0;
+        // counters 0..3 serve the trips (the slot pool holds three trips, so a warp is at most two trips ahead
+        // of the slowest one), counter 4 the single odd page below: the two must never share a counter, or a
+        // warp that races through the tail page hands back the wrong trip's slots and the pool leaks
+        if (atomicAdd(&sh->att_done[(blk >> 1) & 3], 1) == kCW - 1) {
+          sh->att_done[(blk >> 1) & 3] = 0;
           atomicOr(&sh->slot_avail, (uint32_t)(ka_mask | va_mask | kb_mask | vb_mask) & kSlotMaskAll);
         }
         sh->warp_next[q.warp] = q.head + e0i + 4u;
@@ -1089,8 +1092,9 @@ VDC_TASK void task_attn_decode(Compute& q, const AttnArgs& a) {
     // ---- the warp is done with this page pair; the last of the eight gives the slots back
     __syncwarp();
     if (q.lane == 0) {
-      if (atomicAdd(&sh->att_done[blk & 7], 1) == kCW - 1) {
-        sh->att_done[blk & 7] = 0;
+      const int di = kTwo ? 4 : (blk & 7);
+      if (atomicAdd(&sh->att_done[di], 1) == kCW - 1) {
+        sh->att_done[di] = 0;
         atomicOr(&sh->slot_avail, (uint32_t)(k_mask | v_mask) & kSlotMaskAll);
         CHUNK_STAMP(c, q.head + 2u * (unsigned)blk + 1u, 3);
       }
